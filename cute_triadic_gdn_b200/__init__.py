@@ -1,0 +1,12 @@
+"""cute_triadic_gdn_b200: hand-written sm_100a CUDA kernels for Triadic Gated DeltaNet behind the reference's Python API.
+
+    chunk_gdn_joint       Triadic GDN with autograd, as a plain autograd call
+    gdn_joint_call        the same behind torch.library custom ops (one node under torch.compile)
+    conv_split_act_call   causal depthwise convolution (width 4) with SiLU on the leading channels only
+
+Same names, signatures, shapes and dtypes as cute_triadic_gdn/__init__.py:7-11 of the reference.
+"""
+from .conv_split_act import conv_split_act_call
+
+__all__ = ["conv_split_act_call"]
+__version__ = "0.1.0"

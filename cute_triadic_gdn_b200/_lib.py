@@ -1,0 +1,78 @@
+"""ctypes binding of libtgdn_b200.so (the C ABI declared in include/tgdn.h).
+
+The library is the only implementation of the hot path: there is no fallback.  If the shared object is missing it is
+built once with nvcc (cute_triadic_gdn_b200/build.py); if that is impossible the import fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtgdn_b200.so")
+HEADER = os.path.join(_PKG, "..", "include", "tgdn.h")
+
+_c = ctypes
+_P, _I, _L, _F = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float
+
+# name -> (restype, argtypes); kept in the order of include/tgdn.h
+SIGNATURES = {
+    "tgdn_error_string": (_c.c_char_p, [_I]),
+    "tgdn_abi_version": (_I, []),
+    "tgdn_device_status": (_I, [_P]),
+    "tgdn_conv_fwd": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _I, _P]),
+    "tgdn_conv_bwd_scratch_bytes": (_L, [_I, _I, _I]),
+    "tgdn_conv_bwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _P, _L, _P]),
+    "tgdn_chunk_capacity": (_I, [_I, _I]),
+    "tgdn_metadata": (_I, [_P, _I, _I, _I, _P, _P, _I, _P, _P]),
+    "tgdn_selftest_mma": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "tgdn_selftest_tma": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
+}
+
+
+class TgdnError(RuntimeError):
+    """A call into libtgdn_b200 returned a non-zero code."""
+
+
+def declared_symbols():
+    """Names of the functions declared in include/tgdn.h."""
+    with open(HEADER) as fh:
+        text = re.sub(r"/\*.*?\*/", "", fh.read(), flags=re.S)
+    return sorted(set(re.findall(r"\b(tgdn_[a-z0-9_]+)\s*\(", text)))
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        from .build import build
+        build()
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+
+
+def check(code, what):
+    if code != 0:
+        raise TgdnError(f"{what}: {lib.tgdn_error_string(code).decode()} (code {code})")
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream_of(t):
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def device_status():
+    """Blocking read-and-clear of the device status word (0 = every kernel ran to completion normally)."""
+    out = ctypes.c_int(0)
+    check(lib.tgdn_device_status(ctypes.byref(out)), "tgdn_device_status")
+    return out.value

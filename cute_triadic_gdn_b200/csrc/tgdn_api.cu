@@ -1,0 +1,93 @@
+// Host-side plumbing of libtgdn_b200: return codes, the device status word, tensor-map construction.
+#include <stdio.h>
+
+#include "tgdn_common.cuh"
+#include "tgdn_host.h"
+
+namespace {
+
+__device__ int g_status_word = 0;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+int tgdn_cuda_error(cudaError_t e) { return e == cudaSuccess ? 0 : -(1000 + static_cast<int>(e)); }
+
+int* tgdn_status_word() {
+  int* p = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;
+  return p;
+}
+
+int tgdn_check_device() {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+  return major == 10;
+}
+
+int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H, int box_cols, int box_rows,
+                        int swizzle128) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TGDN_ERR_DRIVER;
+  if (reinterpret_cast<uintptr_t>(base) & 15) return TGDN_ERR_ALIGN;
+  if (swizzle128 && box_cols != 64) return TGDN_ERR_SHAPE;
+  const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {256, static_cast<cuuint64_t>(H) * 256, static_cast<cuuint64_t>(T) * H * 256};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(box_cols), 1, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
+}
+
+extern "C" const char* tgdn_error_string(int code) {
+  static thread_local char buf[160];
+  switch (code) {
+    case TGDN_OK: return "ok";
+    case TGDN_ERR_SHAPE: return "unsupported or inconsistent sizes";
+    case TGDN_ERR_NULL: return "a required pointer is NULL";
+    case TGDN_ERR_ALIGN: return "a pointer or stride is not 16-byte aligned";
+    case TGDN_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
+    case TGDN_ERR_SCRATCH: return "scratch buffer missing or too small";
+    case TGDN_ERR_DEVICE: return "the current device is not compute capability 10.x (sm_100a kernels)";
+    default: break;
+  }
+  if (code <= -1000) {
+    snprintf(buf, sizeof(buf), "CUDA error %d: %s", -code - 1000, cudaGetErrorString(static_cast<cudaError_t>(-code - 1000)));
+    return buf;
+  }
+  snprintf(buf, sizeof(buf), "unknown tgdn code %d", code);
+  return buf;
+}
+
+extern "C" int tgdn_abi_version(void) { return 100; }
+
+extern "C" int tgdn_device_status(int* host_status) {
+  if (!host_status) return TGDN_ERR_NULL;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  int v = 0, zero = 0;
+  e = cudaMemcpyFromSymbol(&v, g_status_word, sizeof(int));
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  e = cudaMemcpyToSymbol(g_status_word, &zero, sizeof(int));
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  *host_status = v;
+  return 0;
+}

@@ -1,0 +1,21 @@
+// Host-side helpers shared by the translation units of libtgdn_b200 (not part of the public ABI).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tgdn.h"
+
+// -(1000 + e) for a CUDA runtime error, 0 for cudaSuccess.
+int tgdn_cuda_error(cudaError_t e);
+
+// Device pointer of the status word of the current device (a __device__ int of this library).
+int* tgdn_status_word();
+
+// Tensor map over a (B, T, H, 128) bf16 tensor in token layout: box = [box_cols columns][1 head][box_rows tokens][1 row].
+// swizzle128 = 1 asks for the 128-byte swizzle (box_cols must then be 64).
+int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H, int box_cols, int box_rows, int swizzle128);
+
+// True when the current device is compute capability 10.x.
+int tgdn_check_device();

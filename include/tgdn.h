@@ -1,0 +1,89 @@
+/* C ABI of libtgdn_b200: hand-written sm_100a CUDA kernels for the Triadic Gated DeltaNet hot path.
+ *
+ * Conventions shared by every entry point
+ *   - every pointer is a device pointer unless its name starts with host_; the caller owns every buffer
+ *     (PyTorch in the Python package), the library never allocates or frees device memory and never synchronises;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns at once;
+ *   - the return value is 0 on success, a negative TGDN_ERR_* code for a rejected argument, or
+ *     -(1000 + cudaError) for a CUDA runtime error at launch; tgdn_error_string() explains either;
+ *   - bf16 tensors are raw 16-bit words; "token layout" means the caller's (B, T, H, X) contiguous tensors, "chunk
+ *     layout" means (B, NC, H, ...) with NC = T/64 for dense rows or the chunk-map capacity for packed rows;
+ *   - packed rows (B = 1) pass the chunk map built by tgdn_metadata; dense rows pass NULL.
+ *
+ * The reference package has no C interface: its boundary is Python.  Each entry point below names the reference
+ * function (path inside the reference project) whose device work it replaces.
+ */
+#ifndef TGDN_H_
+#define TGDN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TGDN_OK 0
+#define TGDN_ERR_SHAPE (-1)       /* unsupported or inconsistent sizes */
+#define TGDN_ERR_NULL (-2)        /* a required pointer is NULL */
+#define TGDN_ERR_ALIGN (-3)       /* a pointer or stride breaks the 16-byte alignment the kernels need */
+#define TGDN_ERR_DRIVER (-4)      /* the CUDA driver entry point for tensor maps is unavailable or failed */
+#define TGDN_ERR_SCRATCH (-5)     /* scratch buffer missing or too small */
+#define TGDN_ERR_DEVICE (-6)      /* the current device is not compute capability 10.x */
+
+/* Human-readable text for a return code of this library. */
+const char* tgdn_error_string(int code);
+
+/* Version of this ABI (major * 100 + minor). */
+int tgdn_abi_version(void);
+
+/* Blocking read-and-clear of the device status word of the current device: 0 = no kernel gave up on a wait;
+ * 1 = a load barrier timed out, 2 = an MMA barrier timed out, 3 = a chunk map entry was out of range.
+ * Synchronises the device; meant for tests and debugging, not for the hot path. */
+int tgdn_device_status(int* host_status);
+
+/* ---- convolution pre-pass -----------------------------------------------------------------------------------------
+ * Width-4 causal depthwise convolution, f32 accumulation, SiLU on channels [0, act_channels), one bf16 rounding.
+ * x (B, T, C) bf16 with element strides (stride_b, stride_t, 1); weight (C, 4) bf16 contiguous; y (B, T, C) contiguous.
+ * cu_seqlens: NULL, or n_docs+1 int32 offsets of a packed row (B = 1); the window restarts at every document.
+ * Replaces: cute_triadic_gdn/ops/conv_split_act.py:20-55 (_fwd_kernel), :133-146 (_forward, conv_split_act_fwd). */
+int tgdn_conv_fwd(const void* x, const void* weight, void* y, const int32_t* cu_seqlens, int n_docs, int B, int T, int C,
+                  int64_t stride_b, int64_t stride_t, int act_channels, void* stream);
+
+/* Bytes of f32 scratch tgdn_conv_bwd needs for its per-tile weight-gradient partials. */
+int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C);
+
+/* Backward of the convolution: dx (B, T, C) bf16 contiguous and dw (C, 4) bf16.  dy has element strides
+ * (dy_stride_b, dy_stride_t, 1).  The SiLU derivative is evaluated at the bf16-rounded pre-activation, recomputed in
+ * the same kernel; dw is summed in f32 over token tiles in a fixed order and rounded once.
+ * Replaces: cute_triadic_gdn/ops/conv_split_act.py:58-107 (_bwd_kernel), :154-168 (conv_split_act_bwd). */
+int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, void* dx, void* dw, const int32_t* cu_seqlens,
+                  int n_docs, int B, int T, int C, int64_t stride_b, int64_t stride_t, int64_t dy_stride_b,
+                  int64_t dy_stride_t, int act_channels, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- packed-document metadata -------------------------------------------------------------------------------------
+ * Chunk-map capacity for n_docs documents over T tokens: ceil(T/64) + n_docs - 1 rounded up to a multiple of 16.
+ * Replaces: cute_triadic_gdn/ops/joint_packing.py:16-20 (chunk_capacity). */
+int tgdn_chunk_capacity(int T, int n_docs);
+
+/* Builds, on the device and without reading the offsets on the host: offsets (n_docs+1) int32 = first chunk of every
+ * document; mapping (3, capacity) int32 = [first token of chunk | valid rows of chunk | documents longest first];
+ * valid (1 byte) = offsets start at 0, end at T and strictly increase.  Never writes out of bounds for bad offsets.
+ * cu_seqlens holds int32 (cu_is_int64 = 0) or int64 values.
+ * Replaces: cute_triadic_gdn/kernels/sm90_joint_packed.py:64-129 (metadata_kernel, joint_metadata). */
+int tgdn_metadata(const void* cu_seqlens, int cu_is_int64, int n_docs, int T, int32_t* offsets, int32_t* mapping,
+                  int capacity, uint8_t* valid, void* stream);
+
+/* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
+ * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
+ * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).
+ * No counterpart in the reference. */
+int tgdn_selftest_mma(const void* A, const void* B, void* D, int M, int N, int K, int layout_a, int layout_b, void* stream);
+/* Returns the shared-memory image (8192 bytes) of one 64x64 128B-swizzled tile load of a (B,T,H,128) bf16 tensor at
+ * (batch, tok0, head, col0), followed by bulk_bytes copied by a 1-D bulk copy.  No counterpart in the reference. */
+int tgdn_selftest_tma(const void* x, int B, int T, int H, int col0, int head, int tok0, int batch, const void* bulk_src,
+                      int bulk_bytes, void* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TGDN_H_ */

@@ -1,0 +1,42 @@
+"""The C ABI without a GPU: the library builds, loads and exports what include/tgdn.h declares; argument checks that
+run before any launch return the documented codes."""
+import ctypes
+
+import pytest
+
+from cute_triadic_gdn_b200 import _lib
+from oracle.packing_oracle import chunk_capacity
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    declared = _lib.declared_symbols()
+    assert declared, "no declarations found in include/tgdn.h"
+    for name in declared:
+        assert hasattr(_lib.lib, name), f"{name} is declared but not exported"
+    assert sorted(_lib.SIGNATURES) == declared
+
+
+def test_version_and_error_strings():
+    assert _lib.lib.tgdn_abi_version() >= 100
+    assert _lib.lib.tgdn_error_string(0) == b"ok"
+    for code in (-1, -2, -3, -4, -5, -6, -1002, -77):
+        assert len(_lib.lib.tgdn_error_string(code)) > 3
+
+
+@pytest.mark.parametrize("T,N", [(64, 1), (640, 4), (3000, 6), (131072, 57), (1, 1), (65, 2)])
+def test_chunk_capacity_matches_reference_formula(T, N):
+    assert _lib.lib.tgdn_chunk_capacity(T, N) == chunk_capacity(T, N)
+
+
+def test_null_and_shape_arguments_are_rejected_before_launch():
+    L = _lib.lib
+    null = ctypes.c_void_p(None)
+    fake = ctypes.c_void_p(4096)
+    assert L.tgdn_conv_fwd(null, null, null, null, 0, 1, 64, 64, 0, 64, 0, null) == -2
+    assert L.tgdn_conv_fwd(fake, fake, fake, null, 0, 1, 64, 63, 0, 63, 0, null) == -1       # C % 8
+    assert L.tgdn_conv_fwd(ctypes.c_void_p(4098), fake, fake, null, 0, 1, 64, 64, 0, 64, 0, null) == -3
+    assert L.tgdn_conv_bwd(fake, fake, fake, fake, fake, null, 0, 1, 64, 64, 0, 64, 0, 64, 0, null, 0, null) == -5
+    assert L.tgdn_conv_bwd_scratch_bytes(1, 300, 64) == 2 * 64 * 4 * 4
+    assert L.tgdn_metadata(null, 0, 1, 64, null, null, 16, null, null) == -2
+    assert L.tgdn_metadata(fake, 0, 3, 640, fake, fake, 8, fake, null) == -1                  # capacity too small
+    assert L.tgdn_selftest_mma(fake, fake, fake, 96, 64, 64, 0, 0, null) == -1
