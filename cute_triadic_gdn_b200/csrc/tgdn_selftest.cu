@@ -122,7 +122,7 @@ extern "C" int tgdn_selftest_mma(const void* A, const void* B, void* D, int M, i
                                  void* stream) {
   if ((M != 128 && M != 64) || N % 16 || N < 16 || N > 128 || K % 64 || K < 64 || K > 256) return TGDN_ERR_SHAPE;
   if (layout_a < 0 || layout_a > 3 || layout_b < 0 || layout_b > 3) return TGDN_ERR_SHAPE;
-  const int smem = 1024 + ((128 * K * 2 + 1023) & ~1023) + N * K * 2 + 1024;
+  const int smem = 1024 + ((128 * K * 2 + 1023) & ~1023) + (N < 64 ? 64 : N) * K * 2 + 1024;   // swizzled rows are 64 wide
   cudaError_t e = cudaFuncSetAttribute(selftest_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   selftest_mma_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(
