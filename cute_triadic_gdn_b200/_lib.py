@@ -26,6 +26,8 @@ SIGNATURES = {
     "tgdn_conv_bwd": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _P, _L, _P]),
     "tgdn_chunk_capacity": (_I, [_I, _I]),
     "tgdn_metadata": (_I, [_P, _I, _I, _I, _P, _P, _I, _P, _P]),
+    "tgdn_masks": (_I, [_P, _P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "tgdn_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "tgdn_selftest_mma": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "tgdn_selftest_tma": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
 }
@@ -43,9 +45,16 @@ def declared_symbols():
 
 
 def _load():
-    if not os.path.exists(LIB_PATH):
-        from .build import build
-        build()
+    # (re)build when a source changed since the library was linked; a no-op otherwise
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_tgdn_build", os.path.join(_PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    try:
+        mod.build()
+    except Exception:
+        if not os.path.exists(LIB_PATH):
+            raise
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)

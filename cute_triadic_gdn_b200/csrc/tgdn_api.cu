@@ -3,6 +3,7 @@
 
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
+#include "tgdn_kernels.h"
 
 namespace {
 
@@ -56,6 +57,21 @@ int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
 }
+
+int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed) {
+  if (B <= 0 || T <= 0 || H <= 0 || NC <= 0) return TGDN_ERR_SHAPE;
+  if (E != 1 && E != 2 && E != 4 && E != 8 && E != 12 && E != 16) return TGDN_ERR_SHAPE;
+  if (packed) {
+    if (B != 1 || NC < (T + 63) / 64) return TGDN_ERR_SHAPE;
+  } else if (T % 64 || NC != T / 64) {
+    return TGDN_ERR_SHAPE;
+  }
+  if (static_cast<long long>(B) * NC * H > 0x7fffffffLL) return TGDN_ERR_SHAPE;
+  if (!tgdn_check_device()) return TGDN_ERR_DEVICE;
+  return 0;
+}
+
+int tgdn_value_block(int E) { return E >= 12 ? 16 : 32; }
 
 extern "C" const char* tgdn_error_string(int code) {
   static thread_local char buf[160];

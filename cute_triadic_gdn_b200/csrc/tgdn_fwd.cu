@@ -1,0 +1,407 @@
+// Forward chunk recurrence of the Triadic GDN.
+//
+// One CTA of 512 threads owns one (sequence, head, value block of VC columns) and walks the sequence's 64-token
+// chunks in order, with the E state slices S_e[:, value block] (128 x VC each, f32) in registers.  Per chunk:
+//   (1) R  = [K;Q] S          tcgen05, M=128, N=E*VC, K=128   rows 0..63: K S_e, rows 64..127: Q S_e
+//       W  = V - sum_e a_e*R_e (K rows);   Oq = sum_e c_e*R_e (Q rows)
+//   (2) [U;Oi] = [A;PmA] (beta*W)   tcgen05, M=128, N=VC, K=64
+//       o  = Oq + Oi  ->  bf16;   Vn_e = r_e*U
+//   (3) dS = K^T Vn           tcgen05, M=128, N=E*VC, K=64
+//       S_e <- d_e S_e + dS_e  (registers), bf16 copy -> shared memory operand of the next (1) and saved state h
+// with a = k2 exp(gc), r = k2 exp(gL-gc), c = scale q2 exp(gc), d = exp(gL).
+//
+// Replaces cute_triadic_gdn/kernels/sm100_joint_fwd.py:66-527 (fwd_kernel); math as cute_triadic_gdn/ops/gdn_joint.py:63-90.
+// K/Q tiles arrive by TMA (128B swizzle) one chunk ahead, the [A;PmA] operand image by a bulk copy; every wait is bounded.
+//
+// Column order inside the CTA: thread (warpgroup w, row i) owns, for every slice e, the CW = VC/4 value columns
+// w*CW..w*CW+CW-1; its E*CW columns are contiguous in tensor memory and in the operand images:
+// n' = w*(E*CW) + e*CW + c  <->  (slice e, value column w*CW + c of the block).
+#include "tgdn_common.cuh"
+#include "tgdn_host.h"
+#include "tgdn_kernels.h"
+
+namespace tgdn {
+
+constexpr int FWD_THREADS = 512;
+
+__device__ __forceinline__ float fexp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int E, int VC>
+struct FwdCfg {
+  static constexpr int NCOLS = E * VC;            // columns of R and dS
+  static constexpr int CW = VC / 4;               // value columns per thread and slice
+  static constexpr int TPC = E * CW;              // state columns per thread
+  static constexpr int ES = E | 1;                // row stride of the gate tables (odd: conflict-free)
+  static constexpr int TMEM_COLS = (NCOLS + VC) <= 64 ? 64 : (NCOLS + VC) <= 128 ? 128 : (NCOLS + VC) <= 256 ? 256 : 512;
+  // shared memory carve-up (bytes); every operand base is 1024-byte aligned
+  static constexpr int KQ_BYTES = 32768;
+  static constexpr int AP_BYTES = 16384;
+  static constexpr int S_BYTES = NCOLS * 256;     // image (i = d, j = n'), SI = 128, SJ = 2048
+  static constexpr int VN_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
+  static constexpr int BW_BYTES = VC * 128;       // image (i = s, j = v),  SI = 128, SJ = 1024
+  static constexpr int OFF_KQ = 0;
+  static constexpr int OFF_AP = OFF_KQ + 2 * KQ_BYTES;
+  static constexpr int OFF_S = OFF_AP + 2 * AP_BYTES;
+  static constexpr int OFF_VN = OFF_S + S_BYTES;
+  static constexpr int OFF_BW = OFF_VN + VN_BYTES;
+  static constexpr int OFF_GATES = OFF_BW + ((BW_BYTES + 1023) & ~1023);
+  static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;     // a, r, c tables, beta, d
+  static constexpr int OFF_CTRL = OFF_GATES + GATE_FLOATS * 4;
+  static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;       // + control block + alignment slack
+};
+
+struct FwdCtrl {
+  uint64_t bar_load[2];
+  uint64_t bar_mma;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int E, int VC>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, FwdParams p) {
+  using C = FwdCfg<E, VC>;
+  constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
+  constexpr float LOG2E = 1.4426950408889634f;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* g_a = reinterpret_cast<float*>(smem + C::OFF_GATES);
+  float* g_r = g_a + 64 * ES;
+  float* g_c = g_r + 64 * ES;
+  float* g_beta = g_c + 64 * ES;
+  float* g_d = g_beta + 64;
+  FwdCtrl& ctrl = *reinterpret_cast<FwdCtrl*>(smem + C::OFF_CTRL);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;                         // warpgroup: which CW columns of every slice
+  const int row = (warp & 3) * 32 + lane;           // tensor-memory lane = operand row
+  const bool krow = row < 64;                       // rows 0..63 work on K rows (W, U, Vn), 64..127 on Q rows (o)
+  const int t = row & 63;
+
+  // work item
+  constexpr int NV = HEAD / VC;
+  const int vb = blockIdx.x % NV, h = (blockIdx.x / NV) % p.H, seq_rank = blockIdx.x / (NV * p.H);
+  int b = seq_rank, first = 0, count = p.NC;
+  if (p.cmap != nullptr) {
+    const int doc = p.cmap[2 * p.NC + seq_rank];    // longest documents first
+    if (doc < 0 || doc >= p.n_seq) return;
+    b = 0;
+    first = p.offsets[doc];
+    count = p.offsets[doc + 1] - first;
+    if (first < 0 || count <= 0 || first + count > p.NC) return;
+  }
+
+  if (tid == 0) {
+    mbar_init(&ctrl.bar_load[0], 1);
+    mbar_init(&ctrl.bar_load[1], 1);
+    mbar_init(&ctrl.bar_mma, 1);
+    mbar_fence_init();
+    ctrl.abort = 0;
+  }
+  if (warp == 0) { tmem_alloc(&ctrl.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+  // zero state: registers and operand image
+  float S[TPC];
+#pragma unroll
+  for (int j = 0; j < TPC; ++j) S[j] = 0.f;
+  for (int i = tid; i < C::S_BYTES / 16; i += FWD_THREADS) reinterpret_cast<uint4*>(smem + C::OFF_S)[i] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctrl.tmem_base;
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  WaitCtl ctl{&ctrl.abort, p.status};
+
+  auto chunk_info = [&](int i, int& t0, int& rows) {
+    const int n = first + i;
+    if (p.cmap != nullptr) { t0 = p.cmap[n]; rows = p.cmap[p.NC + n]; } else { t0 = n * CHUNK; rows = CHUNK; }
+    if (t0 < 0 || rows < 0 || rows > CHUNK || t0 + rows > p.T) {
+      atomicCAS(p.status, DEV_OK, DEV_BAD_CHUNK_MAP);
+      t0 = 0; rows = 0;
+    }
+  };
+  auto issue_loads = [&](int i) {                   // thread 0: K/Q tiles and the [A;PmA] image of local chunk i
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int st = i & 1;
+    uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES);
+    tma_load_4d(kq, &map_k, &ctrl.bar_load[st], 0, h, t0, b);
+    tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
+    tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
+    tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
+    bulk_load(smem + C::OFF_AP + st * C::AP_BYTES, p.AP + item * (128 * 64), C::AP_BYTES, &ctrl.bar_load[st]);
+  };
+  // saved state of chunk item: this thread's pieces of slice e live at [e][(vb*VC + wg*CW)/8][row][...]
+  auto store_state = [&](int64_t item, const uint32_t* packed /* TPC/2 words */) {
+    if (p.h == nullptr) return;
+    uint8_t* base = reinterpret_cast<uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int v0 = vb * VC + wg * CW;
+      uint8_t* dst = base + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
+      if constexpr (CW == 8) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[e * 4], packed[e * 4 + 1], packed[e * 4 + 2], packed[e * 4 + 3]);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[e * 2], packed[e * 2 + 1]);
+      }
+    }
+  };
+
+  if (tid == 0) issue_loads(0);
+  uint32_t mma_phase = 0;
+  {
+    uint32_t zeros[TPC / 2];
+#pragma unroll
+    for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
+    store_state((static_cast<int64_t>(b) * p.NC + first) * p.H + h, zeros);
+  }
+
+  for (int i = 0; i < count; ++i) {
+    const int st = i & 1;
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
+    uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
+
+    // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
+    mbar_wait(&ctrl.bar_load[st], (i >> 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
+      const uint64_t db = make_desc(smem_u32(smem + C::OFF_S), 128, 2048, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, NCOLS, 0, 1);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)
+        umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma);
+      if (i + 1 < count) issue_loads(i + 1);         // the other stage was released by the previous chunk's (3)
+    }
+    // gate tables of this chunk (all threads), value row of this thread
+    for (int idx = tid; idx < 64 * E; idx += FWD_THREADS) {
+      const int r = idx / E, e = idx % E;
+      const float* gcp = p.gc + item * (64 * E);
+      const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
+      const bool ok = r < rows;
+      const int64_t off = ((tok + r) * p.H + h) * E + e;
+      const float k2v = ok ? p.k2[off] : 0.f, q2v = ok ? p.q2[off] : 0.f;
+      const float eg = fexp2(gcv);
+      g_a[r * ES + e] = k2v * eg;
+      g_r[r * ES + e] = k2v * fexp2(gl - gcv);
+      g_c[r * ES + e] = p.scale * q2v * eg;
+      if (r == 0) g_d[e] = fexp2(gl);
+    }
+    if (tid < 64) g_beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+    float vrow[CW];
+#pragma unroll
+    for (int c = 0; c < CW; ++c) vrow[c] = 0.f;
+    if (krow) {
+      if (t < rows) {
+        const __nv_bfloat16* vp = p.v + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
+        if constexpr (CW == 8) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(vp));
+          vrow[0] = bf16_lo(u.x); vrow[1] = bf16_hi(u.x); vrow[2] = bf16_lo(u.y); vrow[3] = bf16_hi(u.y);
+          vrow[4] = bf16_lo(u.z); vrow[5] = bf16_hi(u.z); vrow[6] = bf16_lo(u.w); vrow[7] = bf16_hi(u.w);
+        } else {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(vp));
+          vrow[0] = bf16_lo(u.x); vrow[1] = bf16_hi(u.x); vrow[2] = bf16_lo(u.y); vrow[3] = bf16_hi(u.y);
+        }
+      }
+    }
+    __syncthreads();                                 // gate tables visible
+    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++mma_phase;
+    tc_fence_after();
+
+    float acc[CW];                                   // K rows: W; Q rows: Oq
+#pragma unroll
+    for (int c = 0; c < CW; ++c) acc[c] = krow ? vrow[c] : 0.f;
+    {
+      const float* tab = krow ? g_a : g_c;
+#pragma unroll
+      for (int e0 = 0; e0 < E; e0 += (16 / CW)) {    // 16 columns per tensor-memory load where possible
+        constexpr int EP = (16 / CW) < E ? (16 / CW) : E;
+        float rr[EP * CW];
+        tmem_ld<EP * CW>(tmem_row + wg * TPC + e0 * CW, rr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int ee = 0; ee < EP; ++ee) {
+          const float gsc = tab[t * ES + e0 + ee];
+          const float sg = krow ? -gsc : gsc;
+#pragma unroll
+          for (int c = 0; c < CW; ++c) acc[c] = fmaf(sg, rr[ee * CW + c], acc[c]);
+        }
+      }
+    }
+    if (krow) {
+      // W -> saved (bf16), beta*W -> operand image (i = s, j = v)
+      const float bt = g_beta[t];
+      uint32_t wsave[CW / 2], wop[CW / 2];
+#pragma unroll
+      for (int c = 0; c < CW; c += 2) {
+        wsave[c / 2] = pack_bf16(acc[c], acc[c + 1]);
+        wop[c / 2] = pack_bf16(bt * acc[c], bt * acc[c + 1]);
+      }
+      const int v0 = wg * CW;
+      const uint32_t dst = smem_u32(smem + C::OFF_BW) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2;
+      if constexpr (CW == 8) st_shared_v4(dst, wop[0], wop[1], wop[2], wop[3]); else st_shared_v2(dst, wop[0], wop[1]);
+      if (p.W != nullptr) {
+        __nv_bfloat16* wp = p.W + (item * 64 + t) * HEAD + vb * VC + v0;
+        if constexpr (CW == 8) *reinterpret_cast<uint4*>(wp) = make_uint4(wsave[0], wsave[1], wsave[2], wsave[3]);
+        else *reinterpret_cast<uint2*>(wp) = make_uint2(wsave[0], wsave[1]);
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- (2) [U;Oi] = [A;PmA] (beta W) ------------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t da = make_desc(smem_u32(ap), 2048, 128, LAYOUT_PLAIN);
+      const uint64_t db = make_desc(smem_u32(smem + C::OFF_BW), 128, 1024, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, VC, 0, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_bf16(tmem + NCOLS, desc_advance(da, kk * 4096), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma);
+    }
+    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++mma_phase;
+    tc_fence_after();
+    {
+      float u[CW];
+      tmem_ld<CW>(tmem_row + NCOLS + wg * CW, u);
+      tmem_wait_ld();
+      if (krow) {
+        if (p.U != nullptr) {
+          __nv_bfloat16* up = p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW;
+          if constexpr (CW == 8)
+            *reinterpret_cast<uint4*>(up) = make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
+          else
+            *reinterpret_cast<uint2*>(up) = make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
+        }
+        // Vn_e = r_e * U -> operand image (i = t, j = n')
+        const uint32_t base = smem_u32(smem + C::OFF_VN) + (t >> 3) * 128 + (t & 7) * 16;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float re = g_r[t * ES + e];
+          const int n0 = wg * TPC + e * CW;
+          const uint32_t dst = base + (n0 >> 3) * 1024 + (n0 & 7) * 2;
+          if constexpr (CW == 8)
+            st_shared_v4(dst, pack_bf16(re * u[0], re * u[1]), pack_bf16(re * u[2], re * u[3]),
+                         pack_bf16(re * u[4], re * u[5]), pack_bf16(re * u[6], re * u[7]));
+          else
+            st_shared_v2(dst, pack_bf16(re * u[0], re * u[1]), pack_bf16(re * u[2], re * u[3]));
+        }
+      } else if (t < rows) {
+        __nv_bfloat16* op = p.o + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
+        if constexpr (CW == 8)
+          *reinterpret_cast<uint4*>(op) = make_uint4(pack_bf16(acc[0] + u[0], acc[1] + u[1]), pack_bf16(acc[2] + u[2], acc[3] + u[3]),
+                                                     pack_bf16(acc[4] + u[4], acc[5] + u[5]), pack_bf16(acc[6] + u[6], acc[7] + u[7]));
+        else
+          *reinterpret_cast<uint2*>(op) = make_uint2(pack_bf16(acc[0] + u[0], acc[1] + u[1]), pack_bf16(acc[2] + u[2], acc[3] + u[3]));
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+
+    // ---- (3) dS = K^T Vn, S <- d S + dS -----------------------------------------------------------------------
+    if (tid == 0) {
+      tc_fence_after();
+      const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
+      const uint64_t db = make_desc(smem_u32(smem + C::OFF_VN), 128, 1024, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, NCOLS, 1, 1);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk)
+        umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma);
+    }
+    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++mma_phase;
+    tc_fence_after();
+    {
+      uint32_t packed[TPC / 2];
+#pragma unroll
+      for (int j0 = 0; j0 < TPC; j0 += 16) {
+        constexpr int PIECE = TPC < 16 ? TPC : 16;
+        float ds[PIECE];
+        tmem_ld<PIECE>(tmem_row + wg * TPC + j0, ds);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < PIECE; ++j) {
+          const float de = g_d[(j0 + j) / CW];
+          S[j0 + j] = fmaf(de, S[j0 + j], ds[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < PIECE; j += 2) packed[(j0 + j) / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
+      }
+      // operand image (i = d, j = n') for the next chunk's (1)
+      const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
+#pragma unroll
+      for (int j0 = 0; j0 < TPC; j0 += 8) {
+        const int n0 = wg * TPC + j0;
+        st_shared_v4(base + (n0 >> 3) * 2048, packed[j0 / 2], packed[j0 / 2 + 1], packed[j0 / 2 + 2], packed[j0 / 2 + 3]);
+      }
+      if (i + 1 < count) store_state(item + p.H, packed);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem, C::TMEM_COLS);
+}
+
+}  // namespace tgdn
+
+using namespace tgdn;
+
+template <int E, int VC>
+static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const FwdParams& p, cudaStream_t s) {
+  using C = FwdCfg<E, VC>;
+  static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
+  cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  const int grid = p.n_seq * p.H * (HEAD / VC);
+  fwd_kernel<E, VC><<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  return tgdn_cuda_error(cudaGetLastError());
+}
+
+extern "C" int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
+                        const float* gc, const void* AP, float scale, const int32_t* doc_offsets,
+                        const int32_t* chunk_map, int n_docs, int B, int T, int H, int E, int NC, void* o, void* W,
+                        void* U, void* h, void* stream) {
+  if (!q || !k || !v || !k2 || !q2 || !beta || !gc || !AP || !o) return TGDN_ERR_NULL;
+  const bool packed = chunk_map != nullptr;
+  if (packed && (!doc_offsets || n_docs < 1)) return TGDN_ERR_NULL;
+  int rc = tgdn_check_core_shape(B, T, H, E, NC, packed);
+  if (rc) return rc;
+  if ((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(AP) |
+       reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(U) | reinterpret_cast<uintptr_t>(h)) & 15)
+    return TGDN_ERR_ALIGN;
+  CUtensorMap mk, mq;
+  if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
+  if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
+  FwdParams p{static_cast<const __nv_bfloat16*>(v), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
+              static_cast<__nv_bfloat16*>(o), static_cast<__nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(U),
+              static_cast<__nv_bfloat16*>(h), doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale,
+              tgdn_status_word()};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (E) {
+    case 1: return launch_fwd<1, 32>(mk, mq, p, s);
+    case 2: return launch_fwd<2, 32>(mk, mq, p, s);
+    case 4: return launch_fwd<4, 32>(mk, mq, p, s);
+    case 8: return launch_fwd<8, 32>(mk, mq, p, s);
+    case 12: return launch_fwd<12, 16>(mk, mq, p, s);
+    case 16: return launch_fwd<16, 16>(mk, mq, p, s);
+    default: return TGDN_ERR_SHAPE;
+  }
+}

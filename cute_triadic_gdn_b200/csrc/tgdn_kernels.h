@@ -1,0 +1,55 @@
+// Parameter blocks of the Triadic GDN kernels and the layouts of the tensors that travel between them.
+//
+// Chunk-layout tensors are indexed by item = (b * NC + n) * H + h (b batch row, n chunk, h head):
+//   gc   f32  [item][64][E]              cumulative log gate of the chunk
+//   AP   bf16 [item][16 KB image]        [A; Pm A] stacked, image (i = row 0..127, j = column 0..63), SI = 128, SJ = 2048
+//   Pm   bf16 [item][ 8 KB image]        image (i = t, j = s), SI = 128, SJ = 1024
+//   W, U, dU  bf16 [item][64][128]       row-major token rows of the chunk (rows past a document end are zero)
+//   h, ds     bf16 [item][E][16][128][8] state slice e as [value column / 8][key row d][value column % 8]: a plain
+//                                        operand image (i = d, j = v) with SI = 16 bytes * 8 = 128, SJ = 2048
+// "image" = 8x8 core matrices of 128 contiguous bytes, see tgdn_common.cuh.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace tgdn {
+
+struct MaskParams {
+  const float* k2;
+  const float* q2;
+  const float* g;
+  const float* beta;
+  float* gc;
+  __nv_bfloat16* AP;
+  __nv_bfloat16* Pm;
+  const int32_t* cmap;      // (3, NC) chunk map of a packed row, or nullptr
+  int B, T, H, NC;
+  float scale;
+  int* status;
+};
+
+struct FwdParams {
+  const __nv_bfloat16* v;   // token layout
+  const float* k2;
+  const float* q2;
+  const float* beta;
+  const float* gc;
+  const __nv_bfloat16* AP;
+  __nv_bfloat16* o;         // token layout
+  __nv_bfloat16* W;         // chunk layout; may be nullptr (inference: nothing saved)
+  __nv_bfloat16* U;
+  __nv_bfloat16* h;
+  const int32_t* offsets;   // packed: first chunk of every document (n_seq + 1 entries), else nullptr
+  const int32_t* cmap;
+  int B, T, H, NC, n_seq;   // n_seq = documents (packed) or batch rows (dense)
+  float scale;
+  int* status;
+};
+
+}  // namespace tgdn
+
+// E in {1,2,4,8,12,16}; dense rows need T % 64 == 0 and NC == T/64; packed rows need B == 1.
+int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed);
+// Width of the value-axis block one CTA of the recurrences owns, by E.
+int tgdn_value_block(int E);

@@ -1,0 +1,94 @@
+"""Triadic Gated DeltaNet: `chunk_gdn_joint`, the plain autograd entry, and the kernel pipeline behind it.
+
+Mirrors the operator layer of the reference, cute_triadic_gdn/ops/gdn_joint.py: `_check` (:235-249), the forward
+pipeline `_cute_forward` (:144-164), the autograd function `_JointCute` (:201-232), the GJ_SAVE_MASKS switch
+(:167-198) and `chunk_gdn_joint` (:252-278).  The device work is the C ABI of libtgdn_b200 (include/tgdn.h); this file
+only checks arguments, allocates outputs with torch and enqueues the kernels on torch's current stream.
+
+    S_e <- exp(g_te) S_e ;  S <- S + beta_t kappa_t (v_t - S^T kappa_t)^T ;  o_t = S^T (q2_t (x) q_t) * scale
+
+Inputs (contiguous, one CUDA device): q, k, v (B,T,H,128) bf16; k2, q2, g (B,T,H,E) f32; beta (B,T,H) f32;
+E in {1,2,4,8,12,16}.  Without cu_seqlens T % 64 == 0; with cu_seqlens B = 1 and the state restarts at every document.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import _lib
+
+CHUNK = 64
+SUPPORTED_E = (1, 2, 4, 8, 12, 16)
+
+
+def _check(q, k, v, k2, q2, g, beta, packed=False):
+    B, T, H, D = q.shape
+    E = k2.shape[-1]
+    assert q.shape == k.shape and v.shape[:3] == q.shape[:3], "q, k, v must be (B, T, H, D)"
+    assert D == 128 and v.shape[-1] == 128, f"head dim must be 128 (got {D}, {v.shape[-1]})"
+    assert T > 0 and (packed or T % CHUNK == 0), f"T must be a multiple of {CHUNK} (got {T})"
+    assert E > 0, f"E must be positive (got E={E})"
+    assert k2.shape == q2.shape == g.shape == (B, T, H, E), "k2, q2, g must be (B, T, H, E)"
+    assert beta.shape == (B, T, H), "beta is one write strength per head: (B, T, H)"
+    for n, t in (("q", q), ("k", k), ("v", v), ("k2", k2), ("q2", q2), ("g", g), ("beta", beta)):
+        assert t.is_contiguous(), f"{n} must be contiguous"
+        assert t.is_cuda and t.device == q.device, f"{n} must be on the same CUDA device as q"
+    assert q.dtype == k.dtype == v.dtype == torch.bfloat16, "q, k, v must be bf16"
+    for n, t in (("k2", k2), ("q2", q2), ("g", g), ("beta", beta)):
+        assert t.dtype == torch.float32, f"{n} must be f32"
+
+
+def _check_device_and_e(q, E):
+    if torch.cuda.get_device_capability(q.device)[0] != 10 or E not in SUPPORTED_E:
+        raise ValueError("the Triadic GDN kernels require an sm_100 device and E=1/2/4/8/12/16")
+
+
+def _save_masks():
+    """GJ_SAVE_MASKS=1 (default) keeps the chunk operators of the forward for the backward; GJ_SAVE_MASKS=0 drops them
+    and lets the backward recompute them with the same kernel (bitwise identical), trading one extra launch for
+    24 KiB per (chunk, head) of saved memory.  Read at forward time, like the reference (ops/gdn_joint.py:167-173)."""
+    return os.environ.get("GJ_SAVE_MASKS", "1") == "1"
+
+
+def _dims(q, k2, token_map):
+    B, T, H, _ = q.shape
+    E = k2.shape[-1]
+    NC = token_map.shape[1] if token_map is not None else T // CHUNK
+    return B, T, H, E, NC
+
+
+def _run_masks(q, k, k2, q2, g, beta, scale, token_map, gc=None):
+    """(gc, AP, Pm) of every chunk.  AP = [A; Pm A] operand image, Pm image; see include/tgdn.h."""
+    B, T, H, E, NC = _dims(q, k2, token_map)
+    dev = q.device
+    gc_out = torch.empty((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
+    AP = torch.empty((B, NC, H, 128 * 64), dtype=torch.bfloat16, device=dev)
+    Pm = torch.empty((B, NC, H, 64 * 64), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.tgdn_masks(_lib.ptr(q), _lib.ptr(k), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(g), _lib.ptr(beta),
+                                       float(scale), _lib.ptr(token_map), B, T, H, E, NC, _lib.ptr(gc_out), _lib.ptr(AP),
+                                       _lib.ptr(Pm), _lib.stream_of(q)), "tgdn_masks")
+    return gc_out, AP, Pm
+
+
+def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, token_map=None):
+    """masks -> forward recurrence.  Returns o and, with save=True, (gc, AP, Pm, h, W, U)."""
+    B, T, H, E, NC = _dims(q, k2, token_map)
+    dev = q.device
+    gc, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
+    o = torch.empty_like(v)
+    if token_map is not None:
+        o.zero_()  # rows of a packed row are all covered by documents; kept defined even for a rejected chunk map
+    h = W = U = None
+    if save:
+        h = torch.empty((B, NC, H, E, 16, 128, 8), dtype=torch.bfloat16, device=dev)
+        W = torch.empty((B, NC, H, CHUNK, 128), dtype=torch.bfloat16, device=dev)
+        U = torch.empty((B, NC, H, CHUNK, 128), dtype=torch.bfloat16, device=dev)
+    n_docs = chunk_starts.numel() - 1 if chunk_starts is not None else 0
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.tgdn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta),
+                                     _lib.ptr(gc), _lib.ptr(AP), float(scale), _lib.ptr(chunk_starts),
+                                     _lib.ptr(token_map), n_docs, B, T, H, E, NC, _lib.ptr(o), _lib.ptr(W), _lib.ptr(U),
+                                     _lib.ptr(h), _lib.stream_of(q)), "tgdn_fwd")
+    return o, gc, AP, Pm, h, W, U

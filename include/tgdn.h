@@ -73,6 +73,27 @@ int tgdn_chunk_capacity(int T, int n_docs);
 int tgdn_metadata(const void* cu_seqlens, int cu_is_int64, int n_docs, int T, int32_t* offsets, int32_t* mapping,
                   int capacity, uint8_t* valid, void* stream);
 
+/* ---- Triadic GDN core ----------------------------------------------------------------------------------------------
+ * Shapes: q, k, v, o (B, T, H, 128) bf16; k2, q2, g (B, T, H, E) f32; beta (B, T, H) f32; E in {1,2,4,8,12,16}.
+ * Dense rows: T % 64 == 0, NC = T/64, chunk_map = doc_offsets = NULL.  Packed rows: B = 1, NC = chunk-map capacity,
+ * chunk_map / doc_offsets from tgdn_metadata, n_docs documents; the state restarts at every document.
+ * Chunk-layout intermediates, indexed by item = (b*NC + n)*H + h:
+ *   gc f32 [item][64][E];  AP bf16 [item][128*64] ([A; Pm A] operand image);  Pm bf16 [item][64*64];
+ *   W, U, dU bf16 [item][64][128];  h, ds bf16 [item][E][16][128][8] (state slice as [v/8][d][v%8]).
+ *
+ * tgdn_masks: chunk-local cumulative log gate, UT transform and intra-chunk operators of every chunk.
+ * Replaces: cute_triadic_gdn/kernels/sm90_joint_scan.py:92-110 (joint_scan, forward) and
+ * cute_triadic_gdn/kernels/sm100_joint_masks.py:291-323 (joint_masks_sm100). */
+int tgdn_masks(const void* q, const void* k, const float* k2, const float* q2, const float* g, const float* beta,
+               float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* gc, void* AP, void* Pm,
+               void* stream);
+
+/* tgdn_fwd: the forward chunk recurrence; writes o and, unless NULL, the tensors the backward needs (W, U, h).
+ * Replaces: cute_triadic_gdn/kernels/sm100_joint_fwd.py:569-618 (joint_fwd_sm100). */
+int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
+             const float* gc, const void* AP, float scale, const int32_t* doc_offsets, const int32_t* chunk_map,
+             int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h, void* stream);
+
 /* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
  * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
  * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).
