@@ -47,6 +47,68 @@ struct FwdParams {
   int* status;
 };
 
+struct RecParams {
+  const __nv_bfloat16* dO;  // token layout
+  const float* k2;
+  const float* q2;
+  const float* beta;
+  const float* gc;
+  const __nv_bfloat16* AP;
+  const __nv_bfloat16* Pm;
+  const __nv_bfloat16* U;   // chunk layout
+  __nv_bfloat16* dV;        // token layout (out): the gradient of v, and the dW the later stages use
+  __nv_bfloat16* dU;        // chunk layout (out)
+  __nv_bfloat16* ds;        // chunk layout (out), same form as h: dL/dS at the END of every chunk
+  float* dr;                // f32 [item][128/VC][64][E] (out): sum_v U*(K G_e) per value block
+  const int32_t* offsets;
+  const int32_t* cmap;
+  int B, T, H, NC, n_seq;
+  float scale;
+  int* status;
+};
+
+struct SgParams {
+  const __nv_bfloat16* dO;  // token layout
+  const __nv_bfloat16* dV;  // token layout
+  const __nv_bfloat16* U;   // chunk layout
+  const __nv_bfloat16* h;
+  const __nv_bfloat16* ds;
+  const float* k2;
+  const float* q2;
+  const float* gc;
+  float* dkq;               // f32 [item][128][128] (out): rows 0..63 state part of dK, rows 64..127 of dQ
+  float* da;                // f32 [item][64][E] (out)
+  float* dc;                // f32 [item][64][E] (out)
+  float* dd;                // f32 [item][E] (out)
+  const int32_t* cmap;
+  int B, T, H, NC;
+  float scale;
+  int* status;
+};
+
+struct MatParams {
+  const float* k2;
+  const float* q2;
+  const float* beta;
+  const float* gc;
+  const __nv_bfloat16* AP;
+  const float* dkq;
+  const float* da;
+  const float* dc;
+  const float* dd;
+  const float* dr;          // [item][NV][64][E]
+  __nv_bfloat16* dq;        // token layout (out)
+  __nv_bfloat16* dk;
+  float* dk2;               // token layout (out)
+  float* dq2;
+  float* dg;
+  float* dbeta;
+  const int32_t* cmap;
+  int B, T, H, NC, NV;
+  float scale;
+  int* status;
+};
+
 }  // namespace tgdn
 
 // E in {1,2,4,8,12,16}; dense rows need T % 64 == 0 and NC == T/64; packed rows need B == 1.

@@ -92,3 +92,27 @@ def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, to
                                      _lib.ptr(token_map), n_docs, B, T, H, E, NC, _lib.ptr(o), _lib.ptr(W), _lib.ptr(U),
                                      _lib.ptr(h), _lib.stream_of(q)), "tgdn_fwd")
     return o, gc, AP, Pm, h, W, U
+
+
+def _value_block(E):
+    """Width of the value-axis block one CTA of the recurrences owns (fixed by the library per E)."""
+    return 16 if E >= 12 else 32
+
+
+def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None, token_map=None):
+    """Reverse recurrence: (dV, dU, ds, dr)."""
+    B, T, H, E, NC = _dims(q, k2, token_map)
+    dev = q.device
+    NV = 128 // _value_block(E)
+    dV = torch.zeros_like(do) if token_map is not None else torch.empty_like(do)
+    dU = torch.empty((B, NC, H, CHUNK, 128), dtype=torch.bfloat16, device=dev)
+    ds = torch.empty((B, NC, H, E, 16, 128, 8), dtype=torch.bfloat16, device=dev)
+    dr = torch.empty((B, NC, H, NV, CHUNK, E), dtype=torch.float32, device=dev)
+    n_docs = chunk_starts.numel() - 1 if chunk_starts is not None else 0
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.tgdn_bwd_recurrent(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta), _lib.ptr(gc),
+            _lib.ptr(AP), _lib.ptr(Pm), _lib.ptr(U), float(scale), _lib.ptr(chunk_starts), _lib.ptr(token_map), n_docs,
+            B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dr), _lib.stream_of(q)),
+            "tgdn_bwd_recurrent")
+    return dV, dU, ds, dr

@@ -94,6 +94,15 @@ int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const
              const float* gc, const void* AP, float scale, const int32_t* doc_offsets, const int32_t* chunk_map,
              int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h, void* stream);
 
+/* tgdn_bwd_recurrent: the reverse chunk recurrence.  Reads the upstream gradient dO (token layout) and the forward's
+ * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), ds (chunk layout, dL/dS at the end of
+ * every chunk, same form as h) and dr f32 [item][128/VC][64][E] (VC = 32 for E <= 8, 16 for E >= 12).
+ * Replaces: cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:561-609 (joint_bwd_recurrent_sm100, recurrence part). */
+int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2, const float* beta,
+                       const float* gc, const void* AP, const void* Pm, const void* U, float scale,
+                       const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B, int T, int H, int E,
+                       int NC, void* dV, void* dU, void* ds, float* dr, void* stream);
+
 /* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
  * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
  * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).

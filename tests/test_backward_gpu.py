@@ -1,0 +1,37 @@
+"""Backward kernels on the device, stage by stage against the torch model of the kernels' dataflow."""
+import pytest
+import torch
+
+from cute_triadic_gdn_b200 import _lib
+from cute_triadic_gdn_b200 import gdn_joint as gj
+from oracle import kernel_plan as plan
+from oracle import triadic_oracle as orc
+from plan_helpers import decode_items, state_to_matrix
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu(ts):
+    return [t.cuda() for t in ts]
+
+
+@pytest.mark.parametrize("E", [1, 2, 4, 8, 12, 16])
+@pytest.mark.parametrize("dist", ["baseline", "mild"])
+def test_reverse_recurrence_dense(E, dist):
+    B, T, H = 2, 256, 2
+    ins = orc.make_inputs(B, T, H, E, seed=200 + E, dist=dist)
+    do = orc.make_grad_output((B, T, H, 128), 7)
+    scale = 128 ** -0.5
+    q, k, v, k2, q2, g, beta = _gpu(ins)
+    o, gc, AP, Pm, h, W, U = gj._kernel_forward(q, k, v, k2, q2, g, beta, scale, True)
+    dV, dU, ds, dr = gj._run_reverse(q, k, do.cuda(), k2, q2, beta, gc, AP, Pm, U, scale)
+    assert _lib.device_status() == 0
+    _, grads, st = plan.run_plan(*ins, do, rounding=True)
+    rv = st["rev"]
+    conv = lambda t: t.cpu().float().permute(0, 2, 1, 3, 4).reshape(B * H, T // 64, 64, 128)
+    assert orc.rel_l2(conv(dU), rv["dU"]) < 8e-3
+    assert orc.rel_l2(dV.cpu().float(), grads[2]) < 8e-3
+    dsm = decode_items(ds.cpu().float(), state_to_matrix)
+    assert orc.rel_l2(dsm, rv["ds"]) < 1e-2
+    drs = dr.cpu().sum(3).permute(0, 2, 1, 3, 4).reshape(B * H, T // 64, 64, E)
+    assert orc.rel_l2(drs, rv["dr"]) < 1e-2
