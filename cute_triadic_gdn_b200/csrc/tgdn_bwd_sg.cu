@@ -1,0 +1,314 @@
+// State gradients of the Triadic GDN backward: everything that contracts over the value axis with the saved states.
+//
+// One CTA of 256 threads per (batch, chunk, head).  With h_e the forward state at the start of the chunk and G_e the
+// gradient state at its end (both 128x128 bf16, streamed from HBM in 16 KB half-slices by bulk copies):
+//   dK_state = sum_e (-a_e*dW) h_e^T + (r_e*U) G_e^T          (64 x 128)
+//   dQ_state = sum_e ( c_e*dO) h_e^T                          (64 x 128)
+//   da_e[t]  = -sum_v dW[t,v] (K h_e)[t,v]     dc_e[t] = sum_v dO[t,v] (Q h_e)[t,v]     dd_e = <h_e, G_e>
+// The first two are accumulated over all slices in tensor memory (operands pre-scaled by the gates, so the slice index
+// is just more K), the row sums come from R = [K;Q] h_e, the same product the forward used.
+//
+// Replaces cute_triadic_gdn/kernels/sm100_joint_state_grads.py:53-449 (sg_kernel).
+#include "tgdn_common.cuh"
+#include "tgdn_host.h"
+#include "tgdn_kernels.h"
+
+namespace tgdn {
+
+constexpr int SG_THREADS = 256;
+
+__device__ __forceinline__ float sexp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct SgSmem {
+  uint8_t kq[32768];            // [K;Q] tile, 128B swizzle
+  uint8_t hp[2][16384];         // half-slices of h: image (i = d, j = v), SI = 128, SJ = 2048
+  uint8_t gp[2][16384];         // half-slices of G
+  uint8_t va[8192];             // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: xa follows)
+  uint8_t xa[16384];            // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
+  float ga[64 * 17], gr[64 * 17], gcq[64 * 17];
+  float part[2 * 128 * 17];     // row sums per column half
+  float red[SG_THREADS / 32];
+  uint64_t bar_kq, bar_load[2], bar_mma;
+  uint32_t tmem_base;
+  int abort;
+};
+
+template <int E>
+__global__ void __launch_bounds__(SG_THREADS, 1)
+sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, SgParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  SgSmem& sm = *reinterpret_cast<SgSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int ES = 17;
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wg = warp >> 2;                          // column half inside a 64-column step
+  const int row = (warp & 3) * 32 + lane;
+  const bool krow = row < 64;
+  const int t = row & 63;
+  const int h = blockIdx.x % p.H, n = (blockIdx.x / p.H) % p.NC, b = blockIdx.x / (p.H * p.NC);
+  const int64_t item = blockIdx.x;
+
+  int t0 = n * CHUNK, rows = CHUNK;
+  if (p.cmap != nullptr) {
+    t0 = p.cmap[n];
+    rows = p.cmap[p.NC + n];
+    if (rows <= 0) return;
+    if (t0 < 0 || rows > CHUNK || t0 + rows > p.T) {
+      if (tid == 0) atomicCAS(p.status, DEV_OK, DEV_BAD_CHUNK_MAP);
+      return;
+    }
+  }
+  if (tid == 0) {
+    mbar_init(&sm.bar_kq, 1);
+    mbar_init(&sm.bar_load[0], 1);
+    mbar_init(&sm.bar_load[1], 1);
+    mbar_init(&sm.bar_mma, 1);
+    mbar_fence_init();
+    sm.abort = 0;
+  }
+  if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  WaitCtl ctl{&sm.abort, p.status};
+  constexpr int STEPS = 2 * E;
+  const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
+  const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
+  auto issue_step = [&](int s) {                     // thread 0
+    const int st = s & 1;
+    mbar_expect_tx(&sm.bar_load[st], 32768);
+    bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
+    bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&sm.bar_kq, 32768);
+    tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
+    tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
+    tma_load_4d(sm.kq + 16384, &map_k, &sm.bar_kq, 64, h, t0, b);
+    tma_load_4d(sm.kq + 24576, &map_q, &sm.bar_kq, 64, h, t0, b);
+    issue_step(0);
+    issue_step(1);
+  }
+
+  // gate tables
+  const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+  for (int idx = tid; idx < 64 * E; idx += SG_THREADS) {
+    const int r = idx / E, e = idx % E;
+    const float* gcp = p.gc + item * (64 * E);
+    const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
+    const bool ok = r < rows;
+    const int64_t off = ((tok + r) * p.H + h) * E + e;
+    const float k2v = ok ? p.k2[off] : 0.f, q2v = ok ? p.q2[off] : 0.f;
+    const float eg = sexp2(gcv);
+    sm.ga[r * ES + e] = k2v * eg;
+    sm.gr[r * ES + e] = k2v * sexp2(gl - gcv);
+    sm.gcq[r * ES + e] = p.scale * q2v * eg;
+  }
+  // this thread's row data: K rows dW and U, Q rows dO; columns vh*64 + wg*32 .. +32 for vh = 0, 1 (packed bf16 pairs)
+  uint32_t xw[2][16], uw[2][16];
+#pragma unroll
+  for (int vh = 0; vh < 2; ++vh) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { xw[vh][j] = 0u; uw[vh][j] = 0u; }
+    const int c0 = vh * 64 + wg * 32;
+    if (krow) {
+      const uint4* up = reinterpret_cast<const uint4*>(p.U + (item * 64 + t) * HEAD + c0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = __ldg(up + j);
+        uw[vh][4 * j] = u.x; uw[vh][4 * j + 1] = u.y; uw[vh][4 * j + 2] = u.z; uw[vh][4 * j + 3] = u.w;
+      }
+    }
+    if (t < rows) {
+      const __nv_bfloat16* src = (krow ? p.dV : p.dO) + ((tok + t) * p.H + h) * HEAD + c0;
+      const uint4* xp = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = __ldg(xp + j);
+        xw[vh][4 * j] = u.x; xw[vh][4 * j + 1] = u.y; xw[vh][4 * j + 2] = u.z; xw[vh][4 * j + 3] = u.w;
+      }
+    }
+  }
+  __syncthreads();
+  mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);
+
+  uint32_t mma_phase = 0;
+  for (int e = 0; e < E; ++e) {
+    float rowsum = 0.f;                              // da_e (K rows) or dc_e (Q rows), this thread's columns
+    float dot = 0.f;                                 // <h_e, G_e>, this thread's elements
+    const float fx = krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e];
+    const float fu = sm.gr[t * ES + e];
+#pragma unroll
+    for (int vh = 0; vh < 2; ++vh) {
+      const int s = 2 * e + vh, st = s & 1;
+      // operands of this step (the previous step's MMAs have completed)
+      {
+        const uint32_t xbase = smem_u32(sm.xa) + (row >> 3) * 128 + (row & 7) * 16 + (wg * 4) * 2048;
+        const uint32_t vbase = smem_u32(sm.va) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t o[4];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const uint32_t x = xw[vh][4 * j + w];
+            o[w] = pack_bf16(fx * bf16_lo(x), fx * bf16_hi(x));
+          }
+          st_shared_v4(xbase + j * 2048, o[0], o[1], o[2], o[3]);
+          if (krow) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t x = uw[vh][4 * j + w];
+              o[w] = pack_bf16(fu * bf16_lo(x), fu * bf16_hi(x));
+            }
+            st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      mbar_wait(&sm.bar_load[st], (s >> 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+      const uint32_t rcol = 256 + (s & 1) * 64;
+      if (tid == 0) {
+        tc_fence_after();
+        const uint64_t dxa = make_desc(smem_u32(sm.xa), 2048, 128, LAYOUT_PLAIN);
+        const uint64_t dva = make_desc(smem_u32(sm.va), 1024, 128, LAYOUT_PLAIN);
+        const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);   // K = v
+        const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
+        const uint64_t dhm = make_desc(smem_u32(sm.hp[st]), 128, 2048, LAYOUT_PLAIN);   // K = d, N = v
+        const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
+        constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
+        constexpr uint32_t id_r = make_idesc(128, 64, 0, 1);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem, desc_advance(dxa, kk * 4096), desc_advance(dhk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem + 128, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + rcol, desc_advance(dkq, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dhm, kk * 256), id_r, kk > 0);
+        umma_commit(&sm.bar_mma);
+      }
+      // <h, G> over this half-slice while the tensor core works: 1024 16-byte pieces, 4 per thread
+      {
+        const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[st]);
+        const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[st]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 a = hp4[j * SG_THREADS + tid], g = gp4[j * SG_THREADS + tid];
+          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            dot = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), dot);
+            dot = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), dot);
+          }
+        }
+      }
+      mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+      ++mma_phase;
+      tc_fence_after();
+      {
+        float rr[32];
+        tmem_ld<32>(tmem_row + rcol + wg * 32, rr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          rowsum = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], rowsum);
+          rowsum = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], rowsum);
+        }
+      }
+      tc_fence_before();
+      __syncthreads();                               // operands and this stage's half-slices are free again
+      if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);
+    }
+    sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
+    // block sum of the dot product, fixed order
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) sm.red[warp] = dot;
+    __syncthreads();
+    if (tid == 0) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[w];
+      p.dd[item * E + e] = total;
+    }
+  }
+  __syncthreads();
+  // row sums: add the two column halves
+  for (int idx = tid; idx < 128 * E; idx += SG_THREADS) {
+    const int r = idx / E, e = idx % E;
+    const float v = sm.part[r * ES + e] + sm.part[(128 + r) * ES + e];
+    if (r < 64) p.da[(item * 64 + r) * E + e] = v; else p.dc[(item * 64 + r - 64) * E + e] = v;
+  }
+  // accumulators -> dkq f32: rows 0..63 = ACC + ACC2 (dK), rows 64..127 = ACC (dQ); this thread: 64 columns
+  tc_fence_after();
+  float* outp = p.dkq + (item * 128 + row) * HEAD + wg * 64;
+#pragma unroll
+  for (int c0 = 0; c0 < 64; c0 += 16) {
+    float a[16], a2[16];
+    tmem_ld<16>(tmem_row + wg * 64 + c0, a);
+    tmem_ld<16>(tmem_row + 128 + wg * 64 + c0, a2);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+      float4 v4;
+      v4.x = a[j] + (krow ? a2[j] : 0.f);
+      v4.y = a[j + 1] + (krow ? a2[j + 1] : 0.f);
+      v4.z = a[j + 2] + (krow ? a2[j + 2] : 0.f);
+      v4.w = a[j + 3] + (krow ? a2[j + 3] : 0.f);
+      *reinterpret_cast<float4*>(outp + c0 + j) = v4;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace tgdn
+
+using namespace tgdn;
+
+template <int E>
+static int launch_sg(const CUtensorMap& mk, const CUtensorMap& mq, const SgParams& p, cudaStream_t s) {
+  const int smem = static_cast<int>(sizeof(SgSmem)) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(sg_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  sg_kernel<E><<<p.B * p.NC * p.H, SG_THREADS, smem, s>>>(mk, mq, p);
+  return tgdn_cuda_error(cudaGetLastError());
+}
+
+extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U,
+                                    const void* h, const void* ds, const float* k2, const float* q2, const float* gc,
+                                    float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* dkq,
+                                    float* da, float* dc, float* dd, void* stream) {
+  if (!q || !k || !dO || !dV || !U || !h || !ds || !k2 || !q2 || !gc || !dkq || !da || !dc || !dd) return TGDN_ERR_NULL;
+  int rc = tgdn_check_core_shape(B, T, H, E, NC, chunk_map != nullptr);
+  if (rc) return rc;
+  if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(U) |
+       reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkq)) & 15)
+    return TGDN_ERR_ALIGN;
+  CUtensorMap mk, mq;
+  if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
+  if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
+  SgParams p{static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
+             static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(h),
+             static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, dkq, da, dc, dd, chunk_map, B, T, H, NC, scale,
+             tgdn_status_word()};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (E) {
+    case 1: return launch_sg<1>(mk, mq, p, s);
+    case 2: return launch_sg<2>(mk, mq, p, s);
+    case 4: return launch_sg<4>(mk, mq, p, s);
+    case 8: return launch_sg<8>(mk, mq, p, s);
+    case 12: return launch_sg<12>(mk, mq, p, s);
+    case 16: return launch_sg<16>(mk, mq, p, s);
+    default: return TGDN_ERR_SHAPE;
+  }
+}

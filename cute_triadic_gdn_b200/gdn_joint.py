@@ -116,3 +116,20 @@ def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None
             B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dr), _lib.stream_of(q)),
             "tgdn_bwd_recurrent")
     return dV, dU, ds, dr
+
+
+def _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map=None):
+    """State gradients: (dkq, da, dc, dd)."""
+    B, T, H, E, NC = _dims(q, k2, token_map)
+    dev = q.device
+    alloc = torch.zeros if token_map is not None else torch.empty     # unused map entries stay defined
+    dkq = alloc((B, NC, H, 128, 128), dtype=torch.float32, device=dev)
+    da = alloc((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
+    dc = alloc((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
+    dd = alloc((B, NC, H, E), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib.tgdn_bwd_state_grads(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(dV), _lib.ptr(U), _lib.ptr(h), _lib.ptr(ds), _lib.ptr(k2),
+            _lib.ptr(q2), _lib.ptr(gc), float(scale), _lib.ptr(token_map), B, T, H, E, NC, _lib.ptr(dkq), _lib.ptr(da),
+            _lib.ptr(dc), _lib.ptr(dd), _lib.stream_of(q)), "tgdn_bwd_state_grads")
+    return dkq, da, dc, dd

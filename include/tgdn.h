@@ -103,6 +103,16 @@ int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float
                        const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B, int T, int H, int E,
                        int NC, void* dV, void* dU, void* ds, float* dr, void* stream);
 
+/* tgdn_bwd_state_grads: per (chunk, head), the gradient terms that contract the saved states h (forward, chunk start)
+ * and ds (backward, chunk end) over the value axis.  Writes dkq f32 [item][128][128] (rows 0..63: state part of dK,
+ * rows 64..127: of dQ), da, dc f32 [item][64][E] (gradients of the gate tables a = k2 exp(gc), c = scale q2 exp(gc))
+ * and dd f32 [item][E] (gradient of the chunk decay exp(gL)).
+ * Replaces: cute_triadic_gdn/kernels/sm100_joint_state_grads.py:480-520 (joint_state_grads_sm100). */
+int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U, const void* h,
+                         const void* ds, const float* k2, const float* q2, const float* gc, float scale,
+                         const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* dkq, float* da, float* dc,
+                         float* dd, void* stream);
+
 /* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
  * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
  * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).

@@ -35,3 +35,26 @@ def test_reverse_recurrence_dense(E, dist):
     assert orc.rel_l2(dsm, rv["ds"]) < 1e-2
     drs = dr.cpu().sum(3).permute(0, 2, 1, 3, 4).reshape(B * H, T // 64, 64, E)
     assert orc.rel_l2(drs, rv["dr"]) < 1e-2
+
+
+@pytest.mark.parametrize("E", [1, 2, 4, 8, 12, 16])
+def test_state_grads_dense(E):
+    B, T, H = 1, 256, 2
+    ins = orc.make_inputs(B, T, H, E, seed=300 + E, dist="baseline")
+    do = orc.make_grad_output((B, T, H, 128), 7)
+    scale = 128 ** -0.5
+    q, k, v, k2, q2, g, beta = _gpu(ins)
+    dog = do.cuda()
+    o, gc, AP, Pm, h, W, U = gj._kernel_forward(q, k, v, k2, q2, g, beta, scale, True)
+    dV, dU, ds, dr = gj._run_reverse(q, k, dog, k2, q2, beta, gc, AP, Pm, U, scale)
+    dkq, da, dc, dd = gj._run_state_grads(q, k, dog, dV, U, h, ds, k2, q2, gc, scale)
+    assert _lib.device_status() == 0
+    _, _, st = plan.run_plan(*ins, do, rounding=True)
+    sg = st["sg"]
+    NC = T // 64
+    ch = lambda t: t.cpu().permute(0, 2, 1, 3, 4).reshape(B * H, NC, *t.shape[3:])
+    assert orc.rel_l2(ch(dkq)[:, :, :64], sg["dK"]) < 1e-2
+    assert orc.rel_l2(ch(dkq)[:, :, 64:], sg["dQ"]) < 1e-2
+    assert orc.rel_l2(ch(da), sg["da"]) < 1e-2
+    assert orc.rel_l2(ch(dc), sg["dc"]) < 1e-2
+    assert orc.rel_l2(dd.cpu().permute(0, 2, 1, 3).reshape(B * H, NC, E), sg["dd"]) < 1e-2
