@@ -7,6 +7,8 @@
 Same names, signatures, shapes and dtypes as cute_triadic_gdn/__init__.py:7-11 of the reference.
 """
 from .conv_split_act import conv_split_act_call
+from .gdn_joint import chunk_gdn_joint
+from .joint_torch_ops import gdn_joint_call
 
-__all__ = ["conv_split_act_call"]
+__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call"]
 __version__ = "0.1.0"

@@ -133,3 +133,85 @@ def _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map=None):
             _lib.ptr(q2), _lib.ptr(gc), float(scale), _lib.ptr(token_map), B, T, H, E, NC, _lib.ptr(dkq), _lib.ptr(da),
             _lib.ptr(dc), _lib.ptr(dd), _lib.stream_of(q)), "tgdn_bwd_state_grads")
     return dkq, da, dc, dd
+
+
+def _run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale, token_map=None):
+    """Matrix gradients, mask gradients and final assembly: (dq, dk, dk2, dq2, dg, dbeta)."""
+    B, T, H, E, NC = _dims(q, k2, token_map)
+    dq, dk = torch.empty_like(q), torch.empty_like(k)
+    dk2, dq2, dg, db = torch.empty_like(k2), torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(beta)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib.tgdn_bwd_matrix(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(dU), _lib.ptr(W), _lib.ptr(U), _lib.ptr(AP), _lib.ptr(k2),
+            _lib.ptr(q2), _lib.ptr(beta), _lib.ptr(gc), _lib.ptr(dkq), _lib.ptr(da), _lib.ptr(dc), _lib.ptr(dd),
+            _lib.ptr(dr), float(scale), _lib.ptr(token_map), B, T, H, E, NC, _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dk2),
+            _lib.ptr(dq2), _lib.ptr(dg), _lib.ptr(db), _lib.stream_of(q)), "tgdn_bwd_matrix")
+    return dq, dk, dk2, dq2, dg, db
+
+
+def _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do, scale, chunk_starts=None, token_map=None):
+    """reverse recurrence -> state gradients -> matrix gradients.  Returns (dq, dk, dv, dk2, dq2, dg, dbeta)."""
+    if AP is None:      # GJ_SAVE_MASKS=0: the forward's own kernel again, bitwise identical
+        _, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
+    dV, dU, ds, dr = _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts, token_map)
+    dkq, da, dc, dd = _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map)
+    del ds
+    dq, dk, dk2, dq2, dg, db = _run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale,
+                                           token_map)
+    return dq, dk, dV, dk2, dq2, dg, db
+
+
+def _save_list(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, chunk_starts, token_map):
+    """Tensors kept for the backward: 14 with the chunk operators, 12 without (GJ_SAVE_MASKS=0)."""
+    if _save_masks():
+        return (q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, chunk_starts, token_map)
+    return (q, k, k2, q2, g, beta, gc, h, W, U, chunk_starts, token_map)
+
+
+def _unpack_saved(saved):
+    if len(saved) == 14:
+        return saved
+    q, k, k2, q2, g, beta, gc, h, W, U, chunk_starts, token_map = saved
+    return (q, k, k2, q2, g, beta, gc, None, None, h, W, U, chunk_starts, token_map)
+
+
+class _JointKernels(torch.autograd.Function):
+    """The kernel pipeline as a plain autograd function (reference: ops/gdn_joint.py:201-232, _JointCute)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k2, q2, g, beta, scale, chunk_starts=None, token_map=None):
+        o, gc, AP, Pm, h, W, U = _kernel_forward(q, k, v, k2, q2, g, beta, scale, True, chunk_starts, token_map)
+        ctx.save_for_backward(*_save_list(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, chunk_starts, token_map))
+        ctx.scale = scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, chunk_starts, token_map = _unpack_saved(ctx.saved_tensors)
+        grads = _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do.contiguous(), ctx.scale,
+                                 chunk_starts, token_map)
+        return (*(gr if need else None for gr, need in zip(grads, ctx.needs_input_grad)),
+                *([None] * (len(ctx.needs_input_grad) - 7)))
+
+
+def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, reference=False):
+    """Triadic GDN with autograd for all seven tensor inputs, on the sm_100a kernels.
+
+    With cu_seqlens the inputs are one packed row (1, T, ...): contiguous int32/int64 CUDA offsets that start at 0,
+    end at T and strictly increase; document lengths are arbitrary and the state resets at every document start.
+    `reference=True` asked the reference package for its torch pipeline; this package ships kernels only (its CPU
+    restatement of that pipeline lives with the tests), so the flag is rejected instead of silently running something else.
+    """
+    if reference:
+        raise NotImplementedError("reference=True: this package has no torch fallback; the CPU oracle used by the "
+                                  "tests is oracle/triadic_oracle.py")
+    _check(q, k, v, k2, q2, g, beta, packed=cu_seqlens is not None)
+    _check_device_and_e(q, k2.shape[-1])
+    chunk_starts = token_map = None
+    if cu_seqlens is not None:
+        from .joint_packing import prepare_documents
+        chunk_starts, token_map = prepare_documents((q, k, v, k2, q2, g, beta), cu_seqlens)
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, k2, q2, g, beta)):
+        return _JointKernels.apply(q, k, v, k2, q2, g, beta, float(scale), chunk_starts, token_map)
+    return _kernel_forward(q, k, v, k2, q2, g, beta, float(scale), False, chunk_starts, token_map)[0]

@@ -113,6 +113,17 @@ int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const voi
                          const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* dkq, float* da, float* dc,
                          float* dd, void* stream);
 
+/* tgdn_bwd_matrix: per (chunk, head), the matrix gradients through the chunk operators, the mask gradients, and the
+ * final assembly: dq, dk (bf16, token layout; local part + dkq), dk2, dq2, dg, dbeta (f32, token layout).  dg is the
+ * reverse chunk-local cumulative sum of the gradient of gc.
+ * Replaces: cute_triadic_gdn/kernels/sm100_joint_bwd_parallel.py:442-491 (joint_bwd_parallel_sm100: matrix_kernel and
+ * mask_grad_kernel) and the reverse cute_triadic_gdn/kernels/sm90_joint_scan.py:92-110 (joint_scan(reverse=True)). */
+int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, const void* dU, const void* W, const void* U,
+                    const void* AP, const float* k2, const float* q2, const float* beta, const float* gc,
+                    const float* dkq, const float* da, const float* dc, const float* dd, const float* dr, float scale,
+                    const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dq, void* dk, float* dk2,
+                    float* dq2, float* dg, float* dbeta, void* stream);
+
 /* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
  * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
  * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).
