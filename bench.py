@@ -1,0 +1,371 @@
+"""Benchmark of the Triadic GDN hot path: forward + backward tokens/s at T=8192, H=32, E=8, B=8 (heads sharded over N GPUs).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|conv]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+One step = one forward + backward of the whole (B, T, H) problem through `gdn_joint_call` (the public API).  Prints ONE
+JSON line from rank 0.  `value` is timed with the inputs resident in HBM; `e2e` repeats the measurement with the
+inputs in pinned host memory, copied to the device every step, and the output and all seven gradients copied back.
+`roofline` describes the kernel with the largest share of the step; `cpu_baseline` times the CPU oracle (a port of the
+reference's torch path) on a bounded sample.  `--impl reference` times that CPU path alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+U_FLOP = 2 * 64 * 64 * 128          # one 64x64x128 product
+
+WORKLOADS = {
+    # name: (B, T, H, E, backward)
+    "c2": (8, 8192, 32, 8, True),
+    "c1": (4, 4096, 16, 4, False),
+    "c3": (1, 131072, 16, 16, True),
+    "small": (2, 1024, 4, 8, True),
+    "prof": (2, 8192, 16, 8, True),     # 4096 (chunk, head) items, a few GB: the size used for ncu captures
+}
+
+
+def algorithmic_flops(E, items, backward):
+    """(15 + 18E) u per (chunk, head) forward + backward, (4 + 6E) u forward only."""
+    per = (4 + 6 * E) + ((11 + 12 * E) if backward else 0)
+    return per * U_FLOP * items
+
+
+# per-kernel algorithmic work, in u per (chunk, head)
+KERNEL_U = {
+    "masks": lambda E: 2, "fwd": lambda E: 2 + 6 * E, "rec": lambda E: 3 + 6 * E, "sg": lambda E: 6 * E, "mat": lambda E: 8,
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return {"tflops": d.get("bf16_tflops_sustained", d.get("bf16_tflops")), "gbs": d.get("hbm_gbs"), "kind": "measured (sustained)"}
+    return {"tflops": 1400.0, "gbs": 6650.0, "kind": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(int(r[1]) for r in self.rows if len(r) >= 9 and r[1].isdigit())
+        mx = [int(r[2]) for r in self.rows if len(r) >= 9 and r[2].isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_inputs(B, T, H, E, seed=0):
+    """Seeded synthetic inputs of the BASELINE distribution, generated in slices to bound host memory."""
+    from oracle import triadic_oracle as orc
+    ins = orc.make_inputs(B, T, H, E, seed)
+    do = orc.make_grad_output((B, T, H, 128), seed + 1)
+    return ins, do
+
+
+def cpu_reference_rate(B, T, H, E, backward, budget_s=20.0, threads=None):
+    """tokens/s of the CPU oracle, from as many (batch row, head) slices of the workload as fit the time budget."""
+    from oracle import triadic_oracle as orc
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    Ts = T
+    done, t_used = 0, 0.0
+    while True:
+        ins = orc.make_inputs(1, Ts, 1, E, seed=100 + done)
+        do = orc.make_grad_output((1, Ts, 1, 128), 7)
+        t0 = time.perf_counter()
+        if backward:
+            orc.reference_with_grads(orc.chunk_reference, ins, do, dtype=torch.float32)
+        else:
+            with torch.no_grad():
+                orc.chunk_reference(*ins, dtype=torch.float32)
+        t_used += time.perf_counter() - t0
+        done += 1
+        if t_used > budget_s or done >= B * H:
+            break
+    per_slice = t_used / done
+    rate = B * T / (per_slice * B * H)
+    return rate, done, threads, per_slice
+
+
+def run_reference(args, rank, world):
+    B, T, H, E, backward = WORKLOADS[args.workload]
+    if rank != 0:
+        return
+    steps, rates = max(1, args.steps), []
+    sample = None
+    for _ in range(args.warmup + steps):
+        rate, n, threads, per_slice = cpu_reference_rate(B, T, H, E, backward, budget_s=max(2.0, 40.0 / (args.warmup + steps)))
+        rates.append(rate)
+        sample = f"{n} of {B * H} (batch row, head) slices of T={T} per step, scaled linearly"
+    rates = rates[args.warmup:]
+    value = sum(rates) / len(rates)
+    line = {"impl": "reference", "metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value,
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 * B * T / value, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'fwd+bwd' if backward else 'fwd'}",
+                       "path": "CPU port of the reference torch path (oracle/triadic_oracle.py)"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def stage_times(leaves, do, E, reps=2):
+    """Per-kernel device time (ms) of one forward + backward: CUDA events around each C-ABI call on torch's stream."""
+    from cute_triadic_gdn_b200 import gdn_joint as gj
+    q, k, v, k2, q2, g, beta = [t.detach() for t in leaves]
+    scale = 128 ** -0.5
+    names = ["masks", "fwd", "rec", "sg", "mat"]
+    acc = {n: 0.0 for n in names}
+    for rep in range(reps + 1):                        # the first repetition warms the allocator and is dropped
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        ev[0].record()
+        gc, AP, Pm = gj._run_masks(q, k, k2, q2, g, beta, scale, None)
+        ev[1].record()
+        o, h, W, U = gj._run_forward(q, k, v, k2, q2, beta, gc, AP, scale, True)
+        ev[2].record()
+        dV, dU, ds, dr = gj._run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale)
+        ev[3].record()
+        dkq, da, dc, dd = gj._run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale)
+        ev[4].record()
+        gj._run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale)
+        ev[5].record()
+        torch.cuda.synchronize()
+        if rep > 0:
+            for i, n in enumerate(names):
+                acc[n] += ev[i].elapsed_time(ev[i + 1])
+        del h, ds, dkq, W, U, dU, o
+    return {n: acc[n] / reps for n in names}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from cute_triadic_gdn_b200 import _lib, gdn_joint_call
+    B, T, H, E, backward = WORKLOADS[args.workload]
+    if H % world:
+        raise SystemExit(f"H={H} is not divisible by {world} GPUs")
+    Hl = H // world                                   # heads of this rank (strong scaling: total work fixed)
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    ins, do = host_inputs(B, T, Hl, E, seed=1000 + rank)
+    pinned = [t.pin_memory() for t in ins]
+    do_pinned = do.pin_memory()
+    leaves = [t.to(dev).requires_grad_(backward) for t in ins]
+    do_dev = do.to(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        for t in leaves:
+            t.grad = None
+        o = gdn_joint_call(*leaves)
+        if backward:
+            o.backward(do_dev)
+        return o
+
+    out_host = None
+
+    def step_e2e():
+        nonlocal out_host
+        dev_in = [t.to(dev, non_blocking=True).requires_grad_(backward) for t in pinned]
+        dod = do_pinned.to(dev, non_blocking=True)
+        o = gdn_joint_call(*dev_in)
+        outs = [o.detach()]
+        if backward:
+            o.backward(dod)
+            outs += [t.grad for t in dev_in]
+        if out_host is None:
+            out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+        for hbuf, t in zip(out_host, outs):
+            hbuf.copy_(t, non_blocking=True)
+        return outs
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    if args.kernels_only:
+        if rank == 0:
+            print(json.dumps({"metric": "fwd+bwd tokens/s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s",
+                              "ms_per_step": ms / args.steps, "config": {"workload": args.workload}, "kernels_only": True}))
+        return
+    ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2))
+    status = _lib.device_status()
+
+    tokens = B * T
+    value = tokens * args.steps / (ms * 1e-3)
+    e2e_value = tokens * args.steps / (ms_e2e * 1e-3)
+    nbytes = lambda ts: int(sum(t.numel() * t.element_size() for t in ts))
+    h2d = nbytes(pinned) + nbytes([do_pinned])
+    d2h = nbytes(out_host) if out_host else 0
+    if rank != 0:
+        return
+
+    pk = peaks()
+    items = B * (T // 64) * Hl
+    roof = None
+    if backward:
+        st = stage_times(leaves, do_dev, E)
+        total = sum(st.values())
+        top = max(st, key=st.get)
+        flops = KERNEL_U[top](E) * U_FLOP * items
+        achieved = flops / (st[top] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+                "frac": achieved / pk["tflops"], "traffic": None, "peak_kind": pk["kind"],
+                "kernel_ms": {k: round(v, 3) for k, v in st.items()}, "share": round(st[top] / total, 3),
+                "step_achieved": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12,
+                "step_frac": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12 / pk["tflops"]}
+    cpu_rate, n_slices, threads, per_slice = cpu_reference_rate(B, T, H, E, backward, budget_s=15.0)
+    line = {"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'fwd+bwd' if backward else 'fwd'}, GJ_SAVE_MASKS="
+                                   f"{os.environ.get('GJ_SAVE_MASKS', '1')}",
+                       "parallelism": f"heads sharded over {world} GPU(s), no collective", "l2": "inputs larger than L2",
+                       "api": "gdn_joint_call + backward"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * (5 if backward else 2),
+            "clocks": clocks, "roofline": roof, "device_status": status,
+            "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": f"{n_slices} of {B * H} (batch row, head) slices of T={T}, {per_slice:.2f} s each, scaled linearly"}}
+    print(json.dumps(line))
+
+
+def run_conv(args):
+    """Secondary workload: the convolution pre-pass at (1, 32768, 13056), HBM roofline."""
+    from cute_triadic_gdn_b200 import conv_split_act_call
+    dev = torch.device("cuda", 0)
+    T, C, act = 32768, 13056, 12288
+    x = torch.randn(1, T, C, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = (0.5 * torch.randn(C, 4, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(1, T, C, device=dev).to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, 4096, device=dev, dtype=torch.int32)
+
+    def ev_time(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    with torch.no_grad():
+        fwd_ms = ev_time(lambda: conv_split_act_call(x, w, act, cu), args.steps)
+    y = conv_split_act_call(x, w, act, cu)
+    from cute_triadic_gdn_b200.conv_split_act import conv_split_act_bwd
+    bwd_ms = ev_time(lambda: conv_split_act_bwd(x.detach(), dy, w.detach(), act, cu), args.steps)
+    pk = peaks()
+    fb, bb = 4 * T * C, 6 * T * C
+    line = {"metric": "conv_split_act GB/s", "value": fb / (fwd_ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": fwd_ms, "higher_is_better": True, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": f"conv (1,{T},{C}) act={act}, 8 documents"},
+            "roofline": {"bound": "hbm", "kernel": "conv_fwd", "achieved": fb / (fwd_ms * 1e-3) / 1e9, "peak": pk["gbs"],
+                         "unit": "GB/s", "frac": fb / (fwd_ms * 1e-3) / 1e9 / pk["gbs"], "traffic": None,
+                         "peak_kind": pk["kind"]},
+            "conv_bwd": {"ms": bwd_ms, "achieved": bb / (bwd_ms * 1e-3) / 1e9, "frac": bb / (bwd_ms * 1e-3) / 1e9 / pk["gbs"]}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=list(WORKLOADS) + ["conv"])
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="skip the end-to-end, per-kernel and CPU-baseline legs (used for profiler captures)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if args.workload == "conv":
+        run_conv(args)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

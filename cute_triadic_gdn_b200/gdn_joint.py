@@ -72,11 +72,10 @@ def _run_masks(q, k, k2, q2, g, beta, scale, token_map, gc=None):
     return gc_out, AP, Pm
 
 
-def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, token_map=None):
-    """masks -> forward recurrence.  Returns o and, with save=True, (gc, AP, Pm, h, W, U)."""
+def _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, save, chunk_starts=None, token_map=None):
+    """Forward recurrence: (o, h, W, U); h, W, U are None unless save."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
-    gc, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
     o = torch.empty_like(v)
     if token_map is not None:
         o.zero_()  # rows of a packed row are all covered by documents; kept defined even for a rejected chunk map
@@ -91,6 +90,13 @@ def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, to
                                      _lib.ptr(gc), _lib.ptr(AP), float(scale), _lib.ptr(chunk_starts),
                                      _lib.ptr(token_map), n_docs, B, T, H, E, NC, _lib.ptr(o), _lib.ptr(W), _lib.ptr(U),
                                      _lib.ptr(h), _lib.stream_of(q)), "tgdn_fwd")
+    return o, h, W, U
+
+
+def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, token_map=None):
+    """masks -> forward recurrence.  Returns (o, gc, AP, Pm, h, W, U); h, W, U are None unless save."""
+    gc, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
+    o, h, W, U = _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, save, chunk_starts, token_map)
     return o, gc, AP, Pm, h, W, U
 
 
