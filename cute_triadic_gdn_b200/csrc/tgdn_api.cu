@@ -83,6 +83,7 @@ extern "C" const char* tgdn_error_string(int code) {
     case TGDN_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
     case TGDN_ERR_SCRATCH: return "scratch buffer missing or too small";
     case TGDN_ERR_DEVICE: return "the current device is not compute capability 10.x (sm_100a kernels)";
+    case TGDN_ERR_STATIC_LIMIT: return "the problem needs more scratch than the library's built-in static buffer holds";
     default: break;
   }
   if (code <= -1000) {

@@ -6,6 +6,8 @@
 // recomputes the bf16-rounded pre-activation from the same window (the reference launches a second forward for it),
 // reads x and dy once, writes dx once, and leaves one f32 weight-gradient partial per token tile in scratch memory; a
 // second small kernel sums the partials in a fixed order.
+#include <mutex>
+
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 
@@ -300,5 +302,70 @@ extern "C" int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, 
   const int n_elem = C * CONV_W;
   conv_dw_reduce_kernel<<<(n_elem + 255) / 256, 256, 0, s>>>(static_cast<const float*>(scratch),
                                                              static_cast<__nv_bfloat16*>(dw), B * tiles, n_elem);
+  return tgdn_cuda_error(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// tgdn_conv_bwd_static: the same backward, for hosts that may not allocate device memory.
+//
+// Some embedders load this library into a process whose device memory is owned by someone else: an inference server
+// with a fixed arena, a plugin inside a framework that forbids cudaMalloc on its worker threads, a latency-critical loop
+// in which an allocation (which can synchronise the whole device, or fail once memory is fragmented) is not acceptable.
+// They can hand over inputs and outputs but have no pool to take the weight-gradient partials from.  For them the
+// partials live in a fixed array that is part of the library image itself.
+//
+// The array costs TGDN_CONV_STATIC_SCRATCH_BYTES on every GPU that loads the library, until the process exits.
+// Its device address is looked up once per device (cudaGetSymbolAddress, with that device current) on the first call
+// made on that device; make that first call outside any stream capture.  The array is shared by every call on the
+// device and keeps whatever the previous call left in it: this kernel overwrites every partial it later reads, so
+// nothing has to be cleared, but two calls that overlap on the GPU (different streams) would corrupt each other.
+// ---------------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_conv_static_scratch[TGDN_CONV_STATIC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_mutex;
+
+// Device address of the static scratch array on the current device (looked up once per device).
+int conv_static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevices) return TGDN_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_conv_static_scratch);
+    if (e != cudaSuccess) return tgdn_cuda_error(e);
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int tgdn_conv_bwd_static(const void* x, const void* weight, const void* dy, void* dx, void* dw,
+                                    const int32_t* cu_seqlens, int n_docs, int B, int T, int C, int64_t stride_b,
+                                    int64_t stride_t, int64_t dy_stride_b, int64_t dy_stride_t, int act_channels,
+                                    void* stream) {
+  int rc = conv_check(x, weight, dx, cu_seqlens, n_docs, B, T, C, stride_b, stride_t);
+  if (rc) return rc;
+  if (!dy || !dw) return TGDN_ERR_NULL;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (dy_stride_b % 8) || (dy_stride_t % 8)) return TGDN_ERR_ALIGN;
+  if (tgdn_conv_bwd_scratch_bytes(B, T, C) > static_cast<int64_t>(TGDN_CONV_STATIC_SCRATCH_BYTES)) return TGDN_ERR_STATIC_LIMIT;
+  float* scratch = nullptr;
+  if ((rc = conv_static_scratch(&scratch))) return rc;
+  const int tiles = (T + CONV_BWD_TOKENS - 1) / CONV_BWD_TOKENS;
+  dim3 grid((C / 8 + CONV_THREADS - 1) / CONV_THREADS, tiles, B);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  conv_bwd_kernel<<<grid, CONV_THREADS, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
+      static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C, stride_b,
+      stride_t, dy_stride_b, dy_stride_t, act_channels);
+  rc = tgdn_cuda_error(cudaGetLastError());
+  if (rc) return rc;
+  const int n_elem = C * CONV_W;
+  conv_dw_reduce_kernel<<<(n_elem + 255) / 256, 256, 0, s>>>(scratch, static_cast<__nv_bfloat16*>(dw), B * tiles, n_elem);
   return tgdn_cuda_error(cudaGetLastError());
 }

@@ -29,6 +29,7 @@ extern "C" {
 #define TGDN_ERR_DRIVER (-4)      /* the CUDA driver entry point for tensor maps is unavailable or failed */
 #define TGDN_ERR_SCRATCH (-5)     /* scratch buffer missing or too small */
 #define TGDN_ERR_DEVICE (-6)      /* the current device is not compute capability 10.x */
+#define TGDN_ERR_STATIC_LIMIT (-7) /* the problem needs more scratch than the library's built-in static buffer holds */
 
 /* Human-readable text for a return code of this library. */
 const char* tgdn_error_string(int code);
@@ -59,6 +60,22 @@ int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C);
 int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, void* dx, void* dw, const int32_t* cu_seqlens,
                   int n_docs, int B, int T, int C, int64_t stride_b, int64_t stride_t, int64_t dy_stride_b,
                   int64_t dy_stride_t, int act_channels, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Size of the scratch array built into the library for tgdn_conv_bwd_static (held on every GPU that loads the library). */
+#define TGDN_CONV_STATIC_SCRATCH_BYTES (8u << 20)
+
+/* tgdn_conv_bwd_static: tgdn_conv_bwd for callers that cannot give it scratch memory because they are not allowed to
+ * allocate on the device (a host with a fixed, externally owned memory arena; a thread on which cudaMalloc is forbidden
+ * or too slow because it may synchronise the device).  Same arguments and results as tgdn_conv_bwd without the scratch
+ * pair; the weight-gradient partials go to a TGDN_CONV_STATIC_SCRATCH_BYTES array inside the library image.
+ * Limit: tgdn_conv_bwd_scratch_bytes(B, T, C) must not exceed that size, otherwise TGDN_ERR_STATIC_LIMIT is returned
+ * and nothing is launched.  The first call on each device looks up the array's device address (make it outside any
+ * stream capture); the array is shared by all calls on a device, so calls that overlap on the GPU race with each other.
+ * Neither this call nor anything under it allocates or frees memory.
+ * No counterpart in the reference (its wrappers always allocate with torch). */
+int tgdn_conv_bwd_static(const void* x, const void* weight, const void* dy, void* dx, void* dw, const int32_t* cu_seqlens,
+                         int n_docs, int B, int T, int C, int64_t stride_b, int64_t stride_t, int64_t dy_stride_b,
+                         int64_t dy_stride_t, int act_channels, void* stream);
 
 /* ---- packed-document metadata -------------------------------------------------------------------------------------
  * Chunk-map capacity for n_docs documents over T tokens: ceil(T/64) + n_docs - 1 rounded up to a multiple of 16.
