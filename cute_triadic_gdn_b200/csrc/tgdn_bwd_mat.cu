@@ -1,7 +1,8 @@
 // Per-chunk matrix gradients of the Triadic GDN backward, the mask gradients and the final assembly of dq, dk, dk2,
 // dq2, dg, dbeta.
 //
-// One CTA of 128 threads per (batch, chunk, head); thread r < 64 owns key row t = r, thread 64 + t owns query row t.
+// One CTA of 512 threads per (batch, chunk, head).  Thread (r, cq): r = tensor-memory lane = matrix row (r < 64: key row
+// t = r, r >= 64: query row t = r - 64), cq = which 16 of the 64 columns s it works on.
 //   G1  P    = [K;Q] K^T                     (Pkk rows 0..63, Pqk rows 64..127)
 //   G2  [dU;dO] [W;U]^T                      (rows 0..63, cols 0..63: dA' = dU W^T;  rows 64..127, cols 64..127: dPm' = dO U^T)
 //       X    = scale*lower(Mp*dPm'),  dmp = scale*lower(Pqk*dPm'),  dA = dA' diag(beta),  dbeta_col = colsum(dA'*A)
@@ -10,6 +11,8 @@
 //   G5  [dK;dQ] = [[dPkk+dPkk^T, X^T],[X, 0]] [K;Q]  + state part (from the state-gradient kernel)
 //   mask gradients r1, c1 (from dmp) and r2, c2 (from dm) with the decay factors recomputed, gate-table gradients
 //   folded in, reverse cumulative sum of dgc inside the chunk -> dg.
+// Row and column sums that span the four column quarters go through four-copy partial tables in shared memory and are
+// added in a fixed order (no atomics: results are bitwise reproducible).
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_parallel.py:80-405 (matrix_kernel),
 // cute_triadic_gdn/kernels/sm90_joint_bwd_parallel.py:278-372 (mask_grad_kernel) and the reverse pass of
@@ -20,7 +23,7 @@
 
 namespace tgdn {
 
-constexpr int MAT_THREADS = 128;
+constexpr int MAT_THREADS = 512;
 
 __device__ __forceinline__ float mexp2(float x) {
   float y;
@@ -33,7 +36,9 @@ __device__ __forceinline__ void st_shared_b16(uint32_t saddr, float v) {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"(b) : "memory");
 }
 
+template <int E>
 struct MatSmem {
+  static constexpr int ES = E | 1;
   uint8_t kq[32768];                 // [K;Q] tile
   union {
     uint8_t dudo[32768];             // [dU;dO] tile (until G2), then the 128x128 operand of G5:
@@ -47,9 +52,11 @@ struct MatSmem {
   uint8_t da[8192];                  // dA image (i = t, j = s), SI = 128, SJ = 1024
   uint8_t y[8192];                   // Y image (i = s', j = t'), SI = 128, SJ = 1024 (read as 128 rows: daa follows)
   float daa[4096];                   // dA' * A, for the column sums
-  float gc2[64 * 17], k2[64 * 17], q2[64 * 17];
-  float r1[64 * 17], c1[64 * 17], dgc[64 * 17];
-  float beta[64];
+  float gc2[64 * ES], k2[64 * ES], q2[64 * ES];
+  float r1[64 * ES], c1[64 * ES], r2[64 * ES], c2[64 * ES], dgc[64 * ES], drr[64 * ES];
+  float part[2][4][64 * ES];         // per column quarter partial sums
+  float browp[4][64];
+  float beta[64], brow[64], bcol[64];
   uint64_t bar_load, bar_mma;
   uint32_t tmem_base;
   int abort;
@@ -61,12 +68,16 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_du,
            const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u, MatParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  MatSmem& sm = *reinterpret_cast<MatSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int ES = 17;
+  using SM = MatSmem<E>;
+  SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int ES = SM::ES;
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool krow = tid < 64;
-  const int t = tid & 63;
+  const int cq = warp >> 2;                                // column quarter
+  const int r = (warp & 3) * 32 + lane;                    // tensor-memory lane = matrix row
+  const bool krow = r < 64;
+  const int t = r & 63;
+  const int s0 = cq * 16;
   const int h = blockIdx.x % p.H, n = (blockIdx.x / p.H) % p.NC, b = blockIdx.x / (p.H * p.NC);
   const int64_t item = blockIdx.x;
 
@@ -91,7 +102,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&sm.abort, p.status};
   const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
 
@@ -108,15 +119,18 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     bulk_load(sm.ap, p.AP + item * (128 * 64), 16384, &sm.bar_load);
   }
-  // gates (log2 domain), rows past the document end: k2 = q2 = beta = 0
+  // gates (log2 domain), rows past the document end: k2 = q2 = beta = 0; dr summed over the value blocks
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
-    const int r = idx / E, e = idx % E;
-    const bool ok = r < rows;
-    const int64_t off = ((tok + r) * p.H + h) * E + e;
-    sm.gc2[r * ES + e] = p.gc[item * (64 * E) + idx] * LOG2E;
-    sm.k2[r * ES + e] = ok ? p.k2[off] : 0.f;
-    sm.q2[r * ES + e] = ok ? p.q2[off] : 0.f;
+    const int rr = idx / E, e = idx % E;
+    const bool ok = rr < rows;
+    const int64_t off = ((tok + rr) * p.H + h) * E + e;
+    sm.gc2[rr * ES + e] = p.gc[item * (64 * E) + idx] * LOG2E;
+    sm.k2[rr * ES + e] = ok ? p.k2[off] : 0.f;
+    sm.q2[rr * ES + e] = ok ? p.q2[off] : 0.f;
+    float drv = 0.f;
+    for (int v = 0; v < p.NV; ++v) drv += p.dr[((item * p.NV + v) * 64 + rr) * E + e];
+    sm.drr[rr * ES + e] = drv;
   }
   if (tid < 64) sm.beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
   __syncthreads();
@@ -145,10 +159,10 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
-  float pr[64];                                            // Pkk row (key rows) / Pqk row (query rows)
-  float gr[64];                                            // dA' row (key rows) / dPm' row (query rows)
-  tmem_ld<64>(tmem_row, pr);
-  tmem_ld<64>(tmem_row + 64 + (krow ? 0 : 64), gr);
+  float pr[16];                                            // Pkk (key rows) / Pqk (query rows), this thread's 16 columns
+  float gr[16];                                            // dA' (key rows) / dPm' (query rows)
+  tmem_ld<16>(tmem_row + s0, pr);
+  tmem_ld<16>(tmem_row + 64 + (krow ? 0 : 64) + s0, gr);
   tmem_wait_ld();
   tc_fence_before();
   __syncthreads();                                         // dudo and wu are dead: a5, dmp, dm take their place
@@ -160,19 +174,20 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mygc[e] = sm.gc2[t * ES + e];
   }
   const uint32_t a5 = smem_u32(sm.u1.a5);
-  float r1v[E];                                            // query rows: r1;  key rows (later): r2
-#pragma unroll
-  for (int e = 0; e < E; ++e) r1v[e] = 0.f;
-  float dbeta = 0.f;
+  const int warp_tmax = (warp & 1) ? 63 : 31;              // largest row index t in this warp
 
   if (!krow) {
-    // query row t: X row -> a5 (row 64+t and, transposed, column 64+t), dmp row, r1
+    // query row t, columns s0..s0+15: X -> a5 (row 64+t and, transposed, column 64+t), dmp, partial r1
     const float live = (t < rows) ? 1.f : 0.f;
-    float xrow[64];
+    float r1v[E];
 #pragma unroll
-    for (int s = 0; s < 64; ++s) {
+    for (int e = 0; e < E; ++e) r1v[e] = 0.f;
+    float xrow[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int s = s0 + j;
       float x = 0.f, dmpv = 0.f;
-      if (s <= ((warp & 1) ? 63 : 31) && s <= t) {
+      if (s0 <= warp_tmax && s <= t) {
         float dec[E];
         float mp = 0.f;
 #pragma unroll
@@ -180,41 +195,41 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           dec[e] = mexp2(mygc[e] - sm.gc2[s * ES + e]) * sm.k2[s * ES + e];
           mp = fmaf(my2[e], dec[e], mp);
         }
-        x = p.scale * mp * gr[s];
-        dmpv = live * p.scale * pr[s] * gr[s];
+        x = p.scale * mp * gr[j];
+        dmpv = live * p.scale * pr[j] * gr[j];
 #pragma unroll
         for (int e = 0; e < E; ++e) r1v[e] = fmaf(dmpv, dec[e], r1v[e]);
       }
-      xrow[s] = x;
+      xrow[j] = x;
       sm.u2.f.dmp[midx(t, s)] = dmpv;
       st_shared_b16(a5 + (s >> 3) * 128 + ((64 + t) >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, x);   // a5[s][64+t]
     }
     const uint32_t rowbase = a5 + ((64 + t) >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-    for (int jb = 0; jb < 8; ++jb) {
-      st_shared_v4(rowbase + jb * 2048, pack_bf16(xrow[jb * 8], xrow[jb * 8 + 1]), pack_bf16(xrow[jb * 8 + 2], xrow[jb * 8 + 3]),
+    for (int jb = 0; jb < 2; ++jb) {
+      st_shared_v4(rowbase + (2 * cq + jb) * 2048, pack_bf16(xrow[jb * 8], xrow[jb * 8 + 1]), pack_bf16(xrow[jb * 8 + 2], xrow[jb * 8 + 3]),
                    pack_bf16(xrow[jb * 8 + 4], xrow[jb * 8 + 5]), pack_bf16(xrow[jb * 8 + 6], xrow[jb * 8 + 7]));
-      st_shared_v4(rowbase + (8 + jb) * 2048, 0u, 0u, 0u, 0u);
+      st_shared_v4(rowbase + (8 + 2 * cq + jb) * 2048, 0u, 0u, 0u, 0u);
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) sm.r1[t * ES + e] = r1v[e];
+    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r1v[e];
   } else {
-    // key row t: dA = dA' diag(beta) -> operand image; dA' * A -> column sums
+    // key row t, columns s0..s0+15: dA = dA' diag(beta) -> operand image; dA' * A -> column sums
     const uint32_t apr = smem_u32(sm.ap) + (t >> 3) * 128 + (t & 7) * 16;
     const uint32_t dar = smem_u32(sm.da) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-    for (int jb = 0; jb < 8; ++jb) {
+    for (int jb = 0; jb < 2; ++jb) {
       uint32_t aw[4];
-      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(aw[0]), "=r"(aw[1]), "=r"(aw[2]), "=r"(aw[3]) : "r"(apr + jb * 2048));
+      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(aw[0]), "=r"(aw[1]), "=r"(aw[2]), "=r"(aw[3]) : "r"(apr + (2 * cq + jb) * 2048));
       float dav[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        const int s = jb * 8 + c;
+        const int j = jb * 8 + c, s = s0 + j;
         const float a_ts = (c & 1) ? bf16_hi(aw[c >> 1]) : bf16_lo(aw[c >> 1]);
-        sm.daa[midx(t, s)] = gr[s] * a_ts;
-        dav[c] = gr[s] * sm.beta[s];
+        sm.daa[midx(t, s)] = gr[j] * a_ts;
+        dav[c] = gr[j] * sm.beta[s];
       }
-      st_shared_v4(dar + jb * 1024, pack_bf16(dav[0], dav[1]), pack_bf16(dav[2], dav[3]), pack_bf16(dav[4], dav[5]),
+      st_shared_v4(dar + (2 * cq + jb) * 1024, pack_bf16(dav[0], dav[1]), pack_bf16(dav[2], dav[3]), pack_bf16(dav[4], dav[5]),
                    pack_bf16(dav[6], dav[7]));
     }
   }
@@ -232,22 +247,28 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 192, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
-  if (krow) {                                              // meanwhile: dbeta_col[s = t] = sum_t' dA'[t',s] A[t',s]
+  // meanwhile: r1 = sum of the four partials; dbeta_col[s] = sum_t dA'[t,s] A[t,s]
+  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
+    const int o = (idx / E) * ES + idx % E;
+    sm.r1[o] = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
+  }
+  if (tid >= 448) {
+    const int s = tid - 448;
     float acc = 0.f;
-    for (int tt = 0; tt < 64; ++tt) acc += sm.daa[midx(tt, t)];
-    dbeta = acc;
+    for (int tt = 0; tt < 64; ++tt) acc += sm.daa[midx(tt, s)];
+    sm.bcol[s] = acc;
   }
   mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
-    float yr[64];
-    tmem_ld<64>(tmem_row + 192, yr);
+    float yr[16];
+    tmem_ld<16>(tmem_row + 192 + s0, yr);
     tmem_wait_ld();
     const uint32_t yb = smem_u32(sm.y) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-    for (int jb = 0; jb < 8; ++jb)
-      st_shared_v4(yb + jb * 1024, pack_bf16(yr[jb * 8], yr[jb * 8 + 1]), pack_bf16(yr[jb * 8 + 2], yr[jb * 8 + 3]),
+    for (int jb = 0; jb < 2; ++jb)
+      st_shared_v4(yb + (2 * cq + jb) * 1024, pack_bf16(yr[jb * 8], yr[jb * 8 + 1]), pack_bf16(yr[jb * 8 + 2], yr[jb * 8 + 3]),
                    pack_bf16(yr[jb * 8 + 4], yr[jb * 8 + 5]), pack_bf16(yr[jb * 8 + 6], yr[jb * 8 + 7]));
   }
   fence_async_smem();
@@ -264,20 +285,39 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 256, desc_advance(da, kk * 2048), desc_advance(db, kk * 4096), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
+  if (!krow) {
+    // meanwhile, query thread (64+s, cq): partial c1[s,e] over t' in quarter cq: dmp[t',s] exp(gc[t']-gc[s]) q2[t',e]
+    const int s = t;
+    float c1v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) c1v[e] = 0.f;
+    for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
+      const float dv = sm.u2.f.dmp[midx(tt, s)];
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
+  }
   mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
-    // key row t: dL row, dbeta_row, dm row, r2, and dPkk + dPkk^T into a5[0..63][0..63]
-    float dpr[64];
-    tmem_ld<64>(tmem_row + 256, dpr);
+    // key row t, columns s0..s0+15: dL, partial dbeta_row, dm, partial r2, and dPkk + dPkk^T into a5[0..63][0..63]
+    float dpr[16];
+    tmem_ld<16>(tmem_row + 256 + s0, dpr);
     tmem_wait_ld();
     const float bt = sm.beta[t];
     float brow = 0.f;
+    float r2v[E];
 #pragma unroll
-    for (int s = 0; s < 64; ++s) {
+    for (int e = 0; e < E; ++e) r2v[e] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int s = s0 + j;
       float dmv = 0.f;
-      if (s <= ((warp & 1) ? 63 : 31) && s < t) {
+      if (s0 <= warp_tmax && s < t) {
         float dec[E];
         float m = 0.f;
 #pragma unroll
@@ -285,33 +325,21 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           dec[e] = mexp2(mygc[e] - sm.gc2[s * ES + e]) * sm.k2[s * ES + e];
           m = fmaf(my2[e], dec[e], m);
         }
-        const float dl = -dpr[s];
-        brow = fmaf(dl * pr[s], m, brow);
-        dmv = bt * dl * pr[s];
+        const float dl = -dpr[j];
+        brow = fmaf(dl * pr[j], m, brow);
+        dmv = bt * dl * pr[j];
         const float dpk = bt * dl * m;
 #pragma unroll
-        for (int e = 0; e < E; ++e) r1v[e] = fmaf(dmv, dec[e], r1v[e]);
+        for (int e = 0; e < E; ++e) r2v[e] = fmaf(dmv, dec[e], r2v[e]);
         st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
         st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
       }
       sm.u2.f.dm[midx(t, s)] = dmv;
     }
-    st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);         // diagonal
-    dbeta += brow;
-  } else {
-    // query thread 64+s: c1[s,e] = sum_{t'>=s} dmp[t',s] exp(gc[t']-gc[s]) q2[t',e]
-    const int s = t;
-    float c1v[E];
+    if (cq == (t >> 4)) st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);   // diagonal
 #pragma unroll
-    for (int e = 0; e < E; ++e) c1v[e] = 0.f;
-    for (int tt = s; tt < 64; ++tt) {
-      const float dv = sm.u2.f.dmp[midx(tt, s)];
-#pragma unroll
-      for (int e = 0; e < E; ++e)
-        c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
-    }
-#pragma unroll
-    for (int e = 0; e < E; ++e) sm.c1[s * ES + e] = c1v[e];
+    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r2v[e];
+    sm.browp[cq][t] = brow;
   }
   fence_async_smem();
   tc_fence_before();
@@ -327,45 +355,51 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
-  // meanwhile the gate gradients of key row t
+  // sums of the partials written before the barrier
+  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
+    const int o = (idx / E) * ES + idx % E;
+    sm.r2[o] = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
+    sm.c1[o] = (sm.part[1][0][o] + sm.part[1][1][o]) + (sm.part[1][2][o] + sm.part[1][3][o]);
+  }
+  if (tid < 64) sm.brow[tid] = (sm.browp[0][tid] + sm.browp[1][tid]) + (sm.browp[2][tid] + sm.browp[3][tid]);
+  __syncthreads();
   if (krow) {
+    // key thread (s = t, cq): partial c2[s,e] over t' in quarter cq, t' > s: dm[t',s] exp(gc[t']-gc[s]) k2[t',e]
     float c2v[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) c2v[e] = 0.f;
-    for (int tt = t + 1; tt < 64; ++tt) {
+    for (int tt = max(t + 1, s0); tt < s0 + 16; ++tt) {
       const float dv = sm.u2.f.dm[midx(tt, t)];
 #pragma unroll
       for (int e = 0; e < E; ++e)
         c2v[e] = fmaf(dv * sm.k2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c2v[e]);
     }
-    const bool live = t < rows;
-    const float* dap = p.da + (item * 64 + t) * E;
-    const float* dcp = p.dc + (item * 64 + t) * E;
-    float* dk2p = p.dk2 + ((tok + t) * p.H + h) * E;
-    float* dq2p = p.dq2 + ((tok + t) * p.H + h) * E;
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      float drv = 0.f;
-      for (int v = 0; v < p.NV; ++v) drv += p.dr[((item * p.NV + v) * 64 + t) * E + e];
-      const float gl = sm.gc2[63 * ES + e];
-      const float eg = mexp2(mygc[e]), egr = mexp2(gl - mygc[e]);
-      const float k2v = my2[e], q2v = sm.q2[t * ES + e];
-      const float dav = dap[e], dcv = dcp[e];
-      const float r1e = sm.r1[t * ES + e], c1e = sm.c1[t * ES + e], r2e = r1v[e], c2e = c2v[e];
-      if (live) {
-        dk2p[e] = dav * eg + drv * egr + c1e + r2e + c2e;
-        dq2p[e] = dcv * p.scale * eg + r1e;
-      }
-      // dgc[t,e]; the chunk-end terms are added to row 63 below
-      sm.dgc[t * ES + e] = dav * (k2v * eg) + dcv * (p.scale * q2v * eg) - drv * (k2v * egr) + q2v * r1e + k2v * (r2e - c1e - c2e);
-      sm.r1[t * ES + e] = drv * (k2v * egr);                // reuse: dr*r, summed over the rows below
-    }
-    if (live) p.dbeta[(tok + t) * p.H + h] = dbeta;
+    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = c2v[e];
   }
+  __syncthreads();
+  // gate gradients: one thread per (row, gate column)
+  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
+    const int rr = idx / E, e = idx % E, o = rr * ES + e;
+    const float c2e = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
+    const float gcv = sm.gc2[o], gl = sm.gc2[63 * ES + e];
+    const float eg = mexp2(gcv), egr = mexp2(gl - gcv);
+    const float k2v = sm.k2[o], q2v = sm.q2[o];
+    const float dav = p.da[(item * 64 + rr) * E + e], dcv = p.dc[(item * 64 + rr) * E + e];
+    const float drv = sm.drr[o], r1e = sm.r1[o], c1e = sm.c1[o], r2e = sm.r2[o];
+    if (rr < rows) {
+      const int64_t off = ((tok + rr) * p.H + h) * E + e;
+      p.dk2[off] = dav * eg + drv * egr + c1e + r2e + c2e;
+      p.dq2[off] = dcv * p.scale * eg + r1e;
+    }
+    sm.dgc[o] = dav * (k2v * eg) + dcv * (p.scale * q2v * eg) - drv * (k2v * egr) + q2v * r1e + k2v * (r2e - c1e - c2e);
+    sm.drr[o] = drv * (k2v * egr);                          // dr*r, summed over the rows below
+  }
+  if (tid < 64 && tid < rows) p.dbeta[(tok + tid) * p.H + h] = sm.bcol[tid] + sm.brow[tid];
   __syncthreads();
   if (tid < E) {                                            // chunk-end terms: sum_t dr*r + dd*exp(gL)
     float acc = 0.f;
-    for (int tt = 0; tt < 64; ++tt) acc += sm.r1[tt * ES + tid];
+    for (int tt = 0; tt < 64; ++tt) acc += sm.drr[tt * ES + tid];
     acc += p.dd[item * E + tid] * mexp2(sm.gc2[63 * ES + tid]);
     sm.dgc[63 * ES + tid] += acc;
   }
@@ -384,28 +418,28 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     if (rb < rows) p.dg[((tok + rb) * p.H + h) * E + e] = v0;
   }
 
-  // ---- dk, dq ------------------------------------------------------------------------------------------------------
+  // ---- dk, dq: this thread's row, 32 of the 128 columns ------------------------------------------------------------
   mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   {
-    const float* sp = p.dkq + (item * 128 + tid) * HEAD;
-    __nv_bfloat16* outp = (krow ? p.dk : p.dq) + ((tok + t) * p.H + h) * HEAD;
+    const float* sp = p.dkq + (item * 128 + r) * HEAD + cq * 32;
+    __nv_bfloat16* outp = (krow ? p.dk : p.dq) + ((tok + t) * p.H + h) * HEAD + cq * 32;
     const bool live = t < rows;
 #pragma unroll
-    for (int c0 = 0; c0 < 128; c0 += 16) {
+    for (int c0 = 0; c0 < 32; c0 += 16) {
       float a[16];
-      tmem_ld<16>(tmem_row + c0, a);
+      tmem_ld<16>(tmem_row + cq * 32 + c0, a);
       tmem_wait_ld();
       if (live) {
 #pragma unroll
         for (int j = 0; j < 16; j += 8) {
-          const float4 s0 = *reinterpret_cast<const float4*>(sp + c0 + j), s1 = *reinterpret_cast<const float4*>(sp + c0 + j + 4);
+          const float4 x0 = *reinterpret_cast<const float4*>(sp + c0 + j), x1 = *reinterpret_cast<const float4*>(sp + c0 + j + 4);
           uint4 u;
-          u.x = pack_bf16(a[j] + s0.x, a[j + 1] + s0.y);
-          u.y = pack_bf16(a[j + 2] + s0.z, a[j + 3] + s0.w);
-          u.z = pack_bf16(a[j + 4] + s1.x, a[j + 5] + s1.y);
-          u.w = pack_bf16(a[j + 6] + s1.z, a[j + 7] + s1.w);
+          u.x = pack_bf16(a[j] + x0.x, a[j + 1] + x0.y);
+          u.y = pack_bf16(a[j + 2] + x0.z, a[j + 3] + x0.w);
+          u.z = pack_bf16(a[j + 4] + x1.x, a[j + 5] + x1.y);
+          u.w = pack_bf16(a[j + 6] + x1.z, a[j + 7] + x1.w);
           *reinterpret_cast<uint4*>(outp + c0 + j) = u;
         }
       }
@@ -422,7 +456,8 @@ using namespace tgdn;
 
 template <int E>
 static int launch_mat(const CUtensorMap* maps, const MatParams& p, cudaStream_t s) {
-  const int smem = static_cast<int>(sizeof(MatSmem)) + 1024;
+  const int smem = static_cast<int>(sizeof(MatSmem<E>)) + 1024;
+  static_assert(sizeof(MatSmem<E>) + 1024 <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(mat_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   mat_kernel<E><<<p.B * p.NC * p.H, MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
