@@ -1,6 +1,6 @@
 // Per-chunk masks of the Triadic GDN: cumulative log decay, the UT transform A and the intra-chunk output operator.
 //
-// For every (batch, chunk, head) one CTA computes, with K, Q the 64x128 key/query tiles of the chunk:
+// For every (batch, chunk, head) one CTA of 256 threads computes, with K, Q the 64x128 key/query tiles of the chunk:
 //   gc[t,e]  = inclusive cumulative sum of the log gate over the chunk (rows past the end of a document add 0)
 //   M[t,s]   = sum_e k2[t,e] k2[s,e] exp(gc[t,e]-gc[s,e]) (s <  t),  Mp[t,s] = sum_e q2[t,e] k2[s,e] exp(.) (s <= t)
 //   A        = (I + strict_lower(beta_t (K K^T)[t,s] M[t,s]))^-1
@@ -10,16 +10,19 @@
 //
 // Replaces cute_triadic_gdn/kernels/sm90_joint_scan.py:21-80 (scan_kernel, forward direction) and
 // cute_triadic_gdn/kernels/sm100_joint_masks.py:34-267 (masks_kernel); math as in
-// cute_triadic_gdn/ops/gdn_joint.py:36-39, :45-60.  The Gram product [K;Q] K^T is one tcgen05 MMA group (M=128, N=64,
-// K=128) on TMA-staged 128B-swizzled tiles; the mask sums, the blocked triangular inverse (16 -> 32 -> 64) and Pm A run
-// on the CUDA cores in f32 and are rounded to bf16 once, when stored.
+// cute_triadic_gdn/ops/gdn_joint.py:36-39, :45-60.
+//   * Gram product [K;Q] K^T: one tcgen05 MMA group (M=128, N=64, K=128) on TMA-staged 128B-swizzled tiles.
+//   * Mask sums: thread (row, column half) with the half's 8-column blocks interleaved so that the triangle is balanced.
+//   * Triangular inverse in f32: four 16x16 diagonal blocks by forward substitution, then the 16->32 and 32->64
+//     merges X21 = -X22 (L21 X11) as warp-level mma.sync m16n8k8 products with a 3-term TF32 split (f32-grade accuracy).
+//   * PA = Pm A: a second tcgen05 MMA group on the bf16 images of Pm and A that are about to be stored anyway.
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"
 
 namespace tgdn {
 
-constexpr int MASK_THREADS = 128;
+constexpr int MASK_THREADS = 256;
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -30,7 +33,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // 64x64 f32 matrix in shared memory, column index XOR-swizzled with the row so that both "lanes along a row" and
 // "lanes along a column" accesses are conflict-free.
 __device__ __forceinline__ int mat_idx(int i, int j) { return i * 64 + (j ^ (i & 31)); }
+__device__ __forceinline__ int t_idx(int k, int j) { return k * 32 + ((j ^ k) & 31); }
 
+// ---- warp-level TF32 products with a 3-term split --------------------------------------------------------------------
+__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  const float rest = x - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+__device__ __forceinline__ void mma_tf32(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// c (16x8 tile, standard fragment) += A(16x8) B(8x8) with A(i,k), B(k,j) given as element functors
+template <typename FA, typename FB>
+__device__ __forceinline__ void mma_step_3x(float* c, FA a_at, FB b_at, int lane) {
+  const int gid = lane >> 2, tig = lane & 3;
+  uint32_t ah[4], al[4], bh[2], bl[2];
+  tf32_split(a_at(gid, tig), ah[0], al[0]);
+  tf32_split(a_at(gid + 8, tig), ah[1], al[1]);
+  tf32_split(a_at(gid, tig + 4), ah[2], al[2]);
+  tf32_split(a_at(gid + 8, tig + 4), ah[3], al[3]);
+  tf32_split(b_at(tig, gid), bh[0], bl[0]);
+  tf32_split(b_at(tig + 4, gid), bh[1], bl[1]);
+  mma_tf32(c, al, bh);
+  mma_tf32(c, ah, bl);
+  mma_tf32(c, ah, bh);
+}
+
+template <int E>
 struct MaskSmem {
   // KQ tile (two 64-column blocks of 128 rows x 128 B) while the Gram product runs; L and X afterwards
   union {
@@ -39,42 +71,62 @@ struct MaskSmem {
   } u;
   float Pm[4096];
   float T[1024];
-  float gc2[64 * 17];      // log2-domain cumulative gate, row stride E+1
-  float k2[64 * 17];
-  float q2[64 * 17];
+  uint8_t img_ap[16384];   // [A; PA] image (i = row 0..127, j = column), SI = 128, SJ = 2048
+  uint8_t img_pm[8192];    // Pm image (i = t, j = s), SI = 128, SJ = 1024; read as 128 rows by the PA product: keep >= 8 KB behind it
+  float gc2[64 * E];       // log2-domain cumulative gate
+  float k2[64 * E];
+  float q2[64 * E];
+  float pad[(3 * 64 * E * 4 >= 8192) ? 1 : (8192 - 3 * 64 * E * 4) / 4];
   float beta[64];
   uint64_t bar_load, bar_mma;
   uint32_t tmem_base;
   int abort;
 };
 
-// X21 = -X22 (L21 X11) for `nm` diagonal blocks of size 2n, all 128 threads.
-__device__ __forceinline__ void tri_merge(float* L, float* X, float* T, int n, int nm, int tid) {
-  const int total = nm * n * n;
-  for (int idx = tid; idx < total; idx += MASK_THREADS) {
-    const int m = idx / (n * n), rem = idx % (n * n), i = rem / n, j = rem % n, r = m * 2 * n;
-    float acc = 0.f;
-    for (int k = j; k < n; ++k) acc = fmaf(L[mat_idx(r + n + i, r + k)], X[mat_idx(r + k, r + j)], acc);
-    T[idx] = acc;
+// X21 = -X22 (L21 X11) for the diagonal blocks of size 2n (n = 16: two blocks, n = 32: one), one 16x8 tile per warp.
+template <int N>
+__device__ __forceinline__ void tri_merge_mma(const float* L, float* X, float* T, int warp, int lane) {
+  constexpr int NT = N / 8, MT = N / 16, TASKS = (64 / (2 * N)) * MT * NT;      // 4 tasks (N=16) or 8 (N=32)
+  const int gid = lane >> 2, tig = lane & 3;
+  const int m = warp / (MT * NT), mt = (warp / NT) % MT, nt = warp % NT, r = m * 2 * N;
+  if (warp < TASKS) {
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kb = nt; kb < NT; ++kb)                           // X11 is lower triangular: rows k < column block are zero
+      mma_step_3x(c,
+                  [&](int i, int k) { return L[mat_idx(r + N + 16 * mt + i, r + 8 * kb + k)]; },
+                  [&](int k, int j) { return X[mat_idx(r + 8 * kb + k, r + 8 * nt + j)]; }, lane);
+    float* Tm = T + m * 512;
+    Tm[t_idx(16 * mt + gid, 8 * nt + 2 * tig)] = c[0];
+    Tm[t_idx(16 * mt + gid, 8 * nt + 2 * tig + 1)] = c[1];
+    Tm[t_idx(16 * mt + gid + 8, 8 * nt + 2 * tig)] = c[2];
+    Tm[t_idx(16 * mt + gid + 8, 8 * nt + 2 * tig + 1)] = c[3];
   }
   __syncthreads();
-  for (int idx = tid; idx < total; idx += MASK_THREADS) {
-    const int m = idx / (n * n), rem = idx % (n * n), i = rem / n, j = rem % n, r = m * 2 * n;
-    float acc = 0.f;
-    for (int k = 0; k <= i; ++k) acc = fmaf(X[mat_idx(r + n + i, r + n + k)], T[m * n * n + k * n + j], acc);
-    X[mat_idx(r + n + i, r + j)] = -acc;
+  if (warp < TASKS) {
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* Tm = T + m * 512;
+    for (int kb = 0; kb <= 2 * mt + 1; ++kb)                   // X22 is lower triangular: columns k > row block are zero
+      mma_step_3x(c,
+                  [&](int i, int k) { return X[mat_idx(r + N + 16 * mt + i, r + N + 8 * kb + k)]; },
+                  [&](int k, int j) { return Tm[t_idx(8 * kb + k, 8 * nt + j)]; }, lane);
+    X[mat_idx(r + N + 16 * mt + gid, r + 8 * nt + 2 * tig)] = -c[0];
+    X[mat_idx(r + N + 16 * mt + gid, r + 8 * nt + 2 * tig + 1)] = -c[1];
+    X[mat_idx(r + N + 16 * mt + gid + 8, r + 8 * nt + 2 * tig)] = -c[2];
+    X[mat_idx(r + N + 16 * mt + gid + 8, r + 8 * nt + 2 * tig + 1)] = -c[3];
   }
   __syncthreads();
 }
 
 template <int E>
-__global__ void __launch_bounds__(MASK_THREADS)
+__global__ void __launch_bounds__(MASK_THREADS, 2)
 masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, MaskParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  MaskSmem& sm = *reinterpret_cast<MaskSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using SM = MaskSmem<E>;
+  SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = warp >> 2;                                 // column half (interleaved 8-column blocks)
+  const int r = (warp & 3) * 32 + lane;                     // tensor-memory lane = row of [K K^T ; Q K^T]
   const int h = blockIdx.x % p.H, n = (blockIdx.x / p.H) % p.NC, b = blockIdx.x / (p.H * p.NC);
-  constexpr int ES = E + 1;
   constexpr float LOG2E = 1.4426950408889634f;
 
   int t0 = n * CHUNK, rows = CHUNK;
@@ -93,7 +145,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     mbar_fence_init();
     sm.abort = 0;
   }
-  if (warp == 0) { tmem_alloc(&sm.tmem_base, 64); tmem_relinquish(); }
+  if (warp == 0) { tmem_alloc(&sm.tmem_base, 128); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -110,19 +162,19 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
   for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
-    const int r = idx / E, e = idx % E;
-    const bool ok = r < rows;
-    const int64_t g_off = ((tok + r) * p.H + h) * E + e;
-    sm.gc2[r * ES + e] = ok ? p.g[g_off] : 0.f;
-    sm.k2[r * ES + e] = ok ? p.k2[g_off] : 0.f;
-    sm.q2[r * ES + e] = ok ? p.q2[g_off] : 0.f;
+    const int rr = idx / E;
+    const bool ok = rr < rows;
+    const int64_t g_off = ((tok + rr) * p.H + h) * E + (idx % E);
+    sm.gc2[idx] = ok ? p.g[g_off] : 0.f;
+    sm.k2[idx] = ok ? p.k2[g_off] : 0.f;
+    sm.q2[idx] = ok ? p.q2[g_off] : 0.f;
   }
   if (tid < 64) sm.beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
   __syncthreads();
   // inclusive scan over the 64 rows, one warp per gate column
   float* gc_out = p.gc + ((static_cast<int64_t>(b) * p.NC + n) * p.H + h) * (64 * E);
   for (int e = warp; e < E; e += MASK_THREADS / 32) {
-    float v0 = sm.gc2[lane * ES + e], v1 = sm.gc2[(lane + 32) * ES + e];
+    float v0 = sm.gc2[lane * E + e], v1 = sm.gc2[(lane + 32) * E + e];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const float a0 = __shfl_up_sync(0xffffffffu, v0, o), a1 = __shfl_up_sync(0xffffffffu, v1, o);
@@ -131,14 +183,15 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     v1 += __shfl_sync(0xffffffffu, v0, 31);
     gc_out[lane * E + e] = v0;
     gc_out[(lane + 32) * E + e] = v1;
-    sm.gc2[lane * ES + e] = v0 * LOG2E;
-    sm.gc2[(lane + 32) * ES + e] = v1 * LOG2E;
+    sm.gc2[lane * E + e] = v0 * LOG2E;
+    sm.gc2[(lane + 32) * E + e] = v1 * LOG2E;
   }
   __syncthreads();
 
   // Gram product [K;Q] K^T
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
   const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   if (tid == 0) {
     tc_fence_after();
     const uint64_t desc = make_desc(smem_u32(sm.u.kq), 16, 1024, LAYOUT_SW128);
@@ -152,39 +205,54 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   }
   mbar_wait(&sm.bar_mma, 0, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
-  float pr[64];                                             // row `tid` of [K K^T ; Q K^T]
-  tmem_ld<64>(tmem + (static_cast<uint32_t>(warp * 32) << 16), pr);
+  float pr[32];                                             // this thread's 4 blocks of 8 columns of its row
+#pragma unroll
+  for (int i = 0; i < 4; ++i) tmem_ld8(tmem_row + 16 * i + 8 * ch, pr + 8 * i);
   tmem_wait_ld();
   tc_fence_before();
   __syncthreads();                                          // the KQ tile is dead from here: L and X take its place
 
-  // mask sums: threads 0..63 rows of M (strictly lower) -> L, threads 64..127 rows of Mp (lower) -> Pm
+  // mask sums: rows 0..63 -> M (strictly lower) -> L, rows 64..127 -> Mp (lower) -> Pm
   {
-    const int t = tid & 63;
-    const bool isq = tid >= 64;
+    const int t = r & 63;
+    const bool isq = r >= 64;
     float my2[E], mygc[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      my2[e] = isq ? sm.q2[t * ES + e] : sm.k2[t * ES + e];
-      mygc[e] = sm.gc2[t * ES + e];
+      my2[e] = isq ? sm.q2[t * E + e] : sm.k2[t * E + e];
+      mygc[e] = sm.gc2[t * E + e];
     }
     const float rowscale = isq ? p.scale : sm.beta[t];
     float* dst = isq ? sm.Pm : sm.u.m.L;
-    const int smax = ((warp & 1) ? 63 : 31);              // largest row of this warp
+    const int tmax = (warp & 1) ? 63 : 31;                  // largest row of this warp
 #pragma unroll
-    for (int s = 0; s < 64; ++s) {
-      float val = 0.f;
-      if (s <= smax) {
-        const bool use = isq ? (s <= t) : (s < t);
-        if (use) {
+    for (int i = 0; i < 4; ++i) {
+      const int sb = 16 * i + 8 * ch;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int s = sb + c;
+        float val = 0.f;
+        if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
           float acc = 0.f;
+          if constexpr (E % 4 == 0) {
 #pragma unroll
-          for (int e = 0; e < E; ++e)
-            acc = fmaf(my2[e] * sm.k2[s * ES + e], fast_exp2(mygc[e] - sm.gc2[s * ES + e]), acc);
-          val = rowscale * pr[s] * acc;
+            for (int e = 0; e < E; e += 4) {
+              const float4 g4 = *reinterpret_cast<const float4*>(&sm.gc2[s * E + e]);
+              const float4 k4 = *reinterpret_cast<const float4*>(&sm.k2[s * E + e]);
+              acc = fmaf(my2[e] * k4.x, fast_exp2(mygc[e] - g4.x), acc);
+              acc = fmaf(my2[e + 1] * k4.y, fast_exp2(mygc[e + 1] - g4.y), acc);
+              acc = fmaf(my2[e + 2] * k4.z, fast_exp2(mygc[e + 2] - g4.z), acc);
+              acc = fmaf(my2[e + 3] * k4.w, fast_exp2(mygc[e + 3] - g4.w), acc);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+              acc = fmaf(my2[e] * sm.k2[s * E + e], fast_exp2(mygc[e] - sm.gc2[s * E + e]), acc);
+          }
+          val = rowscale * pr[8 * i + c] * acc;
         }
+        dst[mat_idx(t, s)] = val;
       }
-      dst[mat_idx(t, s)] = val;
     }
   }
   __syncthreads();
@@ -205,54 +273,71 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
 #pragma unroll
     for (int i = 0; i < 16; ++i) X[mat_idx(r0 + i, r0 + j)] = x[i];
   } else {
-    // zero everything outside the diagonal 16x16 blocks that the merges do not write (the upper triangle)
-    for (int idx = tid - 64; idx < 4096; idx += 64) {
+    // zero the blocks above the block diagonal, which the merges never write
+    for (int idx = tid - 64; idx < 4096; idx += MASK_THREADS - 64) {
       const int i = idx >> 6, j = idx & 63;
       if ((j >> 4) > (i >> 4)) X[mat_idx(i, j)] = 0.f;
     }
   }
   __syncthreads();
-  tri_merge(L, X, sm.T, 16, 2, tid);
-  tri_merge(L, X, sm.T, 32, 1, tid);
+  tri_merge_mma<16>(L, X, sm.T, warp, lane);
+  tri_merge_mma<32>(L, X, sm.T, warp, lane);
 
-  // PA = Pm X (both lower triangular); L is dead, PA takes its place
-  float* PA = sm.u.m.L;
-  for (int idx = tid; idx < 4096; idx += MASK_THREADS) {
-    const int t = idx >> 6, j = idx & 63;
-    float acc = 0.f;
-    for (int k = j; k <= t; ++k) acc = fmaf(sm.Pm[mat_idx(t, k)], X[mat_idx(k, j)], acc);
-    PA[mat_idx(t, j)] = acc;
+  // bf16 images of A (rows 0..63 of the [A;PA] image) and Pm: one 16-byte piece per thread and step
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int piece = it * MASK_THREADS + tid, i = piece & 63, jb = piece >> 6;
+    float va[8], vp[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      va[c] = X[mat_idx(i, jb * 8 + c)];
+      vp[c] = sm.Pm[mat_idx(i, jb * 8 + c)];
+    }
+    st_shared_v4(smem_u32(sm.img_ap) + (i >> 3) * 128 + (i & 7) * 16 + jb * 2048, pack_bf16(va[0], va[1]),
+                 pack_bf16(va[2], va[3]), pack_bf16(va[4], va[5]), pack_bf16(va[6], va[7]));
+    st_shared_v4(smem_u32(sm.img_pm) + (i >> 3) * 128 + (i & 7) * 16 + jb * 1024, pack_bf16(vp[0], vp[1]),
+                 pack_bf16(vp[2], vp[3]), pack_bf16(vp[4], vp[5]), pack_bf16(vp[6], vp[7]));
   }
+  fence_async_smem();
+  tc_fence_before();
   __syncthreads();
 
-  // stores: operand images, one 16-byte piece (8 columns of one row) per thread and step, linear in global memory
-  const int64_t item = (static_cast<int64_t>(b) * p.NC + n) * p.H + h;
-  uint4* ap_out = reinterpret_cast<uint4*>(p.AP + item * (128 * 64));
-  uint4* pm_out = reinterpret_cast<uint4*>(p.Pm + item * (64 * 64));
+  // PA = Pm A on the tensor core, from the bf16 images
+  if (tid == 0) {
+    tc_fence_after();
+    const uint64_t da = make_desc(smem_u32(sm.img_pm), 1024, 128, LAYOUT_PLAIN);   // Pm, K-major (rows past 63: don't care)
+    const uint64_t db = make_desc(smem_u32(sm.img_ap), 128, 2048, LAYOUT_PLAIN);   // A as (K = s, N = j), MN-major
+    constexpr uint32_t idesc = make_idesc(128, 64, 0, 1);
 #pragma unroll
-  for (int jb = 0; jb < 8; ++jb) {
-    const float* src = (tid < 64) ? X : PA;
-    const int i = tid & 63;
-    float v[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) v[c] = src[mat_idx(i, jb * 8 + c)];
-    uint4 u;
-    u.x = pack_bf16(v[0], v[1]); u.y = pack_bf16(v[2], v[3]); u.z = pack_bf16(v[4], v[5]); u.w = pack_bf16(v[6], v[7]);
-    ap_out[jb * 128 + tid] = u;                              // image (i = row 0..127, j = column), SI = 128, SJ = 2048
+    for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 64, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
+    umma_commit(&sm.bar_mma);
   }
+  mbar_wait(&sm.bar_mma, 1, ctl, DEV_TIMEOUT_MMA);
+  tc_fence_after();
+  if (r < 64) {                                             // PA row r, columns 32*ch .. +32 -> rows 64.. of the image
+    float pa[32];
+    tmem_ld<32>(tmem_row + 64 + 32 * ch, pa);
+    tmem_wait_ld();
+    const uint32_t base = smem_u32(sm.img_ap) + ((64 + r) >> 3) * 128 + (r & 7) * 16;
 #pragma unroll
-  for (int it = 0; it < 4; ++it) {
-    const int piece = it * MASK_THREADS + tid, i = piece & 63, jb = piece >> 6;
-    float v[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) v[c] = sm.Pm[mat_idx(i, jb * 8 + c)];
-    uint4 u;
-    u.x = pack_bf16(v[0], v[1]); u.y = pack_bf16(v[2], v[3]); u.z = pack_bf16(v[4], v[5]); u.w = pack_bf16(v[6], v[7]);
-    pm_out[piece] = u;                                       // image (i = t, j = s), SI = 128, SJ = 1024
+    for (int jb = 0; jb < 4; ++jb)
+      st_shared_v4(base + (4 * ch + jb) * 2048, pack_bf16(pa[jb * 8], pa[jb * 8 + 1]), pack_bf16(pa[jb * 8 + 2], pa[jb * 8 + 3]),
+                   pack_bf16(pa[jb * 8 + 4], pa[jb * 8 + 5]), pack_bf16(pa[jb * 8 + 6], pa[jb * 8 + 7]));
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 64);
+
+  // images -> global, linear 16-byte copies
+  const int64_t item = (static_cast<int64_t>(b) * p.NC + n) * p.H + h;
+  uint4* ap_out = reinterpret_cast<uint4*>(p.AP + item * (128 * 64));
+  uint4* pm_out = reinterpret_cast<uint4*>(p.Pm + item * (64 * 64));
+  const uint4* ap_src = reinterpret_cast<const uint4*>(sm.img_ap);
+  const uint4* pm_src = reinterpret_cast<const uint4*>(sm.img_pm);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) ap_out[it * MASK_THREADS + tid] = ap_src[it * MASK_THREADS + tid];
+#pragma unroll
+  for (int it = 0; it < 2; ++it) pm_out[it * MASK_THREADS + tid] = pm_src[it * MASK_THREADS + tid];
+  if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
 }  // namespace tgdn
@@ -261,7 +346,7 @@ using namespace tgdn;
 
 template <int E>
 static int launch_masks(const CUtensorMap& mk, const CUtensorMap& mq, const MaskParams& p, cudaStream_t s) {
-  const int smem = static_cast<int>(sizeof(MaskSmem)) + 1024;
+  const int smem = static_cast<int>(sizeof(MaskSmem<E>)) + 1024;
   cudaError_t e = cudaFuncSetAttribute(masks_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   masks_kernel<E><<<p.B * p.NC * p.H, MASK_THREADS, smem, s>>>(mk, mq, p);

@@ -58,7 +58,7 @@ def masks_stage(K, Q, k2, q2, g, beta, scale, rounding):
     eye = torch.eye(CHUNK, dtype=K.dtype)
     A = torch.linalg.inv(eye + (beta[..., None] * Pkk * M).tril(-1))
     Pm = scale * (Pqk * Mp).tril(0)
-    PA = Pm @ A
+    PA = rd(Pm) @ rd(A)                      # the kernel multiplies the two bf16 images it is about to store
     return dict(gc=gc, A=rd(A), Pm=rd(Pm), PA=rd(PA), M=M, Mp=Mp, decay=decay, Pkk=Pkk, Pqk=Pqk)
 
 
