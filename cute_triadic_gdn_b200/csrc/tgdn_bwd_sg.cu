@@ -9,6 +9,8 @@
 // is just more K), the row sums come from R = [K;Q] h_e, the same product the forward used.
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_state_grads.py:53-449 (sg_kernel).
+#include <type_traits>
+
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"
@@ -25,14 +27,14 @@ __device__ __forceinline__ float sexp2(float x) {
 
 struct SgSmem {
   uint8_t kq[32768];            // [K;Q] tile, 128B swizzle
-  uint8_t hp[2][16384];         // half-slices of h: image (i = d, j = v), SI = 128, SJ = 2048
-  uint8_t gp[2][16384];         // half-slices of G
-  uint8_t va[8192];             // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: xa follows)
-  uint8_t xa[16384];            // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
+  uint8_t hp[3][16384];         // half-slices of h, three stages: image (i = d, j = v), SI = 128, SJ = 2048
+  uint8_t gp[3][16384];         // half-slices of G
+  uint8_t va[2][8192];          // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: more owned memory follows)
+  uint8_t xa[2][16384];         // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
   float ga[64 * 17], gr[64 * 17], gcq[64 * 17];
   float part[2 * 128 * 17];     // row sums per column half
   float red[SG_THREADS / 32];
-  uint64_t bar_kq, bar_load[2], bar_mma;
+  uint64_t bar_kq, bar_load[3], bar_mma[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -66,7 +68,9 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     mbar_init(&sm.bar_kq, 1);
     mbar_init(&sm.bar_load[0], 1);
     mbar_init(&sm.bar_load[1], 1);
-    mbar_init(&sm.bar_mma, 1);
+    mbar_init(&sm.bar_load[2], 1);
+    mbar_init(&sm.bar_mma[0], 1);
+    mbar_init(&sm.bar_mma[1], 1);
     mbar_fence_init();
     sm.abort = 0;
   }
@@ -81,7 +85,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
   const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
   auto issue_step = [&](int s) {                     // thread 0
-    const int st = s & 1;
+    const int st = s % 3;
     mbar_expect_tx(&sm.bar_load[st], 32768);
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
     bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
@@ -138,108 +142,136 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   __syncthreads();
   mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);
 
-  uint32_t mma_phase = 0;
-  for (int e = 0; e < E; ++e) {
-    float rowsum = 0.f;                              // da_e (K rows) or dc_e (Q rows), this thread's columns
-    float dot = 0.f;                                 // <h_e, G_e>, this thread's elements
+  // Software pipeline over the 2E half-slice steps s = 2e + vh.  In iteration s: the MMAs of step s are issued; while they
+  // run, the row sums of step s-1 are taken from its (double-buffered) R tile, the operands of step s+1 are built in the
+  // other operand buffer, and <h,G> of step s is accumulated from shared memory.
+  auto build = [&](int e, auto vh_tag) {                 // operands of step (e, vh) into buffer vh
+    constexpr int vh = decltype(vh_tag)::value;
     const float fx = krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e];
     const float fu = sm.gr[t * ES + e];
+    const uint32_t xbase = smem_u32(sm.xa[vh]) + (row >> 3) * 128 + (row & 7) * 16 + (wg * 4) * 2048;
+    const uint32_t vbase = smem_u32(sm.va[vh]) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
 #pragma unroll
-    for (int vh = 0; vh < 2; ++vh) {
-      const int s = 2 * e + vh, st = s & 1;
-      // operands of this step (the previous step's MMAs have completed)
-      {
-        const uint32_t xbase = smem_u32(sm.xa) + (row >> 3) * 128 + (row & 7) * 16 + (wg * 4) * 2048;
-        const uint32_t vbase = smem_u32(sm.va) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
+    for (int j = 0; j < 4; ++j) {
+      uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t o[4];
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const uint32_t x = xw[vh][4 * j + w];
-            o[w] = pack_bf16(fx * bf16_lo(x), fx * bf16_hi(x));
-          }
-          st_shared_v4(xbase + j * 2048, o[0], o[1], o[2], o[3]);
-          if (krow) {
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const uint32_t x = uw[vh][4 * j + w];
-              o[w] = pack_bf16(fu * bf16_lo(x), fu * bf16_hi(x));
-            }
-            st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
-          }
-        }
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t x = xw[vh][4 * j + w];
+        o[w] = pack_bf16(fx * bf16_lo(x), fx * bf16_hi(x));
       }
+      st_shared_v4(xbase + j * 2048, o[0], o[1], o[2], o[3]);
+      if (krow) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t x = uw[vh][4 * j + w];
+          o[w] = pack_bf16(fu * bf16_lo(x), fu * bf16_hi(x));
+        }
+        st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
+      }
+    }
+  };
+  auto issue_mma = [&](int s, int vh) {                  // thread 0
+    const int st = s % 3;
+    tc_fence_after();
+    const uint64_t dxa = make_desc(smem_u32(sm.xa[vh]), 2048, 128, LAYOUT_PLAIN);
+    const uint64_t dva = make_desc(smem_u32(sm.va[vh]), 1024, 128, LAYOUT_PLAIN);
+    const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);   // K = v
+    const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
+    const uint64_t dhm = make_desc(smem_u32(sm.hp[st]), 128, 2048, LAYOUT_PLAIN);   // K = d, N = v
+    const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
+    constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
+    constexpr uint32_t id_r = make_idesc(128, 64, 0, 1);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma_bf16(tmem, desc_advance(dxa, kk * 4096), desc_advance(dhk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      umma_bf16(tmem + 128, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+      umma_bf16(tmem + 256 + vh * 64, desc_advance(dkq, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dhm, kk * 256), id_r, kk > 0);
+    umma_commit(&sm.bar_mma[vh]);
+  };
+  auto row_sums = [&](int s, auto vh_tag, float& rowsum) {   // R tile of step s (its MMAs waited for here)
+    constexpr int vh = decltype(vh_tag)::value;
+    mbar_wait(&sm.bar_mma[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+    tc_fence_after();
+    float rr[32];
+    tmem_ld<32>(tmem_row + 256 + vh * 64 + wg * 32, rr);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      rowsum = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], rowsum);
+      rowsum = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], rowsum);
+    }
+  };
+  auto dot_half = [&](int s, float& dot) {               // <h, G> over the half-slice of step s: 1024 16-byte pieces
+    const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[s % 3]);
+    const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[s % 3]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 a = hp4[j * SG_THREADS + tid], g = gp4[j * SG_THREADS + tid];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        dot = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), dot);
+        dot = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), dot);
+      }
+    }
+  };
+  using V0 = std::integral_constant<int, 0>;
+  using V1 = std::integral_constant<int, 1>;
+
+  build(0, V0{});
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  float rowsum = 0.f;
+  for (int e = 0; e < E; ++e) {
+    float dot = 0.f;
+    // ---- step s = 2e (vh = 0) ----
+    {
+      const int s = 2 * e;
+      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (tid == 0) issue_mma(s, 0);
+      if (e > 0) {
+        row_sums(s - 1, V1{}, rowsum);                   // finishes slice e-1
+        sm.part[(wg * 128 + row) * ES + e - 1] = krow ? -rowsum : rowsum;
+        rowsum = 0.f;
+        if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);  // stage (s+2)%3 = (s-1)%3 is free: its MMAs are done
+      } else if (tid == 0 && STEPS > 2) {
+        issue_step(2);
+      }
+      build(e, V1{});
+      dot_half(s, dot);
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
-      mbar_wait(&sm.bar_load[st], (s >> 1) & 1, ctl, DEV_TIMEOUT_LOAD);
-      const uint32_t rcol = 256 + (s & 1) * 64;
-      if (tid == 0) {
-        tc_fence_after();
-        const uint64_t dxa = make_desc(smem_u32(sm.xa), 2048, 128, LAYOUT_PLAIN);
-        const uint64_t dva = make_desc(smem_u32(sm.va), 1024, 128, LAYOUT_PLAIN);
-        const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);   // K = v
-        const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
-        const uint64_t dhm = make_desc(smem_u32(sm.hp[st]), 128, 2048, LAYOUT_PLAIN);   // K = d, N = v
-        const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
-        constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
-        constexpr uint32_t id_r = make_idesc(128, 64, 0, 1);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem, desc_advance(dxa, kk * 4096), desc_advance(dhk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem + 128, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem + rcol, desc_advance(dkq, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dhm, kk * 256), id_r, kk > 0);
-        umma_commit(&sm.bar_mma);
-      }
-      // <h, G> over this half-slice while the tensor core works: 1024 16-byte pieces, 4 per thread
-      {
-        const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[st]);
-        const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[st]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 a = hp4[j * SG_THREADS + tid], g = gp4[j * SG_THREADS + tid];
-          const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            dot = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), dot);
-            dot = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), dot);
-          }
-        }
-      }
-      mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-      ++mma_phase;
-      tc_fence_after();
-      {
-        float rr[32];
-        tmem_ld<32>(tmem_row + rcol + wg * 32, rr);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          rowsum = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], rowsum);
-          rowsum = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], rowsum);
-        }
-      }
-      tc_fence_before();
-      __syncthreads();                               // operands and this stage's half-slices are free again
-      if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);
     }
-    sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
-    // block sum of the dot product, fixed order
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (lane == 0) sm.red[warp] = dot;
-    __syncthreads();
-    if (tid == 0) {
-      float total = 0.f;
+    // ---- step s = 2e + 1 (vh = 1) ----
+    {
+      const int s = 2 * e + 1;
+      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (tid == 0) issue_mma(s, 1);
+      row_sums(s - 1, V0{}, rowsum);
+      if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);
+      if (e + 1 < E) build(e + 1, V0{});
+      dot_half(s, dot);
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (lane == 0) sm.red[warp] = dot;
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        float total = 0.f;
 #pragma unroll
-      for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[w];
-      p.dd[item * E + e] = total;
+        for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[w];
+        p.dd[item * E + e] = total;
+      }
     }
   }
+  row_sums(STEPS - 1, V1{}, rowsum);
+  sm.part[(wg * 128 + row) * ES + E - 1] = krow ? -rowsum : rowsum;
   __syncthreads();
   // row sums: add the two column halves
   for (int idx = tid; idx < 128 * E; idx += SG_THREADS) {

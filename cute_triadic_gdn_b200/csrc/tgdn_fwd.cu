@@ -50,7 +50,7 @@ struct FwdCfg {
   static constexpr int OFF_BW = OFF_VN + VN_BYTES;
   static constexpr int OFF_GATES = OFF_BW + ((BW_BYTES + 1023) & ~1023);
   static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;     // a, r, c tables, beta, d
-  static constexpr int OFF_CTRL = OFF_GATES + GATE_FLOATS * 4;
+  static constexpr int OFF_CTRL = OFF_GATES + 2 * GATE_FLOATS * 4;    // two buffers: the next chunk's tables are built early
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;       // + control block + alignment slack
 };
 
@@ -69,11 +69,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* g_a = reinterpret_cast<float*>(smem + C::OFF_GATES);
-  float* g_r = g_a + 64 * ES;
-  float* g_c = g_r + 64 * ES;
-  float* g_beta = g_c + 64 * ES;
-  float* g_d = g_beta + 64;
+  float* gate_base = reinterpret_cast<float*>(smem + C::OFF_GATES);
   FwdCtrl& ctrl = *reinterpret_cast<FwdCtrl*>(smem + C::OFF_CTRL);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -153,7 +149,80 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
   };
 
+  // raw gate inputs of one chunk for this thread's (at most two) table entries, and the table builder
+  struct GateRaw { float gcv[2], gl[2], k2v[2], q2v[2], beta; };
+  constexpr int GATE_ITERS = (64 * E + FWD_THREADS - 1) / FWD_THREADS;
+  static_assert(GATE_ITERS <= 2, "gate tables: at most two entries per thread");
+  auto load_gates = [&](int i) {
+    GateRaw g;
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const float* gcp = p.gc + item * (64 * E);
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * FWD_THREADS;
+      g.gcv[it] = g.gl[it] = g.k2v[it] = g.q2v[it] = 0.f;
+      if (idx < 64 * E) {
+        const int r = idx / E, e = idx % E;
+        g.gcv[it] = gcp[idx];
+        g.gl[it] = gcp[63 * E + e];
+        if (r < rows) {
+          const int64_t off = ((tok + r) * p.H + h) * E + e;
+          g.k2v[it] = p.k2[off];
+          g.q2v[it] = p.q2[off];
+        }
+      }
+    }
+    g.beta = (tid < 64 && tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+    return g;
+  };
+  auto write_gates = [&](const GateRaw& g, int buf) {
+    float* ga = gate_base + buf * C::GATE_FLOATS;
+    float* gr = ga + 64 * ES;
+    float* gc_ = gr + 64 * ES;
+    float* gb = gc_ + 64 * ES;
+    float* gd = gb + 64;
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * FWD_THREADS;
+      if (idx < 64 * E) {
+        const int r = idx / E, e = idx % E;
+        const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
+        const float eg = fexp2(gcv);
+        ga[r * ES + e] = g.k2v[it] * eg;
+        gr[r * ES + e] = g.k2v[it] * fexp2(gl - gcv);
+        gc_[r * ES + e] = p.scale * g.q2v[it] * eg;
+        if (r == 0) gd[e] = fexp2(gl);
+      }
+    }
+    if (tid < 64) gb[tid] = g.beta;
+  };
+  auto load_vrow = [&](int i, float* dst) {          // K-row threads: this thread's CW value columns of row t
+#pragma unroll
+    for (int c = 0; c < CW; ++c) dst[c] = 0.f;
+    if (!krow) return;
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    if (t >= rows) return;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const __nv_bfloat16* vp = p.v + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
+    if constexpr (CW == 8) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(vp));
+      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
+      dst[4] = bf16_lo(u.z); dst[5] = bf16_hi(u.z); dst[6] = bf16_lo(u.w); dst[7] = bf16_hi(u.w);
+    } else {
+      const uint2 u = __ldg(reinterpret_cast<const uint2*>(vp));
+      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
+    }
+  };
+
   if (tid == 0) issue_loads(0);
+  float vnext[CW];
+  load_vrow(0, vnext);
+  write_gates(load_gates(0), 0);
+  __syncthreads();
   uint32_t mma_phase = 0;
   {
     uint32_t zeros[TPC / 2];
@@ -184,38 +253,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma);
       if (i + 1 < count) issue_loads(i + 1);         // the other stage was released by the previous chunk's (3)
     }
-    // gate tables of this chunk (all threads), value row of this thread
-    for (int idx = tid; idx < 64 * E; idx += FWD_THREADS) {
-      const int r = idx / E, e = idx % E;
-      const float* gcp = p.gc + item * (64 * E);
-      const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
-      const bool ok = r < rows;
-      const int64_t off = ((tok + r) * p.H + h) * E + e;
-      const float k2v = ok ? p.k2[off] : 0.f, q2v = ok ? p.q2[off] : 0.f;
-      const float eg = fexp2(gcv);
-      g_a[r * ES + e] = k2v * eg;
-      g_r[r * ES + e] = k2v * fexp2(gl - gcv);
-      g_c[r * ES + e] = p.scale * q2v * eg;
-      if (r == 0) g_d[e] = fexp2(gl);
-    }
-    if (tid < 64) g_beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+    // tables of this chunk were built during the previous one; start the loads for the next chunk now, use them last
+    float* g_a = gate_base + (i & 1) * C::GATE_FLOATS;
+    float* g_r = g_a + 64 * ES;
+    float* g_c = g_r + 64 * ES;
+    float* g_beta = g_c + 64 * ES;
+    float* g_d = g_beta + 64;
     float vrow[CW];
 #pragma unroll
-    for (int c = 0; c < CW; ++c) vrow[c] = 0.f;
-    if (krow) {
-      if (t < rows) {
-        const __nv_bfloat16* vp = p.v + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
-        if constexpr (CW == 8) {
-          const uint4 u = __ldg(reinterpret_cast<const uint4*>(vp));
-          vrow[0] = bf16_lo(u.x); vrow[1] = bf16_hi(u.x); vrow[2] = bf16_lo(u.y); vrow[3] = bf16_hi(u.y);
-          vrow[4] = bf16_lo(u.z); vrow[5] = bf16_hi(u.z); vrow[6] = bf16_lo(u.w); vrow[7] = bf16_hi(u.w);
-        } else {
-          const uint2 u = __ldg(reinterpret_cast<const uint2*>(vp));
-          vrow[0] = bf16_lo(u.x); vrow[1] = bf16_hi(u.x); vrow[2] = bf16_lo(u.y); vrow[3] = bf16_hi(u.y);
-        }
-      }
+    for (int c = 0; c < CW; ++c) vrow[c] = vnext[c];
+    GateRaw raw_next = {};
+    if (i + 1 < count) {
+      raw_next = load_gates(i + 1);
+      load_vrow(i + 1, vnext);
     }
-    __syncthreads();                                 // gate tables visible
     mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -353,6 +404,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       if (i + 1 < count) store_state(item + p.H, packed);
     }
+    if (i + 1 < count) write_gates(raw_next, (i + 1) & 1);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
