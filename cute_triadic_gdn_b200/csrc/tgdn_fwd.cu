@@ -22,7 +22,6 @@
 
 namespace tgdn {
 
-constexpr int FWD_THREADS = 512;
 
 __device__ __forceinline__ float fexp2(float x) {
   float y;
@@ -30,10 +29,13 @@ __device__ __forceinline__ float fexp2(float x) {
   return y;
 }
 
-template <int E, int VC>
+// NWG warpgroups (128 threads each) split the VC value columns; STAGES = 2 prefetches the next chunk's tiles and runs
+// one CTA per SM, STAGES = 1 is sized so that two CTAs share an SM and hide each other's dependent-MMA latency.
+template <int E, int VC, int NWG, int STAGES>
 struct FwdCfg {
+  static constexpr int THREADS = NWG * 128;
   static constexpr int NCOLS = E * VC;            // columns of R and dS
-  static constexpr int CW = VC / 4;               // value columns per thread and slice
+  static constexpr int CW = VC / NWG;             // value columns per thread and slice
   static constexpr int TPC = E * CW;              // state columns per thread
   static constexpr int ES = E | 1;                // row stride of the gate tables (odd: conflict-free)
   static constexpr int TMEM_COLS = (NCOLS + VC) <= 64 ? 64 : (NCOLS + VC) <= 128 ? 128 : (NCOLS + VC) <= 256 ? 256 : 512;
@@ -44,13 +46,13 @@ struct FwdCfg {
   static constexpr int VN_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
   static constexpr int BW_BYTES = VC * 128;       // image (i = s, j = v),  SI = 128, SJ = 1024
   static constexpr int OFF_KQ = 0;
-  static constexpr int OFF_AP = OFF_KQ + 2 * KQ_BYTES;
-  static constexpr int OFF_S = OFF_AP + 2 * AP_BYTES;
+  static constexpr int OFF_AP = OFF_KQ + STAGES * KQ_BYTES;
+  static constexpr int OFF_S = OFF_AP + STAGES * AP_BYTES;
   static constexpr int OFF_VN = OFF_S + S_BYTES;
   static constexpr int OFF_BW = OFF_VN + VN_BYTES;
   static constexpr int OFF_GATES = OFF_BW + ((BW_BYTES + 1023) & ~1023);
   static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;     // a, r, c tables, beta, d
-  static constexpr int OFF_CTRL = OFF_GATES + 2 * GATE_FLOATS * 4;    // two buffers: the next chunk's tables are built early
+  static constexpr int OFF_CTRL = OFF_GATES + GATE_FLOATS * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;       // + control block + alignment slack
 };
 
@@ -61,10 +63,11 @@ struct FwdCtrl {
   int abort;
 };
 
-template <int E, int VC>
-__global__ void __launch_bounds__(FWD_THREADS, 1)
+template <int E, int VC, int NWG, int STAGES>
+__global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
 fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, FwdParams p) {
-  using C = FwdCfg<E, VC>;
+  using C = FwdCfg<E, VC, NWG, STAGES>;
+  constexpr int FWD_THREADS = C::THREADS;
   constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -123,7 +126,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   auto issue_loads = [&](int i) {                   // thread 0: K/Q tiles and the [A;PmA] image of local chunk i
     int t0, rows;
     chunk_info(i, t0, rows);
-    const int st = i & 1;
+    const int st = (STAGES == 2) ? (i & 1) : 0;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES);
@@ -178,8 +181,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     g.beta = (tid < 64 && tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
     return g;
   };
-  auto write_gates = [&](const GateRaw& g, int buf) {
-    float* ga = gate_base + buf * C::GATE_FLOATS;
+  auto write_gates = [&](const GateRaw& g) {
+    float* ga = gate_base;
     float* gr = ga + 64 * ES;
     float* gc_ = gr + 64 * ES;
     float* gb = gc_ + 64 * ES;
@@ -221,8 +224,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (tid == 0) issue_loads(0);
   float vnext[CW];
   load_vrow(0, vnext);
-  write_gates(load_gates(0), 0);
-  __syncthreads();
+  GateRaw raw_cur = load_gates(0);
   uint32_t mma_phase = 0;
   {
     uint32_t zeros[TPC / 2];
@@ -232,7 +234,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
 
   for (int i = 0; i < count; ++i) {
-    const int st = i & 1;
+    const int st = (STAGES == 2) ? (i & 1) : 0;
     int t0, rows;
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
@@ -241,7 +243,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
 
     // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
-    mbar_wait(&ctrl.bar_load[st], (i >> 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+    write_gates(raw_cur);                            // loaded while the previous chunk was processed
+    mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (i >> 1) : i) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (tid == 0) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -251,10 +254,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       for (int kk = 0; kk < 8; ++kk)
         umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
-      if (i + 1 < count) issue_loads(i + 1);         // the other stage was released by the previous chunk's (3)
+      if (STAGES == 2 && i + 1 < count) issue_loads(i + 1);   // the other stage was released by the previous chunk's (3)
     }
-    // tables of this chunk were built during the previous one; start the loads for the next chunk now, use them last
-    float* g_a = gate_base + (i & 1) * C::GATE_FLOATS;
+    // start the loads for the next chunk's tables and value row now; they are consumed at the top of the next iteration
+    float* g_a = gate_base;
     float* g_r = g_a + 64 * ES;
     float* g_c = g_r + 64 * ES;
     float* g_beta = g_c + 64 * ES;
@@ -262,11 +265,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     float vrow[CW];
 #pragma unroll
     for (int c = 0; c < CW; ++c) vrow[c] = vnext[c];
-    GateRaw raw_next = {};
     if (i + 1 < count) {
-      raw_next = load_gates(i + 1);
+      raw_cur = load_gates(i + 1);
       load_vrow(i + 1, vnext);
     }
+    __syncthreads();                                 // gate tables visible
     mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -379,6 +382,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
+    if (STAGES == 1 && tid == 0 && i + 1 < count) issue_loads(i + 1);   // the only stage is free once (3) has completed
     {
       uint32_t packed[TPC / 2];
 #pragma unroll
@@ -404,7 +408,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       if (i + 1 < count) store_state(item + p.H, packed);
     }
-    if (i + 1 < count) write_gates(raw_next, (i + 1) & 1);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -416,14 +419,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
 using namespace tgdn;
 
-template <int E, int VC>
+template <int E, int VC, int NWG, int STAGES>
 static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const FwdParams& p, cudaStream_t s) {
-  using C = FwdCfg<E, VC>;
+  using C = FwdCfg<E, VC, NWG, STAGES>;
+  static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
-  cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  fwd_kernel<E, VC><<<grid, FWD_THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  fwd_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -448,12 +452,12 @@ extern "C" int tgdn_fwd(const void* q, const void* k, const void* v, const float
               tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 32>(mk, mq, p, s);
-    case 2: return launch_fwd<2, 32>(mk, mq, p, s);
-    case 4: return launch_fwd<4, 32>(mk, mq, p, s);
-    case 8: return launch_fwd<8, 32>(mk, mq, p, s);
-    case 12: return launch_fwd<12, 16>(mk, mq, p, s);
-    case 16: return launch_fwd<16, 16>(mk, mq, p, s);
+    case 1: return launch_fwd<1, 32, 4, 2>(mk, mq, p, s);
+    case 2: return launch_fwd<2, 32, 4, 2>(mk, mq, p, s);
+    case 4: return launch_fwd<4, 32, 4, 2>(mk, mq, p, s);
+    case 8: return launch_fwd<8, 16, 2, 1>(mk, mq, p, s);
+    case 12: return launch_fwd<12, 16, 4, 2>(mk, mq, p, s);
+    case 16: return launch_fwd<16, 16, 4, 2>(mk, mq, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }
