@@ -156,7 +156,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     umma_commit(&sm.bar_mma);
   }
   uint32_t mma_phase = 0;
-  mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   float pr[16];                                            // Pkk (key rows) / Pqk (query rows), this thread's 16 columns
@@ -258,7 +258,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int tt = 0; tt < 64; ++tt) acc += sm.daa[midx(tt, s)];
     sm.bcol[s] = acc;
   }
-  mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
@@ -300,7 +300,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
     for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
   }
-  mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
@@ -419,7 +419,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
 
   // ---- dk, dq: this thread's row, 32 of the 128 columns ------------------------------------------------------------
-  mbar_wait(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
   {

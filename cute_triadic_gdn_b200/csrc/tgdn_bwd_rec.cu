@@ -249,7 +249,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma);
       if (kstep + 1 < count) issue_loads(i - 1, st ^ 1);
     }
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     if (krow) {
@@ -299,7 +299,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
                        (drp[(2 * 64 + r) * ES + e] + drp[(3 * 64 + r) * ES + e]);
       p.dr[((item * NV + vb) * 64 + r) * E + e] = s4;
     }
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     {
@@ -341,7 +341,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     {

@@ -194,7 +194,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   };
   auto row_sums = [&](int s, auto vh_tag, float& rowsum) {   // R tile of step s (its MMAs waited for here)
     constexpr int vh = decltype(vh_tag)::value;
-    mbar_wait(&sm.bar_mma[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&sm.bar_mma[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
     tc_fence_after();
     float rr[32];
     tmem_ld<32>(tmem_row + 256 + vh * 64 + wg * 32, rr);

@@ -55,6 +55,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe: unlike try_wait it never parks the warp, so a spinning waiter sees the flip within a few cycles.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared per-CTA control block of a kernel with bounded waits.
 struct WaitCtl {
   volatile int* abort;   // shared-memory flag: once set, every wait of the CTA returns at once
@@ -76,6 +89,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       return false;
     }
   }
+}
+
+// Same contract as mbar_wait, for waits that are expected to end within a microsecond or two (an MMA group that has
+// just been issued): spins on the non-parking probe first, then falls back to the parking wait.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+#pragma unroll 1
+  for (int it = 0; it < 4096; ++it)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, ctl, code);
 }
 
 // ------------------------------------------------------------------------------------------------

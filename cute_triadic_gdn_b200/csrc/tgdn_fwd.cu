@@ -152,33 +152,32 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
   };
 
-  // raw gate inputs of one chunk for this thread's (at most two) table entries, and the table builder
-  struct GateRaw { float gcv[2], gl[2], k2v[2], q2v[2], beta; };
+  // Raw gate inputs of one chunk for this thread's (at most two) table entries, and the table builder.  The loads are
+  // issued unconditionally from clamped (always valid) addresses and masked when they are consumed: a predicated
+  // load followed by a select would make the issuing thread wait for the data at once.
+  struct GateRaw { float gcv[2], gl[2], k2v[2], q2v[2], beta; int rows; };
   constexpr int GATE_ITERS = (64 * E + FWD_THREADS - 1) / FWD_THREADS;
   static_assert(GATE_ITERS <= 2, "gate tables: at most two entries per thread");
   auto load_gates = [&](int i) {
     GateRaw g;
     int t0, rows;
     chunk_info(i, t0, rows);
+    g.rows = rows;
+    const int last = max(rows, 1) - 1;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
     const float* gcp = p.gc + item * (64 * E);
 #pragma unroll
     for (int it = 0; it < GATE_ITERS; ++it) {
-      const int idx = tid + it * FWD_THREADS;
-      g.gcv[it] = g.gl[it] = g.k2v[it] = g.q2v[it] = 0.f;
-      if (idx < 64 * E) {
-        const int r = idx / E, e = idx % E;
-        g.gcv[it] = gcp[idx];
-        g.gl[it] = gcp[63 * E + e];
-        if (r < rows) {
-          const int64_t off = ((tok + r) * p.H + h) * E + e;
-          g.k2v[it] = p.k2[off];
-          g.q2v[it] = p.q2[off];
-        }
-      }
+      const int idx = min(tid + it * FWD_THREADS, 64 * E - 1);
+      const int r = idx / E, e = idx % E;
+      const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
+      g.gcv[it] = gcp[idx];
+      g.gl[it] = gcp[63 * E + e];
+      g.k2v[it] = p.k2[off];
+      g.q2v[it] = p.q2[off];
     }
-    g.beta = (tid < 64 && tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+    g.beta = p.beta[(tok + min(tid & 63, last)) * p.H + h];
     return g;
   };
   auto write_gates = [&](const GateRaw& g) {
@@ -192,38 +191,35 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int idx = tid + it * FWD_THREADS;
       if (idx < 64 * E) {
         const int r = idx / E, e = idx % E;
+        const bool ok = r < g.rows;
+        const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
         const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
         const float eg = fexp2(gcv);
-        ga[r * ES + e] = g.k2v[it] * eg;
-        gr[r * ES + e] = g.k2v[it] * fexp2(gl - gcv);
-        gc_[r * ES + e] = p.scale * g.q2v[it] * eg;
+        ga[r * ES + e] = k2v * eg;
+        gr[r * ES + e] = k2v * fexp2(gl - gcv);
+        gc_[r * ES + e] = p.scale * q2v * eg;
         if (r == 0) gd[e] = fexp2(gl);
       }
     }
-    if (tid < 64) gb[tid] = g.beta;
+    if (tid < 64) gb[tid] = (tid < g.rows) ? g.beta : 0.f;
   };
-  auto load_vrow = [&](int i, float* dst) {          // K-row threads: this thread's CW value columns of row t
-#pragma unroll
-    for (int c = 0; c < CW; ++c) dst[c] = 0.f;
-    if (!krow) return;
+  auto load_vrow = [&](int i) {                      // this thread's CW value columns of row t (clamped), raw bf16
     int t0, rows;
     chunk_info(i, t0, rows);
-    if (t >= rows) return;
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    const __nv_bfloat16* vp = p.v + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
+    const __nv_bfloat16* vp = p.v + ((tok + min(t, max(rows, 1) - 1)) * p.H + h) * HEAD + vb * VC + wg * CW;
+    uint4 u;
     if constexpr (CW == 8) {
-      const uint4 u = __ldg(reinterpret_cast<const uint4*>(vp));
-      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
-      dst[4] = bf16_lo(u.z); dst[5] = bf16_hi(u.z); dst[6] = bf16_lo(u.w); dst[7] = bf16_hi(u.w);
+      u = __ldg(reinterpret_cast<const uint4*>(vp));
     } else {
-      const uint2 u = __ldg(reinterpret_cast<const uint2*>(vp));
-      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(vp));
+      u = make_uint4(w.x, w.y, 0u, 0u);
     }
+    return u;
   };
 
   if (tid == 0) issue_loads(0);
-  float vnext[CW];
-  load_vrow(0, vnext);
+  uint4 vnext = load_vrow(0);
   GateRaw raw_cur = load_gates(0);
   uint32_t mma_phase = 0;
   {
@@ -262,21 +258,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     float* g_c = g_r + 64 * ES;
     float* g_beta = g_c + 64 * ES;
     float* g_d = g_beta + 64;
-    float vrow[CW];
-#pragma unroll
-    for (int c = 0; c < CW; ++c) vrow[c] = vnext[c];
+    const uint4 vraw = vnext;
     if (i + 1 < count) {
       raw_cur = load_gates(i + 1);
-      load_vrow(i + 1, vnext);
+      vnext = load_vrow(i + 1);
     }
     __syncthreads();                                 // gate tables visible
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
 
-    float acc[CW];                                   // K rows: W; Q rows: Oq
+    float acc[CW];                                   // K rows: W (starts from V); Q rows: Oq
+    {
+      const uint32_t vw[4] = {vraw.x, vraw.y, vraw.z, vraw.w};
 #pragma unroll
-    for (int c = 0; c < CW; ++c) acc[c] = krow ? vrow[c] : 0.f;
+      for (int c = 0; c < CW; ++c)
+        acc[c] = (krow && t < rows) ? ((c & 1) ? bf16_hi(vw[c >> 1]) : bf16_lo(vw[c >> 1])) : 0.f;
+    }
     {
       const float* tab = krow ? g_a : g_c;
 #pragma unroll
@@ -327,7 +325,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem + NCOLS, desc_advance(da, kk * 4096), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     {
@@ -379,7 +377,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
-    mbar_wait(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     if (STAGES == 1 && tid == 0 && i + 1 < count) issue_loads(i + 1);   // the only stage is free once (3) has completed

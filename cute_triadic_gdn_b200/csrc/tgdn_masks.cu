@@ -203,7 +203,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     }
     umma_commit(&sm.bar_mma);
   }
-  mbar_wait(&sm.bar_mma, 0, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, 0, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
   float pr[32];                                             // this thread's 4 blocks of 8 columns of its row
 #pragma unroll
@@ -312,7 +312,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 64, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
-  mbar_wait(&sm.bar_mma, 1, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&sm.bar_mma, 1, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
   if (r < 64) {                                             // PA row r, columns 32*ch .. +32 -> rows 64.. of the image
     float pa[32];

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(128) selftest_mma_kernel(const __nv_bfloat16* 
                 desc_advance(db, st_operand_kstep(lb, kk, N, K)), idesc, (M != 128 || kk > 0) ? 1u : 0u);
     umma_commit(&bar);
   }
-  mbar_wait(&bar, 0, ctl, DEV_TIMEOUT_MMA);
+  mbar_wait_spin(&bar, 0, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   for (int c0 = 0; c0 < N; c0 += 8) {
