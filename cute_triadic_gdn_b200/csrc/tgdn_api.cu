@@ -71,7 +71,7 @@ int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed) {
   return 0;
 }
 
-int tgdn_value_block(int E) { return E >= 12 ? 16 : 32; }
+int tgdn_value_block(int E) { return E >= 8 ? 16 : 32; }   // must match the dispatch in tgdn_bwd_rec.cu
 
 extern "C" const char* tgdn_error_string(int code) {
   static thread_local char buf[160];

@@ -19,7 +19,6 @@
 
 namespace tgdn {
 
-constexpr int REC_THREADS = 512;
 
 __device__ __forceinline__ float rexp2(float x) {
   float y;
@@ -27,10 +26,13 @@ __device__ __forceinline__ float rexp2(float x) {
   return y;
 }
 
-template <int E, int VC>
+// NWG warpgroups split the VC value columns; STAGES = 2 prefetches the next chunk's tiles (one CTA per SM), STAGES = 1 is
+// sized so that two CTAs share an SM and hide each other's dependent-MMA latency.
+template <int E, int VC, int NWG, int STAGES>
 struct RecCfg {
+  static constexpr int THREADS = NWG * 128;
   static constexpr int NCOLS = E * VC;
-  static constexpr int CW = VC / 4;
+  static constexpr int CW = VC / NWG;
   static constexpr int TPC = E * CW;
   static constexpr int ES = E | 1;
   static constexpr int TMEM_NEED = NCOLS + 2 * VC;
@@ -41,16 +43,16 @@ struct RecCfg {
   static constexpr int GX_BYTES = NCOLS * 256;    // image (i = row 0..127, j = n'), SI = 128, SJ = 2048
   static constexpr int DO_BYTES = VC * 128;       // image (i = t, j = v), SI = 128, SJ = 1024
   static constexpr int OFF_KQ = 0;
-  static constexpr int OFF_GX = OFF_KQ + 2 * KQ_BYTES;
+  static constexpr int OFF_GX = OFF_KQ + STAGES * KQ_BYTES;
   static constexpr int OFF_AP = OFF_GX + GX_BYTES;
-  static constexpr int OFF_PM = OFF_AP + 2 * AP_BYTES;
+  static constexpr int OFF_PM = OFF_AP + STAGES * AP_BYTES;
   // the 128-row descriptors over the 64-row Pm image read up to 8 KB past it: keep 8 KB of owned memory behind it
-  static constexpr int OFF_DO = OFF_PM + 2 * PM_BYTES;
+  static constexpr int OFF_DO = OFF_PM + STAGES * PM_BYTES;
   static constexpr int OFF_DU = OFF_DO + ((DO_BYTES + 1023) & ~1023);
   static constexpr int OFF_GATES = OFF_DU + ((DO_BYTES + 1023) & ~1023);
   static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;
   static constexpr int OFF_DRP = OFF_GATES + GATE_FLOATS * 4;
-  static constexpr int DRP_FLOATS = 4 * 64 * ES;
+  static constexpr int DRP_FLOATS = NWG * 64 * ES;
   static constexpr int OFF_PAD = OFF_DRP + DRP_FLOATS * 4;
   static constexpr int PAD = (OFF_PAD - OFF_DO) >= 8192 ? 0 : 8192 - (OFF_PAD - OFF_DO);
   static constexpr int OFF_CTRL = OFF_PAD + PAD;
@@ -64,10 +66,11 @@ struct RecCtrl {
   int abort;
 };
 
-template <int E, int VC>
-__global__ void __launch_bounds__(REC_THREADS, 1)
+template <int E, int VC, int NWG, int STAGES>
+__global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
 rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, RecParams p) {
-  using C = RecCfg<E, VC>;
+  using C = RecCfg<E, VC, NWG, STAGES>;
+  constexpr int REC_THREADS = C::THREADS;
   constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
   constexpr int NV = HEAD / VC;
   constexpr float LOG2E = 1.4426950408889634f;
@@ -152,15 +155,58 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
     }
   };
-  auto load_row = [&](const __nv_bfloat16* ptr, float* dst) {
+  // Prefetched inputs of one chunk: this thread's row piece (K-row threads: U, Q-row threads: dO) as raw bf16, and the raw
+  // gate inputs of its (at most two) table entries.  Loads are unconditional from clamped addresses and masked at use.
+  struct ChunkRaw { uint4 rowp; float gcv[2], gl[2], k2v[2], q2v[2], beta; int rows; };
+  constexpr int GATE_ITERS = (64 * E + REC_THREADS - 1) / REC_THREADS;
+  static_assert(GATE_ITERS <= 2, "gate tables: at most two entries per thread");
+  auto load_chunk = [&](int i) {
+    ChunkRaw g;
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    g.rows = rows;
+    const int last = max(rows, 1) - 1;
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const float* gcp = p.gc + item * (64 * E);
+    const __nv_bfloat16* rp = krow ? p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW
+                                   : p.dO + ((tok + min(t, last)) * p.H + h) * HEAD + vb * VC + wg * CW;
     if constexpr (CW == 8) {
-      const uint4 u = __ldg(reinterpret_cast<const uint4*>(ptr));
-      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
-      dst[4] = bf16_lo(u.z); dst[5] = bf16_hi(u.z); dst[6] = bf16_lo(u.w); dst[7] = bf16_hi(u.w);
+      g.rowp = __ldg(reinterpret_cast<const uint4*>(rp));
     } else {
-      const uint2 u = __ldg(reinterpret_cast<const uint2*>(ptr));
-      dst[0] = bf16_lo(u.x); dst[1] = bf16_hi(u.x); dst[2] = bf16_lo(u.y); dst[3] = bf16_hi(u.y);
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
+      g.rowp = make_uint4(w.x, w.y, 0u, 0u);
     }
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = min(tid + it * REC_THREADS, 64 * E - 1);
+      const int r = idx / E, e = idx % E;
+      const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
+      g.gcv[it] = gcp[idx];
+      g.gl[it] = gcp[63 * E + e];
+      g.k2v[it] = p.k2[off];
+      g.q2v[it] = p.q2[off];
+    }
+    g.beta = p.beta[(tok + min(tid & 63, last)) * p.H + h];
+    return g;
+  };
+  auto write_gates = [&](const ChunkRaw& g) {
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * REC_THREADS;
+      if (idx < 64 * E) {
+        const int r = idx / E, e = idx % E;
+        const bool ok = r < g.rows;
+        const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
+        const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
+        const float eg = rexp2(gcv);
+        g_a[r * ES + e] = k2v * eg;
+        g_r[r * ES + e] = k2v * rexp2(gl - gcv);
+        g_c[r * ES + e] = p.scale * q2v * eg;
+        if (r == 0) g_d[e] = rexp2(gl);
+      }
+    }
+    if (tid < 64) g_beta[tid] = (tid < g.rows) ? g.beta : 0.f;
   };
   auto store_row_global = [&](__nv_bfloat16* ptr, const float* src) {
     if constexpr (CW == 8)
@@ -178,6 +224,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   };
 
   if (tid == 0) issue_loads(count - 1, 0);
+  ChunkRaw raw_cur = load_chunk(count - 1);
   uint32_t mma_phase = 0;
   {
     uint32_t zeros[TPC / 2];
@@ -188,7 +235,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
   for (int kstep = 0; kstep < count; ++kstep) {
     const int i = count - 1 - kstep;
-    const int st = kstep & 1;
+    const int st = (STAGES == 2) ? (kstep & 1) : 0;
     int t0, rows;
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
@@ -198,36 +245,25 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* pm = smem + C::OFF_PM + st * C::PM_BYTES;
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
-    // rows of dO (Q-row threads) and U (K-row threads); dO operand image; gate tables
+    // this chunk's inputs were loaded while the previous one was processed: row piece of U (K-row threads) or dO (Q-row
+    // threads), dO operand image, gate tables
     float rowv[CW];
+    {
+      const uint32_t rw[4] = {raw_cur.rowp.x, raw_cur.rowp.y, raw_cur.rowp.z, raw_cur.rowp.w};
+      const bool live = krow || t < rows;
 #pragma unroll
-    for (int c = 0; c < CW; ++c) rowv[c] = 0.f;
-    if (krow) {
-      load_row(p.U + (item * 64 + t) * HEAD + vb * VC + v0, rowv);
-    } else {
-      if (t < rows) load_row(p.dO + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, rowv);
+      for (int c = 0; c < CW; ++c) rowv[c] = live ? ((c & 1) ? bf16_hi(rw[c >> 1]) : bf16_lo(rw[c >> 1])) : 0.f;
+    }
+    if (!krow)
       store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, rowv, 1.f);
-    }
-    for (int idx = tid; idx < 64 * E; idx += REC_THREADS) {
-      const int r = idx / E, e = idx % E;
-      const float* gcp = p.gc + item * (64 * E);
-      const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
-      const bool ok = r < rows;
-      const int64_t off = ((tok + r) * p.H + h) * E + e;
-      const float k2v = ok ? p.k2[off] : 0.f, q2v = ok ? p.q2[off] : 0.f;
-      const float eg = rexp2(gcv);
-      g_a[r * ES + e] = k2v * eg;
-      g_r[r * ES + e] = k2v * rexp2(gl - gcv);
-      g_c[r * ES + e] = p.scale * q2v * eg;
-      if (r == 0) g_d[e] = rexp2(gl);
-    }
-    if (tid < 64) g_beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+    write_gates(raw_cur);
+    if (kstep + 1 < count) raw_cur = load_chunk(i - 1);      // consumed at the top of the next iteration
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
-    mbar_wait(&ctrl.bar_load[st], (kstep >> 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+    mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (tid == 0) {
       tc_fence_after();
       {
@@ -247,7 +283,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           umma_bf16(tmem + NCOLS, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
       }
       umma_commit(&ctrl.bar_mma);
-      if (kstep + 1 < count) issue_loads(i - 1, st ^ 1);
+      if (STAGES == 2 && kstep + 1 < count) issue_loads(i - 1, st ^ 1);
     }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
@@ -295,8 +331,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     // meanwhile: the value-block partial of dr, summed over the four warpgroups in a fixed order
     for (int idx = tid; idx < 64 * E; idx += REC_THREADS) {
       const int r = idx / E, e = idx % E;
-      const float s4 = (drp[(0 * 64 + r) * ES + e] + drp[(1 * 64 + r) * ES + e]) +
-                       (drp[(2 * 64 + r) * ES + e] + drp[(3 * 64 + r) * ES + e]);
+      float s4 = 0.f;
+#pragma unroll
+      for (int w = 0; w < NWG; ++w) s4 += drp[(w * 64 + r) * ES + e];
       p.dr[((item * NV + vb) * 64 + r) * E + e] = s4;
     }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
@@ -344,6 +381,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
+    if (STAGES == 1 && tid == 0 && kstep + 1 < count) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
     {
       uint32_t packed[TPC / 2];
 #pragma unroll
@@ -379,14 +417,15 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
 using namespace tgdn;
 
-template <int E, int VC>
+template <int E, int VC, int NWG, int STAGES>
 static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const RecParams& p, cudaStream_t s) {
-  using C = RecCfg<E, VC>;
+  using C = RecCfg<E, VC, NWG, STAGES>;
+  static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
-  cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  rec_kernel<E, VC><<<grid, REC_THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -412,12 +451,12 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
               doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale, tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_rec<1, 32>(mk, mq, p, s);
-    case 2: return launch_rec<2, 32>(mk, mq, p, s);
-    case 4: return launch_rec<4, 32>(mk, mq, p, s);
-    case 8: return launch_rec<8, 32>(mk, mq, p, s);
-    case 12: return launch_rec<12, 16>(mk, mq, p, s);
-    case 16: return launch_rec<16, 16>(mk, mq, p, s);
+    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, p, s);
+    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, p, s);
+    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, p, s);
+    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, p, s);
+    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, p, s);
+    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

@@ -113,7 +113,7 @@ int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const
 
 /* tgdn_bwd_recurrent: the reverse chunk recurrence.  Reads the upstream gradient dO (token layout) and the forward's
  * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), ds (chunk layout, dL/dS at the end of
- * every chunk, same form as h) and dr f32 [item][128/VC][64][E] (VC = 32 for E <= 8, 16 for E >= 12).
+ * every chunk, same form as h) and dr f32 [item][128/VC][64][E] (VC = 32 for E <= 4, 16 for E >= 8).
  * Replaces: cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:561-609 (joint_bwd_recurrent_sm100, recurrence part). */
 int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2, const float* beta,
                        const float* gc, const void* AP, const void* Pm, const void* U, float scale,
