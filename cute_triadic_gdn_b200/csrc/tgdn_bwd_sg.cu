@@ -1,6 +1,7 @@
 // State gradients of the Triadic GDN backward: everything that contracts over the value axis with the saved states.
 //
-// One CTA of 256 threads per (batch, chunk, head).  With h_e the forward state at the start of the chunk and G_e the
+// One CTA per (batch, chunk, head): 256 worker threads plus one warp that only issues the bulk loads and the MMAs, so
+// that instruction issue to the tensor core never sits on the workers' path.  With h_e the forward state at the start of the chunk and G_e the
 // gradient state at its end (both 128x128 bf16, streamed from HBM in 16 KB half-slices by bulk copies):
 //   dK_state = sum_e (-a_e*dW) h_e^T + (r_e*U) G_e^T          (64 x 128)
 //   dQ_state = sum_e ( c_e*dO) h_e^T                          (64 x 128)
@@ -17,7 +18,8 @@
 
 namespace tgdn {
 
-constexpr int SG_THREADS = 256;
+constexpr int SG_THREADS = 256;      // eight worker warps ...
+constexpr int SG_BLOCK = SG_THREADS + 32;   // ... plus one warp that only issues TMA loads and MMAs
 
 __device__ __forceinline__ float sexp2(float x) {
   float y;
@@ -40,14 +42,16 @@ struct SgSmem {
 };
 
 template <int E>
-__global__ void __launch_bounds__(SG_THREADS, 1)
+__global__ void __launch_bounds__(SG_BLOCK, 1)
 sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, SgParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   SgSmem& sm = *reinterpret_cast<SgSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int ES = 17;
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wg = warp >> 2;                          // column half inside a 64-column step
+  const bool worker = warp < SG_THREADS / 32;
+  const bool issuer = tid == SG_THREADS;             // first lane of the extra warp
+  const int wg = (warp >> 2) & 1;                    // column half inside a 64-column step
   const int row = (warp & 3) * 32 + lane;
   const bool krow = row < 64;
   const int t = row & 63;
@@ -90,7 +94,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
     bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
   };
-  if (tid == 0) {
+  if (issuer) {
     mbar_expect_tx(&sm.bar_kq, 32768);
     tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
@@ -102,7 +106,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
 
   // gate tables
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-  for (int idx = tid; idx < 64 * E; idx += SG_THREADS) {
+  for (int idx = tid; idx < 64 * E && worker; idx += SG_THREADS) {
     const int r = idx / E, e = idx % E;
     const float* gcp = p.gc + item * (64 * E);
     const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
@@ -121,7 +125,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
 #pragma unroll
     for (int j = 0; j < 16; ++j) { xw[vh][j] = 0u; uw[vh][j] = 0u; }
     const int c0 = vh * 64 + wg * 32;
-    if (krow) {
+    if (krow && worker) {
       const uint4* up = reinterpret_cast<const uint4*>(p.U + (item * 64 + t) * HEAD + c0);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -129,7 +133,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
         uw[vh][4 * j] = u.x; uw[vh][4 * j + 1] = u.y; uw[vh][4 * j + 2] = u.z; uw[vh][4 * j + 3] = u.w;
       }
     }
-    if (t < rows) {
+    if (t < rows && worker) {
       const __nv_bfloat16* src = (krow ? p.dV : p.dO) + ((tok + t) * p.H + h) * HEAD + c0;
       const uint4* xp = reinterpret_cast<const uint4*>(src);
 #pragma unroll
@@ -222,7 +226,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   using V0 = std::integral_constant<int, 0>;
   using V1 = std::integral_constant<int, 1>;
 
-  build(0, V0{});
+  if (worker) build(0, V0{});
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -233,17 +237,24 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     {
       const int s = 2 * e;
       mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (tid == 0) issue_mma(s, 0);
-      if (e > 0) {
-        row_sums(s - 1, V1{}, rowsum);                   // finishes slice e-1
-        sm.part[(wg * 128 + row) * ES + e - 1] = krow ? -rowsum : rowsum;
-        rowsum = 0.f;
-        if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);  // stage (s+2)%3 = (s-1)%3 is free: its MMAs are done
-      } else if (tid == 0 && STEPS > 2) {
-        issue_step(2);
+      if (issuer) {
+        issue_mma(s, 0);
+        if (e > 0) {                                     // stage (s+2)%3 = (s-1)%3 is free once the MMAs of step s-1 are done
+          mbar_wait(&sm.bar_mma[1], ((s - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+          if (s + 2 < STEPS) issue_step(s + 2);
+        } else if (STEPS > 2) {
+          issue_step(2);
+        }
       }
-      build(e, V1{});
-      dot_half(s, dot);
+      if (worker) {
+        if (e > 0) {
+          row_sums(s - 1, V1{}, rowsum);                 // finishes slice e-1
+          sm.part[(wg * 128 + row) * ES + e - 1] = krow ? -rowsum : rowsum;
+          rowsum = 0.f;
+        }
+        build(e, V1{});
+        dot_half(s, dot);
+      }
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
@@ -252,13 +263,18 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     {
       const int s = 2 * e + 1;
       mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (tid == 0) issue_mma(s, 1);
-      row_sums(s - 1, V0{}, rowsum);
-      if (tid == 0 && s + 2 < STEPS) issue_step(s + 2);
-      if (e + 1 < E) build(e + 1, V0{});
-      dot_half(s, dot);
-      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      if (lane == 0) sm.red[warp] = dot;
+      if (issuer) {
+        issue_mma(s, 1);
+        mbar_wait(&sm.bar_mma[0], ((s - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+        if (s + 2 < STEPS) issue_step(s + 2);
+      }
+      if (worker) {
+        row_sums(s - 1, V0{}, rowsum);
+        if (e + 1 < E) build(e + 1, V0{});
+        dot_half(s, dot);
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) sm.red[warp] = dot;
+      }
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
@@ -270,11 +286,15 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       }
     }
   }
-  row_sums(STEPS - 1, V1{}, rowsum);
-  sm.part[(wg * 128 + row) * ES + E - 1] = krow ? -rowsum : rowsum;
+  if (worker) {
+    row_sums(STEPS - 1, V1{}, rowsum);
+    sm.part[(wg * 128 + row) * ES + E - 1] = krow ? -rowsum : rowsum;
+  } else {
+    mbar_wait(&sm.bar_mma[1], ((STEPS - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+  }
   __syncthreads();
   // row sums: add the two column halves
-  for (int idx = tid; idx < 128 * E; idx += SG_THREADS) {
+  for (int idx = tid; idx < 128 * E && worker; idx += SG_THREADS) {
     const int r = idx / E, e = idx % E;
     const float v = sm.part[r * ES + e] + sm.part[(128 + r) * ES + e];
     if (r < 64) p.da[(item * 64 + r) * E + e] = v; else p.dc[(item * 64 + r - 64) * E + e] = v;
@@ -283,7 +303,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   tc_fence_after();
   float* outp = p.dkq + (item * 128 + row) * HEAD + wg * 64;
 #pragma unroll
-  for (int c0 = 0; c0 < 64; c0 += 16) {
+  for (int c0 = 0; c0 < 64 && worker; c0 += 16) {
     float a[16], a2[16];
     tmem_ld<16>(tmem_row + wg * 64 + c0, a);
     tmem_ld<16>(tmem_row + 128 + wg * 64 + c0, a2);
@@ -312,7 +332,7 @@ static int launch_sg(const CUtensorMap& mk, const CUtensorMap& mq, const SgParam
   const int smem = static_cast<int>(sizeof(SgSmem)) + 1024;
   cudaError_t e = cudaFuncSetAttribute(sg_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
-  sg_kernel<E><<<p.B * p.NC * p.H, SG_THREADS, smem, s>>>(mk, mq, p);
+  sg_kernel<E><<<p.B * p.NC * p.H, SG_BLOCK, smem, s>>>(mk, mq, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 

@@ -77,26 +77,26 @@ struct WaitCtl {
 constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second of SM clocks
 
 // Wait for `parity` of `bar`; gives up after WAIT_LIMIT_CYCLES, records `code` and raises the CTA's abort flag.
+// Spins on the non-parking probe: the parking form (try_wait) was measured to wake a waiter up to a microsecond after
+// the barrier flipped, which is as long as a whole pipeline phase here.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (int it = 0; it < 2048; ++it)
+    if (mbar_test_wait(bar, parity)) return true;
   const long long start = clock64();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*ctl.abort) return false;
-    if ((it & 255u) == 0u && clock64() - start > WAIT_LIMIT_CYCLES) {
-      *ctl.abort = 1;
-      atomicCAS(ctl.status, DEV_OK, code);
-      return false;
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (*ctl.abort) return false;
+      if (clock64() - start > WAIT_LIMIT_CYCLES) {
+        *ctl.abort = 1;
+        atomicCAS(ctl.status, DEV_OK, code);
+        return false;
+      }
     }
   }
 }
-
-// Same contract as mbar_wait, for waits that are expected to end within a microsecond or two (an MMA group that has
-// just been issued): spins on the non-parking probe first, then falls back to the parking wait.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
-#pragma unroll 1
-  for (int it = 0; it < 4096; ++it)
-    if (mbar_test_wait(bar, parity)) return true;
   return mbar_wait(bar, parity, ctl, code);
 }
 
