@@ -38,6 +38,10 @@ int* tgdn_status_word() {
 int tgdn_check_device() {
   int dev = 0, major = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  // Make the device's primary context current on the calling thread.  The tensor-map encoder is a driver call and
+  // fails with "invalid context" on a thread that has not touched the runtime yet (an autograd worker whose tensors all
+  // came out of the allocator's cache); setting the current device again is the documented way to bind the context.
+  if (cudaSetDevice(dev) != cudaSuccess) return 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
   return major == 10;
 }
@@ -55,6 +59,24 @@ int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H,
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
+}
+
+int tgdn_make_rows_map(CUtensorMap* map, const void* base, int C, int T, int B, int64_t stride_t, int64_t stride_b, int box_cols,
+                       int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TGDN_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (stride_t % 8) || (stride_b % 8)) return TGDN_ERR_ALIGN;
+  if (box_cols > 256 || box_rows > 256) return TGDN_ERR_SHAPE;
+  // a single batch row needs no third stride; give it any valid multiple of 16 bytes
+  const cuuint64_t sb = (B > 1) ? static_cast<cuuint64_t>(stride_b) * 2 : static_cast<cuuint64_t>(stride_t) * 2 * static_cast<cuuint64_t>(T);
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_t) * 2, sb};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
 }
 

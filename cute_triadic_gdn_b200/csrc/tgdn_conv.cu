@@ -1,10 +1,14 @@
 // Width-4 causal depthwise convolution with SiLU on the leading channels: forward and backward.
 //
 // Replaces the reference's Triton kernels cute_triadic_gdn/ops/conv_split_act.py:20-55 (_fwd_kernel) and :58-107
-// (_bwd_kernel).  HBM-bound: every thread owns 8 adjacent channels (one 16-byte vector) and walks a run of
-// consecutive tokens with the 4-tap window held in registers, so x is read once, y written once.  The backward
-// recomputes the bf16-rounded pre-activation from the same window (the reference launches a second forward for it),
-// reads x and dy once, writes dx once, and leaves one f32 weight-gradient partial per token tile in scratch memory; a
+// (_bwd_kernel).  HBM-bound, so the kernels are built around bytes in flight: a CTA owns a tile of 256 channels and
+// walks a run of 32-token tiles; the [tokens + halo][256 channels] input tiles arrive by TMA (cp.async.bulk.tensor, no
+// swizzle) into a multi-stage shared-memory ring, several tiles ahead of the arithmetic, and rows before the start of a
+// batch row come back as zeros from the tensor map's out-of-range fill.  Each warp computes 8 of the 32 output rows
+// for the tile's 256 channels (8 channels = one 16-byte vector per lane) and stores them with coalesced 512-byte rows.
+// The backward recomputes the bf16-rounded pre-activation from the same x window (the reference launches a second
+// forward for it), so x and dy are read once and dx written once; the weight gradient is accumulated in registers
+// over all tiles of the CTA, reduced across its warps in shared memory and written as one f32 partial per CTA; a
 // second small kernel sums the partials in a fixed order.
 #include <mutex>
 
@@ -14,83 +18,77 @@
 namespace tgdn {
 
 constexpr int CONV_W = 4;
-constexpr int CONV_THREADS = 128;
-constexpr int CONV_FWD_TOKENS = 32;    // tokens per thread in the forward
-constexpr int CONV_BWD_TOKENS = 256;   // tokens per thread (= per weight-gradient partial) in the backward
+constexpr int CONV_THREADS = 256;      // 8 warps = 4 row groups x 2 channel halves
+constexpr int CONV_CH = 256;           // channels per CTA tile (2 halves x 32 lanes x 4)
+constexpr int CONV_VEC = 4;            // channels per thread (one 8-byte vector)
+constexpr int CONV_TOK = 32;           // output tokens per tile (4 row groups x 8 rows)
+constexpr int CONV_FWD_ROWS = CONV_TOK + 3;       // x rows t0-3 .. t0+31
+constexpr int CONV_BWD_XROWS = CONV_TOK + 6;      // x rows t0-3 .. t0+34
+constexpr int CONV_BWD_GROWS = CONV_TOK + 3;      // dy rows t0 .. t0+34
+constexpr int CONV_FWD_STAGES = 3;     // 54 KB per CTA: four CTAs per SM
+constexpr int CONV_BWD_STAGES = 2;     // 75 KB per CTA: three CTAs per SM
 
-struct Vec8 {
-  float v[8];
+struct Vec4 {
+  float v[4];
 };
 
-__device__ __forceinline__ Vec8 load8(const __nv_bfloat16* p) {
-  uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
-  Vec8 r;
+__device__ __forceinline__ Vec4 unpack4(uint2 u) {
+  Vec4 r;
   r.v[0] = bf16_lo(u.x); r.v[1] = bf16_hi(u.x); r.v[2] = bf16_lo(u.y); r.v[3] = bf16_hi(u.y);
-  r.v[4] = bf16_lo(u.z); r.v[5] = bf16_hi(u.z); r.v[6] = bf16_lo(u.w); r.v[7] = bf16_hi(u.w);
   return r;
 }
-__device__ __forceinline__ Vec8 zero8() {
-  Vec8 r;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) r.v[i] = 0.f;
+__device__ __forceinline__ Vec4 zero4() {
+  Vec4 r;
+  r.v[0] = r.v[1] = r.v[2] = r.v[3] = 0.f;
   return r;
 }
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const Vec8& a) {
-  uint4 u;
-  u.x = pack_bf16(a.v[0], a.v[1]); u.y = pack_bf16(a.v[2], a.v[3]);
-  u.z = pack_bf16(a.v[4], a.v[5]); u.w = pack_bf16(a.v[6], a.v[7]);
-  *reinterpret_cast<uint4*>(p) = u;
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const Vec4& a) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(a.v[0], a.v[1]), pack_bf16(a.v[2], a.v[3]));
 }
-__device__ __forceinline__ float silu(float y) { return y / (1.f + __expf(-y)); }
+// sigmoid with the fast exponential and the fast reciprocal: relative error of a few f32 ulps
+__device__ __forceinline__ float fast_sigmoid(float y) { return __fdividef(1.f, 1.f + __expf(-y)); }
+__device__ __forceinline__ float silu(float y) { return y * fast_sigmoid(y); }
 __device__ __forceinline__ float silu_grad(float y) {
-  float s = 1.f / (1.f + __expf(-y));
-  return s * (1.f + y * (1.f - s));
+  const float s = fast_sigmoid(y);
+  return s * fmaf(y, 1.f - s, 1.f);
 }
 
-// Index of the document that holds token t: largest d with cu[d] <= t.
-__device__ __forceinline__ int find_doc(const int32_t* cu, int n_docs, int t) {
+// Start of the document that holds token t (largest cu[d] <= t); 0 for rows without documents.
+__device__ __forceinline__ int doc_start_of(const int32_t* cu, int n_docs, int t) {
+  if (cu == nullptr) return 0;
   int lo = 0, hi = n_docs - 1;
   while (lo < hi) {
     int mid = (lo + hi + 1) >> 1;
     if (__ldg(cu + mid) <= t) lo = mid; else hi = mid - 1;
   }
-  return lo;
+  return __ldg(cu + lo);
 }
 
-// Walks document boundaries as the token index grows.
-struct DocCursor {
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+struct ConvArgs {
+  const __nv_bfloat16* weight;
+  __nv_bfloat16* out;            // y (forward) or dx (backward), contiguous (B, T, C)
+  float* dw_partial;             // backward: [B * groups][C][4]
   const int32_t* cu;
-  int n_docs, d, start, next;
-  __device__ __forceinline__ void init(const int32_t* cu_, int n_docs_, int t, int T) {
-    cu = cu_; n_docs = n_docs_;
-    if (cu == nullptr) { d = 0; start = 0; next = T; return; }
-    d = find_doc(cu, n_docs, t);
-    start = __ldg(cu + d);
-    next = __ldg(cu + d + 1);
-  }
-  __device__ __forceinline__ void advance(int t) {      // call with increasing t
-    while (cu != nullptr && t >= next && d + 1 < n_docs) {
-      ++d; start = next; next = __ldg(cu + d + 1);
-    }
-  }
+  int n_docs, T, C, act_channels, tiles_per_group;
+  int* status;
 };
 
-__global__ void __launch_bounds__(CONV_THREADS)
-conv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ weight,
-                __nv_bfloat16* __restrict__ y, const int32_t* __restrict__ cu, int n_docs, int T, int C,
-                int64_t stride_b, int64_t stride_t, int act_channels) {
-  const int c0 = (blockIdx.x * CONV_THREADS + threadIdx.x) * 8;
-  if (c0 >= C) return;
-  const int t0 = blockIdx.y * CONV_FWD_TOKENS;
-  const int t1 = min(T, t0 + CONV_FWD_TOKENS);
-  const __nv_bfloat16* xb = x + static_cast<int64_t>(blockIdx.z) * stride_b + c0;
-  __nv_bfloat16* yb = y + (static_cast<int64_t>(blockIdx.z) * T) * C + c0;
-
-  float w[8][CONV_W];
-  {
+__device__ __forceinline__ void load_weights(const __nv_bfloat16* weight, int c0, int C, float (*w)[CONV_W]) {
+#pragma unroll
+  for (int c = 0; c < CONV_VEC; ++c)
+#pragma unroll
+    for (int j = 0; j < CONV_W; ++j) w[c][j] = 0.f;
+  if (c0 < C) {                                 // C % 8 == 0 and c0 % 4 == 0: the four channels are all inside
     const uint4* wp = reinterpret_cast<const uint4*>(weight + static_cast<int64_t>(c0) * CONV_W);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {              // 8 channels x 4 taps = 32 bf16 = 4 vectors
+    for (int i = 0; i < 2; ++i) {               // 4 channels x 4 taps = 16 bf16 = 2 vectors
       uint4 u = __ldg(wp + i);
       const uint32_t ws[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -99,143 +97,210 @@ conv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         w[e / 4][e % 4] = bf16_lo(ws[j]);
         w[(e + 1) / 4][(e + 1) % 4] = bf16_hi(ws[j]);
       }
-    }
-  }
-  DocCursor doc;
-  doc.init(cu, n_docs, t0, T);
-  Vec8 xm1 = zero8(), xm2 = zero8(), xm3 = zero8();
-  if (t0 - 1 >= doc.start) xm1 = load8(xb + static_cast<int64_t>(t0 - 1) * stride_t);
-  if (t0 - 2 >= doc.start) xm2 = load8(xb + static_cast<int64_t>(t0 - 2) * stride_t);
-  if (t0 - 3 >= doc.start) xm3 = load8(xb + static_cast<int64_t>(t0 - 3) * stride_t);
-
-  for (int tb = t0; tb < t1; tb += 8) {
-    Vec8 xs[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      xs[i] = (tb + i < t1) ? load8(xb + static_cast<int64_t>(tb + i) * stride_t) : zero8();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int t = tb + i;
-      if (t >= t1) break;
-      doc.advance(t);
-      if (t == doc.start) { xm1 = zero8(); xm2 = zero8(); xm3 = zero8(); }
-      Vec8 out;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float acc = xm3.v[c] * w[c][0];
-        acc = fmaf(xm2.v[c], w[c][1], acc);
-        acc = fmaf(xm1.v[c], w[c][2], acc);
-        acc = fmaf(xs[i].v[c], w[c][3], acc);
-        out.v[c] = (c0 + c < act_channels) ? silu(acc) : acc;
-      }
-      store8(yb + static_cast<int64_t>(t) * C, out);
-      xm3 = xm2; xm2 = xm1; xm1 = xs[i];
     }
   }
 }
 
-__global__ void __launch_bounds__(CONV_THREADS)
-conv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ weight,
-                const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
-                const int32_t* __restrict__ cu, int n_docs, int T, int C, int64_t stride_b, int64_t stride_t,
-                int64_t dy_stride_b, int64_t dy_stride_t, int act_channels) {
-  const int c0 = (blockIdx.x * CONV_THREADS + threadIdx.x) * 8;
-  if (c0 >= C) return;
-  const int t0 = blockIdx.y * CONV_BWD_TOKENS;
-  const int t1 = min(T, t0 + CONV_BWD_TOKENS);
-  const __nv_bfloat16* xb = x + static_cast<int64_t>(blockIdx.z) * stride_b + c0;
-  const __nv_bfloat16* dyb = dy + static_cast<int64_t>(blockIdx.z) * dy_stride_b + c0;
-  __nv_bfloat16* dxb = dx + (static_cast<int64_t>(blockIdx.z) * T) * C + c0;
-
-  float w[8][CONV_W];
-  {
-    const uint4* wp = reinterpret_cast<const uint4*>(weight + static_cast<int64_t>(c0) * CONV_W);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 u = __ldg(wp + i);
-      const uint32_t ws[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int e = i * 8 + j * 2;
-        w[e / 4][e % 4] = bf16_lo(ws[j]);
-        w[(e + 1) / 4][(e + 1) % 4] = bf16_hi(ws[j]);
-      }
-    }
+__global__ void __launch_bounds__(CONV_THREADS, 4)
+conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  constexpr int STAGE_BYTES = CONV_FWD_ROWS * CONV_CH * 2;
+  __shared__ uint64_t full[CONV_FWD_STAGES];
+  __shared__ int abort_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int half = warp & 1, rg = warp >> 1;
+  const int cbase = blockIdx.x * CONV_CH, c0 = cbase + half * 128 + lane * CONV_VEC, b = blockIdx.z;
+  const int n_tiles = (a.T + CONV_TOK - 1) / CONV_TOK;
+  const int tile_lo = blockIdx.y * a.tiles_per_group, tile_hi = min(n_tiles, tile_lo + a.tiles_per_group);
+  if (tile_lo >= tile_hi) return;
+  if (tid == 0) {
+    for (int s = 0; s < CONV_FWD_STAGES; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    abort_s = 0;
   }
-  float dwa[8][CONV_W];
+  __syncthreads();
+  WaitCtl ctl{&abort_s, a.status};
+  auto issue = [&](int tile) {                         // thread 0
+    const int s = (tile - tile_lo) % CONV_FWD_STAGES;
+    mbar_expect_tx(&full[s], STAGE_BYTES);
+    tma_load_3d(smem + s * STAGE_BYTES, &map_x, &full[s], cbase, tile * CONV_TOK - 3, b);
+  };
+  if (tid == 0)
+    for (int i = 0; i < CONV_FWD_STAGES && tile_lo + i < tile_hi; ++i) issue(tile_lo + i);
+
+  float w[CONV_VEC][CONV_W];
+  load_weights(a.weight, c0, a.C, w);
+  __nv_bfloat16* yb = a.out + (static_cast<int64_t>(b) * a.T) * a.C + c0;
+  const int col_off = half * 256 + lane * 8;             // byte offset of this thread's channels inside a tile row
+
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int k = tile - tile_lo, s = k % CONV_FWD_STAGES;
+    mbar_wait(&full[s], (k / CONV_FWD_STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    const uint8_t* st = smem + s * STAGE_BYTES + col_off;
+    const int t_first = tile * CONV_TOK + rg * 8;         // this warp's first output token; its smem row is rg*8 + 3
+    int dstart = doc_start_of(a.cu, a.n_docs, min(t_first, a.T - 1));
+    Vec4 xm[3];                                           // x[t-1], x[t-2], x[t-3]
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
+    for (int j = 0; j < 3; ++j) {
+      const int tj = t_first - 1 - j;
+      xm[j] = (tj >= dstart) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = t_first + i;
+      if (t >= a.T) break;
+      if (a.cu != nullptr && i > 0) {                     // a document may start inside the warp's rows
+        const int ds = doc_start_of(a.cu, a.n_docs, t);
+        if (ds != dstart) { dstart = ds; xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }
+      }
+      const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+      Vec4 out;
+#pragma unroll
+      for (int c = 0; c < CONV_VEC; ++c) {
+        float acc = xm[2].v[c] * w[c][0];
+        acc = fmaf(xm[1].v[c], w[c][1], acc);
+        acc = fmaf(xm[0].v[c], w[c][2], acc);
+        acc = fmaf(x0.v[c], w[c][3], acc);
+        out.v[c] = (c0 + c < a.act_channels) ? silu(acc) : acc;
+      }
+      if (c0 < a.C) store4(yb + static_cast<int64_t>(t) * a.C, out);
+      xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
+    }
+    __syncthreads();                                      // every warp is done with this stage
+    if (tid == 0 && tile + CONV_FWD_STAGES < tile_hi) issue(tile + CONV_FWD_STAGES);
+  }
+}
+
+__global__ void __launch_bounds__(CONV_THREADS, 3)
+conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy, ConvArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  constexpr int X_BYTES = CONV_BWD_XROWS * CONV_CH * 2, G_BYTES = CONV_BWD_GROWS * CONV_CH * 2;
+  constexpr int STAGE_BYTES = X_BYTES + G_BYTES;
+  __shared__ uint64_t full[CONV_BWD_STAGES];
+  __shared__ int abort_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int half = warp & 1, rg = warp >> 1;
+  const int cbase = blockIdx.x * CONV_CH, c0 = cbase + half * 128 + lane * CONV_VEC, b = blockIdx.z;
+  const int n_tiles = (a.T + CONV_TOK - 1) / CONV_TOK;
+  const int tile_lo = blockIdx.y * a.tiles_per_group, tile_hi = min(n_tiles, tile_lo + a.tiles_per_group);
+  if (tid == 0) {
+    for (int s = 0; s < CONV_BWD_STAGES; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    abort_s = 0;
+  }
+  __syncthreads();
+  WaitCtl ctl{&abort_s, a.status};
+  auto issue = [&](int tile) {                         // thread 0
+    const int s = (tile - tile_lo) % CONV_BWD_STAGES;
+    mbar_expect_tx(&full[s], STAGE_BYTES);
+    tma_load_3d(smem + s * STAGE_BYTES, &map_x, &full[s], cbase, tile * CONV_TOK - 3, b);
+    tma_load_3d(smem + s * STAGE_BYTES + X_BYTES, &map_dy, &full[s], cbase, tile * CONV_TOK, b);
+  };
+  if (tid == 0)
+    for (int i = 0; i < CONV_BWD_STAGES && tile_lo + i < tile_hi; ++i) issue(tile_lo + i);
+
+  float w[CONV_VEC][CONV_W];
+  load_weights(a.weight, c0, a.C, w);
+  float dwa[CONV_VEC][CONV_W];
+#pragma unroll
+  for (int c = 0; c < CONV_VEC; ++c)
 #pragma unroll
     for (int j = 0; j < CONV_W; ++j) dwa[c][j] = 0.f;
+  __nv_bfloat16* dxb = a.out + (static_cast<int64_t>(b) * a.T) * a.C + c0;
+  const int col_off = half * 256 + lane * 8;
 
-  DocCursor doc;
-  doc.init(cu, n_docs, t0, T);
-  // x window: xw[j] = x[t - j] while token t is processed (xw[0] is loaded in the loop)
-  Vec8 xw1 = zero8(), xw2 = zero8(), xw3 = zero8();
-  if (t0 - 1 >= doc.start) xw1 = load8(xb + static_cast<int64_t>(t0 - 1) * stride_t);
-  if (t0 - 2 >= doc.start) xw2 = load8(xb + static_cast<int64_t>(t0 - 2) * stride_t);
-  if (t0 - 3 >= doc.start) xw3 = load8(xb + static_cast<int64_t>(t0 - 3) * stride_t);
-  // dy' of the last four tokens (gw0 = token t ... gw3 = token t-3) and the document start of each
-  Vec8 gw1 = zero8(), gw2 = zero8(), gw3 = zero8();
-  int ds1 = 0x7fffffff, ds2 = 0x7fffffff;
-
-  // dx[u] = sum_j dy'[u+j] * w[3-j] over tokens u+j of the same document: token u is complete once t = u+3 is seen,
-  // so the loop runs three tokens past the tile (dy' = 0 past the end of the row).
-  for (int t = t0; t < t1 + CONV_W - 1; ++t) {
-    Vec8 gy = zero8();
-    Vec8 x0 = zero8();
-    int ds0 = 0x7fffffff;
-    if (t < T) {
-      doc.advance(t);
-      ds0 = doc.start;
-      if (t == doc.start) { xw1 = zero8(); xw2 = zero8(); xw3 = zero8(); }
-      x0 = load8(xb + static_cast<int64_t>(t) * stride_t);
-      const Vec8 g = load8(dyb + static_cast<int64_t>(t) * dy_stride_t);
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int k = tile - tile_lo, s = k % CONV_BWD_STAGES;
+    mbar_wait(&full[s], (k / CONV_BWD_STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    const uint8_t* sx = smem + s * STAGE_BYTES + col_off;              // row r holds x[t0 - 3 + r]
+    const uint8_t* sg = sx + X_BYTES;                                  // row r holds dy[t0 + r]
+    const int t0 = tile * CONV_TOK, u_first = t0 + rg * 8;             // this warp's output tokens u_first .. +7
+    // dx[u] = sum_j dy'[u+j] w[3-j] over tokens of the same document; dy'[t] needs x[t-3..t].  Walk t = u_first .. u_first+10
+    // (three tokens past the warp's rows) with the x window and the last three dy' in registers.
+    int dstart = doc_start_of(a.cu, a.n_docs, min(u_first, a.T - 1));
+    Vec4 xw[3];                                                        // x[t-1], x[t-2], x[t-3]
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {                // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
-        float gv = g.v[c];
-        if (c0 + c < act_channels) {
-          float pre = xw3.v[c] * w[c][0];
-          pre = fmaf(xw2.v[c], w[c][1], pre);
-          pre = fmaf(xw1.v[c], w[c][2], pre);
-          pre = fmaf(x0.v[c], w[c][3], pre);
-          gv *= silu_grad(round_bf16(pre));
-        }
-        gy.v[c] = gv;
-      }
-      if (t < t1) {                                // the weight gradient of token t belongs to this tile
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          dwa[c][0] = fmaf(gy.v[c], xw3.v[c], dwa[c][0]);
-          dwa[c][1] = fmaf(gy.v[c], xw2.v[c], dwa[c][1]);
-          dwa[c][2] = fmaf(gy.v[c], xw1.v[c], dwa[c][2]);
-          dwa[c][3] = fmaf(gy.v[c], x0.v[c], dwa[c][3]);
-        }
-      }
+    for (int j = 0; j < 3; ++j) {
+      const int tj = u_first - 1 - j;
+      xw[j] = (tj >= dstart) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
     }
-    const int u = t - 3;
-    if (u >= t0) {
-      const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
-      Vec8 out;
+    Vec4 gw[3] = {zero4(), zero4(), zero4()};                          // dy'[t-1], dy'[t-2], dy'[t-3]
+    int ds1 = 0x7fffffff, ds2 = 0x7fffffff;                            // document starts of tokens t-1, t-2
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float acc = gw3.v[c] * w[c][3];
-        acc = fmaf(m2 * gw2.v[c], w[c][2], acc);
-        acc = fmaf(m1 * gw1.v[c], w[c][1], acc);
-        acc = fmaf(m0 * gy.v[c], w[c][0], acc);
-        out.v[c] = acc;
+    for (int i = 0; i < 11; ++i) {
+      const int t = u_first + i;
+      Vec4 gy = zero4(), x0 = zero4();
+      int ds0 = 0x7fffffff;
+      if (t < a.T) {
+        if (a.cu != nullptr && i > 0) {
+          const int ds = doc_start_of(a.cu, a.n_docs, t);
+          if (ds != dstart) { dstart = ds; xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
+        }
+        ds0 = dstart;
+        x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+        const Vec4 g = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+#pragma unroll
+        for (int c = 0; c < CONV_VEC; ++c) {                           // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
+          float gv = g.v[c];
+          if (c0 + c < a.act_channels) {
+            float pre = xw[2].v[c] * w[c][0];
+            pre = fmaf(xw[1].v[c], w[c][1], pre);
+            pre = fmaf(xw[0].v[c], w[c][2], pre);
+            pre = fmaf(x0.v[c], w[c][3], pre);
+            gv *= silu_grad(round_bf16(pre));
+          }
+          gy.v[c] = gv;
+        }
+        if (i < 8) {                                                   // the weight gradient of token t belongs to this warp
+#pragma unroll
+          for (int c = 0; c < CONV_VEC; ++c) {
+            dwa[c][0] = fmaf(gy.v[c], xw[2].v[c], dwa[c][0]);
+            dwa[c][1] = fmaf(gy.v[c], xw[1].v[c], dwa[c][1]);
+            dwa[c][2] = fmaf(gy.v[c], xw[0].v[c], dwa[c][2]);
+            dwa[c][3] = fmaf(gy.v[c], x0.v[c], dwa[c][3]);
+          }
+        }
       }
-      store8(dxb + static_cast<int64_t>(u) * C, out);
+      if (i >= 3) {
+        const int u = t - 3;
+        if (u < a.T && c0 < a.C) {
+          const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
+          Vec4 out;
+#pragma unroll
+          for (int c = 0; c < CONV_VEC; ++c) {
+            float acc = gw[2].v[c] * w[c][3];
+            acc = fmaf(m2 * gw[1].v[c], w[c][2], acc);
+            acc = fmaf(m1 * gw[0].v[c], w[c][1], acc);
+            acc = fmaf(m0 * gy.v[c], w[c][0], acc);
+            out.v[c] = acc;
+          }
+          store4(dxb + static_cast<int64_t>(u) * a.C, out);
+        }
+      }
+      gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
+      ds2 = ds1; ds1 = ds0;
+      xw[2] = xw[1]; xw[1] = xw[0]; xw[0] = x0;
     }
-    gw3 = gw2; gw2 = gw1; gw1 = gy;
-    ds2 = ds1; ds1 = ds0;
-    xw3 = xw2; xw2 = xw1; xw1 = x0;
+    __syncthreads();
+    if (tid == 0 && tile + CONV_BWD_STAGES < tile_hi) issue(tile + CONV_BWD_STAGES);
   }
-  float* out = dw_partial + (static_cast<int64_t>(blockIdx.z) * gridDim.y + blockIdx.y) * (static_cast<int64_t>(C) * CONV_W) +
-               static_cast<int64_t>(c0) * CONV_W;
+  // weight-gradient partial of this CTA: sum over its four row groups in a fixed order through shared memory
+  float* red = reinterpret_cast<float*>(smem);                         // [4 row groups][256 channels][4 taps]
+  __syncthreads();
 #pragma unroll
-  for (int c = 0; c < 8; ++c)
-    *reinterpret_cast<float4*>(out + c * CONV_W) = make_float4(dwa[c][0], dwa[c][1], dwa[c][2], dwa[c][3]);
+  for (int c = 0; c < CONV_VEC; ++c)
+    *reinterpret_cast<float4*>(red + (rg * CONV_CH + half * 128 + lane * CONV_VEC + c) * CONV_W) =
+        make_float4(dwa[c][0], dwa[c][1], dwa[c][2], dwa[c][3]);
+  __syncthreads();
+  float* out = a.dw_partial + (static_cast<int64_t>(b) * gridDim.y + blockIdx.y) * (static_cast<int64_t>(a.C) * CONV_W);
+  for (int e = tid; e < CONV_CH * CONV_W; e += CONV_THREADS) {
+    const int ch = cbase + e / CONV_W;
+    if (ch < a.C)
+      out[static_cast<int64_t>(ch) * CONV_W + e % CONV_W] =
+          (red[e] + red[CONV_CH * CONV_W + e]) + (red[2 * CONV_CH * CONV_W + e] + red[3 * CONV_CH * CONV_W + e]);
+  }
 }
 
 __global__ void conv_dw_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int n_partial,
@@ -259,25 +324,74 @@ static int conv_check(const void* x, const void* weight, const void* y, const in
   if (B > 65535) return TGDN_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(y)) & 15)
     return TGDN_ERR_ALIGN;
-  if ((stride_b % 8) || (stride_t % 8)) return TGDN_ERR_ALIGN;
+  if ((stride_b % 8) || (stride_t % 8) || stride_t < C) return TGDN_ERR_ALIGN;
   return 0;
+}
+
+// Token tiles per CTA and number of CTAs along the token axis: about two CTAs per SM in total, so that every CTA keeps
+// its ring of tiles in flight for a long run of tokens and the number of weight-gradient partials stays small.
+static void conv_groups(int T, int C, int* groups, int* tiles_per_group) {
+  const int n_tiles = (T + CONV_TOK - 1) / CONV_TOK;
+  const int n_ctile = (C + CONV_CH - 1) / CONV_CH;
+  int g = (2 * 148 + n_ctile - 1) / n_ctile;
+  if (g < 1) g = 1;
+  if (g > n_tiles) g = n_tiles;
+  *tiles_per_group = (n_tiles + g - 1) / g;
+  *groups = (n_tiles + *tiles_per_group - 1) / *tiles_per_group;
 }
 
 extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const int32_t* cu_seqlens, int n_docs, int B,
                              int T, int C, int64_t stride_b, int64_t stride_t, int act_channels, void* stream) {
   int rc = conv_check(x, weight, y, cu_seqlens, n_docs, B, T, C, stride_b, stride_t);
   if (rc) return rc;
-  dim3 grid((C / 8 + CONV_THREADS - 1) / CONV_THREADS, (T + CONV_FWD_TOKENS - 1) / CONV_FWD_TOKENS, B);
-  conv_fwd_kernel<<<grid, CONV_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y),
-      cu_seqlens, n_docs, T, C, stride_b, stride_t, act_channels);
+  // the device query also binds the CUDA context to the calling thread, which the tensor-map encoder needs
+  if (!tgdn_check_device()) return TGDN_ERR_DEVICE;
+  CUtensorMap mx;
+  if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_FWD_ROWS))) return rc;
+  int groups, tpg;
+  conv_groups(T, C, &groups, &tpg);
+  ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y), nullptr, cu_seqlens, n_docs, T, C,
+             act_channels, tpg, tgdn_status_word()};
+  const int smem = CONV_FWD_STAGES * CONV_FWD_ROWS * CONV_CH * 2 + 128;
+  cudaError_t e = cudaFuncSetAttribute(conv_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  dim3 grid((C + CONV_CH - 1) / CONV_CH, groups, B);
+  conv_fwd_kernel<<<grid, CONV_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(mx, a);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
 extern "C" int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C) {
   if (B <= 0 || T <= 0 || C <= 0) return 0;
-  const int64_t tiles = (T + CONV_BWD_TOKENS - 1) / CONV_BWD_TOKENS;
-  return static_cast<int64_t>(B) * tiles * C * CONV_W * static_cast<int64_t>(sizeof(float));
+  int groups, tpg;
+  conv_groups(T, C, &groups, &tpg);
+  return static_cast<int64_t>(B) * groups * C * CONV_W * static_cast<int64_t>(sizeof(float));
+}
+
+// Shared by tgdn_conv_bwd and tgdn_conv_bwd_static: both kernels of the backward with the partials in `scratch`.
+static int conv_bwd_launch(const void* x, const void* weight, const void* dy, void* dx, void* dw, const int32_t* cu_seqlens,
+                           int n_docs, int B, int T, int C, int64_t stride_b, int64_t stride_t, int64_t dy_stride_b,
+                           int64_t dy_stride_t, int act_channels, float* scratch, cudaStream_t s) {
+  // the device query also binds the CUDA context to the calling thread (autograd runs the backward on a worker thread
+  // that may not have made a runtime call yet), which the tensor-map encoder needs
+  if (!tgdn_check_device()) return TGDN_ERR_DEVICE;
+  CUtensorMap mx, mg;
+  int rc;
+  if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_BWD_XROWS))) return rc;
+  if ((rc = tgdn_make_rows_map(&mg, dy, C, T, B, dy_stride_t, dy_stride_b, CONV_CH, CONV_BWD_GROWS))) return rc;
+  int groups, tpg;
+  conv_groups(T, C, &groups, &tpg);
+  ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C,
+             act_channels, tpg, tgdn_status_word()};
+  const int smem = CONV_BWD_STAGES * (CONV_BWD_XROWS + CONV_BWD_GROWS) * CONV_CH * 2 + 128;
+  cudaError_t e = cudaFuncSetAttribute(conv_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  dim3 grid((C + CONV_CH - 1) / CONV_CH, groups, B);
+  conv_bwd_kernel<<<grid, CONV_THREADS, smem, s>>>(mx, mg, a);
+  rc = tgdn_cuda_error(cudaGetLastError());
+  if (rc) return rc;
+  const int n_elem = C * CONV_W;
+  conv_dw_reduce_kernel<<<(n_elem + 255) / 256, 256, 0, s>>>(scratch, static_cast<__nv_bfloat16*>(dw), B * groups, n_elem);
+  return tgdn_cuda_error(cudaGetLastError());
 }
 
 extern "C" int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, void* dx, void* dw,
@@ -287,22 +401,11 @@ extern "C" int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, 
   int rc = conv_check(x, weight, dx, cu_seqlens, n_docs, B, T, C, stride_b, stride_t);
   if (rc) return rc;
   if (!dy || !dw) return TGDN_ERR_NULL;
-  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (dy_stride_b % 8) || (dy_stride_t % 8)) return TGDN_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (dy_stride_b % 8) || (dy_stride_t % 8) || dy_stride_t < C) return TGDN_ERR_ALIGN;
   if (!scratch || scratch_bytes < tgdn_conv_bwd_scratch_bytes(B, T, C) || (reinterpret_cast<uintptr_t>(scratch) & 15))
     return TGDN_ERR_SCRATCH;
-  const int tiles = (T + CONV_BWD_TOKENS - 1) / CONV_BWD_TOKENS;
-  dim3 grid((C / 8 + CONV_THREADS - 1) / CONV_THREADS, tiles, B);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  conv_bwd_kernel<<<grid, CONV_THREADS, 0, s>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
-      static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), static_cast<float*>(scratch), cu_seqlens,
-      n_docs, T, C, stride_b, stride_t, dy_stride_b, dy_stride_t, act_channels);
-  rc = tgdn_cuda_error(cudaGetLastError());
-  if (rc) return rc;
-  const int n_elem = C * CONV_W;
-  conv_dw_reduce_kernel<<<(n_elem + 255) / 256, 256, 0, s>>>(static_cast<const float*>(scratch),
-                                                             static_cast<__nv_bfloat16*>(dw), B * tiles, n_elem);
-  return tgdn_cuda_error(cudaGetLastError());
+  return conv_bwd_launch(x, weight, dy, dx, dw, cu_seqlens, n_docs, B, T, C, stride_b, stride_t, dy_stride_b, dy_stride_t,
+                         act_channels, static_cast<float*>(scratch), static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -352,20 +455,10 @@ extern "C" int tgdn_conv_bwd_static(const void* x, const void* weight, const voi
   int rc = conv_check(x, weight, dx, cu_seqlens, n_docs, B, T, C, stride_b, stride_t);
   if (rc) return rc;
   if (!dy || !dw) return TGDN_ERR_NULL;
-  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (dy_stride_b % 8) || (dy_stride_t % 8)) return TGDN_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (dy_stride_b % 8) || (dy_stride_t % 8) || dy_stride_t < C) return TGDN_ERR_ALIGN;
   if (tgdn_conv_bwd_scratch_bytes(B, T, C) > static_cast<int64_t>(TGDN_CONV_STATIC_SCRATCH_BYTES)) return TGDN_ERR_STATIC_LIMIT;
   float* scratch = nullptr;
   if ((rc = conv_static_scratch(&scratch))) return rc;
-  const int tiles = (T + CONV_BWD_TOKENS - 1) / CONV_BWD_TOKENS;
-  dim3 grid((C / 8 + CONV_THREADS - 1) / CONV_THREADS, tiles, B);
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  conv_bwd_kernel<<<grid, CONV_THREADS, 0, s>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(weight),
-      static_cast<const __nv_bfloat16*>(dy), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C, stride_b,
-      stride_t, dy_stride_b, dy_stride_t, act_channels);
-  rc = tgdn_cuda_error(cudaGetLastError());
-  if (rc) return rc;
-  const int n_elem = C * CONV_W;
-  conv_dw_reduce_kernel<<<(n_elem + 255) / 256, 256, 0, s>>>(scratch, static_cast<__nv_bfloat16*>(dw), B * tiles, n_elem);
-  return tgdn_cuda_error(cudaGetLastError());
+  return conv_bwd_launch(x, weight, dy, dx, dw, cu_seqlens, n_docs, B, T, C, stride_b, stride_t, dy_stride_b, dy_stride_t,
+                         act_channels, scratch, static_cast<cudaStream_t>(stream));
 }

@@ -17,5 +17,9 @@ int* tgdn_status_word();
 // swizzle128 = 1 asks for the 128-byte swizzle (box_cols must then be 64).
 int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H, int box_cols, int box_rows, int swizzle128);
 
-// True when the current device is compute capability 10.x.
+// Tensor map over a (B, T, C) bf16 tensor with element strides (stride_b, stride_t, 1): box = [box_cols][box_rows][1], no swizzle.
+int tgdn_make_rows_map(CUtensorMap* map, const void* base, int C, int T, int B, int64_t stride_t, int64_t stride_b, int box_cols,
+                       int box_rows);
+
+// True when the current device is compute capability 10.x; also binds the device's primary context to the calling thread.
 int tgdn_check_device();

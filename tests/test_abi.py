@@ -28,6 +28,15 @@ def test_chunk_capacity_matches_reference_formula(T, N):
     assert _lib.lib.tgdn_chunk_capacity(T, N) == chunk_capacity(T, N)
 
 
+def _conv_scratch(B, T, C):
+    """One f32 weight-gradient partial of C x 4 per CTA along the token axis (about two CTAs per SM in total)."""
+    n_tiles, n_ctile = (T + 31) // 32, (C + 255) // 256
+    g = max(1, min(n_tiles, (2 * 148 + n_ctile - 1) // n_ctile))
+    tpg = (n_tiles + g - 1) // g
+    groups = (n_tiles + tpg - 1) // tpg
+    return B * groups * C * 4 * 4
+
+
 def test_null_and_shape_arguments_are_rejected_before_launch():
     L = _lib.lib
     null = ctypes.c_void_p(None)
@@ -36,7 +45,8 @@ def test_null_and_shape_arguments_are_rejected_before_launch():
     assert L.tgdn_conv_fwd(fake, fake, fake, null, 0, 1, 64, 63, 0, 63, 0, null) == -1       # C % 8
     assert L.tgdn_conv_fwd(ctypes.c_void_p(4098), fake, fake, null, 0, 1, 64, 64, 0, 64, 0, null) == -3
     assert L.tgdn_conv_bwd(fake, fake, fake, fake, fake, null, 0, 1, 64, 64, 0, 64, 0, 64, 0, null, 0, null) == -5
-    assert L.tgdn_conv_bwd_scratch_bytes(1, 300, 64) == 2 * 64 * 4 * 4
+    assert L.tgdn_conv_bwd_scratch_bytes(1, 300, 64) == _conv_scratch(1, 300, 64)
+    assert L.tgdn_conv_bwd_scratch_bytes(1, 32768, 13056) == _conv_scratch(1, 32768, 13056)
     assert L.tgdn_metadata(null, 0, 1, 64, null, null, 16, null, null) == -2
     assert L.tgdn_metadata(fake, 0, 3, 640, fake, fake, 8, fake, null) == -1                  # capacity too small
     assert L.tgdn_selftest_mma(fake, fake, fake, 96, 64, 64, 0, 0, null) == -1

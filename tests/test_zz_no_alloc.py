@@ -52,7 +52,7 @@ def test_static_scratch_variant_matches_two_calls_in_a_row():
 def test_static_scratch_variant_refuses_oversized_problems():
     L = _lib.lib
     fake = ctypes.c_void_p(4096)
-    B, T, C = 1, 32768, 13056                      # needs 26.7 MB of partials: more than the built-in array
+    B, T, C = 48, 4096, 13056                      # needs 60 MB of partials: more than the built-in array
     assert L.tgdn_conv_bwd_scratch_bytes(B, T, C) > STATIC_BYTES
     rc = L.tgdn_conv_bwd_static(fake, fake, fake, fake, fake, None, 0, B, T, C, T * C, C, T * C, C, 0, None)
     assert rc == -7
