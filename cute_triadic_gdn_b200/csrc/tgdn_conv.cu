@@ -53,16 +53,32 @@ __device__ __forceinline__ float silu_grad(float y) {
   return s * fmaf(y, 1.f - s, 1.f);
 }
 
-// Start of the document that holds token t (largest cu[d] <= t); 0 for rows without documents.
-__device__ __forceinline__ int doc_start_of(const int32_t* cu, int n_docs, int t) {
-  if (cu == nullptr) return 0;
-  int lo = 0, hi = n_docs - 1;
-  while (lo < hi) {
-    int mid = (lo + hi + 1) >> 1;
-    if (__ldg(cu + mid) <= t) lo = mid; else hi = mid - 1;
+// Walks document boundaries as the token index grows: one binary search per tile, then a compare per token.
+struct DocCursor {
+  const int32_t* cu;
+  int n_docs, d, start, next;
+  __device__ __forceinline__ void init(const int32_t* cu_, int n_docs_, int t, int T) {
+    cu = cu_; n_docs = n_docs_; d = 0; start = 0; next = 0x7fffffff;
+    if (cu == nullptr) return;
+    int lo = 0, hi = n_docs - 1;
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if (__ldg(cu + mid) <= t) lo = mid; else hi = mid - 1;
+    }
+    d = lo;
+    start = __ldg(cu + d);
+    next = (d + 1 < n_docs) ? __ldg(cu + d + 1) : 0x7fffffff;
   }
-  return __ldg(cu + lo);
-}
+  // true when token t is the first token of a document that starts after the one the cursor was on
+  __device__ __forceinline__ bool advance(int t) {
+    if (t < next) return false;
+    do {
+      ++d; start = next;
+      next = (d + 1 < n_docs) ? __ldg(cu + d + 1) : 0x7fffffff;
+    } while (t >= next);
+    return true;
+  }
+};
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
   asm volatile(
@@ -133,27 +149,30 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
   load_weights(a.weight, c0, a.C, w);
   __nv_bfloat16* yb = a.out + (static_cast<int64_t>(b) * a.T) * a.C + c0;
   const int col_off = half * 256 + lane * 8;             // byte offset of this thread's channels inside a tile row
+  const bool live = c0 < a.C;
+  bool act[CONV_VEC];
+#pragma unroll
+  for (int c = 0; c < CONV_VEC; ++c) act[c] = c0 + c < a.act_channels;
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int k = tile - tile_lo, s = k % CONV_FWD_STAGES;
     mbar_wait(&full[s], (k / CONV_FWD_STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
     const uint8_t* st = smem + s * STAGE_BYTES + col_off;
     const int t_first = tile * CONV_TOK + rg * 8;         // this warp's first output token; its smem row is rg*8 + 3
-    int dstart = doc_start_of(a.cu, a.n_docs, min(t_first, a.T - 1));
+    DocCursor doc;
+    doc.init(a.cu, a.n_docs, min(t_first, a.T - 1), a.T);
     Vec4 xm[3];                                           // x[t-1], x[t-2], x[t-3]
 #pragma unroll
     for (int j = 0; j < 3; ++j) {
       const int tj = t_first - 1 - j;
-      xm[j] = (tj >= dstart) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+      xm[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
     }
+    __nv_bfloat16* yrow = yb + static_cast<int64_t>(t_first) * a.C;
+    const int n_rows = min(8, a.T - t_first);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const int t = t_first + i;
-      if (t >= a.T) break;
-      if (a.cu != nullptr && i > 0) {                     // a document may start inside the warp's rows
-        const int ds = doc_start_of(a.cu, a.n_docs, t);
-        if (ds != dstart) { dstart = ds; xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }
-      }
+      if (i >= n_rows) break;
+      if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
       const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
       Vec4 out;
 #pragma unroll
@@ -162,9 +181,10 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
         acc = fmaf(xm[1].v[c], w[c][1], acc);
         acc = fmaf(xm[0].v[c], w[c][2], acc);
         acc = fmaf(x0.v[c], w[c][3], acc);
-        out.v[c] = (c0 + c < a.act_channels) ? silu(acc) : acc;
+        out.v[c] = act[c] ? silu(acc) : acc;
       }
-      if (c0 < a.C) store4(yb + static_cast<int64_t>(t) * a.C, out);
+      if (live) store4(yrow, out);
+      yrow += a.C;
       xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
     }
     __syncthreads();                                      // every warp is done with this stage
@@ -210,6 +230,10 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     for (int j = 0; j < CONV_W; ++j) dwa[c][j] = 0.f;
   __nv_bfloat16* dxb = a.out + (static_cast<int64_t>(b) * a.T) * a.C + c0;
   const int col_off = half * 256 + lane * 8;
+  const bool live = c0 < a.C;
+  bool act[CONV_VEC];
+#pragma unroll
+  for (int c = 0; c < CONV_VEC; ++c) act[c] = c0 + c < a.act_channels;
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int k = tile - tile_lo, s = k % CONV_BWD_STAGES;
@@ -219,12 +243,13 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int t0 = tile * CONV_TOK, u_first = t0 + rg * 8;             // this warp's output tokens u_first .. +7
     // dx[u] = sum_j dy'[u+j] w[3-j] over tokens of the same document; dy'[t] needs x[t-3..t].  Walk t = u_first .. u_first+10
     // (three tokens past the warp's rows) with the x window and the last three dy' in registers.
-    int dstart = doc_start_of(a.cu, a.n_docs, min(u_first, a.T - 1));
+    DocCursor doc;
+    doc.init(a.cu, a.n_docs, min(u_first, a.T - 1), a.T);
     Vec4 xw[3];                                                        // x[t-1], x[t-2], x[t-3]
 #pragma unroll
     for (int j = 0; j < 3; ++j) {
       const int tj = u_first - 1 - j;
-      xw[j] = (tj >= dstart) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+      xw[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
     }
     Vec4 gw[3] = {zero4(), zero4(), zero4()};                          // dy'[t-1], dy'[t-2], dy'[t-3]
     int ds1 = 0x7fffffff, ds2 = 0x7fffffff;                            // document starts of tokens t-1, t-2
@@ -234,17 +259,14 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       Vec4 gy = zero4(), x0 = zero4();
       int ds0 = 0x7fffffff;
       if (t < a.T) {
-        if (a.cu != nullptr && i > 0) {
-          const int ds = doc_start_of(a.cu, a.n_docs, t);
-          if (ds != dstart) { dstart = ds; xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
-        }
-        ds0 = dstart;
+        if (i > 0 && doc.advance(t)) { xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
+        ds0 = doc.start;
         x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
         const Vec4 g = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
 #pragma unroll
         for (int c = 0; c < CONV_VEC; ++c) {                           // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
           float gv = g.v[c];
-          if (c0 + c < a.act_channels) {
+          if (act[c]) {
             float pre = xw[2].v[c] * w[c][0];
             pre = fmaf(xw[1].v[c], w[c][1], pre);
             pre = fmaf(xw[0].v[c], w[c][2], pre);
@@ -265,7 +287,7 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       }
       if (i >= 3) {
         const int u = t - 3;
-        if (u < a.T && c0 < a.C) {
+        if (u < a.T && live) {
           const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
           Vec4 out;
 #pragma unroll
@@ -328,12 +350,12 @@ static int conv_check(const void* x, const void* weight, const void* y, const in
   return 0;
 }
 
-// Token tiles per CTA and number of CTAs along the token axis: about two CTAs per SM in total, so that every CTA keeps
+// Token tiles per CTA and number of CTAs along the token axis: as many CTAs as fit on the GPU at once, so that every CTA keeps
 // its ring of tiles in flight for a long run of tokens and the number of weight-gradient partials stays small.
-static void conv_groups(int T, int C, int* groups, int* tiles_per_group) {
+static void conv_groups(int T, int C, int ctas_per_sm, int* groups, int* tiles_per_group) {
   const int n_tiles = (T + CONV_TOK - 1) / CONV_TOK;
   const int n_ctile = (C + CONV_CH - 1) / CONV_CH;
-  int g = (2 * 148 + n_ctile - 1) / n_ctile;
+  int g = (ctas_per_sm * 148 + n_ctile - 1) / n_ctile;
   if (g < 1) g = 1;
   if (g > n_tiles) g = n_tiles;
   *tiles_per_group = (n_tiles + g - 1) / g;
@@ -349,7 +371,7 @@ extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const i
   CUtensorMap mx;
   if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_FWD_ROWS))) return rc;
   int groups, tpg;
-  conv_groups(T, C, &groups, &tpg);
+  conv_groups(T, C, 4, &groups, &tpg);
   ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y), nullptr, cu_seqlens, n_docs, T, C,
              act_channels, tpg, tgdn_status_word()};
   const int smem = CONV_FWD_STAGES * CONV_FWD_ROWS * CONV_CH * 2 + 128;
@@ -363,7 +385,7 @@ extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const i
 extern "C" int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C) {
   if (B <= 0 || T <= 0 || C <= 0) return 0;
   int groups, tpg;
-  conv_groups(T, C, &groups, &tpg);
+  conv_groups(T, C, 3, &groups, &tpg);
   return static_cast<int64_t>(B) * groups * C * CONV_W * static_cast<int64_t>(sizeof(float));
 }
 
@@ -379,7 +401,7 @@ static int conv_bwd_launch(const void* x, const void* weight, const void* dy, vo
   if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_BWD_XROWS))) return rc;
   if ((rc = tgdn_make_rows_map(&mg, dy, C, T, B, dy_stride_t, dy_stride_b, CONV_CH, CONV_BWD_GROWS))) return rc;
   int groups, tpg;
-  conv_groups(T, C, &groups, &tpg);
+  conv_groups(T, C, 3, &groups, &tpg);
   ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C,
              act_channels, tpg, tgdn_status_word()};
   const int smem = CONV_BWD_STAGES * (CONV_BWD_XROWS + CONV_BWD_GROWS) * CONV_CH * 2 + 128;
