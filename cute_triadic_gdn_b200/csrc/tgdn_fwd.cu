@@ -136,6 +136,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
     bulk_load(smem + C::OFF_AP + st * C::AP_BYTES, p.AP + item * (128 * 64), C::AP_BYTES, &ctrl.bar_load[st]);
   };
+  auto prefetch_loads = [&](int i) {                // thread 0: pull the next chunk's tiles into L2 while this chunk is worked on
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    tma_prefetch_4d(&map_k, 0, h, t0, b);
+    tma_prefetch_4d(&map_q, 0, h, t0, b);
+    tma_prefetch_4d(&map_k, 64, h, t0, b);
+    tma_prefetch_4d(&map_q, 64, h, t0, b);
+    bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
+  };
   // saved state of chunk item: this thread's pieces of slice e live at [e][(vb*VC + wg*CW)/8][row][...]
   auto store_state = [&](int64_t item, const uint32_t* packed /* TPC/2 words */) {
     if (p.h == nullptr) return;
@@ -251,6 +261,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
       if (STAGES == 2 && i + 1 < count) issue_loads(i + 1);   // the other stage was released by the previous chunk's (3)
+      if (STAGES == 1 && i + 1 < count) prefetch_loads(i + 1);
     }
     // start the loads for the next chunk's tables and value row now; they are consumed at the top of the next iteration
     float* g_a = gate_base;
@@ -277,9 +288,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     {
       const float* tab = krow ? g_a : g_c;
+      constexpr int EP = (TPC % 32 == 0) ? 32 / CW : ((TPC % 16 == 0) ? 16 / CW : E);   // slices per tensor-memory round trip
 #pragma unroll
-      for (int e0 = 0; e0 < E; e0 += (16 / CW)) {    // 16 columns per tensor-memory load where possible
-        constexpr int EP = (16 / CW) < E ? (16 / CW) : E;
+      for (int e0 = 0; e0 < E; e0 += EP) {
         float rr[EP * CW];
         tmem_ld<EP * CW>(tmem_row + wg * TPC + e0 * CW, rr);
         tmem_wait_ld();
@@ -382,29 +393,42 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_after();
     if (STAGES == 1 && tid == 0 && i + 1 < count) issue_loads(i + 1);   // the only stage is free once (3) has completed
     {
-      uint32_t packed[TPC / 2];
+      constexpr int PIECE = (TPC % 32 == 0) ? 32 : ((TPC % 16 == 0) ? 16 : TPC);
+      const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
+      uint8_t* hbase = (p.h != nullptr && i + 1 < count)
+                           ? reinterpret_cast<uint8_t*>(p.h) + (item + p.H) * (static_cast<int64_t>(E) * 32768) : nullptr;
+      const int v0 = vb * VC + wg * CW;
 #pragma unroll
-      for (int j0 = 0; j0 < TPC; j0 += 16) {
-        constexpr int PIECE = TPC < 16 ? TPC : 16;
+      for (int j0 = 0; j0 < TPC; j0 += PIECE) {
         float ds[PIECE];
         tmem_ld<PIECE>(tmem_row + wg * TPC + j0, ds);
         tmem_wait_ld();
+        uint32_t packed[PIECE / 2];
 #pragma unroll
-        for (int j = 0; j < PIECE; ++j) {
-          const float de = g_d[(j0 + j) / CW];
-          S[j0 + j] = fmaf(de, S[j0 + j], ds[j]);
+        for (int j = 0; j < PIECE; j += 2) {
+          S[j0 + j] = fmaf(g_d[(j0 + j) / CW], S[j0 + j], ds[j]);
+          S[j0 + j + 1] = fmaf(g_d[(j0 + j + 1) / CW], S[j0 + j + 1], ds[j + 1]);
+          packed[j / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
         }
+        // operand image (i = d, j = n') for the next chunk's (1)
 #pragma unroll
-        for (int j = 0; j < PIECE; j += 2) packed[(j0 + j) / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
-      }
-      // operand image (i = d, j = n') for the next chunk's (1)
-      const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
+        for (int j = 0; j < PIECE; j += 8) {
+          const int n0 = wg * TPC + j0 + j;
+          st_shared_v4(base + (n0 >> 3) * 2048, packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
+        }
+        // saved state of the next chunk: slice e as [v/8][d][v%8]
+        if (hbase != nullptr) {
 #pragma unroll
-      for (int j0 = 0; j0 < TPC; j0 += 8) {
-        const int n0 = wg * TPC + j0;
-        st_shared_v4(base + (n0 >> 3) * 2048, packed[j0 / 2], packed[j0 / 2 + 1], packed[j0 / 2 + 2], packed[j0 / 2 + 3]);
+          for (int j = 0; j < PIECE; j += CW) {
+            const int e = (j0 + j) / CW;
+            uint8_t* dst = hbase + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
+            if constexpr (CW == 8)
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
+            else
+              *reinterpret_cast<uint2*>(dst) = make_uint2(packed[j / 2], packed[j / 2 + 1]);
+          }
+        }
       }
-      if (i + 1 < count) store_state(item + p.H, packed);
     }
     fence_async_smem();
     tc_fence_before();
