@@ -203,25 +203,31 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     float rr[32];
     tmem_ld<32>(tmem_row + 256 + vh * 64 + wg * 32, rr);
     tmem_wait_ld();
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;          // independent chains
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      rowsum = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], rowsum);
-      rowsum = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], rowsum);
+    for (int j = 0; j < 16; j += 2) {
+      a0 = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], a0);
+      a1 = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], a1);
+      a2 = fmaf(bf16_lo(xw[vh][j + 1]), rr[2 * j + 2], a2);
+      a3 = fmaf(bf16_hi(xw[vh][j + 1]), rr[2 * j + 3], a3);
     }
+    rowsum += (a0 + a1) + (a2 + a3);
   };
   auto dot_half = [&](int s, float& dot) {               // <h, G> over the half-slice of step s: 1024 16-byte pieces
     const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[s % 3]);
     const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[s % 3]);
+    float d[4] = {0.f, 0.f, 0.f, 0.f};                     // independent chains
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint4 a = hp4[j * SG_THREADS + tid], g = gp4[j * SG_THREADS + tid];
       const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        dot = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), dot);
-        dot = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), dot);
+        d[w] = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), d[w]);
+        d[w] = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), d[w]);
       }
     }
+    dot += (d[0] + d[1]) + (d[2] + d[3]);
   };
   using V0 = std::integral_constant<int, 0>;
   using V1 = std::integral_constant<int, 1>;
