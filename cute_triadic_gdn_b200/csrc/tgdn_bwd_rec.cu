@@ -117,7 +117,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = ctrl.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, ctrl.tmem_base, 0);
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&ctrl.abort, p.status};
 
@@ -182,12 +183,12 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int idx = min(tid + it * REC_THREADS, 64 * E - 1);
       const int r = idx / E, e = idx % E;
       const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
-      g.gcv[it] = gcp[idx];
-      g.gl[it] = gcp[63 * E + e];
-      g.k2v[it] = p.k2[off];
-      g.q2v[it] = p.q2[off];
+      g.gcv[it] = __ldg(gcp + idx);
+      g.gl[it] = __ldg(gcp + 63 * E + e);
+      g.k2v[it] = __ldg(p.k2 + off);
+      g.q2v[it] = __ldg(p.q2 + off);
     }
-    g.beta = p.beta[(tok + min(tid & 63, last)) * p.H + h];
+    g.beta = __ldg(p.beta + (tok + min(tid & 63, last)) * p.H + h);
     return g;
   };
   auto write_gates = [&](const ChunkRaw& g) {
@@ -264,7 +265,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       {
         const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -283,8 +284,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           umma_bf16(tmem + NCOLS, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
       }
       umma_commit(&ctrl.bar_mma);
-      if (STAGES == 2 && kstep + 1 < count) issue_loads(i - 1, st ^ 1);
     }
+    if (STAGES == 2 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, st ^ 1);
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -318,7 +319,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (c) Z = A^T dU -----------------------------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(ap), 128, 2048, LAYOUT_PLAIN);         // A^T: MN-major over (i = t, j = s)
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_DU), 128, 1024, LAYOUT_PLAIN);
@@ -368,7 +369,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (d) dG = [K^T | Q^T] X, G <- d G + dG ------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_GX), 128, 2048, LAYOUT_PLAIN);
@@ -381,7 +382,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
-    if (STAGES == 1 && tid == 0 && kstep + 1 < count) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
+    if (STAGES == 1 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
     {
       uint32_t packed[TPC / 2];
 #pragma unroll

@@ -157,6 +157,13 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       : "memory");
 }
 // Arrive once on `bar` when every tcgen05.mma issued so far by this thread has completed.
+// One lane of a fully active warp.  Tensor-core and TMA instructions are issued as "warp-uniform branch, then elected
+// lane": their operands then stay warp-uniform values, which a branch on the thread index would not allow.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -261,6 +268,25 @@ __device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t a, uint32_
 }
 __device__ __forceinline__ void st_shared_v2(uint32_t saddr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(saddr), "r"(a), "r"(b) : "memory");
+}
+
+// Global loads that stay where they are written.  A plain read-only load may be sunk by the compiler to its first use,
+// which turns a prefetch issued one loop iteration ahead back into an exposed memory round trip; volatile asm keeps its
+// program order relative to the barrier and tensor-core instructions around it.
+__device__ __forceinline__ float ldg_pinned_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_pinned_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_pinned_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
 }
 
 }  // namespace tgdn

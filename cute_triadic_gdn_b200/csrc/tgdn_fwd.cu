@@ -111,7 +111,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = ctrl.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, ctrl.tmem_base, 0);
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&ctrl.abort, p.status};
 
@@ -251,7 +252,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
     write_gates(raw_cur);                            // loaded while the previous chunk was processed
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (i >> 1) : i) & 1, ctl, DEV_TIMEOUT_LOAD);
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_S), 128, 2048, LAYOUT_PLAIN);
@@ -260,8 +261,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       for (int kk = 0; kk < 8; ++kk)
         umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
-      if (STAGES == 2 && i + 1 < count) issue_loads(i + 1);   // the other stage was released by the previous chunk's (3)
-      if (STAGES == 1 && i + 1 < count) prefetch_loads(i + 1);
+    }
+    if (warp_u == 1 && i + 1 < count && elect_one()) {
+      if (STAGES == 2) issue_loads(i + 1);             // the other stage was released by the previous chunk's (3)
+      if (STAGES == 1) prefetch_loads(i + 1);
     }
     // start the loads for the next chunk's tables and value row now; they are consumed at the top of the next iteration
     float* g_a = gate_base;
@@ -326,7 +329,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (2) [U;Oi] = [A;PmA] (beta W) ------------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(ap), 2048, 128, LAYOUT_PLAIN);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_BW), 128, 1024, LAYOUT_PLAIN);
@@ -378,7 +381,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (3) dS = K^T Vn, S <- d S + dS -----------------------------------------------------------------------
-    if (tid == 0) {
+    if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_VN), 128, 1024, LAYOUT_PLAIN);
@@ -391,7 +394,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
-    if (STAGES == 1 && tid == 0 && i + 1 < count) issue_loads(i + 1);   // the only stage is free once (3) has completed
+    if (STAGES == 1 && warp_u == 1 && i + 1 < count && elect_one()) issue_loads(i + 1);   // the only stage is free once (3) has completed
     {
       constexpr int PIECE = (TPC % 32 == 0) ? 32 : ((TPC % 16 == 0) ? 16 : TPC);
       const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
