@@ -1,6 +1,6 @@
 // State gradients of the Triadic GDN backward: everything that contracts over the value axis with the saved states.
 //
-// One CTA per (batch, chunk, head): 256 worker threads plus one warp that only issues the bulk loads and the MMAs, so
+// One CTA per (batch, chunk, head): 256 worker threads, one warp that only issues the MMAs and one that only issues the bulk loads, so
 // that instruction issue to the tensor core never sits on the workers' path.  With h_e the forward state at the start of the chunk and G_e the
 // gradient state at its end (both 128x128 bf16, streamed from HBM in 16 KB half-slices by bulk copies):
 //   dK_state = sum_e (-a_e*dW) h_e^T + (r_e*U) G_e^T          (64 x 128)
@@ -19,7 +19,7 @@
 namespace tgdn {
 
 constexpr int SG_THREADS = 256;      // eight worker warps ...
-constexpr int SG_BLOCK = SG_THREADS + 32;   // ... plus one warp that only issues TMA loads and MMAs
+constexpr int SG_BLOCK = SG_THREADS + 64;   // ... plus one warp that only issues MMAs and one that only issues bulk loads
 
 __device__ __forceinline__ float sexp2(float x) {
   float y;
@@ -35,8 +35,8 @@ struct SgSmem {
   uint8_t xa[2][16384];         // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
   float ga[64 * 17], gr[64 * 17], gcq[64 * 17];
   float part[2 * 128 * 17];     // row sums per column half
-  float red[SG_THREADS / 32];
-  uint64_t bar_kq, bar_load[3], bar_mma[2];
+  float red[16 * (SG_THREADS / 32)];   // per slice and worker warp: partial <h,G>
+  uint64_t bar_kq, bar_load[3], bar_mma[2], bar_built[2], bar_read[3];
   uint32_t tmem_base;
   int abort;
 };
@@ -50,7 +50,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp < SG_THREADS / 32;
-  const bool issuer = tid == SG_THREADS;             // first lane of the extra warp
+  const bool issuer = tid == SG_THREADS;             // first lane of the first extra warp
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
   const int wg = (warp >> 2) & 1;                    // column half inside a 64-column step
   const int row = (warp & 3) * 32 + lane;
   const bool krow = row < 64;
@@ -75,6 +76,11 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     mbar_init(&sm.bar_load[2], 1);
     mbar_init(&sm.bar_mma[0], 1);
     mbar_init(&sm.bar_mma[1], 1);
+    mbar_init(&sm.bar_built[0], SG_THREADS / 32);
+    mbar_init(&sm.bar_built[1], SG_THREADS / 32);
+    mbar_init(&sm.bar_read[0], SG_THREADS / 32);
+    mbar_init(&sm.bar_read[1], SG_THREADS / 32);
+    mbar_init(&sm.bar_read[2], SG_THREADS / 32);
     mbar_fence_init();
     sm.abort = 0;
   }
@@ -82,19 +88,19 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&sm.abort, p.status};
   constexpr int STEPS = 2 * E;
   const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
   const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
-  auto issue_step = [&](int s) {                     // thread 0
+  auto issue_step = [&](int s) {                     // one lane of the issuing warp
     const int st = s % 3;
     mbar_expect_tx(&sm.bar_load[st], 32768);
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
     bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
   };
-  if (issuer) {
+  if (issuer) {                                        // all three stages are free at the start
     mbar_expect_tx(&sm.bar_kq, 32768);
     tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
@@ -102,57 +108,87 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     tma_load_4d(sm.kq + 24576, &map_q, &sm.bar_kq, 64, h, t0, b);
     issue_step(0);
     issue_step(1);
+    if (STEPS > 2) issue_step(2);
   }
 
-  // gate tables
+  // All global loads of the prologue go out together, from clamped (always valid) addresses, and are masked when they are
+  // used: the CTA then pays one memory round trip here instead of one per dependent group.
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-  for (int idx = tid; idx < 64 * E && worker; idx += SG_THREADS) {
-    const int r = idx / E, e = idx % E;
-    const float* gcp = p.gc + item * (64 * E);
-    const float gcv = gcp[r * E + e] * LOG2E, gl = gcp[63 * E + e] * LOG2E;
-    const bool ok = r < rows;
-    const int64_t off = ((tok + r) * p.H + h) * E + e;
-    const float k2v = ok ? p.k2[off] : 0.f, q2v = ok ? p.q2[off] : 0.f;
-    const float eg = sexp2(gcv);
-    sm.ga[r * ES + e] = k2v * eg;
-    sm.gr[r * ES + e] = k2v * sexp2(gl - gcv);
-    sm.gcq[r * ES + e] = p.scale * q2v * eg;
-  }
+  const int tl = min(t, rows - 1);                   // clamped token row of this thread
   // this thread's row data: K rows dW and U, Q rows dO; columns vh*64 + wg*32 .. +32 for vh = 0, 1 (packed bf16 pairs)
   uint32_t xw[2][16], uw[2][16];
+  {
+    const __nv_bfloat16* xsrc = (krow ? p.dV : p.dO) + ((tok + tl) * p.H + h) * HEAD + wg * 32;
+    const __nv_bfloat16* usrc = p.U + (item * 64 + t) * HEAD + wg * 32;
 #pragma unroll
-  for (int vh = 0; vh < 2; ++vh) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) { xw[vh][j] = 0u; uw[vh][j] = 0u; }
-    const int c0 = vh * 64 + wg * 32;
-    if (krow && worker) {
-      const uint4* up = reinterpret_cast<const uint4*>(p.U + (item * 64 + t) * HEAD + c0);
+    for (int vh = 0; vh < 2; ++vh) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint4 u = __ldg(up + j);
+        const uint4 x = __ldg(reinterpret_cast<const uint4*>(xsrc + vh * 64) + j);
+        xw[vh][4 * j] = x.x; xw[vh][4 * j + 1] = x.y; xw[vh][4 * j + 2] = x.z; xw[vh][4 * j + 3] = x.w;
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(usrc + vh * 64) + j);
         uw[vh][4 * j] = u.x; uw[vh][4 * j + 1] = u.y; uw[vh][4 * j + 2] = u.z; uw[vh][4 * j + 3] = u.w;
       }
     }
-    if (t < rows && worker) {
-      const __nv_bfloat16* src = (krow ? p.dV : p.dO) + ((tok + t) * p.H + h) * HEAD + c0;
-      const uint4* xp = reinterpret_cast<const uint4*>(src);
+  }
+  // gate tables: raw inputs first, arithmetic after
+  constexpr int GATE_ITERS = (64 * E + SG_THREADS - 1) / SG_THREADS;
+  float raw_gc[GATE_ITERS], raw_gl[GATE_ITERS], raw_k2[GATE_ITERS], raw_q2[GATE_ITERS];
+  {
+    const float* gcp = p.gc + item * (64 * E);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 u = __ldg(xp + j);
-        xw[vh][4 * j] = u.x; xw[vh][4 * j + 1] = u.y; xw[vh][4 * j + 2] = u.z; xw[vh][4 * j + 3] = u.w;
-      }
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = min(tid + it * SG_THREADS, 64 * E - 1);
+      const int r = idx / E, e = idx % E;
+      const int64_t off = ((tok + min(r, rows - 1)) * p.H + h) * E + e;
+      raw_gc[it] = __ldg(gcp + idx);
+      raw_gl[it] = __ldg(gcp + 63 * E + e);
+      raw_k2[it] = __ldg(p.k2 + off);
+      raw_q2[it] = __ldg(p.q2 + off);
     }
+  }
+#pragma unroll
+  for (int it = 0; it < GATE_ITERS; ++it) {
+    const int idx = tid + it * SG_THREADS;
+    if (idx < 64 * E && worker) {
+      const int r = idx / E, e = idx % E;
+      const bool ok = r < rows;
+      const float gcv = raw_gc[it] * LOG2E, gl = raw_gl[it] * LOG2E;
+      const float k2v = ok ? raw_k2[it] : 0.f, q2v = ok ? raw_q2[it] : 0.f;
+      const float eg = sexp2(gcv);
+      sm.ga[r * ES + e] = k2v * eg;
+      sm.gr[r * ES + e] = k2v * sexp2(gl - gcv);
+      sm.gcq[r * ES + e] = p.scale * q2v * eg;
+    }
+  }
+  if (t >= rows) {                                   // token rows past the end of a ragged chunk contribute nothing
+#pragma unroll
+    for (int vh = 0; vh < 2; ++vh)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) xw[vh][j] = 0u;
+  }
+  if (!krow) {
+#pragma unroll
+    for (int vh = 0; vh < 2; ++vh)
+#pragma unroll
+      for (int j = 0; j < 16; ++j) uw[vh][j] = 0u;
   }
   __syncthreads();
   mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);
 
-  // Software pipeline over the 2E half-slice steps s = 2e + vh.  In iteration s: the MMAs of step s are issued; while they
-  // run, the row sums of step s-1 are taken from its (double-buffered) R tile, the operands of step s+1 are built in the
-  // other operand buffer, and <h,G> of step s is accumulated from shared memory.
+  // Pipeline over the 2E half-slice steps s = 2e + vh.  The MMA warp keeps the tensor core fed: the MMAs of step s go out
+  // as soon as their operands and half-slices are there.  The workers accumulate <h,G> of step s from shared memory while
+  // its MMAs run; once those are complete they take the row sums from the (double-buffered) R tile and build the operands
+  // of step s+2 in the buffer that just became free.  The load warp refills a stage when both of its readers are done.
   auto build = [&](int e, auto vh_tag) {                 // operands of step (e, vh) into buffer vh
     constexpr int vh = decltype(vh_tag)::value;
-    const float fx = krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e];
-    const float fu = sm.gr[t * ES + e];
+    // gate factors rounded to bf16 once, then one packed multiply per pair of elements
+    const __nv_bfloat162 fx = __float2bfloat162_rn(krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e]);
+    const __nv_bfloat162 fu = __float2bfloat162_rn(sm.gr[t * ES + e]);
+    auto scaled = [](__nv_bfloat162 f, uint32_t x) {
+      const __nv_bfloat162 y = __hmul2(f, *reinterpret_cast<const __nv_bfloat162*>(&x));
+      return *reinterpret_cast<const uint32_t*>(&y);
+    };
     const uint32_t xbase = smem_u32(sm.xa[vh]) + (row >> 3) * 128 + (row & 7) * 16 + (wg * 4) * 2048;
     const uint32_t vbase = smem_u32(sm.va[vh]) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
 #pragma unroll
@@ -160,21 +196,19 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       uint32_t o[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const uint32_t x = xw[vh][4 * j + w];
-        o[w] = pack_bf16(fx * bf16_lo(x), fx * bf16_hi(x));
+        o[w] = scaled(fx, xw[vh][4 * j + w]);
       }
       st_shared_v4(xbase + j * 2048, o[0], o[1], o[2], o[3]);
       if (krow) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          const uint32_t x = uw[vh][4 * j + w];
-          o[w] = pack_bf16(fu * bf16_lo(x), fu * bf16_hi(x));
+          o[w] = scaled(fu, uw[vh][4 * j + w]);
         }
         st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
       }
     }
   };
-  auto issue_mma = [&](int s, int vh) {                  // thread 0
+  auto issue_mma = [&](int s, int vh) {                  // one lane of the issuing warp
     const int st = s % 3;
     tc_fence_after();
     const uint64_t dxa = make_desc(smem_u32(sm.xa[vh]), 2048, 128, LAYOUT_PLAIN);
@@ -232,73 +266,90 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   using V0 = std::integral_constant<int, 0>;
   using V1 = std::integral_constant<int, 1>;
 
-  if (worker) build(0, V0{});
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  float rowsum = 0.f;
-  for (int e = 0; e < E; ++e) {
-    float dot = 0.f;
-    // ---- step s = 2e (vh = 0) ----
-    {
-      const int s = 2 * e;
-      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (issuer) {
-        issue_mma(s, 0);
-        if (e > 0) {                                     // stage (s+2)%3 = (s-1)%3 is free once the MMAs of step s-1 are done
-          mbar_wait(&sm.bar_mma[1], ((s - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
-          if (s + 2 < STEPS) issue_step(s + 2);
-        } else if (STEPS > 2) {
-          issue_step(2);
-        }
-      }
-      if (worker) {
-        if (e > 0) {
-          row_sums(s - 1, V1{}, rowsum);                 // finishes slice e-1
-          sm.part[(wg * 128 + row) * ES + e - 1] = krow ? -rowsum : rowsum;
-          rowsum = 0.f;
-        }
-        build(e, V1{});
-        dot_half(s, dot);
-      }
+  // The issuing warp and the workers run decoupled, coupled only by mbarriers:
+  //   bar_built[vh]  workers -> issuer   operands of a step are in buffer vh (and the previous R tile of that parity is read)
+  //   bar_mma[vh]    tensor core -> all  MMAs of a step complete: R tile ready, operand buffer vh reusable
+  //   bar_load[st]   TMA -> all          half-slices of a step landed in stage st
+  //   bar_read[st]   workers -> issuer   <h,G> of a step taken, stage st may be refilled
+  if (worker) {
+    build(0, V0{});
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm.bar_built[0]);
+    if (STEPS > 1) {
+      build(0, V1{});
       fence_async_smem();
-      tc_fence_before();
-      __syncthreads();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.bar_built[1]);
     }
-    // ---- step s = 2e + 1 (vh = 1) ----
-    {
-      const int s = 2 * e + 1;
-      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (issuer) {
-        issue_mma(s, 1);
-        mbar_wait(&sm.bar_mma[0], ((s - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
-        if (s + 2 < STEPS) issue_step(s + 2);
+    float rowsum = 0.f, dot = 0.f;
+#pragma unroll 1
+    for (int e = 0; e < E; ++e) {
+      // ---- step s = 2e (vh = 0) ----
+      {
+        const int s = 2 * e;
+        mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+        dot_half(s, dot);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.bar_read[s % 3]);
+        row_sums(s, V0{}, rowsum);
+        if (e + 1 < E) {
+          build(e + 1, V0{});
+          fence_async_smem();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (e + 1 < E && lane == 0) mbar_arrive(&sm.bar_built[0]);
       }
-      if (worker) {
-        row_sums(s - 1, V0{}, rowsum);
-        if (e + 1 < E) build(e + 1, V0{});
+      // ---- step s = 2e + 1 (vh = 1) ----
+      {
+        const int s = 2 * e + 1;
+        mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
         dot_half(s, dot);
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (lane == 0) sm.red[warp] = dot;
-      }
-      fence_async_smem();
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        float total = 0.f;
-#pragma unroll
-        for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[w];
-        p.dd[item * E + e] = total;
+        if (lane == 0) {
+          sm.red[e * (SG_THREADS / 32) + warp] = dot;
+          mbar_arrive(&sm.bar_read[s % 3]);
+        }
+        dot = 0.f;
+        row_sums(s, V1{}, rowsum);
+        sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
+        rowsum = 0.f;
+        if (e + 1 < E) {
+          build(e + 1, V1{});
+          fence_async_smem();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (e + 1 < E && lane == 0) mbar_arrive(&sm.bar_built[1]);
       }
     }
-  }
-  if (worker) {
-    row_sums(STEPS - 1, V1{}, rowsum);
-    sm.part[(wg * 128 + row) * ES + E - 1] = krow ? -rowsum : rowsum;
-  } else {
-    mbar_wait(&sm.bar_mma[1], ((STEPS - 1) >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+  } else if (warp_u == SG_THREADS / 32) {                // MMA issue
+#pragma unroll 1
+    for (int s = 0; s < STEPS; ++s) {
+      const int vh = s & 1;
+      mbar_wait(&sm.bar_built[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+      tc_fence_after();
+      if (elect_one()) issue_mma(s, vh);
+      __syncwarp();
+    }
+  } else {                                               // bulk loads: step s+3 goes into the stage step s has released
+#pragma unroll 1
+    for (int s = 0; s + 3 < STEPS; ++s) {
+      mbar_wait(&sm.bar_mma[s & 1], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+      mbar_wait(&sm.bar_read[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (elect_one()) issue_step(s + 3);
+      __syncwarp();
+    }
   }
   __syncthreads();
+  if (tid < E) {                                       // <h_e, G_e>: the eight warps' partial sums in a fixed order
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[tid * (SG_THREADS / 32) + w];
+    p.dd[item * E + tid] = total;
+  }
   // row sums: add the two column halves
   for (int idx = tid; idx < 128 * E && worker; idx += SG_THREADS) {
     const int r = idx / E, e = idx % E;
@@ -309,13 +360,13 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   tc_fence_after();
   float* outp = p.dkq + (item * 128 + row) * HEAD + wg * 64;
 #pragma unroll
-  for (int c0 = 0; c0 < 64 && worker; c0 += 16) {
-    float a[16], a2[16];
-    tmem_ld<16>(tmem_row + wg * 64 + c0, a);
-    tmem_ld<16>(tmem_row + 128 + wg * 64 + c0, a2);
+  for (int c0 = 0; c0 < 64 && worker; c0 += 32) {
+    float a[32], a2[32];
+    tmem_ld<32>(tmem_row + wg * 64 + c0, a);
+    tmem_ld<32>(tmem_row + 128 + wg * 64 + c0, a2);
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 16; j += 4) {
+    for (int j = 0; j < 32; j += 4) {
       float4 v4;
       v4.x = a[j] + (krow ? a2[j] : 0.f);
       v4.y = a[j + 1] + (krow ? a2[j + 1] : 0.f);
