@@ -93,6 +93,15 @@ int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed) {
   return 0;
 }
 
+// Number of SMs of the current device.  With one resident CTA per SM and blocks dispatched in index order, block
+// i + count starts about when block i ends, which is what the per-item kernels use to warm L2 for their successor.
+int tgdn_sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return n;
+}
+
 int tgdn_value_block(int E) { return E >= 8 ? 16 : 32; }   // must match the dispatch in tgdn_bwd_rec.cu
 
 extern "C" const char* tgdn_error_string(int code) {

@@ -230,10 +230,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       umma_bf16(tmem + 256 + vh * 64, desc_advance(dkq, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dhm, kk * 256), id_r, kk > 0);
     umma_commit(&sm.bar_mma[vh]);
   };
-  auto row_sums = [&](int s, auto vh_tag, float& rowsum) {   // R tile of step s (its MMAs waited for here)
+  auto row_sums = [&](auto vh_tag, float& rowsum) {         // R tile of a step whose MMAs are complete
     constexpr int vh = decltype(vh_tag)::value;
-    mbar_wait_spin(&sm.bar_mma[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
-    tc_fence_after();
     float rr[32];
     tmem_ld<32>(tmem_row + 256 + vh * 64 + wg * 32, rr);
     tmem_wait_ld();
@@ -270,7 +268,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   //   bar_built[vh]  workers -> issuer   operands of a step are in buffer vh (and the previous R tile of that parity is read)
   //   bar_mma[vh]    tensor core -> all  MMAs of a step complete: R tile ready, operand buffer vh reusable
   //   bar_load[st]   TMA -> all          half-slices of a step landed in stage st
-  //   bar_read[st]   workers -> issuer   <h,G> of a step taken, stage st may be refilled
+  //   bar_read[st]   workers -> loads    <h,G> of a step taken and its MMAs seen complete: stage st may be refilled
   if (worker) {
     build(0, V0{});
     fence_async_smem();
@@ -290,9 +288,11 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
         const int s = 2 * e;
         mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
         dot_half(s, dot);
+        mbar_wait(&sm.bar_mma[0], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+        tc_fence_after();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.bar_read[s % 3]);
-        row_sums(s, V0{}, rowsum);
+        if (lane == 0) mbar_arrive(&sm.bar_read[s % 3]);   // this warp is done with the stage, and so is the tensor core
+        row_sums(V0{}, rowsum);
         if (e + 1 < E) {
           build(e + 1, V0{});
           fence_async_smem();
@@ -307,12 +307,15 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
         mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
         dot_half(s, dot);
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        mbar_wait(&sm.bar_mma[1], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+        __syncwarp();
         if (lane == 0) {
           sm.red[e * (SG_THREADS / 32) + warp] = dot;
           mbar_arrive(&sm.bar_read[s % 3]);
         }
         dot = 0.f;
-        row_sums(s, V1{}, rowsum);
+        row_sums(V1{}, rowsum);
         sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
         rowsum = 0.f;
         if (e + 1 < E) {
@@ -335,13 +338,48 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       __syncwarp();
     }
   } else {                                               // bulk loads: step s+3 goes into the stage step s has released
+    // Late in this block's life, pull the inputs of the block that will follow it on some SM into L2: its prologue then
+    // waits for L2 instead of for an HBM system that the streaming of all the other blocks keeps saturated.
+    auto warm_successor = [&]() {
+      const int64_t item2 = item + p.ahead;
+      if (p.ahead <= 0 || item2 >= static_cast<int64_t>(gridDim.x)) return;
+      const int h2 = static_cast<int>(item2 % p.H), n2 = static_cast<int>((item2 / p.H) % p.NC);
+      const int b2 = static_cast<int>(item2 / (static_cast<int64_t>(p.H) * p.NC));
+      int t2 = n2 * CHUNK, rows2 = CHUNK;
+      if (p.cmap != nullptr) { t2 = p.cmap[n2]; rows2 = p.cmap[p.NC + n2]; }
+      if (rows2 <= 0 || rows2 > CHUNK || t2 < 0 || t2 + rows2 > p.T) return;
+      if (lane == 0) {
+        tma_prefetch_4d(&map_k, 0, h2, t2, b2);
+        tma_prefetch_4d(&map_q, 0, h2, t2, b2);
+        tma_prefetch_4d(&map_k, 64, h2, t2, b2);
+        tma_prefetch_4d(&map_q, 64, h2, t2, b2);
+        const int64_t slice = static_cast<int64_t>(E) * 32768;
+        const uint32_t lead = static_cast<uint32_t>(min(3, STEPS)) * 16384u;
+        bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + item2 * slice, lead);
+        bulk_prefetch(reinterpret_cast<const uint8_t*>(p.ds) + item2 * slice, lead);
+        bulk_prefetch(p.U + item2 * (64 * HEAD), 64 * HEAD * 2);
+        bulk_prefetch(p.gc + item2 * (64 * E), 64 * E * 4);
+      }
+      const int64_t tok2 = static_cast<int64_t>(b2) * p.T + t2;
+      for (int r = lane; r < rows2; r += 32) {
+        const int64_t ro = (tok2 + r) * p.H + h2;
+        prefetch_l2(p.dV + ro * HEAD);
+        prefetch_l2(p.dV + ro * HEAD + 64);
+        prefetch_l2(p.dO + ro * HEAD);
+        prefetch_l2(p.dO + ro * HEAD + 64);
+        prefetch_l2(p.k2 + ro * E);
+        prefetch_l2(p.q2 + ro * E);
+      }
+    };
+    // A worker warp releases a stage only after it has seen the MMAs of that step complete, so bar_read alone says that
+    // both readers of the stage are done; this warp never waits on bar_mma, whose phases it could fall behind.
 #pragma unroll 1
     for (int s = 0; s + 3 < STEPS; ++s) {
-      mbar_wait(&sm.bar_mma[s & 1], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
       mbar_wait(&sm.bar_read[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
       if (elect_one()) issue_step(s + 3);
       __syncwarp();
     }
+    warm_successor();                                    // nothing left to wait for: about three steps and the epilogue remain
   }
   __syncthreads();
   if (tid < E) {                                       // <h_e, G_e>: the eight warps' partial sums in a fixed order
@@ -409,7 +447,7 @@ extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO
   SgParams p{static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
              static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(h),
              static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, dkq, da, dc, dd, chunk_map, B, T, H, NC, scale,
-             tgdn_status_word()};
+             tgdn_status_word(), tgdn_sm_count()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
     case 1: return launch_sg<1>(mk, mq, p, s);

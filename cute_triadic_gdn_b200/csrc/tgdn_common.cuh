@@ -127,6 +127,7 @@ __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, 
 __device__ __forceinline__ void bulk_prefetch(const void* src, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // Generic-proxy writes to shared memory -> visible to the async proxy (tcgen05.mma operands, bulk stores).
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

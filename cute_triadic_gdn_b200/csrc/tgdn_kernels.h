@@ -84,6 +84,7 @@ struct SgParams {
   int B, T, H, NC;
   float scale;
   int* status;
+  int ahead;                // block index distance to the block whose inputs this one pulls into L2 (0: none)
 };
 
 struct MatParams {
@@ -115,3 +116,4 @@ struct MatParams {
 int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed);
 // Width of the value-axis block one CTA of the recurrences owns, by E.
 int tgdn_value_block(int E);
+int tgdn_sm_count();
