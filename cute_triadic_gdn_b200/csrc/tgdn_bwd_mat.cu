@@ -119,20 +119,49 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     bulk_load(sm.ap, p.AP + item * (128 * 64), 16384, &sm.bar_load);
   }
-  // gates (log2 domain), rows past the document end: k2 = q2 = beta = 0; dr summed over the value blocks
+  // Every global value this thread needs later is requested here, in one batch, from clamped (always valid) addresses,
+  // and masked when it is used: a load that waits until its consumer is reached costs a full memory round trip, which
+  // under the streaming load of the other blocks is microseconds.
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
-    const int rr = idx / E, e = idx % E;
-    const bool ok = rr < rows;
-    const int64_t off = ((tok + rr) * p.H + h) * E + e;
-    sm.gc2[rr * ES + e] = p.gc[item * (64 * E) + idx] * LOG2E;
-    sm.k2[rr * ES + e] = ok ? p.k2[off] : 0.f;
-    sm.q2[rr * ES + e] = ok ? p.q2[off] : 0.f;
-    float drv = 0.f;
-    for (int v = 0; v < p.NV; ++v) drv += p.dr[((item * p.NV + v) * 64 + rr) * E + e];
-    sm.drr[rr * ES + e] = drv;
+  constexpr int GATE_ITERS = (64 * E + MAT_THREADS - 1) / MAT_THREADS;
+  constexpr int NV_MAX = 8;                                // value blocks of the reverse recurrence (4 or 8)
+  float da_in[GATE_ITERS], dc_in[GATE_ITERS];              // row-sum gradients of the state-gradient kernel, used at the end
+  prefetch_l2(p.dkq + (item * 128 + r) * HEAD + cq * 32);  // this thread's 128 bytes of the state part, read last
+  const float dd_in = __ldg(p.dd + item * E + min(tid, E - 1));
+  const float beta_in = __ldg(p.beta + (tok + min(tid & 63, rows - 1)) * p.H + h);
+  {
+    float gc_in[GATE_ITERS], k2_in[GATE_ITERS], q2_in[GATE_ITERS], dr_in[GATE_ITERS][NV_MAX];
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = min(tid + it * MAT_THREADS, 64 * E - 1);
+      const int rr = idx / E, e = idx % E;
+      const int64_t off = ((tok + min(rr, rows - 1)) * p.H + h) * E + e;
+      gc_in[it] = __ldg(p.gc + item * (64 * E) + idx);
+      k2_in[it] = __ldg(p.k2 + off);
+      q2_in[it] = __ldg(p.q2 + off);
+      da_in[it] = __ldg(p.da + item * (64 * E) + idx);
+      dc_in[it] = __ldg(p.dc + item * (64 * E) + idx);
+#pragma unroll
+      for (int v = 0; v < NV_MAX; ++v)
+        dr_in[it][v] = __ldg(p.dr + ((item * p.NV + min(v, p.NV - 1)) * 64 + rr) * E + e);
+    }
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * MAT_THREADS;
+      if (idx < 64 * E) {
+        const int rr = idx / E, e = idx % E;
+        const bool ok = rr < rows;
+        sm.gc2[rr * ES + e] = gc_in[it] * LOG2E;
+        sm.k2[rr * ES + e] = ok ? k2_in[it] : 0.f;
+        sm.q2[rr * ES + e] = ok ? q2_in[it] : 0.f;
+        float drv = 0.f;                                   // summed over the value blocks in index order
+#pragma unroll
+        for (int v = 0; v < NV_MAX; ++v) drv += (v < p.NV) ? dr_in[it][v] : 0.f;
+        sm.drr[rr * ES + e] = drv;
+      }
+    }
   }
-  if (tid < 64) sm.beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
+  if (tid < 64) sm.beta[tid] = (tid < rows) ? beta_in : 0.f;
   __syncthreads();
 
   // ---- G1, G2 ----------------------------------------------------------------------------------------------------
@@ -379,31 +408,42 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   __syncthreads();
   // gate gradients: one thread per (row, gate column)
-  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
-    const int rr = idx / E, e = idx % E, o = rr * ES + e;
-    const float c2e = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
-    const float gcv = sm.gc2[o], gl = sm.gc2[63 * ES + e];
-    const float eg = mexp2(gcv), egr = mexp2(gl - gcv);
-    const float k2v = sm.k2[o], q2v = sm.q2[o];
-    const float dav = p.da[(item * 64 + rr) * E + e], dcv = p.dc[(item * 64 + rr) * E + e];
-    const float drv = sm.drr[o], r1e = sm.r1[o], c1e = sm.c1[o], r2e = sm.r2[o];
-    if (rr < rows) {
-      const int64_t off = ((tok + rr) * p.H + h) * E + e;
-      p.dk2[off] = dav * eg + drv * egr + c1e + r2e + c2e;
-      p.dq2[off] = dcv * p.scale * eg + r1e;
+#pragma unroll
+  for (int it = 0; it < GATE_ITERS; ++it) {
+    const int idx = tid + it * MAT_THREADS;
+    if (idx < 64 * E) {
+      const int rr = idx / E, e = idx % E, o = rr * ES + e;
+      const float c2e = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
+      const float gcv = sm.gc2[o], gl = sm.gc2[63 * ES + e];
+      const float eg = mexp2(gcv), egr = mexp2(gl - gcv);
+      const float k2v = sm.k2[o], q2v = sm.q2[o];
+      const float dav = da_in[it], dcv = dc_in[it];
+      const float drv = sm.drr[o], r1e = sm.r1[o], c1e = sm.c1[o], r2e = sm.r2[o];
+      if (rr < rows) {
+        const int64_t off = ((tok + rr) * p.H + h) * E + e;
+        p.dk2[off] = dav * eg + drv * egr + c1e + r2e + c2e;
+        p.dq2[off] = dcv * p.scale * eg + r1e;
+      }
+      sm.dgc[o] = dav * (k2v * eg) + dcv * (p.scale * q2v * eg) - drv * (k2v * egr) + q2v * r1e + k2v * (r2e - c1e - c2e);
+      sm.drr[o] = drv * (k2v * egr);                        // dr*r, summed over the rows below
     }
-    sm.dgc[o] = dav * (k2v * eg) + dcv * (p.scale * q2v * eg) - drv * (k2v * egr) + q2v * r1e + k2v * (r2e - c1e - c2e);
-    sm.drr[o] = drv * (k2v * egr);                          // dr*r, summed over the rows below
   }
   if (tid < 64 && tid < rows) p.dbeta[(tok + tid) * p.H + h] = sm.bcol[tid] + sm.brow[tid];
   __syncthreads();
   if (tid < E) {                                            // chunk-end terms: sum_t dr*r + dd*exp(gL)
     float acc = 0.f;
     for (int tt = 0; tt < 64; ++tt) acc += sm.drr[tt * ES + tid];
-    acc += p.dd[item * E + tid] * mexp2(sm.gc2[63 * ES + tid]);
+    acc += dd_in * mexp2(sm.gc2[63 * ES + tid]);
     sm.dgc[63 * ES + tid] += acc;
   }
   __syncthreads();
+  // state part of dk, dq (this thread's row, 32 columns): all eight loads in flight before the scan and the last MMA wait
+  float4 x[8];
+  {
+    const float4* sp = reinterpret_cast<const float4*>(p.dkq + (item * 128 + r) * HEAD + cq * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __ldg(sp + j);
+  }
   // dg = reverse inclusive cumulative sum of dgc over the chunk, one warp per gate column
   for (int e = warp; e < E; e += MAT_THREADS / 32) {
     float v1 = sm.dgc[(63 - lane) * ES + e], v0 = sm.dgc[(31 - lane) * ES + e];      // lane l: rows 63-l and 31-l
@@ -423,25 +463,21 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   ++mma_phase;
   tc_fence_after();
   {
-    const float* sp = p.dkq + (item * 128 + r) * HEAD + cq * 32;
     __nv_bfloat16* outp = (krow ? p.dk : p.dq) + ((tok + t) * p.H + h) * HEAD + cq * 32;
     const bool live = t < rows;
+    float a[32];
+    tmem_ld<32>(tmem_row + cq * 32, a);
+    tmem_wait_ld();
+    if (live) {
 #pragma unroll
-    for (int c0 = 0; c0 < 32; c0 += 16) {
-      float a[16];
-      tmem_ld<16>(tmem_row + cq * 32 + c0, a);
-      tmem_wait_ld();
-      if (live) {
-#pragma unroll
-        for (int j = 0; j < 16; j += 8) {
-          const float4 x0 = *reinterpret_cast<const float4*>(sp + c0 + j), x1 = *reinterpret_cast<const float4*>(sp + c0 + j + 4);
-          uint4 u;
-          u.x = pack_bf16(a[j] + x0.x, a[j + 1] + x0.y);
-          u.y = pack_bf16(a[j + 2] + x0.z, a[j + 3] + x0.w);
-          u.z = pack_bf16(a[j + 4] + x1.x, a[j + 5] + x1.y);
-          u.w = pack_bf16(a[j + 6] + x1.z, a[j + 7] + x1.w);
-          *reinterpret_cast<uint4*>(outp + c0 + j) = u;
-        }
+      for (int j = 0; j < 32; j += 8) {
+        const float4 x0 = x[j / 4], x1 = x[j / 4 + 1];
+        uint4 u;
+        u.x = pack_bf16(a[j] + x0.x, a[j + 1] + x0.y);
+        u.y = pack_bf16(a[j + 2] + x0.z, a[j + 3] + x0.w);
+        u.z = pack_bf16(a[j + 4] + x1.x, a[j + 5] + x1.y);
+        u.w = pack_bf16(a[j + 6] + x1.z, a[j + 7] + x1.w);
+        *reinterpret_cast<uint4*>(outp + j) = u;
       }
     }
   }
