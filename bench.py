@@ -298,14 +298,17 @@ def run_ours(args, rank, world, local_rank):
 
 
 def run_conv(args):
-    """Secondary workload: the convolution pre-pass at (1, 32768, 13056), HBM roofline."""
+    """Secondary workload: the convolution pre-pass at (1, T, 13056), T = 32768 unless --tokens says otherwise; HBM roofline."""
     from cute_triadic_gdn_b200 import conv_split_act_call
     dev = torch.device("cuda", 0)
-    T, C, act = 32768, 13056, 12288
+    T, C, act = (args.tokens or 32768), 13056, 12288
+    if T % 4096:
+        raise SystemExit("--tokens must be a multiple of 4096 (documents of 4096 tokens)")
     x = torch.randn(1, T, C, device=dev).to(torch.bfloat16).requires_grad_(True)
     w = (0.5 * torch.randn(C, 4, device=dev)).to(torch.bfloat16).requires_grad_(True)
     dy = torch.randn(1, T, C, device=dev).to(torch.bfloat16)
     cu = torch.arange(0, T + 1, 4096, device=dev, dtype=torch.int32)
+    n_docs = T // 4096
 
     def ev_time(fn, n):
         for _ in range(3):
@@ -328,7 +331,7 @@ def run_conv(args):
     fb, bb = 4 * T * C, 6 * T * C
     line = {"metric": "conv_split_act GB/s", "value": fb / (fwd_ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": 1,
             "steps": args.steps, "warmup": 3, "ms_per_step": fwd_ms, "higher_is_better": True, "dtype": "bf16",
-            "data": "synthetic", "config": {"workload": f"conv (1,{T},{C}) act={act}, 8 documents"},
+            "data": "synthetic", "config": {"workload": f"conv (1,{T},{C}) act={act}, {n_docs} documents"},
             "roofline": {"bound": "hbm", "kernel": "conv_fwd", "achieved": fb / (fwd_ms * 1e-3) / 1e9, "peak": pk["gbs"],
                          "unit": "GB/s", "frac": fb / (fwd_ms * 1e-3) / 1e9 / pk["gbs"], "traffic": None,
                          "peak_kind": pk["kind"]},
@@ -343,6 +346,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=list(WORKLOADS) + ["conv"])
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="conv workload only: sequence length (multiple of 4096; default 32768); small values size a profiler capture")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, per-kernel and CPU-baseline legs (used for profiler captures)")
     args = ap.parse_args()
