@@ -62,8 +62,6 @@ struct MatSmem {
   int abort;
 };
 
-__device__ long long g_phase[24];
-#define PST(k) do { if (tid == 0 && blockIdx.x == 300) { g_phase[k] = clock64() - tstart; } } while (0)
 template <int E>
 __global__ void __launch_bounds__(MAT_THREADS, 1)
 mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
@@ -74,7 +72,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int ES = SM::ES;
   constexpr float LOG2E = 1.4426950408889634f;
-  const long long tstart = clock64();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cq = warp >> 2;                                // column quarter
   const int r = (warp & 3) * 32 + lane;                    // tensor-memory lane = matrix row
@@ -103,7 +100,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
-  PST(0);
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -167,11 +163,9 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (tid < 64) sm.beta[tid] = (tid < rows) ? beta_in : 0.f;
   __syncthreads();
-  PST(1);
 
   // ---- G1, G2 ----------------------------------------------------------------------------------------------------
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
-  PST(2);
   if (tid == 0) {
     tc_fence_after();
     const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
@@ -192,7 +186,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   uint32_t mma_phase = 0;
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  PST(3);
   ++mma_phase;
   tc_fence_after();
   float pr[16];                                            // Pkk (key rows) / Pqk (query rows), this thread's 16 columns
@@ -202,7 +195,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tmem_wait_ld();
   tc_fence_before();
   __syncthreads();                                         // dudo and wu are dead: a5, dmp, dm take their place
-  PST(4);
 
   float my2[E], mygc[E];
 #pragma unroll
@@ -273,7 +265,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  PST(5);
 
   // ---- G3: Y = A^T dA ----------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -297,7 +288,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     sm.bcol[s] = acc;
   }
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  PST(6);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
@@ -313,7 +303,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  PST(7);
 
   // ---- G4: dp = Y A^T ----------------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -341,7 +330,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
   }
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  PST(8);
   ++mma_phase;
   tc_fence_after();
   if (krow) {
@@ -385,7 +373,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  PST(9);
 
   // ---- G5: [dK;dQ] = a5 [K;Q] --------------------------------------------------------------------------------------
   if (tid == 0) {
@@ -405,7 +392,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (tid < 64) sm.brow[tid] = (sm.browp[0][tid] + sm.browp[1][tid]) + (sm.browp[2][tid] + sm.browp[3][tid]);
   __syncthreads();
-  PST(10);
   if (krow) {
     // key thread (s = t, cq): partial c2[s,e] over t' in quarter cq, t' > s: dm[t',s] exp(gc[t']-gc[s]) k2[t',e]
     float c2v[E];
@@ -421,7 +407,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = c2v[e];
   }
   __syncthreads();
-  PST(11);
   // gate gradients: one thread per (row, gate column)
 #pragma unroll
   for (int it = 0; it < GATE_ITERS; ++it) {
@@ -445,7 +430,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (tid < 64 && tid < rows) p.dbeta[(tok + tid) * p.H + h] = sm.bcol[tid] + sm.brow[tid];
   __syncthreads();
-  PST(12);
   if (tid < E) {                                            // chunk-end terms: sum_t dr*r + dd*exp(gL)
     float acc = 0.f;
     for (int tt = 0; tt < 64; ++tt) acc += sm.drr[tt * ES + tid];
@@ -453,7 +437,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     sm.dgc[63 * ES + tid] += acc;
   }
   __syncthreads();
-  PST(13);
   // state part of dk, dq (this thread's row, 32 columns): all eight loads in flight before the scan and the last MMA wait
   float4 x[8];
   {
@@ -477,7 +460,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
   // ---- dk, dq: this thread's row, 32 of the 128 columns ------------------------------------------------------------
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  PST(14);
   ++mma_phase;
   tc_fence_after();
   {
@@ -501,7 +483,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
-  PST(15);
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -518,8 +499,6 @@ static int launch_mat(const CUtensorMap* maps, const MatParams& p, cudaStream_t 
   mat_kernel<E><<<p.B * p.NC * p.H, MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
   return tgdn_cuda_error(cudaGetLastError());
 }
-
-extern "C" int tgdn_debug_phase(long long* out, int reset) { return (int)cudaMemcpyFromSymbol(out, tgdn::g_phase, 24 * sizeof(long long)); }
 
 extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, const void* dU, const void* W, const void* U,
                                const void* AP, const float* k2, const float* q2, const float* beta, const float* gc,
