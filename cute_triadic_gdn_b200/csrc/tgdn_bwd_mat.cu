@@ -101,12 +101,13 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&sm.abort, p.status};
   const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
 
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     mbar_expect_tx(&sm.bar_load, 3 * 32768 + 16384);
     for (int half = 0; half < 2; ++half) {
       const int col = half * 64;
@@ -119,6 +120,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     bulk_load(sm.ap, p.AP + item * (128 * 64), 16384, &sm.bar_load);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   // Every global value this thread needs later is requested here, in one batch, from clamped (always valid) addresses,
   // and masked when it is used: a load that waits until its consumer is reached costs a full memory round trip, which
   // under the streaming load of the other blocks is microseconds.
@@ -126,7 +128,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   constexpr int GATE_ITERS = (64 * E + MAT_THREADS - 1) / MAT_THREADS;
   constexpr int NV_MAX = 8;                                // value blocks of the reverse recurrence (4 or 8)
   float da_in[GATE_ITERS], dc_in[GATE_ITERS];              // row-sum gradients of the state-gradient kernel, used at the end
-  prefetch_l2(p.dkq + (item * 128 + r) * HEAD + cq * 32);  // this thread's 128 bytes of the state part, read last
   const float dd_in = __ldg(p.dd + item * E + min(tid, E - 1));
   const float beta_in = __ldg(p.beta + (tok + min(tid & 63, rows - 1)) * p.H + h);
   {
@@ -166,7 +167,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
   // ---- G1, G2 ----------------------------------------------------------------------------------------------------
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
     const uint64_t dd = make_desc(smem_u32(sm.u1.dudo), 16, 1024, LAYOUT_SW128);
@@ -184,6 +185,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   uint32_t mma_phase = 0;
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
@@ -267,7 +269,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   __syncthreads();
 
   // ---- G3: Y = A^T dA ----------------------------------------------------------------------------------------------
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t da = make_desc(smem_u32(sm.ap), 128, 2048, LAYOUT_PLAIN);     // A^T, MN-major
     const uint64_t db = make_desc(smem_u32(sm.da), 128, 1024, LAYOUT_PLAIN);     // dA (K = t, N = s), MN-major
@@ -276,6 +278,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 192, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   // meanwhile: r1 = sum of the four partials; dbeta_col[s] = sum_t dA'[t,s] A[t,s]
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
     const int o = (idx / E) * ES + idx % E;
@@ -305,7 +308,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   __syncthreads();
 
   // ---- G4: dp = Y A^T ----------------------------------------------------------------------------------------------
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t da = make_desc(smem_u32(sm.y), 1024, 128, LAYOUT_PLAIN);      // Y, K-major
     const uint64_t db = make_desc(smem_u32(sm.ap), 2048, 128, LAYOUT_PLAIN);     // B[k][j] = A[j][k]: A rows as N, K-major
@@ -314,6 +317,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 256, desc_advance(da, kk * 2048), desc_advance(db, kk * 4096), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   if (!krow) {
     // meanwhile, query thread (64+s, cq): partial c1[s,e] over t' in quarter cq: dmp[t',s] exp(gc[t']-gc[s]) q2[t',e]
     const int s = t;
@@ -332,6 +336,13 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
   tc_fence_after();
+  // ap, da, y and daa (48 KB in a row) are dead from here on: the state part of dK, dQ (32 KB bf16 image written by the
+  // state-gradient kernel) is fetched into their place now, so that its HBM round trip runs under the remaining phases.
+  if (warp_u == 0 && elect_one()) {
+    mbar_expect_tx(&sm.bar_load, 32768);
+    bulk_load(sm.ap, reinterpret_cast<const uint8_t*>(p.dkq) + item * 32768, 32768, &sm.bar_load);
+  }
+  __syncwarp();
   if (krow) {
     // key row t, columns s0..s0+15: dL, partial dbeta_row, dm, partial r2, and dPkk + dPkk^T into a5[0..63][0..63]
     float dpr[16];
@@ -375,7 +386,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   __syncthreads();
 
   // ---- G5: [dK;dQ] = a5 [K;Q] --------------------------------------------------------------------------------------
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t da = make_desc(a5, 2048, 128, LAYOUT_PLAIN);
     const uint64_t db = make_desc(smem_u32(sm.kq), 16384, 1024, LAYOUT_SW128);   // (K = token rows, N = d), MN-major
@@ -384,6 +395,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   // sums of the partials written before the barrier
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
     const int o = (idx / E) * ES + idx % E;
@@ -437,13 +449,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     sm.dgc[63 * ES + tid] += acc;
   }
   __syncthreads();
-  // state part of dk, dq (this thread's row, 32 columns): all eight loads in flight before the scan and the last MMA wait
-  float4 x[8];
-  {
-    const float4* sp = reinterpret_cast<const float4*>(p.dkq + (item * 128 + r) * HEAD + cq * 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) x[j] = __ldg(sp + j);
-  }
   // dg = reverse inclusive cumulative sum of dgc over the chunk, one warp per gate column
   for (int e = warp; e < E; e += MAT_THREADS / 32) {
     float v1 = sm.dgc[(63 - lane) * ES + e], v0 = sm.dgc[(31 - lane) * ES + e];      // lane l: rows 63-l and 31-l
@@ -468,15 +473,18 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     float a[32];
     tmem_ld<32>(tmem_row + cq * 32, a);
     tmem_wait_ld();
+    mbar_wait(&sm.bar_load, 1, ctl, DEV_TIMEOUT_LOAD);     // state part: image [column / 8][row][column % 8]
     if (live) {
+      const uint32_t xb = smem_u32(sm.ap) + (cq * 4) * 2048 + r * 16;
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
-        const float4 x0 = x[j / 4], x1 = x[j / 4 + 1];
+        uint32_t x[4];
+        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xb + (j >> 3) * 2048));
         uint4 u;
-        u.x = pack_bf16(a[j] + x0.x, a[j + 1] + x0.y);
-        u.y = pack_bf16(a[j + 2] + x0.z, a[j + 3] + x0.w);
-        u.z = pack_bf16(a[j + 4] + x1.x, a[j + 5] + x1.y);
-        u.w = pack_bf16(a[j + 6] + x1.z, a[j + 7] + x1.w);
+        u.x = pack_bf16(a[j] + bf16_lo(x[0]), a[j + 1] + bf16_hi(x[0]));
+        u.y = pack_bf16(a[j + 2] + bf16_lo(x[1]), a[j + 3] + bf16_hi(x[1]));
+        u.z = pack_bf16(a[j + 4] + bf16_lo(x[2]), a[j + 5] + bf16_hi(x[2]));
+        u.w = pack_bf16(a[j + 6] + bf16_lo(x[3]), a[j + 7] + bf16_hi(x[3]));
         *reinterpret_cast<uint4*>(outp + j) = u;
       }
     }
@@ -502,7 +510,7 @@ static int launch_mat(const CUtensorMap* maps, const MatParams& p, cudaStream_t 
 
 extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, const void* dU, const void* W, const void* U,
                                const void* AP, const float* k2, const float* q2, const float* beta, const float* gc,
-                               const float* dkq, const float* da, const float* dc, const float* dd, const float* dr,
+                               const void* dkq, const float* da, const float* dc, const float* dd, const float* dr,
                                float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dq,
                                void* dk, float* dk2, float* dq2, float* dg, float* dbeta, void* stream) {
   if (!q || !k || !dO || !dU || !W || !U || !AP || !k2 || !q2 || !beta || !gc || !dkq || !da || !dc || !dd || !dr ||
@@ -523,7 +531,7 @@ extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, con
   if ((rc = tgdn_make_token_map(&maps[3], dU, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[4], W, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[5], U, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
-  MatParams p{k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP), dkq, da, dc, dd, dr,
+  MatParams p{k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP), static_cast<const __nv_bfloat16*>(dkq), da, dc, dd, dr,
               static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), dk2, dq2, dg, dbeta, chunk_map,
               B, T, H, NC, 128 / tgdn_value_block(E), scale, tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);

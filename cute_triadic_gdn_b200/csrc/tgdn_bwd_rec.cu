@@ -285,6 +285,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     if (STAGES == 2 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, st ^ 1);
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
@@ -329,6 +330,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem + NCOLS + VC, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     // meanwhile: the value-block partial of dr, summed over the four warpgroups in a fixed order
     for (int idx = tid; idx < 64 * E; idx += REC_THREADS) {
       const int r = idx / E, e = idx % E;
@@ -379,6 +381,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();

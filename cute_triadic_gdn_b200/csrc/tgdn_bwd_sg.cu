@@ -394,9 +394,10 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     const float v = sm.part[r * ES + e] + sm.part[(128 + r) * ES + e];
     if (r < 64) p.da[(item * 64 + r) * E + e] = v; else p.dc[(item * 64 + r - 64) * E + e] = v;
   }
-  // accumulators -> dkq f32: rows 0..63 = ACC + ACC2 (dK), rows 64..127 = ACC (dQ); this thread: 64 columns
+  // accumulators -> dkq, bf16 image [column / 8][row][column % 8]: rows 0..63 = ACC + ACC2 (dK), rows 64..127 = ACC (dQ).
+  // This thread: its row, 64 columns; a warp's 16-byte store covers 32 consecutive rows = 512 contiguous bytes.
   tc_fence_after();
-  float* outp = p.dkq + (item * 128 + row) * HEAD + wg * 64;
+  uint8_t* outp = reinterpret_cast<uint8_t*>(p.dkq) + item * 32768 + row * 16;
 #pragma unroll
   for (int c0 = 0; c0 < 64 && worker; c0 += 32) {
     float a[32], a2[32];
@@ -404,13 +405,13 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     tmem_ld<32>(tmem_row + 128 + wg * 64 + c0, a2);
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      float4 v4;
-      v4.x = a[j] + (krow ? a2[j] : 0.f);
-      v4.y = a[j + 1] + (krow ? a2[j + 1] : 0.f);
-      v4.z = a[j + 2] + (krow ? a2[j + 2] : 0.f);
-      v4.w = a[j + 3] + (krow ? a2[j + 3] : 0.f);
-      *reinterpret_cast<float4*>(outp + c0 + j) = v4;
+    for (int j = 0; j < 32; j += 8) {
+      uint4 u;
+      u.x = pack_bf16(a[j] + (krow ? a2[j] : 0.f), a[j + 1] + (krow ? a2[j + 1] : 0.f));
+      u.y = pack_bf16(a[j + 2] + (krow ? a2[j + 2] : 0.f), a[j + 3] + (krow ? a2[j + 3] : 0.f));
+      u.z = pack_bf16(a[j + 4] + (krow ? a2[j + 4] : 0.f), a[j + 5] + (krow ? a2[j + 5] : 0.f));
+      u.w = pack_bf16(a[j + 6] + (krow ? a2[j + 6] : 0.f), a[j + 7] + (krow ? a2[j + 7] : 0.f));
+      *reinterpret_cast<uint4*>(outp + ((wg * 64 + c0 + j) >> 3) * 2048) = u;
     }
   }
   tc_fence_before();
@@ -433,7 +434,7 @@ static int launch_sg(const CUtensorMap& mk, const CUtensorMap& mq, const SgParam
 
 extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U,
                                     const void* h, const void* ds, const float* k2, const float* q2, const float* gc,
-                                    float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* dkq,
+                                    float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dkq,
                                     float* da, float* dc, float* dd, void* stream) {
   if (!q || !k || !dO || !dV || !U || !h || !ds || !k2 || !q2 || !gc || !dkq || !da || !dc || !dd) return TGDN_ERR_NULL;
   int rc = tgdn_check_core_shape(B, T, H, E, NC, chunk_map != nullptr);
@@ -446,7 +447,8 @@ extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
   SgParams p{static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
              static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(h),
-             static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, dkq, da, dc, dd, chunk_map, B, T, H, NC, scale,
+             static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, static_cast<__nv_bfloat16*>(dkq), da, dc, dd, chunk_map, B, T, H,
+             NC, scale,
              tgdn_status_word(), tgdn_sm_count()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {

@@ -262,6 +262,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     if (warp_u == 1 && i + 1 < count && elect_one()) {
       if (STAGES == 2) issue_loads(i + 1);             // the other stage was released by the previous chunk's (3)
       if (STAGES == 1) prefetch_loads(i + 1);
@@ -339,6 +340,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem + NCOLS, desc_advance(da, kk * 4096), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -391,6 +393,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
       umma_commit(&ctrl.bar_mma);
     }
+    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();

@@ -76,7 +76,7 @@ struct SgParams {
   const float* k2;
   const float* q2;
   const float* gc;
-  float* dkq;               // f32 [item][128][128] (out): rows 0..63 state part of dK, rows 64..127 of dQ
+  __nv_bfloat16* dkq;       // bf16 image [item][col/8][128 rows][col%8] (out): rows 0..63 state part of dK, 64..127 of dQ
   float* da;                // f32 [item][64][E] (out)
   float* dc;                // f32 [item][64][E] (out)
   float* dd;                // f32 [item][E] (out)
@@ -93,7 +93,7 @@ struct MatParams {
   const float* beta;
   const float* gc;
   const __nv_bfloat16* AP;
-  const float* dkq;
+  const __nv_bfloat16* dkq; // bf16 image [item][col/8][128 rows][col%8] from the state-gradient kernel
   const float* da;
   const float* dc;
   const float* dd;

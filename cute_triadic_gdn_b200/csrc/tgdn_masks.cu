@@ -150,14 +150,16 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   WaitCtl ctl{&sm.abort, p.status};
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
 
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     mbar_expect_tx(&sm.bar_load, 32768);
     tma_load_4d(sm.u.kq, &map_k, &sm.bar_load, 0, h, t0, b);
     tma_load_4d(sm.u.kq + 8192, &map_q, &sm.bar_load, 0, h, t0, b);
     tma_load_4d(sm.u.kq + 16384, &map_k, &sm.bar_load, 64, h, t0, b);
     tma_load_4d(sm.u.kq + 24576, &map_q, &sm.bar_load, 64, h, t0, b);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
 
   // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
@@ -190,9 +192,9 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
 
   // Gram product [K;Q] K^T
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
-  const uint32_t tmem = sm.tmem_base;
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t desc = make_desc(smem_u32(sm.u.kq), 16, 1024, LAYOUT_SW128);
     constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
@@ -203,6 +205,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     }
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   mbar_wait_spin(&sm.bar_mma, 0, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
   float pr[32];                                             // this thread's 4 blocks of 8 columns of its row
@@ -303,7 +306,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   __syncthreads();
 
   // PA = Pm A on the tensor core, from the bf16 images
-  if (tid == 0) {
+  if (warp_u == 0 && elect_one()) {
     tc_fence_after();
     const uint64_t da = make_desc(smem_u32(sm.img_pm), 1024, 128, LAYOUT_PLAIN);   // Pm, K-major (rows past 63: don't care)
     const uint64_t db = make_desc(smem_u32(sm.img_ap), 128, 2048, LAYOUT_PLAIN);   // A as (K = s, N = j), MN-major
@@ -312,6 +315,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 64, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
     umma_commit(&sm.bar_mma);
   }
+  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   mbar_wait_spin(&sm.bar_mma, 1, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
   if (r < 64) {                                             // PA row r, columns 32*ch .. +32 -> rows 64.. of the image

@@ -129,7 +129,7 @@ def _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map=None):
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
     alloc = torch.zeros if token_map is not None else torch.empty     # unused map entries stay defined
-    dkq = alloc((B, NC, H, 128, 128), dtype=torch.float32, device=dev)
+    dkq = alloc((B, NC, H, 16, 128, 8), dtype=torch.bfloat16, device=dev)    # image [column / 8][row][column % 8]
     da = alloc((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
     dc = alloc((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
     dd = alloc((B, NC, H, E), dtype=torch.float32, device=dev)

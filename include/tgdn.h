@@ -121,13 +121,13 @@ int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float
                        int NC, void* dV, void* dU, void* ds, float* dr, void* stream);
 
 /* tgdn_bwd_state_grads: per (chunk, head), the gradient terms that contract the saved states h (forward, chunk start)
- * and ds (backward, chunk end) over the value axis.  Writes dkq f32 [item][128][128] (rows 0..63: state part of dK,
- * rows 64..127: of dQ), da, dc f32 [item][64][E] (gradients of the gate tables a = k2 exp(gc), c = scale q2 exp(gc))
+ * and ds (backward, chunk end) over the value axis.  Writes dkq, a bf16 image [item][column / 8][128 rows][column % 8]
+ * (32 KB per item; rows 0..63: state part of dK, rows 64..127: of dQ; 16-byte aligned), da, dc f32 [item][64][E] (gradients of the gate tables a = k2 exp(gc), c = scale q2 exp(gc))
  * and dd f32 [item][E] (gradient of the chunk decay exp(gL)).
  * Replaces: cute_triadic_gdn/kernels/sm100_joint_state_grads.py:480-520 (joint_state_grads_sm100). */
 int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U, const void* h,
                          const void* ds, const float* k2, const float* q2, const float* gc, float scale,
-                         const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* dkq, float* da, float* dc,
+                         const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dkq, float* da, float* dc,
                          float* dd, void* stream);
 
 /* tgdn_bwd_matrix: per (chunk, head), the matrix gradients through the chunk operators, the mask gradients, and the
@@ -137,7 +137,7 @@ int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const voi
  * mask_grad_kernel) and the reverse cute_triadic_gdn/kernels/sm90_joint_scan.py:92-110 (joint_scan(reverse=True)). */
 int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, const void* dU, const void* W, const void* U,
                     const void* AP, const float* k2, const float* q2, const float* beta, const float* gc,
-                    const float* dkq, const float* da, const float* dc, const float* dd, const float* dr, float scale,
+                    const void* dkq, const float* da, const float* dc, const float* dd, const float* dr, float scale,
                     const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dq, void* dk, float* dk2,
                     float* dq2, float* dg, float* dbeta, void* stream);
 

@@ -53,6 +53,8 @@ def test_state_grads_dense(E):
     sg = st["sg"]
     NC = T // 64
     ch = lambda t: t.cpu().permute(0, 2, 1, 3, 4).reshape(B * H, NC, *t.shape[3:])
+    # dkq is a bf16 image [column / 8][row][column % 8] per (batch, chunk, head): back to [row][column]
+    dkq = dkq.float().permute(0, 1, 2, 4, 3, 5).reshape(B, NC, H, 128, 128)
     assert orc.rel_l2(ch(dkq)[:, :, :64], sg["dK"]) < 1e-2
     assert orc.rel_l2(ch(dkq)[:, :, 64:], sg["dQ"]) < 1e-2
     assert orc.rel_l2(ch(da), sg["da"]) < 1e-2
