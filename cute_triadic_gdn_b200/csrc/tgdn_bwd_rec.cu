@@ -51,7 +51,7 @@ struct RecCfg {
   static constexpr int OFF_DU = OFF_DO + ((DO_BYTES + 1023) & ~1023);
   static constexpr int OFF_GATES = OFF_DU + ((DO_BYTES + 1023) & ~1023);
   static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;
-  static constexpr int OFF_DRP = OFF_GATES + GATE_FLOATS * 4;
+  static constexpr int OFF_DRP = OFF_GATES + 2 * GATE_FLOATS * 4;   // two table buffers: next chunk's are built ahead
   static constexpr int DRP_FLOATS = NWG * 64 * ES;
   static constexpr int OFF_PAD = OFF_DRP + DRP_FLOATS * 4;
   static constexpr int PAD = (OFF_PAD - OFF_DO) >= 8192 ? 0 : 8192 - (OFF_PAD - OFF_DO);
@@ -76,11 +76,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* g_a = reinterpret_cast<float*>(smem + C::OFF_GATES);
-  float* g_r = g_a + 64 * ES;
-  float* g_c = g_r + 64 * ES;
-  float* g_beta = g_c + 64 * ES;
-  float* g_d = g_beta + 64;
+  float* gate_buf = reinterpret_cast<float*>(smem + C::OFF_GATES);
   float* drp = reinterpret_cast<float*>(smem + C::OFF_DRP);
   RecCtrl& ctrl = *reinterpret_cast<RecCtrl*>(smem + C::OFF_CTRL);
 
@@ -156,13 +152,31 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
     }
   };
-  // Prefetched inputs of one chunk: this thread's row piece (K-row threads: U, Q-row threads: dO) as raw bf16, and the raw
-  // gate inputs of its (at most two) table entries.  Loads are unconditional from clamped addresses and masked at use.
-  struct ChunkRaw { uint4 rowp; float gcv[2], gl[2], k2v[2], q2v[2], beta; int rows; };
-  constexpr int GATE_ITERS = (64 * E + REC_THREADS - 1) / REC_THREADS;
-  static_assert(GATE_ITERS <= 2, "gate tables: at most two entries per thread");
-  auto load_chunk = [&](int i) {
-    ChunkRaw g;
+  // Prefetched inputs of a chunk, one chunk ahead.  Every thread: its row piece (K-row threads: U, Q-row threads: dO) as
+  // raw bf16.  Q-row threads only: the raw gate inputs of their table entries; they turn them into the next chunk's gate
+  // tables while the K-row threads run the epilogue of (a), in which Q rows have nothing else to do.  Loads are
+  // unconditional from clamped addresses and masked at use.
+  constexpr int QTHREADS = REC_THREADS / 2;
+  constexpr int GQ = (64 * E + QTHREADS - 1) / QTHREADS;     // table entries per Q-row thread
+  const int qid = wg * 64 + t;                               // Q-row threads: 0 .. QTHREADS-1
+  struct GateRaw { float gcv[GQ], gl[GQ], k2v[GQ], q2v[GQ], beta; int rows; };
+  auto load_row = [&](int i) {
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int last = max(rows, 1) - 1;
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const __nv_bfloat16* rp = krow ? p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW
+                                   : p.dO + ((tok + min(t, last)) * p.H + h) * HEAD + vb * VC + wg * CW;
+    if constexpr (CW == 8) {
+      return __ldg(reinterpret_cast<const uint4*>(rp));
+    } else {
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
+      return make_uint4(w.x, w.y, 0u, 0u);
+    }
+  };
+  auto load_gates = [&](int i) {                             // Q-row threads
+    GateRaw g;
     int t0, rows;
     chunk_info(i, t0, rows);
     g.rows = rows;
@@ -170,17 +184,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
     const float* gcp = p.gc + item * (64 * E);
-    const __nv_bfloat16* rp = krow ? p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW
-                                   : p.dO + ((tok + min(t, last)) * p.H + h) * HEAD + vb * VC + wg * CW;
-    if constexpr (CW == 8) {
-      g.rowp = __ldg(reinterpret_cast<const uint4*>(rp));
-    } else {
-      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
-      g.rowp = make_uint4(w.x, w.y, 0u, 0u);
-    }
 #pragma unroll
-    for (int it = 0; it < GATE_ITERS; ++it) {
-      const int idx = min(tid + it * REC_THREADS, 64 * E - 1);
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
       const int r = idx / E, e = idx % E;
       const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
       g.gcv[it] = __ldg(gcp + idx);
@@ -188,26 +194,42 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       g.k2v[it] = __ldg(p.k2 + off);
       g.q2v[it] = __ldg(p.q2 + off);
     }
-    g.beta = __ldg(p.beta + (tok + min(tid & 63, last)) * p.H + h);
+    g.beta = __ldg(p.beta + (tok + min(qid & 63, last)) * p.H + h);
     return g;
   };
-  auto write_gates = [&](const ChunkRaw& g) {
+  auto write_gates = [&](const GateRaw& g, int buf) {        // Q-row threads
+    float* ga = gate_buf + buf * C::GATE_FLOATS;
+    float* gr = ga + 64 * ES;
+    float* gc_ = gr + 64 * ES;
+    float* gb = gc_ + 64 * ES;
+    float* gd = gb + 64;
 #pragma unroll
-    for (int it = 0; it < GATE_ITERS; ++it) {
-      const int idx = tid + it * REC_THREADS;
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = qid + it * QTHREADS;
       if (idx < 64 * E) {
         const int r = idx / E, e = idx % E;
         const bool ok = r < g.rows;
         const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
         const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
         const float eg = rexp2(gcv);
-        g_a[r * ES + e] = k2v * eg;
-        g_r[r * ES + e] = k2v * rexp2(gl - gcv);
-        g_c[r * ES + e] = p.scale * q2v * eg;
-        if (r == 0) g_d[e] = rexp2(gl);
+        ga[r * ES + e] = k2v * eg;
+        gr[r * ES + e] = k2v * rexp2(gl - gcv);
+        gc_[r * ES + e] = p.scale * q2v * eg;
+        if (r == 0) gd[e] = rexp2(gl);
       }
     }
-    if (tid < 64) g_beta[tid] = (tid < g.rows) ? g.beta : 0.f;
+    if (qid < 64) gb[qid] = (qid < g.rows) ? g.beta : 0.f;
+  };
+  auto prefetch_loads = [&](int i) {                         // one lane: next chunk's tiles into L2 (single-stage configuration)
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    tma_prefetch_4d(&map_k, 0, h, t0, b);
+    tma_prefetch_4d(&map_q, 0, h, t0, b);
+    tma_prefetch_4d(&map_k, 64, h, t0, b);
+    tma_prefetch_4d(&map_q, 64, h, t0, b);
+    bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
+    bulk_prefetch(p.Pm + item * (64 * 64), C::PM_BYTES);
   };
   auto store_row_global = [&](__nv_bfloat16* ptr, const float* src) {
     if constexpr (CW == 8)
@@ -225,7 +247,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   };
 
   if (tid == 0) issue_loads(count - 1, 0);
-  ChunkRaw raw_cur = load_chunk(count - 1);
+  uint4 row_cur = load_row(count - 1);
+  GateRaw raw_next;
+  if (!krow) {
+    raw_next = load_gates(count - 1);
+    write_gates(raw_next, 0);
+    if (count > 1) raw_next = load_gates(count - 2);
+  }
   uint32_t mma_phase = 0;
   {
     uint32_t zeros[TPC / 2];
@@ -246,19 +274,23 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* pm = smem + C::OFF_PM + st * C::PM_BYTES;
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
-    // this chunk's inputs were loaded while the previous one was processed: row piece of U (K-row threads) or dO (Q-row
-    // threads), dO operand image, gate tables
+    // this chunk's row piece was loaded while the previous one was processed (K-row threads: U, Q-row threads: dO, which
+    // also goes into the dO operand image); its gate tables were built during the previous chunk's (a) epilogue
+    float* g_a = gate_buf + (kstep & 1) * C::GATE_FLOATS;
+    float* g_r = g_a + 64 * ES;
+    float* g_c = g_r + 64 * ES;
+    float* g_beta = g_c + 64 * ES;
+    float* g_d = g_beta + 64;
     float rowv[CW];
     {
-      const uint32_t rw[4] = {raw_cur.rowp.x, raw_cur.rowp.y, raw_cur.rowp.z, raw_cur.rowp.w};
+      const uint32_t rw[4] = {row_cur.x, row_cur.y, row_cur.z, row_cur.w};
       const bool live = krow || t < rows;
 #pragma unroll
       for (int c = 0; c < CW; ++c) rowv[c] = live ? ((c & 1) ? bf16_hi(rw[c >> 1]) : bf16_lo(rw[c >> 1])) : 0.f;
     }
     if (!krow)
       store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, rowv, 1.f);
-    write_gates(raw_cur);
-    if (kstep + 1 < count) raw_cur = load_chunk(i - 1);      // consumed at the top of the next iteration
+    if (kstep + 1 < count) row_cur = load_row(i - 1);        // consumed at the top of the next iteration
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -286,7 +318,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma);
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    if (STAGES == 2 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, st ^ 1);
+    if (warp_u == 1 && kstep + 1 < count && elect_one()) {
+      if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
+    }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -314,6 +348,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       store_row_global(p.dU + (item * 64 + t) * HEAD + vb * VC + v0, du);
       store_row_image(smem_u32(smem + C::OFF_DU) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, du, 1.f);
+    } else if (kstep + 1 < count) {
+      write_gates(raw_next, (kstep + 1) & 1);                // tables of the chunk processed next
+      if (kstep + 2 < count) raw_next = load_gates(i - 2);
     }
     fence_async_smem();
     tc_fence_before();
