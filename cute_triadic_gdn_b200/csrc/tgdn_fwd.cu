@@ -250,7 +250,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
 
     // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
-    write_gates(raw_cur);                            // loaded while the previous chunk was processed
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (i >> 1) : i) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (warp_u == 0 && elect_one()) {
       tc_fence_after();
@@ -267,7 +266,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       if (STAGES == 2) issue_loads(i + 1);             // the other stage was released by the previous chunk's (3)
       if (STAGES == 1) prefetch_loads(i + 1);
     }
-    // start the loads for the next chunk's tables and value row now; they are consumed at the top of the next iteration
+    // (1) does not read the gate tables: they are built in its shadow, from inputs loaded while the previous chunk was
+    // processed; then the loads for the next chunk's tables and value row go out, consumed one iteration later
+    write_gates(raw_cur);
     float* g_a = gate_base;
     float* g_r = g_a + 64 * ES;
     float* g_c = g_r + 64 * ES;
