@@ -51,7 +51,7 @@ struct FwdCfg {
   static constexpr int OFF_VN = OFF_S + S_BYTES;
   static constexpr int OFF_BW = OFF_VN + VN_BYTES;
   static constexpr int OFF_GATES = OFF_BW + ((BW_BYTES + 1023) & ~1023);
-  static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;     // a, r, c tables, beta, d
+  static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 32;     // a, r, c tables, beta, two copies of d
   static constexpr int OFF_CTRL = OFF_GATES + GATE_FLOATS * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;       // + control block + alignment slack
 };
@@ -163,12 +163,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
   };
 
-  // Raw gate inputs of one chunk for this thread's (at most two) table entries, and the table builder.  The loads are
-  // issued unconditionally from clamped (always valid) addresses and masked when they are consumed: a predicated
-  // load followed by a select would make the issuing thread wait for the data at once.
-  struct GateRaw { float gcv[2], gl[2], k2v[2], q2v[2], beta; int rows; };
-  constexpr int GATE_ITERS = (64 * E + FWD_THREADS - 1) / FWD_THREADS;
-  static_assert(GATE_ITERS <= 2, "gate tables: at most two entries per thread");
+  // Gate tables.  The Q-row threads own them.  During the epilogue of (2), where Q rows have little else to do, they load
+  // the next chunk's raw inputs (pulled into L2 one chunk earlier, so the loads are short and nothing is held in
+  // registers across a chunk), turn them into table values and store a, c and beta, which nobody reads after the
+  // epilogue of (1); r, which the K rows still read in (2), and d, which (3) itself uses (two copies), follow at the start
+  // of the epilogue of (3).  Loads are unconditional from clamped (always valid) addresses and masked at use.
+  constexpr int QTHREADS = FWD_THREADS / 2;
+  constexpr int GQ = (64 * E + QTHREADS - 1) / QTHREADS;     // table entries per Q-row thread
+  const int qid = wg * 64 + t;                               // Q-row threads: 0 .. QTHREADS-1
+  struct GateRaw { float gcv[GQ], gl[GQ], k2v[GQ], q2v[GQ], beta; int rows; };
+  struct GateVal { float a[GQ], r[GQ], c[GQ], d[GQ], beta; };
+  float* g_a = gate_base;
+  float* g_r = g_a + 64 * ES;
+  float* g_c = g_r + 64 * ES;
+  float* g_beta = g_c + 64 * ES;
+  float* g_dd = g_beta + 64;                                 // [2][16]
   auto load_gates = [&](int i) {
     GateRaw g;
     int t0, rows;
@@ -179,40 +188,68 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
     const float* gcp = p.gc + item * (64 * E);
 #pragma unroll
-    for (int it = 0; it < GATE_ITERS; ++it) {
-      const int idx = min(tid + it * FWD_THREADS, 64 * E - 1);
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
       const int r = idx / E, e = idx % E;
       const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
-      g.gcv[it] = gcp[idx];
-      g.gl[it] = gcp[63 * E + e];
-      g.k2v[it] = p.k2[off];
-      g.q2v[it] = p.q2[off];
+      g.gcv[it] = __ldg(gcp + idx);
+      g.gl[it] = __ldg(gcp + 63 * E + e);
+      g.k2v[it] = __ldg(p.k2 + off);
+      g.q2v[it] = __ldg(p.q2 + off);
     }
-    g.beta = p.beta[(tok + min(tid & 63, last)) * p.H + h];
+    g.beta = __ldg(p.beta + (tok + min(qid & 63, last)) * p.H + h);
     return g;
   };
-  auto write_gates = [&](const GateRaw& g) {
-    float* ga = gate_base;
-    float* gr = ga + 64 * ES;
-    float* gc_ = gr + 64 * ES;
-    float* gb = gc_ + 64 * ES;
-    float* gd = gb + 64;
+  auto gate_values = [&](const GateRaw& g) {
+    GateVal v;
 #pragma unroll
-    for (int it = 0; it < GATE_ITERS; ++it) {
-      const int idx = tid + it * FWD_THREADS;
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
+      const bool ok = idx / E < g.rows;
+      const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
+      const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
+      const float eg = fexp2(gcv);
+      v.a[it] = k2v * eg;
+      v.r[it] = k2v * fexp2(gl - gcv);
+      v.c[it] = p.scale * q2v * eg;
+      v.d[it] = fexp2(gl);
+    }
+    v.beta = ((qid & 63) < g.rows) ? g.beta : 0.f;
+    return v;
+  };
+  auto store_gates_early = [&](const GateVal& v) {            // a, c, beta
+#pragma unroll
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = qid + it * QTHREADS;
       if (idx < 64 * E) {
         const int r = idx / E, e = idx % E;
-        const bool ok = r < g.rows;
-        const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
-        const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
-        const float eg = fexp2(gcv);
-        ga[r * ES + e] = k2v * eg;
-        gr[r * ES + e] = k2v * fexp2(gl - gcv);
-        gc_[r * ES + e] = p.scale * q2v * eg;
-        if (r == 0) gd[e] = fexp2(gl);
+        g_a[r * ES + e] = v.a[it];
+        g_c[r * ES + e] = v.c[it];
       }
     }
-    if (tid < 64) gb[tid] = (tid < g.rows) ? g.beta : 0.f;
+    if (qid < 64) g_beta[qid] = v.beta;
+  };
+  auto store_gates_late = [&](const float* vr, float vd, int dbuf) {   // r, d
+#pragma unroll
+    for (int it = 0; it < GQ; ++it) {
+      const int idx = qid + it * QTHREADS;
+      if (idx < 64 * E) g_r[(idx / E) * ES + idx % E] = vr[it];
+    }
+    if (qid < E) g_dd[dbuf * 16 + qid] = vd;                  // entry (row 0, e = qid) is this thread's first
+  };
+  auto prefetch_gates = [&](int i) {                         // Q-row threads: one request per distinct 128-byte line
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int last = max(rows, 1) - 1;
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    if (qid < 64) {
+      const int64_t ro = (tok + min(qid, last)) * p.H + h;
+      prefetch_l2(p.k2 + ro * E);
+      prefetch_l2(p.q2 + ro * E);
+      prefetch_l2(p.beta + ro);
+    }
+    if (qid * 32 < 64 * E) prefetch_l2(p.gc + item * (64 * E) + qid * 32);
   };
   auto load_vrow = [&](int i) {                      // this thread's CW value columns of row t (clamped), raw bf16
     int t0, rows;
@@ -231,7 +268,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
   if (tid == 0) issue_loads(0);
   uint4 vnext = load_vrow(0);
-  GateRaw raw_cur = load_gates(0);
+  // Where registers allow (small E), the raw inputs are held in registers one chunk ahead instead of only sitting in L2.
+  constexpr bool HOLD_RAW = E <= 4;
+  GateRaw raw_next;
+  float r_next[GQ], d_next = 0.f;                      // Q-row threads: table values that wait for the epilogue of (3)
+  if (!krow) {
+    const GateVal v = gate_values(load_gates(0));
+    store_gates_early(v);
+    store_gates_late(v.r, v.d[0], 0);
+    if (count > 1) {
+      if constexpr (HOLD_RAW) raw_next = load_gates(1); else prefetch_gates(1);
+    }
+  }
   uint32_t mma_phase = 0;
   {
     uint32_t zeros[TPC / 2];
@@ -239,6 +287,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
     store_state((static_cast<int64_t>(b) * p.NC + first) * p.H + h, zeros);
   }
+  __syncthreads();                                   // first chunk's gate tables visible
 
   for (int i = 0; i < count; ++i) {
     const int st = (STAGES == 2) ? (i & 1) : 0;
@@ -266,20 +315,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       if (STAGES == 2) issue_loads(i + 1);             // the other stage was released by the previous chunk's (3)
       if (STAGES == 1) prefetch_loads(i + 1);
     }
-    // (1) does not read the gate tables: they are built in its shadow, from inputs loaded while the previous chunk was
-    // processed; then the loads for the next chunk's tables and value row go out, consumed one iteration later
-    write_gates(raw_cur);
-    float* g_a = gate_base;
-    float* g_r = g_a + 64 * ES;
-    float* g_c = g_r + 64 * ES;
-    float* g_beta = g_c + 64 * ES;
-    float* g_d = g_beta + 64;
+    // the load of the next chunk's value row goes out now; it is consumed one iteration later
+    const float* g_d = g_dd + (i & 1) * 16;
     const uint4 vraw = vnext;
-    if (i + 1 < count) {
-      raw_cur = load_gates(i + 1);
-      vnext = load_vrow(i + 1);
-    }
-    __syncthreads();                                 // gate tables visible
+    if (i + 1 < count) vnext = load_vrow(i + 1);
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
@@ -378,6 +417,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         else
           *reinterpret_cast<uint2*>(op) = make_uint2(pack_bf16(acc[0] + u[0], acc[1] + u[1]), pack_bf16(acc[2] + u[2], acc[3] + u[3]));
       }
+      if (!krow && i + 1 < count) {                    // next chunk's tables
+        if constexpr (!HOLD_RAW) raw_next = load_gates(i + 1);
+        const GateVal v = gate_values(raw_next);
+        store_gates_early(v);
+#pragma unroll
+        for (int it = 0; it < GQ; ++it) r_next[it] = v.r[it];
+        d_next = v.d[0];
+        if (i + 2 < count) {
+          if constexpr (HOLD_RAW) raw_next = load_gates(i + 2); else prefetch_gates(i + 2);
+        }
+      }
     }
     fence_async_smem();
     tc_fence_before();
@@ -399,6 +449,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     ++mma_phase;
     tc_fence_after();
     if (STAGES == 1 && warp_u == 1 && i + 1 < count && elect_one()) issue_loads(i + 1);   // the only stage is free once (3) has completed
+    if (!krow && i + 1 < count) store_gates_late(r_next, d_next, (i + 1) & 1);   // this chunk's r table is dead by now
     {
       constexpr int PIECE = (TPC % 32 == 0) ? 32 : ((TPC % 16 == 0) ? 16 : TPC);
       const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
