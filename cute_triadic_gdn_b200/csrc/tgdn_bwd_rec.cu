@@ -231,6 +231,23 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
     bulk_prefetch(p.Pm + item * (64 * 64), C::PM_BYTES);
   };
+  auto prefetch_gates = [&](int i) {                         // Q-row threads: one request per distinct 128-byte line
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int last = max(rows, 1) - 1;
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    if (qid < 64) {
+      const int64_t ro = (tok + min(qid, last)) * p.H + h;
+      prefetch_l2(p.k2 + ro * E);
+      prefetch_l2(p.q2 + ro * E);
+      prefetch_l2(p.beta + ro);
+    }
+    if (qid * 32 < 64 * E) prefetch_l2(p.gc + item * (64 * E) + qid * 32);
+  };
+  // Where registers allow (small E) the raw gate inputs are held in registers one chunk ahead; otherwise they are only
+  // pulled into L2 a chunk ahead and loaded where they are used, by threads that have slack there.
+  constexpr bool HOLD_RAW = E <= 4;
   auto store_row_global = [&](__nv_bfloat16* ptr, const float* src) {
     if constexpr (CW == 8)
       *reinterpret_cast<uint4*>(ptr) = make_uint4(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]),
@@ -252,7 +269,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (!krow) {
     raw_next = load_gates(count - 1);
     write_gates(raw_next, 0);
-    if (count > 1) raw_next = load_gates(count - 2);
+    if (count > 1) {
+      if constexpr (HOLD_RAW) raw_next = load_gates(count - 2); else prefetch_gates(count - 2);
+    }
   }
   uint32_t mma_phase = 0;
   {
@@ -349,8 +368,11 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       store_row_global(p.dU + (item * 64 + t) * HEAD + vb * VC + v0, du);
       store_row_image(smem_u32(smem + C::OFF_DU) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, du, 1.f);
     } else if (kstep + 1 < count) {
+      if constexpr (!HOLD_RAW) raw_next = load_gates(i - 1);
       write_gates(raw_next, (kstep + 1) & 1);                // tables of the chunk processed next
-      if (kstep + 2 < count) raw_next = load_gates(i - 2);
+      if (kstep + 2 < count) {
+        if constexpr (HOLD_RAW) raw_next = load_gates(i - 2); else prefetch_gates(i - 2);
+      }
     }
     fence_async_smem();
     tc_fence_before();
