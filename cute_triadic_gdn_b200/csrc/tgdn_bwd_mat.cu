@@ -206,8 +206,15 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   const uint32_t a5 = smem_u32(sm.u1.a5);
   const int warp_tmax = (warp & 1) ? 63 : 31;              // largest row index t in this warp
+  // From here to the barrier before G5 the two halves of the CTA run independent chains and synchronise among
+  // themselves only (named barriers of 256 threads): the key-row warps carry dA -> G3 -> Y -> G4 -> dL, the query-row
+  // warps the Mp-side mask gradients.  Neither waits for the other's long loops.
+  auto half_sync = [&]() {
+    if (krow) asm volatile("bar.sync 1, 256;" ::: "memory"); else asm volatile("bar.sync 2, 256;" ::: "memory");
+  };
 
   if (!krow) {
+    // ================================ query-row chain ================================
     // query row t, columns s0..s0+15: X -> a5 (row 64+t and, transposed, column 64+t), dmp, partial r1
     const float live = (t < rows) ? 1.f : 0.f;
     float r1v[E];
@@ -243,143 +250,151 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       st_shared_v4(rowbase + (8 + 2 * cq + jb) * 2048, 0u, 0u, 0u, 0u);
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r1v[e];
+    for (int e = 0; e < E; ++e) sm.part[1][cq][t * ES + e] = r1v[e];
+    half_sync();
+    // r1 = sum of the four partials (256 query-row threads over the 64*E entries)
+    for (int idx = cq * 64 + t; idx < 64 * E; idx += 256) {
+      const int o = (idx / E) * ES + idx % E;
+      sm.r1[o] = (sm.part[1][0][o] + sm.part[1][1][o]) + (sm.part[1][2][o] + sm.part[1][3][o]);
+    }
+    half_sync();                                           // part[1] is free again, dmp complete
+    // query thread (64+s, cq): partial c1[s,e] over t' in quarter cq: dmp[t',s] exp(gc[t']-gc[s]) q2[t',e]
+    {
+      const int s = t;
+      float c1v[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) c1v[e] = 0.f;
+      for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
+        const float dv = sm.u2.f.dmp[midx(tt, s)];
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
+    }
+    mma_phase += 2;                                        // G3 and G4 complete without the query rows watching
   } else {
+    // ================================ key-row chain ================================
     // key row t, columns s0..s0+15: dA = dA' diag(beta) -> operand image; dA' * A -> column sums
-    const uint32_t apr = smem_u32(sm.ap) + (t >> 3) * 128 + (t & 7) * 16;
-    const uint32_t dar = smem_u32(sm.da) + (t >> 3) * 128 + (t & 7) * 16;
+    {
+      const uint32_t apr = smem_u32(sm.ap) + (t >> 3) * 128 + (t & 7) * 16;
+      const uint32_t dar = smem_u32(sm.da) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-    for (int jb = 0; jb < 2; ++jb) {
-      uint32_t aw[4];
-      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(aw[0]), "=r"(aw[1]), "=r"(aw[2]), "=r"(aw[3]) : "r"(apr + (2 * cq + jb) * 2048));
-      float dav[8];
+      for (int jb = 0; jb < 2; ++jb) {
+        uint32_t aw[4];
+        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(aw[0]), "=r"(aw[1]), "=r"(aw[2]), "=r"(aw[3]) : "r"(apr + (2 * cq + jb) * 2048));
+        float dav[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int j = jb * 8 + c, s = s0 + j;
-        const float a_ts = (c & 1) ? bf16_hi(aw[c >> 1]) : bf16_lo(aw[c >> 1]);
-        sm.daa[midx(t, s)] = gr[j] * a_ts;
-        dav[c] = gr[j] * sm.beta[s];
-      }
-      st_shared_v4(dar + (2 * cq + jb) * 1024, pack_bf16(dav[0], dav[1]), pack_bf16(dav[2], dav[3]), pack_bf16(dav[4], dav[5]),
-                   pack_bf16(dav[6], dav[7]));
-    }
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-
-  // ---- G3: Y = A^T dA ----------------------------------------------------------------------------------------------
-  if (warp_u == 0 && elect_one()) {
-    tc_fence_after();
-    const uint64_t da = make_desc(smem_u32(sm.ap), 128, 2048, LAYOUT_PLAIN);     // A^T, MN-major
-    const uint64_t db = make_desc(smem_u32(sm.da), 128, 1024, LAYOUT_PLAIN);     // dA (K = t, N = s), MN-major
-    constexpr uint32_t idesc = make_idesc(128, 64, 1, 1);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 192, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
-    umma_commit(&sm.bar_mma);
-  }
-  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
-  // meanwhile: r1 = sum of the four partials; dbeta_col[s] = sum_t dA'[t,s] A[t,s]
-  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
-    const int o = (idx / E) * ES + idx % E;
-    sm.r1[o] = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
-  }
-  if (tid >= 448) {
-    const int s = tid - 448;
-    float acc = 0.f;
-    for (int tt = 0; tt < 64; ++tt) acc += sm.daa[midx(tt, s)];
-    sm.bcol[s] = acc;
-  }
-  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  ++mma_phase;
-  tc_fence_after();
-  if (krow) {
-    float yr[16];
-    tmem_ld<16>(tmem_row + 192 + s0, yr);
-    tmem_wait_ld();
-    const uint32_t yb = smem_u32(sm.y) + (t >> 3) * 128 + (t & 7) * 16;
-#pragma unroll
-    for (int jb = 0; jb < 2; ++jb)
-      st_shared_v4(yb + (2 * cq + jb) * 1024, pack_bf16(yr[jb * 8], yr[jb * 8 + 1]), pack_bf16(yr[jb * 8 + 2], yr[jb * 8 + 3]),
-                   pack_bf16(yr[jb * 8 + 4], yr[jb * 8 + 5]), pack_bf16(yr[jb * 8 + 6], yr[jb * 8 + 7]));
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-
-  // ---- G4: dp = Y A^T ----------------------------------------------------------------------------------------------
-  if (warp_u == 0 && elect_one()) {
-    tc_fence_after();
-    const uint64_t da = make_desc(smem_u32(sm.y), 1024, 128, LAYOUT_PLAIN);      // Y, K-major
-    const uint64_t db = make_desc(smem_u32(sm.ap), 2048, 128, LAYOUT_PLAIN);     // B[k][j] = A[j][k]: A rows as N, K-major
-    constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 256, desc_advance(da, kk * 2048), desc_advance(db, kk * 4096), idesc, kk > 0);
-    umma_commit(&sm.bar_mma);
-  }
-  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
-  if (!krow) {
-    // meanwhile, query thread (64+s, cq): partial c1[s,e] over t' in quarter cq: dmp[t',s] exp(gc[t']-gc[s]) q2[t',e]
-    const int s = t;
-    float c1v[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) c1v[e] = 0.f;
-    for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
-      const float dv = sm.u2.f.dmp[midx(tt, s)];
-#pragma unroll
-      for (int e = 0; e < E; ++e)
-        c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
-    }
-#pragma unroll
-    for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
-  }
-  mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-  ++mma_phase;
-  tc_fence_after();
-  // ap, da, y and daa (48 KB in a row) are dead from here on: the state part of dK, dQ (32 KB bf16 image written by the
-  // state-gradient kernel) is fetched into their place now, so that its HBM round trip runs under the remaining phases.
-  if (warp_u == 0 && elect_one()) {
-    mbar_expect_tx(&sm.bar_load, 32768);
-    bulk_load(sm.ap, reinterpret_cast<const uint8_t*>(p.dkq) + item * 32768, 32768, &sm.bar_load);
-  }
-  __syncwarp();
-  if (krow) {
-    // key row t, columns s0..s0+15: dL, partial dbeta_row, dm, partial r2, and dPkk + dPkk^T into a5[0..63][0..63]
-    float dpr[16];
-    tmem_ld<16>(tmem_row + 256 + s0, dpr);
-    tmem_wait_ld();
-    const float bt = sm.beta[t];
-    float brow = 0.f;
-    float r2v[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) r2v[e] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int s = s0 + j;
-      float dmv = 0.f;
-      if (s0 <= warp_tmax && s < t) {
-        float dec[E];
-        float m = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          dec[e] = mexp2(mygc[e] - sm.gc2[s * ES + e]) * sm.k2[s * ES + e];
-          m = fmaf(my2[e], dec[e], m);
+        for (int c = 0; c < 8; ++c) {
+          const int j = jb * 8 + c, s = s0 + j;
+          const float a_ts = (c & 1) ? bf16_hi(aw[c >> 1]) : bf16_lo(aw[c >> 1]);
+          sm.daa[midx(t, s)] = gr[j] * a_ts;
+          dav[c] = gr[j] * sm.beta[s];
         }
-        const float dl = -dpr[j];
-        brow = fmaf(dl * pr[j], m, brow);
-        dmv = bt * dl * pr[j];
-        const float dpk = bt * dl * m;
-#pragma unroll
-        for (int e = 0; e < E; ++e) r2v[e] = fmaf(dmv, dec[e], r2v[e]);
-        st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
-        st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
+        st_shared_v4(dar + (2 * cq + jb) * 1024, pack_bf16(dav[0], dav[1]), pack_bf16(dav[2], dav[3]), pack_bf16(dav[4], dav[5]),
+                     pack_bf16(dav[6], dav[7]));
       }
-      sm.u2.f.dm[midx(t, s)] = dmv;
     }
-    if (cq == (t >> 4)) st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);   // diagonal
+    fence_async_smem();
+    tc_fence_before();
+    half_sync();
+
+    // ---- G3: Y = A^T dA ----
+    if (warp_u == 0 && elect_one()) {
+      tc_fence_after();
+      const uint64_t da = make_desc(smem_u32(sm.ap), 128, 2048, LAYOUT_PLAIN);     // A^T, MN-major
+      const uint64_t db = make_desc(smem_u32(sm.da), 128, 1024, LAYOUT_PLAIN);     // dA (K = t, N = s), MN-major
+      constexpr uint32_t idesc = make_idesc(128, 64, 1, 1);
 #pragma unroll
-    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r2v[e];
-    sm.browp[cq][t] = brow;
+      for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 192, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&sm.bar_mma);
+    }
+    __syncwarp();                                          // the other lanes must not run ahead into a spin wait
+    // meanwhile: dbeta_col[s] = sum_t dA'[t,s] A[t,s] (the 64 key-row threads of the last column quarter)
+    if (cq == 3) {
+      const int s = t;
+      float acc = 0.f;
+      for (int tt = 0; tt < 64; ++tt) acc += sm.daa[midx(tt, s)];
+      sm.bcol[s] = acc;
+    }
+    mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++mma_phase;
+    tc_fence_after();
+    {
+      float yr[16];
+      tmem_ld<16>(tmem_row + 192 + s0, yr);
+      tmem_wait_ld();
+      const uint32_t yb = smem_u32(sm.y) + (t >> 3) * 128 + (t & 7) * 16;
+#pragma unroll
+      for (int jb = 0; jb < 2; ++jb)
+        st_shared_v4(yb + (2 * cq + jb) * 1024, pack_bf16(yr[jb * 8], yr[jb * 8 + 1]), pack_bf16(yr[jb * 8 + 2], yr[jb * 8 + 3]),
+                     pack_bf16(yr[jb * 8 + 4], yr[jb * 8 + 5]), pack_bf16(yr[jb * 8 + 6], yr[jb * 8 + 7]));
+    }
+    fence_async_smem();
+    tc_fence_before();
+    half_sync();
+
+    // ---- G4: dp = Y A^T ----
+    if (warp_u == 0 && elect_one()) {
+      tc_fence_after();
+      const uint64_t da = make_desc(smem_u32(sm.y), 1024, 128, LAYOUT_PLAIN);      // Y, K-major
+      const uint64_t db = make_desc(smem_u32(sm.ap), 2048, 128, LAYOUT_PLAIN);     // B[k][j] = A[j][k]: A rows as N, K-major
+      constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem + 256, desc_advance(da, kk * 2048), desc_advance(db, kk * 4096), idesc, kk > 0);
+      umma_commit(&sm.bar_mma);
+    }
+    __syncwarp();                                          // the other lanes must not run ahead into a spin wait
+    mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++mma_phase;
+    tc_fence_after();
+    // ap, da, y and daa (48 KB in a row) are dead from here on: the state part of dK, dQ (32 KB bf16 image written by
+    // the state-gradient kernel) is fetched into their place now, so that its HBM round trip runs under the remaining
+    // phases.  (The column sums over daa were finished before the barrier that preceded G4.)
+    if (warp_u == 0 && elect_one()) {
+      mbar_expect_tx(&sm.bar_load, 32768);
+      bulk_load(sm.ap, reinterpret_cast<const uint8_t*>(p.dkq) + item * 32768, 32768, &sm.bar_load);
+    }
+    __syncwarp();
+    {
+      // key row t, columns s0..s0+15: dL, partial dbeta_row, dm, partial r2, and dPkk + dPkk^T into a5[0..63][0..63]
+      float dpr[16];
+      tmem_ld<16>(tmem_row + 256 + s0, dpr);
+      tmem_wait_ld();
+      const float bt = sm.beta[t];
+      float brow = 0.f;
+      float r2v[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) r2v[e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int s = s0 + j;
+        float dmv = 0.f;
+        if (s0 <= warp_tmax && s < t) {
+          float dec[E];
+          float m = 0.f;
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            dec[e] = mexp2(mygc[e] - sm.gc2[s * ES + e]) * sm.k2[s * ES + e];
+            m = fmaf(my2[e], dec[e], m);
+          }
+          const float dl = -dpr[j];
+          brow = fmaf(dl * pr[j], m, brow);
+          dmv = bt * dl * pr[j];
+          const float dpk = bt * dl * m;
+#pragma unroll
+          for (int e = 0; e < E; ++e) r2v[e] = fmaf(dmv, dec[e], r2v[e]);
+          st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
+          st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
+        }
+        sm.u2.f.dm[midx(t, s)] = dmv;
+      }
+      if (cq == (t >> 4)) st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);   // diagonal
+#pragma unroll
+      for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r2v[e];
+      sm.browp[cq][t] = brow;
+    }
   }
   fence_async_smem();
   tc_fence_before();
@@ -396,7 +411,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     umma_commit(&sm.bar_mma);
   }
   __syncwarp();                                           // the other lanes must not run ahead into a spin wait
-  // sums of the partials written before the barrier
+  // sums of the partials written before the barrier: r2 (key-row chain) and c1 (query-row chain)
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
     const int o = (idx / E) * ES + idx % E;
     sm.r2[o] = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
@@ -404,19 +419,21 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (tid < 64) sm.brow[tid] = (sm.browp[0][tid] + sm.browp[1][tid]) + (sm.browp[2][tid] + sm.browp[3][tid]);
   __syncthreads();
-  if (krow) {
-    // key thread (s = t, cq): partial c2[s,e] over t' in quarter cq, t' > s: dm[t',s] exp(gc[t']-gc[s]) k2[t',e]
+  {
+    // thread (s = t, cq): partial c2[s,e] = sum over t' > s of dm[t',s] exp(gc[t']-gc[s]) k2[t',e]; the key-row thread takes
+    // the first eight t' of quarter cq, the query-row thread of the same (t, cq) the other eight
     float c2v[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) c2v[e] = 0.f;
-    for (int tt = max(t + 1, s0); tt < s0 + 16; ++tt) {
+    const int lo = s0 + (krow ? 0 : 8);
+    for (int tt = max(t + 1, lo); tt < lo + 8; ++tt) {
       const float dv = sm.u2.f.dm[midx(tt, t)];
 #pragma unroll
       for (int e = 0; e < E; ++e)
         c2v[e] = fmaf(dv * sm.k2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c2v[e]);
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = c2v[e];
+    for (int e = 0; e < E; ++e) sm.part[krow ? 0 : 1][cq][t * ES + e] = c2v[e];
   }
   __syncthreads();
   // gate gradients: one thread per (row, gate column)
@@ -425,7 +442,8 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int idx = tid + it * MAT_THREADS;
     if (idx < 64 * E) {
       const int rr = idx / E, e = idx % E, o = rr * ES + e;
-      const float c2e = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
+      const float c2e = ((sm.part[0][0][o] + sm.part[1][0][o]) + (sm.part[0][1][o] + sm.part[1][1][o])) +
+                        ((sm.part[0][2][o] + sm.part[1][2][o]) + (sm.part[0][3][o] + sm.part[1][3][o]));
       const float gcv = sm.gc2[o], gl = sm.gc2[63 * ES + e];
       const float eg = mexp2(gcv), egr = mexp2(gl - gcv);
       const float k2v = sm.k2[o], q2v = sm.q2[o];
