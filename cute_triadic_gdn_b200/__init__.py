@@ -5,10 +5,16 @@
     conv_split_act_call   causal depthwise convolution (width 4) with SiLU on the leading channels only
 
 Same names, signatures, shapes and dtypes as cute_triadic_gdn/__init__.py:7-11 of the reference.
+
+Beyond the reference's surface:
+
+    HostPipeline / gdn_joint_host   inputs and results in pinned host memory; uploads, kernels and downloads of
+                                    successive batch slices overlap on three streams (host_pipeline.py)
 """
 from .conv_split_act import conv_split_act_call
 from .gdn_joint import chunk_gdn_joint
+from .host_pipeline import HostPipeline, gdn_joint_host
 from .joint_torch_ops import gdn_joint_call
 
-__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call"]
+__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call", "HostPipeline", "gdn_joint_host"]
 __version__ = "0.1.0"

@@ -161,17 +161,33 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   }
   __syncwarp();                                           // the other lanes must not run ahead into a spin wait
 
-  // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0
+  // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0.  All loads are requested first, from
+  // clamped (always valid) addresses, and masked when stored: the block pays one memory round trip, not one per iteration.
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-  for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
-    const int rr = idx / E;
-    const bool ok = rr < rows;
-    const int64_t g_off = ((tok + rr) * p.H + h) * E + (idx % E);
-    sm.gc2[idx] = ok ? p.g[g_off] : 0.f;
-    sm.k2[idx] = ok ? p.k2[g_off] : 0.f;
-    sm.q2[idx] = ok ? p.q2[g_off] : 0.f;
+  {
+    constexpr int GATE_ITERS = (64 * E + MASK_THREADS - 1) / MASK_THREADS;
+    float g_in[GATE_ITERS], k2_in[GATE_ITERS], q2_in[GATE_ITERS];
+    const float beta_in = __ldg(p.beta + (tok + min(tid & 63, rows - 1)) * p.H + h);
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = min(tid + it * MASK_THREADS, 64 * E - 1);
+      const int64_t g_off = ((tok + min(idx / E, rows - 1)) * p.H + h) * E + (idx % E);
+      g_in[it] = __ldg(p.g + g_off);
+      k2_in[it] = __ldg(p.k2 + g_off);
+      q2_in[it] = __ldg(p.q2 + g_off);
+    }
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * MASK_THREADS;
+      if (idx < 64 * E) {
+        const bool ok = idx / E < rows;
+        sm.gc2[idx] = ok ? g_in[it] : 0.f;
+        sm.k2[idx] = ok ? k2_in[it] : 0.f;
+        sm.q2[idx] = ok ? q2_in[it] : 0.f;
+      }
+    }
+    if (tid < 64) sm.beta[tid] = (tid < rows) ? beta_in : 0.f;
   }
-  if (tid < 64) sm.beta[tid] = (tid < rows) ? p.beta[(tok + tid) * p.H + h] : 0.f;
   __syncthreads();
   // inclusive scan over the 64 rows, one warp per gate column
   float* gc_out = p.gc + ((static_cast<int64_t>(b) * p.NC + n) * p.H + h) * (64 * E);
