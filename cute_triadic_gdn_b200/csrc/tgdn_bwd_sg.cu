@@ -27,16 +27,22 @@ __device__ __forceinline__ float sexp2(float x) {
   return y;
 }
 
+// Number of ring stages: four where the gate tables and row-sum partials of the slice count leave room (E <= 8), else
+// three.  Each stage that holds data already consumed by neither reader is a stage not in flight; the fourth stage is what
+// keeps about two half-slice pairs (64 KB) travelling while two more wait for their MMAs.
+template <int E>
 struct SgSmem {
+  static constexpr int ES = E | 1;   // row stride of the gate tables and partials (odd: conflict-free)
+  static constexpr int NSTAGE = E <= 8 ? 4 : 3;
   uint8_t kq[32768];            // [K;Q] tile, 128B swizzle
-  uint8_t hp[3][16384];         // half-slices of h, three stages: image (i = d, j = v), SI = 128, SJ = 2048
-  uint8_t gp[3][16384];         // half-slices of G
+  uint8_t hp[NSTAGE][16384];    // half-slices of h: image (i = d, j = v), SI = 128, SJ = 2048
+  uint8_t gp[NSTAGE][16384];    // half-slices of G
   uint8_t va[2][8192];          // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: more owned memory follows)
   uint8_t xa[2][16384];         // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
-  float ga[64 * 17], gr[64 * 17], gcq[64 * 17];
-  float part[2 * 128 * 17];     // row sums per column half
-  float red[16 * (SG_THREADS / 32)];   // per slice and worker warp: partial <h,G>
-  uint64_t bar_kq, bar_load[3], bar_mma[2], bar_built[2], bar_read[3];
+  float ga[64 * ES], gr[64 * ES], gcq[64 * ES];
+  float part[2 * 128 * ES];     // row sums per column half
+  float red[E * (SG_THREADS / 32)];   // per slice and worker warp: partial <h,G>
+  uint64_t bar_kq, bar_load[NSTAGE], bar_mma[2], bar_built[2], bar_read[NSTAGE];
   uint32_t tmem_base;
   int abort;
 };
@@ -45,8 +51,9 @@ template <int E>
 __global__ void __launch_bounds__(SG_BLOCK, 1)
 sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, SgParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  SgSmem& sm = *reinterpret_cast<SgSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  constexpr int ES = 17;
+  using SM = SgSmem<E>;
+  SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int ES = SM::ES, NS = SM::NSTAGE;
   constexpr float LOG2E = 1.4426950408889634f;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool worker = warp < SG_THREADS / 32;
@@ -71,16 +78,12 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   }
   if (tid == 0) {
     mbar_init(&sm.bar_kq, 1);
-    mbar_init(&sm.bar_load[0], 1);
-    mbar_init(&sm.bar_load[1], 1);
-    mbar_init(&sm.bar_load[2], 1);
+    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_load[i], 1);
     mbar_init(&sm.bar_mma[0], 1);
     mbar_init(&sm.bar_mma[1], 1);
     mbar_init(&sm.bar_built[0], SG_THREADS / 32);
     mbar_init(&sm.bar_built[1], SG_THREADS / 32);
-    mbar_init(&sm.bar_read[0], SG_THREADS / 32);
-    mbar_init(&sm.bar_read[1], SG_THREADS / 32);
-    mbar_init(&sm.bar_read[2], SG_THREADS / 32);
+    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_read[i], SG_THREADS / 32);
     mbar_fence_init();
     sm.abort = 0;
   }
@@ -95,20 +98,18 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
   const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
   auto issue_step = [&](int s) {                     // one lane of the issuing warp
-    const int st = s % 3;
+    const int st = s % NS;
     mbar_expect_tx(&sm.bar_load[st], 32768);
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
     bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
   };
-  if (issuer) {                                        // all three stages are free at the start
+  if (issuer) {                                        // every stage is free at the start
     mbar_expect_tx(&sm.bar_kq, 32768);
     tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 16384, &map_k, &sm.bar_kq, 64, h, t0, b);
     tma_load_4d(sm.kq + 24576, &map_q, &sm.bar_kq, 64, h, t0, b);
-    issue_step(0);
-    issue_step(1);
-    if (STEPS > 2) issue_step(2);
+    issue_step(0);                                     // the rest of the ring follows once the workers' own loads are back
   }
 
   // All global loads of the prologue go out together, from clamped (always valid) addresses, and are masked when they are
@@ -174,7 +175,6 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       for (int j = 0; j < 16; ++j) uw[vh][j] = 0u;
   }
   __syncthreads();
-  mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);
 
   // Pipeline over the 2E half-slice steps s = 2e + vh.  The MMA warp keeps the tensor core fed: the MMAs of step s go out
   // as soon as their operands and half-slices are there.  The workers accumulate <h,G> of step s from shared memory while
@@ -209,7 +209,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     }
   };
   auto issue_mma = [&](int s, int vh) {                  // one lane of the issuing warp
-    const int st = s % 3;
+    const int st = s % NS;
     tc_fence_after();
     const uint64_t dxa = make_desc(smem_u32(sm.xa[vh]), 2048, 128, LAYOUT_PLAIN);
     const uint64_t dva = make_desc(smem_u32(sm.va[vh]), 1024, 128, LAYOUT_PLAIN);
@@ -246,8 +246,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     rowsum += (a0 + a1) + (a2 + a3);
   };
   auto dot_half = [&](int s, float& dot) {               // <h, G> over the half-slice of step s: 1024 16-byte pieces
-    const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[s % 3]);
-    const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[s % 3]);
+    const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[s % NS]);
+    const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[s % NS]);
     float d[4] = {0.f, 0.f, 0.f, 0.f};                     // independent chains
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -286,12 +286,12 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       // ---- step s = 2e (vh = 0) ----
       {
         const int s = 2 * e;
-        mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+        mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
         dot_half(s, dot);
         mbar_wait(&sm.bar_mma[0], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
         tc_fence_after();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.bar_read[s % 3]);   // this warp is done with the stage, and so is the tensor core
+        if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);   // this warp is done with the stage, and so is the tensor core
         row_sums(V0{}, rowsum);
         if (e + 1 < E) {
           build(e + 1, V0{});
@@ -304,7 +304,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       // ---- step s = 2e + 1 (vh = 1) ----
       {
         const int s = 2 * e + 1;
-        mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+        mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
         dot_half(s, dot);
         for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         mbar_wait(&sm.bar_mma[1], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
@@ -312,7 +312,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) {
           sm.red[e * (SG_THREADS / 32) + warp] = dot;
-          mbar_arrive(&sm.bar_read[s % 3]);
+          mbar_arrive(&sm.bar_read[s % NS]);
         }
         dot = 0.f;
         row_sums(V1{}, rowsum);
@@ -328,16 +328,17 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       }
     }
   } else if (warp_u == SG_THREADS / 32) {                // MMA issue
+    mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);       // the R products read the [K;Q] tile
 #pragma unroll 1
     for (int s = 0; s < STEPS; ++s) {
       const int vh = s & 1;
       mbar_wait(&sm.bar_built[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
-      mbar_wait(&sm.bar_load[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
+      mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
       tc_fence_after();
       if (elect_one()) issue_mma(s, vh);
       __syncwarp();
     }
-  } else {                                               // bulk loads: step s+3 goes into the stage step s has released
+  } else {                                               // bulk loads: step s+NS goes into the stage step s has released
     // Late in this block's life, pull the inputs of the block that will follow it on some SM into L2: its prologue then
     // waits for L2 instead of for an HBM system that the streaming of all the other blocks keeps saturated.
     auto warm_successor = [&]() {
@@ -354,7 +355,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
         tma_prefetch_4d(&map_k, 64, h2, t2, b2);
         tma_prefetch_4d(&map_q, 64, h2, t2, b2);
         const int64_t slice = static_cast<int64_t>(E) * 32768;
-        const uint32_t lead = static_cast<uint32_t>(min(3, STEPS)) * 16384u;
+        const uint32_t lead = static_cast<uint32_t>(min(NS, STEPS)) * 16384u;
         bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + item2 * slice, lead);
         bulk_prefetch(reinterpret_cast<const uint8_t*>(p.ds) + item2 * slice, lead);
         bulk_prefetch(p.U + item2 * (64 * HEAD), 64 * HEAD * 2);
@@ -373,13 +374,19 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     };
     // A worker warp releases a stage only after it has seen the MMAs of that step complete, so bar_read alone says that
     // both readers of the stage are done; this warp never waits on bar_mma, whose phases it could fall behind.
+    // The first loads of a block compete with the workers' prologue loads, which gate the first MMA; only the tile and
+    // step 0 went out at the start, the rest of the ring is filled now that the prologue values have arrived.
+    if (elect_one()) {
+      for (int s = 1; s < NS && s < STEPS; ++s) issue_step(s);
+    }
+    __syncwarp();
 #pragma unroll 1
-    for (int s = 0; s + 3 < STEPS; ++s) {
-      mbar_wait(&sm.bar_read[s % 3], (s / 3) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (elect_one()) issue_step(s + 3);
+    for (int s = 0; s + NS < STEPS; ++s) {
+      mbar_wait(&sm.bar_read[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (elect_one()) issue_step(s + NS);
       __syncwarp();
     }
-    warm_successor();                                    // nothing left to wait for: about three steps and the epilogue remain
+    warm_successor();                                    // nothing left to wait for: only the last steps and the epilogue remain
   }
   __syncthreads();
   if (tid < E) {                                       // <h_e, G_e>: the eight warps' partial sums in a fixed order
@@ -425,7 +432,8 @@ using namespace tgdn;
 
 template <int E>
 static int launch_sg(const CUtensorMap& mk, const CUtensorMap& mq, const SgParams& p, cudaStream_t s) {
-  const int smem = static_cast<int>(sizeof(SgSmem)) + 1024;
+  const int smem = static_cast<int>(sizeof(SgSmem<E>)) + 1024;
+  static_assert(sizeof(SgSmem<E>) + 1024 <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(sg_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   sg_kernel<E><<<p.B * p.NC * p.H, SG_BLOCK, smem, s>>>(mk, mq, p);
