@@ -48,6 +48,14 @@ KERNEL_U = {
     "masks": lambda E: 2, "fwd": lambda E: 2 + 6 * E, "rec": lambda E: 3 + 6 * E, "sg": lambda E: 6 * E, "mat": lambda E: 8,
 }
 
+# DRAM bytes (read + write) per (chunk, head) item and launch at E = 8, from one ncu capture of each kernel on the `prof`
+# workload (4096 items; profiles/core_kernels_prof_workload.md).  Traffic grows in proportion to the item count, so a
+# full launch is this figure times its items.
+NCU_DRAM_BYTES_PER_ITEM_E8 = {
+    "masks": (0.161 + 0.073) * 1e9 / 4096, "fwd": (0.378 + 1.222) * 1e9 / 4096, "rec": (0.485 + 1.221) * 1e9 / 4096,
+    "sg": (2.510 + 0.146) * 1e9 / 4096, "mat": (0.714 + 0.143) * 1e9 / 4096,
+}
+
 
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -265,7 +273,8 @@ def run_ours(args, rank, world, local_rank):
         flops = KERNEL_U[top](E) * U_FLOP * items
         achieved = flops / (st[top] * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": achieved / pk["tflops"], "traffic": None, "peak_kind": pk["kind"],
+                "frac": achieved / pk["tflops"],
+                "traffic": NCU_DRAM_BYTES_PER_ITEM_E8[top] * items if E == 8 else None, "peak_kind": pk["kind"],
                 "kernel_ms": {k: round(v, 3) for k, v in st.items()}, "share": round(st[top] / total, 3),
                 "step_achieved": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12,
                 "step_frac": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12 / pk["tflops"]}
