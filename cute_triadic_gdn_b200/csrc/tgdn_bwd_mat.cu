@@ -60,6 +60,7 @@ struct MatSmem {
   uint64_t bar_load, bar_mma;
   uint32_t tmem_base;
   int abort;
+  int steep;                         // set when a 16-row block decays by more than 2^-100: the direct decay path is taken
 };
 
 template <int E>
@@ -96,6 +97,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_init(&sm.bar_mma, 1);
     mbar_fence_init();
     sm.abort = 0;
+    sm.steep = 0;
   }
   if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -186,6 +188,22 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     umma_commit(&sm.bar_mma);
   }
   __syncwarp();                                           // the other lanes must not run ahead into a spin wait
+  // Decay tables, built while G1 and G2 run.  With r0(s) the first row of s's 16-row block,
+  //   exp2(gc[t] - gc[s]) = exp2(gc[t] - gc[r0(s)]) * exp2(gc[r0(s)] - gc[s])        for every t >= s:
+  // a factor that depends on t and on the column block only (E exponentials per thread and block) and a factor that
+  // depends on s only (a table).  The second exponent is positive but bounded by the decay inside one block; when a
+  // block decays by more than 2^-100 (a flush of the first factor could then hide a product of order one) the whole
+  // CTA takes the direct path with one exponential per (t, s, e) instead.
+  //   Hd[s][e] = exp2(gc[r0(s)][e] - gc[s][e]) * k2[s][e]          Xd[t][e] = exp2(gc[t][e] - gc[r0(t)][e])
+  float* const Hd = sm.dgc;                                // dgc itself is written much later (gate gradients)
+  float* const Xd = sm.c2;
+  for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
+    const int rr = idx / E, e = idx % E, o = rr * ES + e;
+    const float up = sm.gc2[(rr & ~15) * ES + e] - sm.gc2[o];    // >= 0 when gc does not increase
+    if (!(up <= 100.f) || up < 0.f) sm.steep = 1;          // too steep, not monotone, or NaN
+    Hd[o] = mexp2(up) * sm.k2[o];
+    Xd[o] = mexp2(-up);
+  }
   uint32_t mma_phase = 0;
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
   ++mma_phase;
@@ -204,6 +222,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     my2[e] = krow ? sm.k2[t * ES + e] : sm.q2[t * ES + e];
     mygc[e] = sm.gc2[t * ES + e];
   }
+  const bool fast = sm.steep == 0;                         // block-uniform
   const uint32_t a5 = smem_u32(sm.u1.a5);
   const int warp_tmax = (warp & 1) ? 63 : 31;              // largest row index t in this warp
   // From here to the barrier before G5 the two halves of the CTA run independent chains and synchronise among
@@ -221,6 +240,39 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
     for (int e = 0; e < E; ++e) r1v[e] = 0.f;
     float xrow[16];
+    if (fast) {
+      float F[E], G[E], accr[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        F[e] = mexp2(fminf(mygc[e] - sm.gc2[s0 * ES + e], 0.f));   // rows above the block (masked below) would give > 0
+        G[e] = my2[e] * F[e];
+        accr[e] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int s = s0 + j;
+        float x = 0.f, dmpv = 0.f;
+        if (s0 <= warp_tmax) {
+          float hk[E];
+          float mp = 0.f;
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            hk[e] = Hd[s * ES + e];
+            mp = fmaf(G[e], hk[e], mp);
+          }
+          const float in = (s <= t) ? p.scale * gr[j] : 0.f;
+          x = in * mp;
+          dmpv = live * in * pr[j];
+#pragma unroll
+          for (int e = 0; e < E; ++e) accr[e] = fmaf(dmpv, hk[e], accr[e]);
+        }
+        xrow[j] = x;
+        sm.u2.f.dmp[midx(t, s)] = dmpv;
+        st_shared_b16(a5 + (s >> 3) * 128 + ((64 + t) >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, x);   // a5[s][64+t]
+      }
+#pragma unroll
+      for (int e = 0; e < E; ++e) r1v[e] = F[e] * accr[e];
+    } else {
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const int s = s0 + j;
@@ -241,6 +293,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       xrow[j] = x;
       sm.u2.f.dmp[midx(t, s)] = dmpv;
       st_shared_b16(a5 + (s >> 3) * 128 + ((64 + t) >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, x);   // a5[s][64+t]
+    }
     }
     const uint32_t rowbase = a5 + ((64 + t) >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
@@ -264,11 +317,23 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       float c1v[E];
 #pragma unroll
       for (int e = 0; e < E; ++e) c1v[e] = 0.f;
-      for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
-        const float dv = sm.u2.f.dmp[midx(tt, s)];
+      if (fast) {
+        for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
+          const float dv = sm.u2.f.dmp[midx(tt, s)];
 #pragma unroll
-        for (int e = 0; e < E; ++e)
-          c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
+          for (int e = 0; e < E; ++e) c1v[e] = fmaf(dv * sm.q2[tt * ES + e], Xd[tt * ES + e], c1v[e]);
+        }
+        if (s0 + 15 >= s) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) c1v[e] *= mexp2(sm.gc2[s0 * ES + e] - mygc[e]);
+        }
+      } else {
+        for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
+          const float dv = sm.u2.f.dmp[midx(tt, s)];
+  #pragma unroll
+          for (int e = 0; e < E; ++e)
+            c1v[e] = fmaf(dv * sm.q2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c1v[e]);
+        }
       }
 #pragma unroll
       for (int e = 0; e < E; ++e) sm.part[1][cq][s * ES + e] = c1v[e];
@@ -367,6 +432,42 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       float r2v[E];
 #pragma unroll
       for (int e = 0; e < E; ++e) r2v[e] = 0.f;
+      if (fast) {
+        float F[E], G[E], accr[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          F[e] = mexp2(fminf(mygc[e] - sm.gc2[s0 * ES + e], 0.f));
+          G[e] = my2[e] * F[e];
+          accr[e] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int s = s0 + j;
+          float dmv = 0.f;
+          if (s0 <= warp_tmax) {
+            float hk[E];
+            float m = 0.f;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              hk[e] = Hd[s * ES + e];
+              m = fmaf(G[e], hk[e], m);
+            }
+            const float dl = (s < t) ? -dpr[j] : 0.f;
+            brow = fmaf(dl * pr[j], m, brow);
+            dmv = bt * dl * pr[j];
+            const float dpk = bt * dl * m;
+#pragma unroll
+            for (int e = 0; e < E; ++e) accr[e] = fmaf(dmv, hk[e], accr[e]);
+            if (s < t) {
+              st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
+              st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
+            }
+          }
+          sm.u2.f.dm[midx(t, s)] = dmv;
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) r2v[e] = F[e] * accr[e];
+      } else {
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int s = s0 + j;
@@ -389,6 +490,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
         }
         sm.u2.f.dm[midx(t, s)] = dmv;
+      }
       }
       if (cq == (t >> 4)) st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);   // diagonal
 #pragma unroll
@@ -426,11 +528,23 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
     for (int e = 0; e < E; ++e) c2v[e] = 0.f;
     const int lo = s0 + (krow ? 0 : 8);
-    for (int tt = max(t + 1, lo); tt < lo + 8; ++tt) {
-      const float dv = sm.u2.f.dm[midx(tt, t)];
+    if (fast) {
+      for (int tt = max(t + 1, lo); tt < lo + 8; ++tt) {
+        const float dv = sm.u2.f.dm[midx(tt, t)];
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        c2v[e] = fmaf(dv * sm.k2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c2v[e]);
+        for (int e = 0; e < E; ++e) c2v[e] = fmaf(dv * sm.k2[tt * ES + e], Xd[tt * ES + e], c2v[e]);
+      }
+      if (s0 + 15 > t) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) c2v[e] *= mexp2(sm.gc2[s0 * ES + e] - mygc[e]);
+      }
+    } else {
+      for (int tt = max(t + 1, lo); tt < lo + 8; ++tt) {
+        const float dv = sm.u2.f.dm[midx(tt, t)];
+  #pragma unroll
+        for (int e = 0; e < E; ++e)
+          c2v[e] = fmaf(dv * sm.k2[tt * ES + e], mexp2(sm.gc2[tt * ES + e] - mygc[e]), c2v[e]);
+      }
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) sm.part[krow ? 0 : 1][cq][t * ES + e] = c2v[e];

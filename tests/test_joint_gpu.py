@@ -94,3 +94,18 @@ def test_inference_path_and_argument_checks():
     with pytest.raises(ValueError):
         gdn_joint_call(*[t.repeat(2, *([1] * (t.ndim - 1))) for t in inputs],
                        cu_seqlens=torch.tensor([0, 128], dtype=torch.int32, device="cuda"))   # packed needs B = 1
+
+
+@pytest.mark.parametrize("E", [2, 8])
+def test_steep_decay_takes_the_direct_mask_gradient_path(E):
+    """Gates of -6 .. -10 per token: a 16-row block decays by far more than 2^-100, which switches the matrix-gradient
+    kernel from its factorised decay tables to one exponential per (t, s, e); the results must still match the oracle."""
+    B, T, H = 1, 256, 2
+    inputs = list(orc.make_inputs(B, T, H, E, seed=900 + E, dist="mild"))
+    gen = torch.Generator().manual_seed(17)
+    inputs[5] = -(6.0 + 4.0 * torch.rand(B, T, H, E, generator=gen))
+    do = orc.make_grad_output((B, T, H, 128), 7)
+    o_ref, g_ref = orc.reference_with_grads(orc.chunk_reference, inputs, do, dtype=torch.float32)
+    o_ker, g_ker = run(chunk_gdn_joint, inputs, do, None)
+    assert _lib.device_status() == 0
+    compare(o_ker, g_ker, o_ref, g_ref)
