@@ -123,9 +123,12 @@ def state_grad_stage(K, Q, dO, fw, rv, rounding):
     a, c, r = (gt[x].transpose(2, 3)[..., None] for x in "acr")                 # (N,NC,E,64,1)
     h, G = fw["h"], rv["ds"]                                                    # (N,NC,E,D,V)
     dW, U = rv["dV"], fw["U"]
-    X1, X2, Vn = rd(-a * dW[:, :, None]), rd(c * dO[:, :, None]), rd(r * U[:, :, None])
-    dK = torch.einsum('ncetv,ncedv->nctd', X1, h) + torch.einsum('ncetv,ncedv->nctd', Vn, G)
-    dQ = torch.einsum('ncetv,ncedv->nctd', X2, h)
+    # the kernel scales its operands with one packed bf16 multiply: the gate factor is rounded to bf16 first, then the
+    # product is rounded once more
+    X1, X2, Vn = rd(rd(-a) * dW[:, :, None]), rd(rd(c) * dO[:, :, None]), rd(rd(r) * U[:, :, None])
+    # the state parts of dK and dQ are handed to the matrix kernel as bf16
+    dK = rd(torch.einsum('ncetv,ncedv->nctd', X1, h) + torch.einsum('ncetv,ncedv->nctd', Vn, G))
+    dQ = rd(torch.einsum('ncetv,ncedv->nctd', X2, h))
     R = torch.einsum('nctd,ncedv->ncetv', K, h)
     Rq = torch.einsum('nctd,ncedv->ncetv', Q, h)
     da = -torch.einsum('nctv,ncetv->ncte', dW, R)
