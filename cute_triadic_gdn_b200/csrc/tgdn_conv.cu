@@ -174,31 +174,57 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
     const int t_first = tile * CONV_TOK + rg * 8;         // this warp's first output token; its smem row is rg*8 + 3
     DocCursor doc;
     doc.init(a.cu, a.n_docs, min(t_first, a.T - 1), a.T);
-    Vec4 xm[3];                                           // x[t-1], x[t-2], x[t-3]
-#pragma unroll
-    for (int j = 0; j < 3; ++j) {
-      const int tj = t_first - 1 - j;
-      xm[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
-    }
     __nv_bfloat16* yrow = yb + static_cast<int64_t>(t_first) * a.C;
-    const int n_rows = min(8, a.T - t_first);
+    // Interior of a document and of the sequence: no start of a document among the warp's eight rows or their three halo
+    // rows (rows before the sequence come back as zeros from the tensor map, which is what a start at token 0 means),
+    // all eight rows exist.  Then the rows need no cursor, no bounds and no window resets; almost every tile is like this.
+    const bool interior = t_first + 8 <= a.T && doc.next >= t_first + 8 && doc.start <= max(t_first - 3, 0);
+    if (interior && live && (act[0] == act[3])) {
+      const bool on = act[0];
+      Vec4 xm[3];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (i >= n_rows) break;
-      if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
-      const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
-      Vec4 out;
+      for (int j = 0; j < 3; ++j) xm[j] = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2)));
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        float2 acc = __fmul2_rn(xm[2].p[p], w2[p][0]);
-        acc = __ffma2_rn(xm[1].p[p], w2[p][1], acc);
-        acc = __ffma2_rn(xm[0].p[p], w2[p][2], acc);
-        acc = __ffma2_rn(x0.p[p], w2[p][3], acc);
-        out.p[p] = make_float2(act[2 * p] ? silu(acc.x) : acc.x, act[2 * p + 1] ? silu(acc.y) : acc.y);
+      for (int i = 0; i < 8; ++i) {
+        const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+        Vec4 out;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          float2 acc = __fmul2_rn(xm[2].p[p], w2[p][0]);
+          acc = __ffma2_rn(xm[1].p[p], w2[p][1], acc);
+          acc = __ffma2_rn(xm[0].p[p], w2[p][2], acc);
+          acc = __ffma2_rn(x0.p[p], w2[p][3], acc);
+          out.p[p] = on ? make_float2(silu(acc.x), silu(acc.y)) : acc;
+        }
+        store4(yrow + static_cast<int64_t>(i) * a.C, out);
+        xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
       }
-      if (live) store4(yrow, out);
-      yrow += a.C;
-      xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
+    } else {
+      Vec4 xm[3];                                           // x[t-1], x[t-2], x[t-3]
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const int tj = t_first - 1 - j;
+        xm[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+      }
+      const int n_rows = min(8, a.T - t_first);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (i >= n_rows) break;
+        if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
+        const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+        Vec4 out;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+          float2 acc = __fmul2_rn(xm[2].p[p], w2[p][0]);
+          acc = __ffma2_rn(xm[1].p[p], w2[p][1], acc);
+          acc = __ffma2_rn(xm[0].p[p], w2[p][2], acc);
+          acc = __ffma2_rn(x0.p[p], w2[p][3], acc);
+          out.p[p] = make_float2(act[2 * p] ? silu(acc.x) : acc.x, act[2 * p + 1] ? silu(acc.y) : acc.y);
+        }
+        if (live) store4(yrow, out);
+        yrow += a.C;
+        xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
+      }
     }
     __syncthreads();                                      // every warp is done with this stage
     if (tid == 0 && tile + CONV_FWD_STAGES < tile_hi) issue(tile + CONV_FWD_STAGES);
@@ -258,35 +284,31 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // (three tokens past the warp's rows) with the x window and the last three dy' in registers.
     DocCursor doc;
     doc.init(a.cu, a.n_docs, min(u_first, a.T - 1), a.T);
-    Vec4 xw[3];                                                        // x[t-1], x[t-2], x[t-3]
+    // Interior of a document and of the sequence: no start of a document among the eleven tokens the warp walks or their
+    // three halo rows, and all of them exist.  Then no cursor, no bounds and no masks are needed; almost every tile is
+    // like this.
+    const bool interior = u_first + 11 <= a.T && doc.next >= u_first + 11 && doc.start <= max(u_first - 3, 0);
+    if (interior && live && (act[0] == act[3])) {
+      const bool on = act[0];
+      Vec4 xw[3];
 #pragma unroll
-    for (int j = 0; j < 3; ++j) {
-      const int tj = u_first - 1 - j;
-      xw[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
-    }
-    Vec4 gw[3] = {zero4(), zero4(), zero4()};                          // dy'[t-1], dy'[t-2], dy'[t-3]
-    int ds1 = 0x7fffffff, ds2 = 0x7fffffff;                            // document starts of tokens t-1, t-2
+      for (int j = 0; j < 3; ++j) xw[j] = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2)));
+      Vec4 gw[3] = {zero4(), zero4(), zero4()};
 #pragma unroll
-    for (int i = 0; i < 11; ++i) {
-      const int t = u_first + i;
-      Vec4 gy = zero4(), x0 = zero4();
-      int ds0 = 0x7fffffff;
-      if (t < a.T) {
-        if (i > 0 && doc.advance(t)) { xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
-        ds0 = doc.start;
-        x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
-        const Vec4 g = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+      for (int i = 0; i < 11; ++i) {
+        const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+        Vec4 gy = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+        if (on) {
 #pragma unroll
-        for (int p = 0; p < 2; ++p) {                                  // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
-          float2 pre = __fmul2_rn(xw[2].p[p], w2[p][0]);
-          pre = __ffma2_rn(xw[1].p[p], w2[p][1], pre);
-          pre = __ffma2_rn(xw[0].p[p], w2[p][2], pre);
-          pre = __ffma2_rn(x0.p[p], w2[p][3], pre);
-          const float2 sg2 = make_float2(act[2 * p] ? silu_grad(round_bf16(pre.x)) : 1.f,
-                                         act[2 * p + 1] ? silu_grad(round_bf16(pre.y)) : 1.f);
-          gy.p[p] = __fmul2_rn(g.p[p], sg2);
+          for (int p = 0; p < 2; ++p) {
+            float2 pre = __fmul2_rn(xw[2].p[p], w2[p][0]);
+            pre = __ffma2_rn(xw[1].p[p], w2[p][1], pre);
+            pre = __ffma2_rn(xw[0].p[p], w2[p][2], pre);
+            pre = __ffma2_rn(x0.p[p], w2[p][3], pre);
+            gy.p[p] = __fmul2_rn(gy.p[p], make_float2(silu_grad(round_bf16(pre.x)), silu_grad(round_bf16(pre.y))));
+          }
         }
-        if (i < 8) {                                                   // the weight gradient of token t belongs to this warp
+        if (i < 8) {
 #pragma unroll
           for (int p = 0; p < 2; ++p) {
             dwa[p][0] = __ffma2_rn(gy.p[p], xw[2].p[p], dwa[p][0]);
@@ -295,27 +317,81 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             dwa[p][3] = __ffma2_rn(gy.p[p], x0.p[p], dwa[p][3]);
           }
         }
-      }
-      if (i >= 3) {
-        const int u = t - 3;
-        if (u < a.T && live) {
-          const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
-          const float2 m22 = make_float2(m2, m2), m12 = make_float2(m1, m1), m02 = make_float2(m0, m0);
+        if (i >= 3) {
           Vec4 out;
 #pragma unroll
           for (int p = 0; p < 2; ++p) {
             float2 acc = __fmul2_rn(gw[2].p[p], w2[p][3]);
-            acc = __ffma2_rn(__fmul2_rn(m22, gw[1].p[p]), w2[p][2], acc);
-            acc = __ffma2_rn(__fmul2_rn(m12, gw[0].p[p]), w2[p][1], acc);
-            acc = __ffma2_rn(__fmul2_rn(m02, gy.p[p]), w2[p][0], acc);
+            acc = __ffma2_rn(gw[1].p[p], w2[p][2], acc);
+            acc = __ffma2_rn(gw[0].p[p], w2[p][1], acc);
+            acc = __ffma2_rn(gy.p[p], w2[p][0], acc);
             out.p[p] = acc;
           }
-          store4(dxb + static_cast<int64_t>(u) * a.C, out);
+          store4(dxb + static_cast<int64_t>(u_first + i - 3) * a.C, out);
         }
+        gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
+        xw[2] = xw[1]; xw[1] = xw[0]; xw[0] = x0;
       }
-      gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
-      ds2 = ds1; ds1 = ds0;
-      xw[2] = xw[1]; xw[1] = xw[0]; xw[0] = x0;
+    } else {
+      Vec4 xw[3];                                                        // x[t-1], x[t-2], x[t-3]
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        const int tj = u_first - 1 - j;
+        xw[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+      }
+      Vec4 gw[3] = {zero4(), zero4(), zero4()};                          // dy'[t-1], dy'[t-2], dy'[t-3]
+      int ds1 = 0x7fffffff, ds2 = 0x7fffffff;                            // document starts of tokens t-1, t-2
+#pragma unroll
+      for (int i = 0; i < 11; ++i) {
+        const int t = u_first + i;
+        Vec4 gy = zero4(), x0 = zero4();
+        int ds0 = 0x7fffffff;
+        if (t < a.T) {
+          if (i > 0 && doc.advance(t)) { xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
+          ds0 = doc.start;
+          x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+          const Vec4 g = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {                                  // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
+            float2 pre = __fmul2_rn(xw[2].p[p], w2[p][0]);
+            pre = __ffma2_rn(xw[1].p[p], w2[p][1], pre);
+            pre = __ffma2_rn(xw[0].p[p], w2[p][2], pre);
+            pre = __ffma2_rn(x0.p[p], w2[p][3], pre);
+            const float2 sg2 = make_float2(act[2 * p] ? silu_grad(round_bf16(pre.x)) : 1.f,
+                                           act[2 * p + 1] ? silu_grad(round_bf16(pre.y)) : 1.f);
+            gy.p[p] = __fmul2_rn(g.p[p], sg2);
+          }
+          if (i < 8) {                                                   // the weight gradient of token t belongs to this warp
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+              dwa[p][0] = __ffma2_rn(gy.p[p], xw[2].p[p], dwa[p][0]);
+              dwa[p][1] = __ffma2_rn(gy.p[p], xw[1].p[p], dwa[p][1]);
+              dwa[p][2] = __ffma2_rn(gy.p[p], xw[0].p[p], dwa[p][2]);
+              dwa[p][3] = __ffma2_rn(gy.p[p], x0.p[p], dwa[p][3]);
+            }
+          }
+        }
+        if (i >= 3) {
+          const int u = t - 3;
+          if (u < a.T && live) {
+            const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
+            const float2 m22 = make_float2(m2, m2), m12 = make_float2(m1, m1), m02 = make_float2(m0, m0);
+            Vec4 out;
+#pragma unroll
+            for (int p = 0; p < 2; ++p) {
+              float2 acc = __fmul2_rn(gw[2].p[p], w2[p][3]);
+              acc = __ffma2_rn(__fmul2_rn(m22, gw[1].p[p]), w2[p][2], acc);
+              acc = __ffma2_rn(__fmul2_rn(m12, gw[0].p[p]), w2[p][1], acc);
+              acc = __ffma2_rn(__fmul2_rn(m02, gy.p[p]), w2[p][0], acc);
+              out.p[p] = acc;
+            }
+            store4(dxb + static_cast<int64_t>(u) * a.C, out);
+          }
+        }
+        gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
+        ds2 = ds1; ds1 = ds0;
+        xw[2] = xw[1]; xw[1] = xw[0]; xw[0] = x0;
+      }
     }
     __syncthreads();
     if (tid == 0 && tile + CONV_BWD_STAGES < tile_hi) issue(tile + CONV_BWD_STAGES);

@@ -76,11 +76,13 @@ struct MaskSmem {
   float gc2[64 * E];       // log2-domain cumulative gate
   float k2[64 * E];
   float q2[64 * E];
+  float hd[64 * E];        // exp2(gc[first row of s's 16-row block] - gc[s]) * k2[s]
   float pad[(3 * 64 * E * 4 >= 8192) ? 1 : (8192 - 3 * 64 * E * 4) / 4];
   float beta[64];
   uint64_t bar_load, bar_mma;
   uint32_t tmem_base;
   int abort;
+  int steep;               // a 16-row block decays by more than 2^-100 (or gc is not monotone): direct decay path
 };
 
 // X21 = -X22 (L21 X11) for the diagonal blocks of size 2n (n = 16: two blocks, n = 32: one), one 16x8 tile per warp.
@@ -144,6 +146,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     mbar_init(&sm.bar_mma, 1);
     mbar_fence_init();
     sm.abort = 0;
+    sm.steep = 0;
   }
   if (warp == 0) { tmem_alloc(&sm.tmem_base, 128); tmem_relinquish(); }
   tc_fence_before();
@@ -205,6 +208,17 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     sm.gc2[(lane + 32) * E + e] = v1 * LOG2E;
   }
   __syncthreads();
+  // Decay table for the mask sums.  With r0(s) the first row of s's 16-row block,
+  //   exp2(gc[t] - gc[s]) = exp2(gc[t] - gc[r0(s)]) * exp2(gc[r0(s)] - gc[s])        for every t >= s:
+  // the first factor costs E exponentials per thread and column block, the second is this table.  Its exponent is
+  // positive but bounded by the decay inside one block; when a block decays by more than 2^-100 (a flush of the first
+  // factor could then hide a product of order one) the CTA takes one exponential per (t, s, e) instead.
+  for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
+    const int rr = idx / E, e = idx % E;
+    const float up = sm.gc2[(rr & ~15) * E + e] - sm.gc2[idx];   // >= 0 when gc does not increase
+    if (!(up <= 100.f) || up < 0.f) sm.steep = 1;                // too steep, not monotone, or NaN
+    sm.hd[idx] = fast_exp2(up) * sm.k2[idx];
+  }
 
   // Gram product [K;Q] K^T
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
@@ -244,33 +258,66 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     const float rowscale = isq ? p.scale : sm.beta[t];
     float* dst = isq ? sm.Pm : sm.u.m.L;
     const int tmax = (warp & 1) ? 63 : 31;                  // largest row of this warp
+    if (sm.steep == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int sb = 16 * i + 8 * ch;
+      for (int i = 0; i < 4; ++i) {
+        const int sb = 16 * i + 8 * ch;
+        float G[E];                                           // my2[e] * exp2(gc[t][e] - gc[16 i][e]); rows above the block are masked
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int s = sb + c;
-        float val = 0.f;
-        if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
-          float acc = 0.f;
-          if constexpr (E % 4 == 0) {
+        for (int e = 0; e < E; ++e) G[e] = my2[e] * fast_exp2(fminf(mygc[e] - sm.gc2[(16 * i) * E + e], 0.f));
 #pragma unroll
-            for (int e = 0; e < E; e += 4) {
-              const float4 g4 = *reinterpret_cast<const float4*>(&sm.gc2[s * E + e]);
-              const float4 k4 = *reinterpret_cast<const float4*>(&sm.k2[s * E + e]);
-              acc = fmaf(my2[e] * k4.x, fast_exp2(mygc[e] - g4.x), acc);
-              acc = fmaf(my2[e + 1] * k4.y, fast_exp2(mygc[e + 1] - g4.y), acc);
-              acc = fmaf(my2[e + 2] * k4.z, fast_exp2(mygc[e + 2] - g4.z), acc);
-              acc = fmaf(my2[e + 3] * k4.w, fast_exp2(mygc[e + 3] - g4.w), acc);
+        for (int c = 0; c < 8; ++c) {
+          const int s = sb + c;
+          float val = 0.f;
+          if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
+            float acc = 0.f;
+            if constexpr (E % 4 == 0) {
+#pragma unroll
+              for (int e = 0; e < E; e += 4) {
+                const float4 h4 = *reinterpret_cast<const float4*>(&sm.hd[s * E + e]);
+                acc = fmaf(G[e], h4.x, acc);
+                acc = fmaf(G[e + 1], h4.y, acc);
+                acc = fmaf(G[e + 2], h4.z, acc);
+                acc = fmaf(G[e + 3], h4.w, acc);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < E; ++e) acc = fmaf(G[e], sm.hd[s * E + e], acc);
             }
-          } else {
-#pragma unroll
-            for (int e = 0; e < E; ++e)
-              acc = fmaf(my2[e] * sm.k2[s * E + e], fast_exp2(mygc[e] - sm.gc2[s * E + e]), acc);
+            val = rowscale * pr[8 * i + c] * acc;
           }
-          val = rowscale * pr[8 * i + c] * acc;
+          dst[mat_idx(t, s)] = val;
         }
-        dst[mat_idx(t, s)] = val;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int sb = 16 * i + 8 * ch;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int s = sb + c;
+          float val = 0.f;
+          if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
+            float acc = 0.f;
+            if constexpr (E % 4 == 0) {
+#pragma unroll
+              for (int e = 0; e < E; e += 4) {
+                const float4 g4 = *reinterpret_cast<const float4*>(&sm.gc2[s * E + e]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&sm.k2[s * E + e]);
+                acc = fmaf(my2[e] * k4.x, fast_exp2(mygc[e] - g4.x), acc);
+                acc = fmaf(my2[e + 1] * k4.y, fast_exp2(mygc[e + 1] - g4.y), acc);
+                acc = fmaf(my2[e + 2] * k4.z, fast_exp2(mygc[e + 2] - g4.z), acc);
+                acc = fmaf(my2[e + 3] * k4.w, fast_exp2(mygc[e + 3] - g4.w), acc);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < E; ++e)
+                acc = fmaf(my2[e] * sm.k2[s * E + e], fast_exp2(mygc[e] - sm.gc2[s * E + e]), acc);
+            }
+            val = rowscale * pr[8 * i + c] * acc;
+          }
+          dst[mat_idx(t, s)] = val;
+        }
       }
     }
   }
