@@ -26,7 +26,7 @@ constexpr int CONV_FWD_ROWS = CONV_TOK + 3;       // x rows t0-3 .. t0+31
 constexpr int CONV_BWD_XROWS = CONV_TOK + 6;      // x rows t0-3 .. t0+34
 constexpr int CONV_BWD_GROWS = CONV_TOK + 3;      // dy rows t0 .. t0+34
 constexpr int CONV_FWD_STAGES = 3;     // 54 KB per CTA: four CTAs per SM
-constexpr int CONV_BWD_STAGES = 2;     // 75 KB per CTA: three CTAs per SM
+constexpr int CONV_BWD_STAGES = 3;     // 112 KB per CTA: two CTAs per SM (the backward needs more than 85 registers)
 
 // Four channels of a thread as two packed pairs: the arithmetic runs on the two-wide f32 instructions (one instruction per
 // pair, each lane an ordinary IEEE fma), which halves the instruction count of the kernels' inner loops.
@@ -231,7 +231,7 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(CONV_THREADS, 3)
+__global__ void __launch_bounds__(CONV_THREADS, 2)
 conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy, ConvArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -475,7 +475,7 @@ extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const i
 extern "C" int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C) {
   if (B <= 0 || T <= 0 || C <= 0) return 0;
   int groups, tpg;
-  conv_groups(T, C, 3, &groups, &tpg);
+  conv_groups(T, C, 2, &groups, &tpg);
   return static_cast<int64_t>(B) * groups * C * CONV_W * static_cast<int64_t>(sizeof(float));
 }
 
@@ -491,7 +491,7 @@ static int conv_bwd_launch(const void* x, const void* weight, const void* dy, vo
   if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_BWD_XROWS))) return rc;
   if ((rc = tgdn_make_rows_map(&mg, dy, C, T, B, dy_stride_t, dy_stride_b, CONV_CH, CONV_BWD_GROWS))) return rc;
   int groups, tpg;
-  conv_groups(T, C, 3, &groups, &tpg);
+  conv_groups(T, C, 2, &groups, &tpg);
   ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C,
              act_channels, tpg, tgdn_status_word()};
   const int smem = CONV_BWD_STAGES * (CONV_BWD_XROWS + CONV_BWD_GROWS) * CONV_CH * 2 + 128;

@@ -29,9 +29,9 @@ def test_chunk_capacity_matches_reference_formula(T, N):
 
 
 def _conv_scratch(B, T, C):
-    """One f32 weight-gradient partial of C x 4 per CTA along the token axis (three CTAs per SM in total)."""
+    """One f32 weight-gradient partial of C x 4 per CTA along the token axis (two CTAs per SM in total)."""
     n_tiles, n_ctile = (T + 31) // 32, (C + 255) // 256
-    g = max(1, min(n_tiles, (3 * 148 + n_ctile - 1) // n_ctile))
+    g = max(1, min(n_tiles, (2 * 148 + n_ctile - 1) // n_ctile))
     tpg = (n_tiles + g - 1) // g
     groups = (n_tiles + tpg - 1) // tpg
     return B * groups * C * 4 * 4
