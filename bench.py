@@ -250,7 +250,7 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop() if sampler else None
     if args.kernels_only:
         if rank == 0:
-            print(json.dumps({"metric": "fwd+bwd tokens/s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s",
+            print(json.dumps({"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": B * T * args.steps / (ms * 1e-3), "unit": "tokens/s",
                               "ms_per_step": ms / args.steps, "config": {"workload": args.workload}, "kernels_only": True}))
         return
     ms_e2e = timed(step_e2e, args.steps, max(1, args.warmup // 2))
