@@ -31,7 +31,7 @@ WORKLOADS = {
     # name: (B, T, H, E, backward)
     "c2": (8, 8192, 32, 8, True),
     "c1": (4, 4096, 16, 4, False),
-    "c3": (1, 131072, 16, 16, True),
+    "c3": (1, 131072, 16, 16, True),    # one packed row of lognormal documents (PACKED below)
     "small": (2, 1024, 4, 8, True),
     "prof": (2, 8192, 16, 8, True),     # 4096 (chunk, head) items, a few GB: the size used for ncu captures
 }
@@ -42,6 +42,8 @@ def algorithmic_flops(E, items, backward):
     per = (4 + 6 * E) + ((11 + 12 * E) if backward else 0)
     return per * U_FLOP * items
 
+
+PACKED = {"c3": 31}                  # workload -> seed of its document lengths
 
 # per-kernel algorithmic work, in u per (chunk, head)
 KERNEL_U = {
@@ -108,12 +110,37 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _l2norm(t):
+    return t * torch.rsqrt((t * t).sum(-1, keepdim=True) + 1e-6)
+
+
 def host_inputs(B, T, H, E, seed=0):
-    """Seeded synthetic inputs of the BASELINE distribution, generated in slices to bound host memory."""
-    from oracle import triadic_oracle as orc
-    ins = orc.make_inputs(B, T, H, E, seed)
-    do = orc.make_grad_output((B, T, H, 128), seed + 1)
-    return ins, do
+    """Seeded synthetic inputs of the BASELINE distribution, generated on the CPU in fp32 and then cast:
+    q, k = l2norm(N(0,1)) bf16; v = N(0,1) bf16; k2, q2 = l2norm(N(0,1)) over E; g = -softplus(N(0,1)); beta = sigmoid(N(0,1));
+    dO = N(0,1) bf16.  One generator, draw order q, k, v, k2, q2, g, beta, dO."""
+    gen = torch.Generator().manual_seed(int(seed))
+    r = lambda *shape: torch.randn(*shape, generator=gen)
+    q = _l2norm(r(B, T, H, 128)).to(torch.bfloat16)
+    k = _l2norm(r(B, T, H, 128)).to(torch.bfloat16)
+    v = r(B, T, H, 128).to(torch.bfloat16)
+    k2 = _l2norm(r(B, T, H, E))
+    q2 = _l2norm(r(B, T, H, E))
+    g = -torch.nn.functional.softplus(r(B, T, H, E))
+    beta = torch.sigmoid(r(B, T, H))
+    do = r(B, T, H, 128).to(torch.bfloat16)
+    return [t.contiguous() for t in (q, k, v, k2, q2, g, beta)], do
+
+
+def lognormal_documents(T, seed, median=2048.0, sigma=1.0):
+    """cu_seqlens of a packed row: document lengths max(1, round(lognormal(ln median, sigma))) from a seeded numpy
+    generator, drawn until they cover T, the last one truncated."""
+    import math
+    import numpy as np
+    rng = np.random.default_rng(int(seed))
+    cu = [0]
+    while cu[-1] < T:
+        cu.append(min(T, cu[-1] + max(1, int(round(float(rng.lognormal(math.log(median), sigma)))))))
+    return torch.tensor(cu, dtype=torch.int32)
 
 
 def cpu_reference_rate(B, T, H, E, backward, budget_s=20.0, threads=None):
@@ -195,13 +222,29 @@ def stage_times(leaves, do, E, reps=2):
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from cute_triadic_gdn_b200 import _lib, gdn_joint_call
+    from cute_triadic_gdn_b200.sharding import document_ranges, head_slice
     B, T, H, E, backward = WORKLOADS[args.workload]
-    if H % world:
-        raise SystemExit(f"H={H} is not divisible by {world} GPUs")
-    Hl = H // world                                   # heads of this rank (strong scaling: total work fixed)
+    packed = args.workload in PACKED
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    ins, do = host_inputs(B, T, Hl, E, seed=1000 + rank)
+    cu_host = cu_dev = None
+    if packed:
+        # one packed row: this rank takes a token-balanced range of whole documents, all heads (strong scaling)
+        cu_all = lognormal_documents(T, PACKED[args.workload])
+        rng = document_ranges(cu_all, world)[rank]
+        if rng.doc_hi == rng.doc_lo:
+            raise SystemExit(f"rank {rank} of {world} got no document")
+        cu_host = (cu_all[rng.doc_lo:rng.doc_hi + 1] - cu_all[rng.doc_lo]).contiguous()
+        cu_dev = cu_host.to(dev)
+        Tl, Hl = rng.tok_hi - rng.tok_lo, H
+        chunks = int(((cu_host[1:] - cu_host[:-1] + 63) // 64).sum())
+    else:
+        if H % world:
+            raise SystemExit(f"H={H} is not divisible by {world} GPUs")
+        hs = head_slice(H, world, rank)               # heads of this rank (strong scaling: total work fixed)
+        Tl, Hl = T, hs.stop - hs.start
+        chunks = B * (T // 64)
+    ins, do = host_inputs(B, Tl, Hl, E, seed=1000 + rank)
     pinned = [t.pin_memory() for t in ins]
     do_pinned = do.pin_memory()
     leaves = [t.to(dev).requires_grad_(backward) for t in ins]
@@ -215,7 +258,7 @@ def run_ours(args, rank, world, local_rank):
     def step_resident():
         for t in leaves:
             t.grad = None
-        o = gdn_joint_call(*leaves)
+        o = gdn_joint_call(*leaves, cu_seqlens=cu_dev)
         if backward:
             o.backward(do_dev)
         return o
@@ -223,7 +266,7 @@ def run_ours(args, rank, world, local_rank):
     # end to end through the host-resident entry point: pinned host inputs -> device -> kernels -> pinned host results,
     # with the three stages of successive batch slices overlapping
     from cute_triadic_gdn_b200 import HostPipeline
-    pipe = HostPipeline(pinned, do_pinned if backward else None, slices=B)
+    pipe = HostPipeline(pinned, do_pinned if backward else None, slices=8 if packed else B, cu_seqlens=cu_host)
 
     def step_e2e():
         return pipe.run(pinned, do_pinned if backward else None)
@@ -264,9 +307,14 @@ def run_ours(args, rank, world, local_rank):
         return
 
     pk = peaks()
-    items = B * (T // 64) * Hl
+    items = chunks * Hl                               # (chunk, head) items of this rank
     roof = None
-    if backward:
+    if backward and packed:
+        step_tf = algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "whole step", "achieved": step_tf, "peak": pk["tflops"], "unit": "TFLOP/s",
+                "frac": step_tf / pk["tflops"], "traffic": None, "peak_kind": pk["kind"], "step_achieved": step_tf,
+                "step_frac": step_tf / pk["tflops"]}
+    elif backward:
         st = stage_times(leaves, do_dev, E)
         total = sum(st.values())
         top = max(st, key=st.get)
@@ -282,9 +330,12 @@ def run_ours(args, rank, world, local_rank):
     line = {"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'fwd+bwd' if backward else 'fwd'}, GJ_SAVE_MASKS="
+            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'packed lognormal documents, ' if packed else ''}"
+                                   f"{'fwd+bwd' if backward else 'fwd'}, GJ_SAVE_MASKS="
                                    f"{os.environ.get('GJ_SAVE_MASKS', '1')}",
-                       "parallelism": f"heads sharded over {world} GPU(s), no collective", "l2": "inputs larger than L2",
+                       "parallelism": (f"whole documents, token-balanced, over {world} GPU(s), no collective" if packed
+                                       else f"heads sharded over {world} GPU(s), no collective"),
+                       "l2": "inputs larger than L2",
                        "api": "gdn_joint_call + backward; e2e: HostPipeline (pinned host tensors, batch slices overlapped on three streams)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},

@@ -7,13 +7,16 @@ through a three-stage pipeline on three CUDA streams:
     upload slice i+1   |   forward (+ backward) of slice i   |   download slice i-1
 
 With PCIe carrying both directions at once, a step costs about max(upload, compute, download) instead of their sum.
-The results are bitwise those of one `gdn_joint_call` over the whole batch.
+The results are bitwise those of one `gdn_joint_call` over the whole batch.  A packed row (`cu_seqlens`) is cut the
+same way along its documents, which are just as independent: token-balanced ranges of whole documents
+(`sharding.document_ranges`), each run with its own re-based offsets.
 """
 from __future__ import annotations
 
 import torch
 
 from .joint_torch_ops import gdn_joint_call
+from .sharding import document_ranges
 
 _NAMES = ("q", "k", "v", "k2", "q2", "g", "beta")
 
@@ -29,10 +32,11 @@ class HostPipeline:
     """Reusable buffers and streams for `run`; build once per shape, call every step.
 
     `inputs` are the seven host tensors (q, k, v, k2, q2, g, beta) in the layouts `gdn_joint_call` takes; `do` is the
-    upstream gradient (None: forward only).  `slices` must divide the batch.
+    upstream gradient (None: forward only).  Dense rows: `slices` must divide the batch.  Packed row: `cu_seqlens` (host
+    or device offsets) and `slices` = number of document ranges (empty ranges are dropped).
     """
 
-    def __init__(self, inputs, do=None, *, scale=None, slices=None, device=None):
+    def __init__(self, inputs, do=None, *, scale=None, slices=None, device=None, cu_seqlens=None):
         if len(inputs) != 7:
             raise ValueError("expected (q, k, v, k2, q2, g, beta)")
         for t, n in zip(inputs, _NAMES):
@@ -41,18 +45,32 @@ class HostPipeline:
             _check_host(do, "do")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         B = inputs[0].shape[0]
-        self.slices = B if slices is None else int(slices)
-        if self.slices < 1 or B % self.slices:
-            raise ValueError(f"slices={self.slices} must divide the batch {B}")
-        self.rows = B // self.slices
+        if cu_seqlens is None:
+            self.slices = B if slices is None else int(slices)
+            if self.slices < 1 or B % self.slices:
+                raise ValueError(f"slices={self.slices} must divide the batch {B}")
+            self.rows = B // self.slices
+            # (first, one past last) along the batch axis, offsets on the device (none: dense rows)
+            self.parts = [(i * self.rows, (i + 1) * self.rows, None) for i in range(self.slices)]
+            self.axis = 0
+        else:
+            if B != 1:
+                raise ValueError("packed rows have batch size 1")
+            cu = cu_seqlens.detach().cpu()
+            ranges = [r for r in document_ranges(cu, 1 if slices is None else int(slices)) if r.doc_hi > r.doc_lo]
+            self.slices = len(ranges)
+            self.rows = max(r.tok_hi - r.tok_lo for r in ranges)       # device buffers hold the longest part
+            self.parts = [(r.tok_lo, r.tok_hi, (cu[r.doc_lo:r.doc_hi + 1] - cu[r.doc_lo]).to(torch.int32).to(self.device))
+                          for r in ranges]
+            self.axis = 1
         self.scale = scale
         self.backward = do is not None
         dev = self.device
         # two device-side input sets (upload of slice i+1 overlaps the kernels of slice i)
-        self._in = [[torch.empty((self.rows,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in inputs]
-                    for _ in range(2)]
-        self._do = [torch.empty((self.rows,) + tuple(do.shape[1:]), dtype=do.dtype, device=dev) for _ in range(2)] \
-            if self.backward else None
+        shape = (lambda t: (self.rows,) + tuple(t.shape[1:])) if self.axis == 0 else \
+            (lambda t: (1, self.rows) + tuple(t.shape[2:]))
+        self._in = [[torch.empty(shape(t), dtype=t.dtype, device=dev) for t in inputs] for _ in range(2)]
+        self._do = [torch.empty(shape(do), dtype=do.dtype, device=dev) for _ in range(2)] if self.backward else None
         self.up, self.down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         self.o_host = torch.empty(tuple(inputs[2].shape), dtype=inputs[2].dtype, pin_memory=True)
         self.grads_host = [torch.empty(tuple(t.shape), dtype=t.dtype, pin_memory=True) for t in inputs] \
@@ -66,7 +84,7 @@ class HostPipeline:
         """One step.  Returns (o_host, grads_host or None); the host buffers are reused by the next call."""
         if (do is not None) != self.backward:
             raise ValueError("`do` must be given exactly when the pipeline was built with one")
-        dev, rows = self.device, self.rows
+        dev = self.device
         compute = torch.cuda.current_stream(dev)
         uploaded = [None, None]      # event: input set s holds the slice
         consumed = [None, None]      # event: the kernels that read input set s are done
@@ -74,24 +92,26 @@ class HostPipeline:
         start.record(compute)
         self.up.wait_event(start)    # do not start uploading over buffers an earlier step may still read
         self.down.wait_event(start)
-        for i in range(self.slices):
+        for i, (lo, hi, cu_dev) in enumerate(self.parts):
             s = i & 1
-            lo, hi = i * rows, (i + 1) * rows
+            n = hi - lo
+            cut = (lambda t: t[lo:hi]) if self.axis == 0 else (lambda t: t[:, lo:hi])        # of a host tensor
+            head = (lambda t: t[:n]) if self.axis == 0 else (lambda t: t[:, :n])            # of a device buffer
             with torch.cuda.stream(self.up):
                 if consumed[s] is not None:
                     self.up.wait_event(consumed[s])
                 for dst, src in zip(self._in[s], inputs):
-                    dst.copy_(src[lo:hi], non_blocking=True)
+                    head(dst).copy_(cut(src), non_blocking=True)
                 if self.backward:
-                    self._do[s].copy_(do[lo:hi], non_blocking=True)
+                    head(self._do[s]).copy_(cut(do), non_blocking=True)
                 uploaded[s] = torch.cuda.Event()
                 uploaded[s].record(self.up)
             compute.wait_event(uploaded[s])
-            leaves = [t.detach().requires_grad_(self.backward) for t in self._in[s]]
-            o = gdn_joint_call(*leaves, scale=self.scale)
+            leaves = [head(t).detach().requires_grad_(self.backward) for t in self._in[s]]
+            o = gdn_joint_call(*leaves, scale=self.scale, cu_seqlens=cu_dev)
             outs = [o.detach()]
             if self.backward:
-                o.backward(self._do[s])
+                o.backward(head(self._do[s]))
                 outs += [t.grad for t in leaves]
             consumed[s] = torch.cuda.Event()
             consumed[s].record(compute)
@@ -99,19 +119,19 @@ class HostPipeline:
                 t.record_stream(self.down)               # keep the allocator from reusing it before the download ran
             with torch.cuda.stream(self.down):
                 self.down.wait_event(consumed[s])
-                self.o_host[lo:hi].copy_(outs[0], non_blocking=True)
+                cut(self.o_host).copy_(outs[0], non_blocking=True)
                 if self.backward:
                     for hbuf, t in zip(self.grads_host, outs[1:]):
-                        hbuf[lo:hi].copy_(t, non_blocking=True)
+                        cut(hbuf).copy_(t, non_blocking=True)
         done = torch.cuda.Event()
         done.record(self.down)
         compute.wait_event(done)     # the step is complete, in stream order, when the last download is
         return self.o_host, self.grads_host
 
 
-def gdn_joint_host(q, k, v, k2, q2, g, beta, do=None, *, scale=None, slices=None, device=None):
+def gdn_joint_host(q, k, v, k2, q2, g, beta, do=None, *, scale=None, slices=None, device=None, cu_seqlens=None):
     """One-shot convenience wrapper around `HostPipeline` (allocates its buffers on every call)."""
-    pipe = HostPipeline((q, k, v, k2, q2, g, beta), do, scale=scale, slices=slices, device=device)
+    pipe = HostPipeline((q, k, v, k2, q2, g, beta), do, scale=scale, slices=slices, device=device, cu_seqlens=cu_seqlens)
     o, grads = pipe.run((q, k, v, k2, q2, g, beta), do)
     torch.cuda.current_stream(pipe.device).synchronize()
     return o, grads

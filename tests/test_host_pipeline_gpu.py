@@ -42,3 +42,22 @@ def test_forward_only_and_argument_checks():
         HostPipeline([t.clone() for t in ins])          # pageable, not pinned
     with pytest.raises(ValueError):
         HostPipeline([t.cuda() for t in ins])           # not host tensors
+
+
+def test_packed_row_is_cut_along_documents():
+    T, H, E = 1536, 2, 8
+    cu = torch.tensor([0, 100, 612, 613, 1000, 1536], dtype=torch.int32)
+    ins = [t.pin_memory() for t in orc.make_inputs(1, T, H, E, seed=77)]
+    do = orc.make_grad_output((1, T, H, 128), 5).pin_memory()
+    leaves = [t.cuda().requires_grad_(True) for t in ins]
+    o = gdn_joint_call(*leaves, cu_seqlens=cu.cuda())
+    o.backward(do.cuda())
+    ref = [o.detach().cpu()] + [t.grad.cpu() for t in leaves]
+    pipe = HostPipeline(ins, do, slices=3, cu_seqlens=cu)
+    assert 1 <= pipe.slices <= 3
+    for _ in range(2):
+        oh, grads = pipe.run(ins, do)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        for a, b in zip([oh] + grads, ref):
+            assert torch.equal(a, b)
