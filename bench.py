@@ -1,6 +1,6 @@
 """Benchmark of the Triadic GDN hot path: forward + backward tokens/s at T=8192, H=32, E=8, B=8 (heads sharded over N GPUs).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|conv]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|conv]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
 
 One step = one forward + backward of the whole (B, T, H) problem through `gdn_joint_call` (the public API).  Prints ONE
@@ -33,6 +33,7 @@ WORKLOADS = {
     "c1": (4, 4096, 16, 4, False),
     "c3": (1, 131072, 16, 16, True),    # one packed row of lognormal documents (PACKED below)
     "small": (2, 1024, 4, 8, True),
+    "c4": (1, 32768, 32, 12, True),     # the core behind the conv pre-pass: eight documents of 4096 tokens (PACKED below)
     "prof": (2, 8192, 16, 8, True),     # 4096 (chunk, head) items, a few GB: the size used for ncu captures
 }
 
@@ -43,7 +44,7 @@ def algorithmic_flops(E, items, backward):
     return per * U_FLOP * items
 
 
-PACKED = {"c3": 31}                  # workload -> seed of its document lengths
+PACKED = {"c3": ("lognormal", 31), "c4": ("uniform", 4096)}   # workload -> how its packed row is cut into documents
 
 # per-kernel algorithmic work, in u per (chunk, head)
 KERNEL_U = {
@@ -230,7 +231,8 @@ def run_ours(args, rank, world, local_rank):
     cu_host = cu_dev = None
     if packed:
         # one packed row: this rank takes a token-balanced range of whole documents, all heads (strong scaling)
-        cu_all = lognormal_documents(T, PACKED[args.workload])
+        kind, arg = PACKED[args.workload]
+        cu_all = lognormal_documents(T, arg) if kind == "lognormal" else torch.arange(0, T + 1, arg, dtype=torch.int32)
         rng = document_ranges(cu_all, world)[rank]
         if rng.doc_hi == rng.doc_lo:
             raise SystemExit(f"rank {rank} of {world} got no document")
@@ -330,7 +332,7 @@ def run_ours(args, rank, world, local_rank):
     line = {"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'packed lognormal documents, ' if packed else ''}"
+            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {('packed, ' + PACKED[args.workload][0] + ' documents, ') if packed else ''}"
                                    f"{'fwd+bwd' if backward else 'fwd'}, GJ_SAVE_MASKS="
                                    f"{os.environ.get('GJ_SAVE_MASKS', '1')}",
                        "parallelism": (f"whole documents, token-balanced, over {world} GPU(s), no collective" if packed
