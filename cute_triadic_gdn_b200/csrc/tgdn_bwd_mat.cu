@@ -92,24 +92,16 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       return;
     }
   }
-  if (tid == 0) {
+  // One thread of the second warp sets the barriers up and sends the tile loads off at once; the first warp allocates
+  // tensor memory meanwhile; everybody else is already requesting its global inputs.  One CTA barrier ends all three.
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
+  const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
+  if (warp_u == 1 && elect_one()) {
     mbar_init(&sm.bar_load, 1);
     mbar_init(&sm.bar_mma, 1);
     mbar_fence_init();
     sm.abort = 0;
     sm.steep = 0;
-  }
-  if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
-  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-  WaitCtl ctl{&sm.abort, p.status};
-  const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
-
-  if (warp_u == 0 && elect_one()) {
     mbar_expect_tx(&sm.bar_load, 3 * 32768 + 16384);
     for (int half = 0; half < 2; ++half) {
       const int col = half * 64;
@@ -122,7 +114,9 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     bulk_load(sm.ap, p.AP + item * (128 * 64), 16384, &sm.bar_load);
   }
-  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
+  __syncwarp();
+  if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
+  WaitCtl ctl{&sm.abort, p.status};
   // Every global value this thread needs later is requested here, in one batch, from clamped (always valid) addresses,
   // and masked when it is used: a load that waits until its consumer is reached costs a full memory round trip, which
   // under the streaming load of the other blocks is microseconds.
@@ -165,7 +159,11 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
   }
   if (tid < 64) sm.beta[tid] = (tid < rows) ? beta_in : 0.f;
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   // ---- G1, G2 ----------------------------------------------------------------------------------------------------
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);

@@ -141,28 +141,25 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
       return;
     }
   }
-  if (tid == 0) {
+  // One thread of the second warp sets the barriers up and sends the tile load off at once; the first warp allocates
+  // tensor memory meanwhile; everybody else is already requesting the gate inputs.  The barrier after the gate stores ends
+  // all three.
+  WaitCtl ctl{&sm.abort, p.status};
+  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
+  if (warp_u == 1 && elect_one()) {
     mbar_init(&sm.bar_load, 1);
     mbar_init(&sm.bar_mma, 1);
     mbar_fence_init();
     sm.abort = 0;
     sm.steep = 0;
-  }
-  if (warp == 0) { tmem_alloc(&sm.tmem_base, 128); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  WaitCtl ctl{&sm.abort, p.status};
-  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
-
-  if (warp_u == 0 && elect_one()) {
     mbar_expect_tx(&sm.bar_load, 32768);
     tma_load_4d(sm.u.kq, &map_k, &sm.bar_load, 0, h, t0, b);
     tma_load_4d(sm.u.kq + 8192, &map_q, &sm.bar_load, 0, h, t0, b);
     tma_load_4d(sm.u.kq + 16384, &map_k, &sm.bar_load, 64, h, t0, b);
     tma_load_4d(sm.u.kq + 24576, &map_q, &sm.bar_load, 64, h, t0, b);
   }
-  __syncwarp();                                           // the other lanes must not run ahead into a spin wait
+  __syncwarp();
+  if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 128); tmem_relinquish(); }
 
   // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0.  All loads are requested first, from
   // clamped (always valid) addresses, and masked when stored: the block pays one memory round trip, not one per iteration.
@@ -191,7 +188,9 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     }
     if (tid < 64) sm.beta[tid] = (tid < rows) ? beta_in : 0.f;
   }
-  __syncthreads();
+  tc_fence_before();
+  __syncthreads();                                          // gate values, barriers and the tensor-memory address are visible
+  tc_fence_after();
   // inclusive scan over the 64 rows, one warp per gate column
   float* gc_out = p.gc + ((static_cast<int64_t>(b) * p.NC + n) * p.H + h) * (64 * E);
   for (int e = warp; e < E; e += MASK_THREADS / 32) {
