@@ -76,23 +76,9 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       return;
     }
   }
-  if (tid == 0) {
-    mbar_init(&sm.bar_kq, 1);
-    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_load[i], 1);
-    mbar_init(&sm.bar_mma[0], 1);
-    mbar_init(&sm.bar_mma[1], 1);
-    mbar_init(&sm.bar_built[0], SG_THREADS / 32);
-    mbar_init(&sm.bar_built[1], SG_THREADS / 32);
-    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_read[i], SG_THREADS / 32);
-    mbar_fence_init();
-    sm.abort = 0;
-  }
-  if (warp == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  // The first lane of the MMA warp sets the barriers up and sends the first tile loads off at once; the first warp
+  // allocates tensor memory meanwhile; the workers are already requesting their global inputs.  The CTA barrier after the
+  // gate tables ends all three.
   WaitCtl ctl{&sm.abort, p.status};
   constexpr int STEPS = 2 * E;
   const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
@@ -103,14 +89,24 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
     bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
   };
-  if (issuer) {                                        // every stage is free at the start
-    mbar_expect_tx(&sm.bar_kq, 32768);
+  if (issuer) {
+    mbar_init(&sm.bar_kq, 1);
+    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_load[i], 1);
+    mbar_init(&sm.bar_mma[0], 1);
+    mbar_init(&sm.bar_mma[1], 1);
+    mbar_init(&sm.bar_built[0], SG_THREADS / 32);
+    mbar_init(&sm.bar_built[1], SG_THREADS / 32);
+    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_read[i], SG_THREADS / 32);
+    mbar_fence_init();
+    sm.abort = 0;
+    mbar_expect_tx(&sm.bar_kq, 32768);                 // every stage is free at the start
     tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.kq + 16384, &map_k, &sm.bar_kq, 64, h, t0, b);
     tma_load_4d(sm.kq + 24576, &map_q, &sm.bar_kq, 64, h, t0, b);
     issue_step(0);                                     // the rest of the ring follows once the workers' own loads are back
   }
+  if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
 
   // All global loads of the prologue go out together, from clamped (always valid) addresses, and are masked when they are
   // used: the CTA then pays one memory round trip here instead of one per dependent group.
@@ -174,7 +170,11 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
 #pragma unroll
       for (int j = 0; j < 16; ++j) uw[vh][j] = 0u;
   }
-  __syncthreads();
+  tc_fence_before();
+  __syncthreads();                                     // gate tables, barriers and the tensor-memory address are visible
+  tc_fence_after();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   // Pipeline over the 2E half-slice steps s = 2e + vh.  The MMA warp keeps the tensor core fed: the MMAs of step s go out
   // as soon as their operands and half-slices are there.  The workers accumulate <h,G> of step s from shared memory while
