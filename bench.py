@@ -55,8 +55,8 @@ KERNEL_U = {
 # workload (4096 items; profiles/core_kernels_prof_workload.md).  Traffic grows in proportion to the item count, so a
 # full launch is this figure times its items.
 NCU_DRAM_BYTES_PER_ITEM_E8 = {
-    "masks": (0.161 + 0.073) * 1e9 / 4096, "fwd": (0.378 + 1.222) * 1e9 / 4096, "rec": (0.485 + 1.221) * 1e9 / 4096,
-    "sg": (2.510 + 0.146) * 1e9 / 4096, "mat": (0.714 + 0.143) * 1e9 / 4096,
+    "masks": (0.161 + 0.076) * 1e9 / 4096, "fwd": (0.373 + 1.223) * 1e9 / 4096, "rec": (0.479 + 1.221) * 1e9 / 4096,
+    "sg": (2.510 + 0.146) * 1e9 / 4096, "mat": (0.715 + 0.146) * 1e9 / 4096,
 }
 
 # Algorithmic HBM bytes per (chunk, head) item: every tensor a kernel must read or write, once (bf16 tiles of 64x128 are
