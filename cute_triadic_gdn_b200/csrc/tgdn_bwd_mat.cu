@@ -598,30 +598,39 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   ++mma_phase;
   tc_fence_after();
   {
-    __nv_bfloat16* outp = (krow ? p.dk : p.dq) + ((tok + t) * p.H + h) * HEAD + cq * 32;
-    const bool live = t < rows;
     float a[32];
     tmem_ld<32>(tmem_row + cq * 32, a);
     tmem_wait_ld();
     mbar_wait(&sm.bar_load, 1, ctl, DEV_TIMEOUT_LOAD);     // state part: image [column / 8][row][column % 8]
-    if (live) {
-      const uint32_t xb = smem_u32(sm.ap) + (cq * 4) * 2048 + r * 16;
+    // Sum with the state part, round once, and stage the 128x128 bf16 result in the [K;Q] buffer (dead since G5) so
+    // that it can leave as whole 256-byte rows: a thread owns one row and 32 columns, and storing those directly would
+    // scatter every warp store over 32 rows.  16-byte chunks are XOR-swizzled with the row so that neither the staging
+    // stores (fixed chunk, 32 rows) nor the row reads (one row, 32 lanes) meet a bank twice.
+    const uint32_t xb = smem_u32(sm.ap) + (cq * 4) * 2048 + r * 16;
+    const uint32_t stage = smem_u32(sm.kq) + r * 256;
 #pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint32_t x[4];
-        asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xb + (j >> 3) * 2048));
-        uint4 u;
-        u.x = pack_bf16(a[j] + bf16_lo(x[0]), a[j + 1] + bf16_hi(x[0]));
-        u.y = pack_bf16(a[j + 2] + bf16_lo(x[1]), a[j + 3] + bf16_hi(x[1]));
-        u.z = pack_bf16(a[j + 4] + bf16_lo(x[2]), a[j + 5] + bf16_hi(x[2]));
-        u.w = pack_bf16(a[j + 6] + bf16_lo(x[3]), a[j + 7] + bf16_hi(x[3]));
-        *reinterpret_cast<uint4*>(outp + j) = u;
-      }
+    for (int j = 0; j < 32; j += 8) {
+      uint32_t x[4];
+      asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xb + (j >> 3) * 2048));
+      st_shared_v4(stage + (((cq * 4 + (j >> 3)) ^ (r & 15)) << 4),
+                   pack_bf16(a[j] + bf16_lo(x[0]), a[j + 1] + bf16_hi(x[0])), pack_bf16(a[j + 2] + bf16_lo(x[1]), a[j + 3] + bf16_hi(x[1])),
+                   pack_bf16(a[j + 4] + bf16_lo(x[2]), a[j + 5] + bf16_hi(x[2])), pack_bf16(a[j + 6] + bf16_lo(x[3]), a[j + 7] + bf16_hi(x[3])));
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+  // rows 0..63 -> dk, rows 64..127 -> dq; warp w stores rows w, w + 16, ...: one coalesced 256-byte row per instruction
+  for (int rr = warp; rr < 128; rr += MAT_THREADS / 32) {
+    const int tt = rr & 63;
+    if (tt < rows) {
+      const uint32_t src = smem_u32(sm.kq) + rr * 256 + ((((lane >> 1) ^ (rr & 15)) << 4) | ((lane & 1) << 3));
+      uint2 v;
+      asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(src));
+      __nv_bfloat16* dst = (rr < 64 ? p.dk : p.dq) + ((tok + tt) * p.H + h) * HEAD + lane * 4;
+      *reinterpret_cast<uint2*>(dst) = v;
+    }
+  }
 }
 
 }  // namespace tgdn
