@@ -26,7 +26,8 @@ constexpr int CONV_FWD_ROWS = CONV_TOK + 3;       // x rows t0-3 .. t0+31
 constexpr int CONV_BWD_XROWS = CONV_TOK + 6;      // x rows t0-3 .. t0+34
 constexpr int CONV_BWD_GROWS = CONV_TOK + 3;      // dy rows t0 .. t0+34
 constexpr int CONV_FWD_STAGES = 3;     // 54 KB per CTA: four CTAs per SM
-constexpr int CONV_BWD_STAGES = 3;     // 112 KB per CTA: two CTAs per SM (the backward needs more than 85 registers)
+constexpr int CONV_BWD_STAGES = 3;     // 112 KB per CTA: two CTAs per SM
+constexpr int CONV_BWD_NP = 2;         // channel pairs per thread of the backward (512 threads per CTA)
 
 // Four channels of a thread as two packed pairs: the arithmetic runs on the two-wide f32 instructions (one instruction per
 // pair, each lane an ordinary IEEE fma), which halves the instruction count of the kernels' inner loops.
@@ -231,17 +232,71 @@ conv_fwd_kernel(const __grid_constant__ CUtensorMap map_x, ConvArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(CONV_THREADS, 2)
+// NP channel pairs of a thread (the forward's Vec4 is the NP = 2 case with its own helpers).
+template <int NP>
+struct VecP {
+  float2 p[NP];
+};
+template <int NP>
+__device__ __forceinline__ VecP<NP> load_pairs(const uint8_t* s) {
+  VecP<NP> r;
+  if constexpr (NP == 2) {
+    const uint2 u = *reinterpret_cast<const uint2*>(s);
+    r.p[0] = make_float2(bf16_lo(u.x), bf16_hi(u.x));
+    r.p[1] = make_float2(bf16_lo(u.y), bf16_hi(u.y));
+  } else {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(s);
+    r.p[0] = make_float2(bf16_lo(u), bf16_hi(u));
+  }
+  return r;
+}
+template <int NP>
+__device__ __forceinline__ VecP<NP> zero_pairs() {
+  VecP<NP> r;
+#pragma unroll
+  for (int p = 0; p < NP; ++p) r.p[p] = make_float2(0.f, 0.f);
+  return r;
+}
+template <int NP>
+__device__ __forceinline__ void store_pairs(__nv_bfloat16* dst, const VecP<NP>& a) {
+  if constexpr (NP == 2)
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(a.p[0].x, a.p[0].y), pack_bf16(a.p[1].x, a.p[1].y));
+  else
+    *reinterpret_cast<uint32_t*>(dst) = pack_bf16(a.p[0].x, a.p[0].y);
+}
+// SiLU' of the bf16-rounded pre-activations of a channel pair: one packed conversion rounds both, the polynomial part runs
+// on the two-wide f32 instructions (each lane the same bits as silu_grad).
+__device__ __forceinline__ float2 silu_grad_pair(float2 pre) {
+  const uint32_t r = pack_bf16(pre.x, pre.y);
+  const float2 y = make_float2(bf16_lo(r), bf16_hi(r));
+  const float2 h = __fmul2_rn(y, make_float2(0.5f, 0.5f));
+  float2 th;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th.x) : "f"(h.x));
+  asm("tanh.approx.f32 %0, %1;" : "=f"(th.y) : "f"(h.y));
+  const float2 half2 = make_float2(0.5f, 0.5f), one2 = make_float2(1.f, 1.f);
+  const float2 s = __ffma2_rn(half2, th, half2);
+  const float2 om = __ffma2_rn(s, make_float2(-1.f, -1.f), one2);
+  return __fmul2_rn(s, __ffma2_rn(y, om, one2));
+}
+
+// Backward.  NP = 1: 512 threads = 4 row groups x 4 channel slices of 64, one channel pair per thread, so that the kernel
+// fits 64 registers and two CTAs put 32 warps on an SM: the per-row chain (4 fma, rounding, tanh, 4 more fma) is all
+// fixed-latency dependency, which only more warps per scheduler hide.
+template <int NP>
+__global__ void __launch_bounds__(CONV_THREADS * 2 / NP, 2)
 conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_dy, ConvArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   constexpr int X_BYTES = CONV_BWD_XROWS * CONV_CH * 2, G_BYTES = CONV_BWD_GROWS * CONV_CH * 2;
   constexpr int STAGE_BYTES = X_BYTES + G_BYTES;
+  constexpr int SLICES = 4 / NP, NCH = 2 * NP;                         // channel slices per tile, channels per thread
+  constexpr int ROW = CONV_CH * 2;                                     // bytes of a tile row
   __shared__ uint64_t full[CONV_BWD_STAGES];
   __shared__ int abort_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int half = warp & 1, rg = warp >> 1;
-  const int cbase = blockIdx.x * CONV_CH, c0 = cbase + half * 128 + lane * CONV_VEC, b = blockIdx.z;
+  const int slice = warp % SLICES, rg = warp / SLICES;
+  const int cin = slice * (32 * NCH) + lane * NCH;                     // first channel of the thread inside the tile
+  const int cbase = blockIdx.x * CONV_CH, c0 = cbase + cin, b = blockIdx.z;
   const int n_tiles = (a.T + CONV_TOK - 1) / CONV_TOK;
   const int tile_lo = blockIdx.y * a.tiles_per_group, tile_hi = min(n_tiles, tile_lo + a.tiles_per_group);
   if (tid == 0) {
@@ -260,19 +315,40 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   if (tid == 0)
     for (int i = 0; i < CONV_BWD_STAGES && tile_lo + i < tile_hi; ++i) issue(tile_lo + i);
 
-  float2 w2[2][CONV_W];
-  load_weights(a.weight, c0, a.C, w2);
-  float2 dwa[2][CONV_W];                                               // weight gradient of the channel pairs
+  const bool live = c0 < a.C;                          // C % 8 == 0 and c0 % NCH == 0: the thread's channels are all inside
+  float2 w2[NP][CONV_W];
+  {
+    float w[NCH][CONV_W];
 #pragma unroll
-  for (int p = 0; p < 2; ++p)
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int j = 0; j < CONV_W; ++j) w[c][j] = 0.f;
+    if (live) {
+      const uint4* wp = reinterpret_cast<const uint4*>(a.weight + static_cast<int64_t>(c0) * CONV_W);
+#pragma unroll
+      for (int i = 0; i < NP; ++i) {                   // two channels x four taps per 16-byte vector
+        const uint4 u = __ldg(wp + i);
+        w[2 * i][0] = bf16_lo(u.x); w[2 * i][1] = bf16_hi(u.x); w[2 * i][2] = bf16_lo(u.y); w[2 * i][3] = bf16_hi(u.y);
+        w[2 * i + 1][0] = bf16_lo(u.z); w[2 * i + 1][1] = bf16_hi(u.z);
+        w[2 * i + 1][2] = bf16_lo(u.w); w[2 * i + 1][3] = bf16_hi(u.w);
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < NP; ++p)
+#pragma unroll
+      for (int j = 0; j < CONV_W; ++j) w2[p][j] = make_float2(w[2 * p][j], w[2 * p + 1][j]);
+  }
+  float2 dwa[NP][CONV_W];                                              // weight gradient of the channel pairs
+#pragma unroll
+  for (int p = 0; p < NP; ++p)
 #pragma unroll
     for (int j = 0; j < CONV_W; ++j) dwa[p][j] = make_float2(0.f, 0.f);
   __nv_bfloat16* dxb = a.out + (static_cast<int64_t>(b) * a.T) * a.C + c0;
-  const int col_off = half * 256 + lane * 8;
-  const bool live = c0 < a.C;
-  bool act[CONV_VEC];
+  const int col_off = cin * 2;
+  bool act[NCH];
 #pragma unroll
-  for (int c = 0; c < CONV_VEC; ++c) act[c] = c0 + c < a.act_channels;
+  for (int c = 0; c < NCH; ++c) act[c] = c0 + c < a.act_channels;
+  using V = VecP<NP>;
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int k = tile - tile_lo, s = k % CONV_BWD_STAGES;
@@ -288,29 +364,30 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     // three halo rows, and all of them exist.  Then no cursor, no bounds and no masks are needed; almost every tile is
     // like this.
     const bool interior = u_first + 11 <= a.T && doc.next >= u_first + 11 && doc.start <= max(u_first - 3, 0);
-    if (interior && live && (act[0] == act[3])) {
+    if (interior && live && (act[0] == act[NCH - 1])) {
       const bool on = act[0];
-      Vec4 xw[3];
+      V xw[3];
 #pragma unroll
-      for (int j = 0; j < 3; ++j) xw[j] = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2)));
-      Vec4 gw[3] = {zero4(), zero4(), zero4()};
+      for (int j = 0; j < 3; ++j) xw[j] = load_pairs<NP>(sx + (rg * 8 + 2 - j) * ROW);
+      V gw[3] = {zero_pairs<NP>(), zero_pairs<NP>(), zero_pairs<NP>()};
+      __nv_bfloat16* dxr = dxb + static_cast<int64_t>(u_first) * a.C;
 #pragma unroll
       for (int i = 0; i < 11; ++i) {
-        const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
-        Vec4 gy = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+        const V x0 = load_pairs<NP>(sx + (rg * 8 + 3 + i) * ROW);
+        V gy = load_pairs<NP>(sg + (rg * 8 + i) * ROW);
         if (on) {
 #pragma unroll
-          for (int p = 0; p < 2; ++p) {
+          for (int p = 0; p < NP; ++p) {
             float2 pre = __fmul2_rn(xw[2].p[p], w2[p][0]);
             pre = __ffma2_rn(xw[1].p[p], w2[p][1], pre);
             pre = __ffma2_rn(xw[0].p[p], w2[p][2], pre);
             pre = __ffma2_rn(x0.p[p], w2[p][3], pre);
-            gy.p[p] = __fmul2_rn(gy.p[p], make_float2(silu_grad(round_bf16(pre.x)), silu_grad(round_bf16(pre.y))));
+            gy.p[p] = __fmul2_rn(gy.p[p], silu_grad_pair(pre));
           }
         }
         if (i < 8) {
 #pragma unroll
-          for (int p = 0; p < 2; ++p) {
+          for (int p = 0; p < NP; ++p) {
             dwa[p][0] = __ffma2_rn(gy.p[p], xw[2].p[p], dwa[p][0]);
             dwa[p][1] = __ffma2_rn(gy.p[p], xw[1].p[p], dwa[p][1]);
             dwa[p][2] = __ffma2_rn(gy.p[p], xw[0].p[p], dwa[p][2]);
@@ -318,52 +395,52 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           }
         }
         if (i >= 3) {
-          Vec4 out;
+          V out;
 #pragma unroll
-          for (int p = 0; p < 2; ++p) {
+          for (int p = 0; p < NP; ++p) {
             float2 acc = __fmul2_rn(gw[2].p[p], w2[p][3]);
             acc = __ffma2_rn(gw[1].p[p], w2[p][2], acc);
             acc = __ffma2_rn(gw[0].p[p], w2[p][1], acc);
             acc = __ffma2_rn(gy.p[p], w2[p][0], acc);
             out.p[p] = acc;
           }
-          store4(dxb + static_cast<int64_t>(u_first + i - 3) * a.C, out);
+          store_pairs<NP>(dxr, out);
+          dxr += a.C;
         }
         gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
         xw[2] = xw[1]; xw[1] = xw[0]; xw[0] = x0;
       }
     } else {
-      Vec4 xw[3];                                                        // x[t-1], x[t-2], x[t-3]
+      V xw[3];                                                           // x[t-1], x[t-2], x[t-3]
 #pragma unroll
       for (int j = 0; j < 3; ++j) {
         const int tj = u_first - 1 - j;
-        xw[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+        xw[j] = (tj >= doc.start) ? load_pairs<NP>(sx + (rg * 8 + 2 - j) * ROW) : zero_pairs<NP>();
       }
-      Vec4 gw[3] = {zero4(), zero4(), zero4()};                          // dy'[t-1], dy'[t-2], dy'[t-3]
+      V gw[3] = {zero_pairs<NP>(), zero_pairs<NP>(), zero_pairs<NP>()};  // dy'[t-1], dy'[t-2], dy'[t-3]
       int ds1 = 0x7fffffff, ds2 = 0x7fffffff;                            // document starts of tokens t-1, t-2
 #pragma unroll
       for (int i = 0; i < 11; ++i) {
         const int t = u_first + i;
-        Vec4 gy = zero4(), x0 = zero4();
+        V gy = zero_pairs<NP>(), x0 = zero_pairs<NP>();
         int ds0 = 0x7fffffff;
         if (t < a.T) {
-          if (i > 0 && doc.advance(t)) { xw[0] = zero4(); xw[1] = zero4(); xw[2] = zero4(); }
+          if (i > 0 && doc.advance(t)) { xw[0] = zero_pairs<NP>(); xw[1] = zero_pairs<NP>(); xw[2] = zero_pairs<NP>(); }
           ds0 = doc.start;
-          x0 = unpack4(*reinterpret_cast<const uint2*>(sx + (rg * 8 + 3 + i) * (CONV_CH * 2)));
-          const Vec4 g = unpack4(*reinterpret_cast<const uint2*>(sg + (rg * 8 + i) * (CONV_CH * 2)));
+          x0 = load_pairs<NP>(sx + (rg * 8 + 3 + i) * ROW);
+          const V g = load_pairs<NP>(sg + (rg * 8 + i) * ROW);
 #pragma unroll
-          for (int p = 0; p < 2; ++p) {                                  // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
+          for (int p = 0; p < NP; ++p) {                                 // dy'[t] = dy[t] * silu'(bf16(pre-activation[t]))
             float2 pre = __fmul2_rn(xw[2].p[p], w2[p][0]);
             pre = __ffma2_rn(xw[1].p[p], w2[p][1], pre);
             pre = __ffma2_rn(xw[0].p[p], w2[p][2], pre);
             pre = __ffma2_rn(x0.p[p], w2[p][3], pre);
-            const float2 sg2 = make_float2(act[2 * p] ? silu_grad(round_bf16(pre.x)) : 1.f,
-                                           act[2 * p + 1] ? silu_grad(round_bf16(pre.y)) : 1.f);
-            gy.p[p] = __fmul2_rn(g.p[p], sg2);
+            const float2 sgp = silu_grad_pair(pre);
+            gy.p[p] = __fmul2_rn(g.p[p], make_float2(act[2 * p] ? sgp.x : 1.f, act[2 * p + 1] ? sgp.y : 1.f));
           }
           if (i < 8) {                                                   // the weight gradient of token t belongs to this warp
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
+            for (int p = 0; p < NP; ++p) {
               dwa[p][0] = __ffma2_rn(gy.p[p], xw[2].p[p], dwa[p][0]);
               dwa[p][1] = __ffma2_rn(gy.p[p], xw[1].p[p], dwa[p][1]);
               dwa[p][2] = __ffma2_rn(gy.p[p], xw[0].p[p], dwa[p][2]);
@@ -376,16 +453,16 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           if (u < a.T && live) {
             const float m2 = (ds2 <= u) ? 1.f : 0.f, m1 = (ds1 <= u) ? 1.f : 0.f, m0 = (ds0 <= u) ? 1.f : 0.f;
             const float2 m22 = make_float2(m2, m2), m12 = make_float2(m1, m1), m02 = make_float2(m0, m0);
-            Vec4 out;
+            V out;
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
+            for (int p = 0; p < NP; ++p) {
               float2 acc = __fmul2_rn(gw[2].p[p], w2[p][3]);
               acc = __ffma2_rn(__fmul2_rn(m22, gw[1].p[p]), w2[p][2], acc);
               acc = __ffma2_rn(__fmul2_rn(m12, gw[0].p[p]), w2[p][1], acc);
               acc = __ffma2_rn(__fmul2_rn(m02, gy.p[p]), w2[p][0], acc);
               out.p[p] = acc;
             }
-            store4(dxb + static_cast<int64_t>(u) * a.C, out);
+            store_pairs<NP>(dxb + static_cast<int64_t>(u) * a.C, out);
           }
         }
         gw[2] = gw[1]; gw[1] = gw[0]; gw[0] = gy;
@@ -400,14 +477,14 @@ conv_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   float* red = reinterpret_cast<float*>(smem);                         // [4 row groups][256 channels][4 taps]
   __syncthreads();
 #pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    float* dst = red + (rg * CONV_CH + half * 128 + lane * CONV_VEC + 2 * p) * CONV_W;
+  for (int p = 0; p < NP; ++p) {
+    float* dst = red + (rg * CONV_CH + cin + 2 * p) * CONV_W;
     *reinterpret_cast<float4*>(dst) = make_float4(dwa[p][0].x, dwa[p][1].x, dwa[p][2].x, dwa[p][3].x);
     *reinterpret_cast<float4*>(dst + CONV_W) = make_float4(dwa[p][0].y, dwa[p][1].y, dwa[p][2].y, dwa[p][3].y);
   }
   __syncthreads();
   float* out = a.dw_partial + (static_cast<int64_t>(b) * gridDim.y + blockIdx.y) * (static_cast<int64_t>(a.C) * CONV_W);
-  for (int e = tid; e < CONV_CH * CONV_W; e += CONV_THREADS) {
+  for (int e = tid; e < CONV_CH * CONV_W; e += blockDim.x) {
     const int ch = cbase + e / CONV_W;
     if (ch < a.C)
       out[static_cast<int64_t>(ch) * CONV_W + e % CONV_W] =
@@ -440,17 +517,22 @@ static int conv_check(const void* x, const void* weight, const void* y, const in
   return 0;
 }
 
-// Token tiles per CTA and number of CTAs along the token axis: as many CTAs as fit on the GPU at once, so that every CTA keeps
-// its ring of tiles in flight for a long run of tokens and the number of weight-gradient partials stays small.
-static void conv_groups(int T, int C, int ctas_per_sm, int* groups, int* tiles_per_group) {
+// Token tiles per CTA and number of CTAs along the token axis.  A CTA walks a run of tokens with its ring of tiles in flight,
+// and each CTA of the backward leaves a weight-gradient partial, so runs should be long; but the grid must not end in a
+// nearly empty wave (306 CTAs on 296 resident slots take as long as 592), and the SMs do not finish in step, so several
+// short waves balance better than one long one.  Measured at (1, 32768, 13056): the time falls until about four waves
+// (backward) or six (forward) and is flat beyond, until the partials of the backward start to cost.  So: as many token
+// groups as fill `waves` waves of resident CTAs without spilling into the next, with runs of at least eight tiles.
+static void conv_groups(int B, int T, int C, int ctas_per_sm, int waves, int* groups, int* tiles_per_group) {
   const int n_tiles = (T + CONV_TOK - 1) / CONV_TOK;
-  const int n_ctile = (C + CONV_CH - 1) / CONV_CH;
-  int g = (ctas_per_sm * 148 + n_ctile - 1) / n_ctile;
+  const int64_t columns = static_cast<int64_t>((C + CONV_CH - 1) / CONV_CH) * B;      // CTAs per token group
+  int64_t g = static_cast<int64_t>(waves) * ctas_per_sm * 148 / columns;
+  if (g > n_tiles / 8) g = n_tiles / 8;
   if (g < 1) g = 1;
-  if (g > n_tiles) g = n_tiles;
-  *tiles_per_group = (n_tiles + g - 1) / g;
+  *tiles_per_group = static_cast<int>((n_tiles + g - 1) / g);
   *groups = (n_tiles + *tiles_per_group - 1) / *tiles_per_group;
 }
+constexpr int CONV_FWD_WAVES = 6, CONV_BWD_WAVES = 4;
 
 extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const int32_t* cu_seqlens, int n_docs, int B,
                              int T, int C, int64_t stride_b, int64_t stride_t, int act_channels, void* stream) {
@@ -461,7 +543,7 @@ extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const i
   CUtensorMap mx;
   if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_FWD_ROWS))) return rc;
   int groups, tpg;
-  conv_groups(T, C, 4, &groups, &tpg);
+  conv_groups(B, T, C, 4, CONV_FWD_WAVES, &groups, &tpg);
   ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(y), nullptr, cu_seqlens, n_docs, T, C,
              act_channels, tpg, tgdn_status_word()};
   const int smem = CONV_FWD_STAGES * CONV_FWD_ROWS * CONV_CH * 2 + 128;
@@ -475,7 +557,7 @@ extern "C" int tgdn_conv_fwd(const void* x, const void* weight, void* y, const i
 extern "C" int64_t tgdn_conv_bwd_scratch_bytes(int B, int T, int C) {
   if (B <= 0 || T <= 0 || C <= 0) return 0;
   int groups, tpg;
-  conv_groups(T, C, 2, &groups, &tpg);
+  conv_groups(B, T, C, 2, CONV_BWD_WAVES, &groups, &tpg);
   return static_cast<int64_t>(B) * groups * C * CONV_W * static_cast<int64_t>(sizeof(float));
 }
 
@@ -491,14 +573,14 @@ static int conv_bwd_launch(const void* x, const void* weight, const void* dy, vo
   if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_BWD_XROWS))) return rc;
   if ((rc = tgdn_make_rows_map(&mg, dy, C, T, B, dy_stride_t, dy_stride_b, CONV_CH, CONV_BWD_GROWS))) return rc;
   int groups, tpg;
-  conv_groups(T, C, 2, &groups, &tpg);
+  conv_groups(B, T, C, 2, CONV_BWD_WAVES, &groups, &tpg);
   ConvArgs a{static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(dx), scratch, cu_seqlens, n_docs, T, C,
              act_channels, tpg, tgdn_status_word()};
   const int smem = CONV_BWD_STAGES * (CONV_BWD_XROWS + CONV_BWD_GROWS) * CONV_CH * 2 + 128;
-  cudaError_t e = cudaFuncSetAttribute(conv_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = cudaFuncSetAttribute(conv_bwd_kernel<CONV_BWD_NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
   dim3 grid((C + CONV_CH - 1) / CONV_CH, groups, B);
-  conv_bwd_kernel<<<grid, CONV_THREADS, smem, s>>>(mx, mg, a);
+  conv_bwd_kernel<CONV_BWD_NP><<<grid, CONV_THREADS * 2 / CONV_BWD_NP, smem, s>>>(mx, mg, a);
   rc = tgdn_cuda_error(cudaGetLastError());
   if (rc) return rc;
   const int n_elem = C * CONV_W;

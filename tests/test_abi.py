@@ -29,9 +29,10 @@ def test_chunk_capacity_matches_reference_formula(T, N):
 
 
 def _conv_scratch(B, T, C):
-    """One f32 weight-gradient partial of C x 4 per CTA along the token axis (two CTAs per SM in total)."""
-    n_tiles, n_ctile = (T + 31) // 32, (C + 255) // 256
-    g = max(1, min(n_tiles, (2 * 148 + n_ctile - 1) // n_ctile))
+    """One f32 weight-gradient partial of C x 4 per CTA along the token axis: four waves of the 2 x 148 resident CTAs of the
+    backward, in runs of at least eight 32-token tiles."""
+    n_tiles, columns = (T + 31) // 32, (C + 255) // 256 * B
+    g = max(1, min(n_tiles // 8, 4 * 2 * 148 // columns))
     tpg = (n_tiles + g - 1) // g
     groups = (n_tiles + tpg - 1) // tpg
     return B * groups * C * 4 * 4
