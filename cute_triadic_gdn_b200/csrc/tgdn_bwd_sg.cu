@@ -6,8 +6,13 @@
 //   dK_state = sum_e (-a_e*dW) h_e^T + (r_e*U) G_e^T          (64 x 128)
 //   dQ_state = sum_e ( c_e*dO) h_e^T                          (64 x 128)
 //   da_e[t]  = -sum_v dW[t,v] (K h_e)[t,v]     dc_e[t] = sum_v dO[t,v] (Q h_e)[t,v]     dd_e = <h_e, G_e>
-// The first two are accumulated over all slices in tensor memory (operands pre-scaled by the gates, so the slice index
-// is just more K), the row sums come from R = [K;Q] h_e, the same product the forward used.
+// The tensor core forms, per slice, P_e = [dW ; dO] h_e^T (128 x 128, f32 in tensor memory, contraction over the value
+// axis in two half-slice steps) from the raw [dW ; dO] tile, which TMA loads once: the workers then take both the row
+// sums (da_e[t] = -<K[t], P_e[t]>, dc_e[t] = <Q[t], P_e[t]>: the same numbers as the sums over v above, with the
+// contractions exchanged) and the gate-weighted accumulation over the slices (f32, in registers) from one read of P_e.
+// Against forming R = [K;Q] h_e for the row sums and pre-scaling [dW ; dO] per slice, that halves the MMA instructions
+// (8 instead of 16 per step) and takes 64 KB of operand reads and 16 KB of operand writes per step off the shared
+// memory, which is what bounds this kernel.  Only (r_e*U) G_e^T still runs on operands scaled per slice.
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_state_grads.py:53-449 (sg_kernel).
 #include <type_traits>
@@ -33,23 +38,22 @@ __device__ __forceinline__ float sexp2(float x) {
 template <int E>
 struct SgSmem {
   static constexpr int ES = E | 1;   // row stride of the gate tables and partials (odd: conflict-free)
-  static constexpr int NSTAGE = E <= 8 ? 4 : 3;
-  uint8_t kq[32768];            // [K;Q] tile, 128B swizzle
+  static constexpr int NSTAGE = 4;
+  uint8_t xt[32768];            // [dW ; dO] tile, 128B swizzle: two column halves of 128 rows x 64 columns
   uint8_t hp[NSTAGE][16384];    // half-slices of h: image (i = d, j = v), SI = 128, SJ = 2048
   uint8_t gp[NSTAGE][16384];    // half-slices of G
   uint8_t va[2][8192];          // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: more owned memory follows)
-  uint8_t xa[2][16384];         // [-a_e*dW ; c_e*dO], image (i = row, j = v), SI = 128, SJ = 2048
   float ga[64 * ES], gr[64 * ES], gcq[64 * ES];
-  float part[2 * 128 * ES];     // row sums per column half
-  float red[E * (SG_THREADS / 32)];   // per slice and worker warp: partial <h,G>
-  uint64_t bar_kq, bar_load[NSTAGE], bar_mma[2], bar_built[2], bar_read[NSTAGE];
+  float part[2 * 128 * ES];     // row sums per half of the key axis
+  float red[E * 4];             // per slice and 32-row block: partial trace of h_e G_e^T
+  uint64_t bar_kq, bar_load[NSTAGE], bar_mma[2], bar_built[2], bar_read[NSTAGE], bar_diag;
   uint32_t tmem_base;
   int abort;
 };
 
 template <int E>
 __global__ void __launch_bounds__(SG_BLOCK, 1)
-sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, SgParams p) {
+sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CUtensorMap map_do, SgParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   using SM = SgSmem<E>;
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -59,7 +63,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   const bool worker = warp < SG_THREADS / 32;
   const bool issuer = tid == SG_THREADS;             // first lane of the first extra warp
   const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
-  const int wg = (warp >> 2) & 1;                    // column half inside a 64-column step
+  const int wg = (warp >> 2) & 1;                    // half of the key axis (P_e, outputs) and of a step's 64 value columns (U)
   const int row = (warp & 3) * 32 + lane;
   const bool krow = row < 64;
   const int t = row & 63;
@@ -97,13 +101,14 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     mbar_init(&sm.bar_built[0], SG_THREADS / 32);
     mbar_init(&sm.bar_built[1], SG_THREADS / 32);
     for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_read[i], SG_THREADS / 32);
+    mbar_init(&sm.bar_diag, 4);
     mbar_fence_init();
     sm.abort = 0;
     mbar_expect_tx(&sm.bar_kq, 32768);                 // every stage is free at the start
-    tma_load_4d(sm.kq, &map_k, &sm.bar_kq, 0, h, t0, b);
-    tma_load_4d(sm.kq + 8192, &map_q, &sm.bar_kq, 0, h, t0, b);
-    tma_load_4d(sm.kq + 16384, &map_k, &sm.bar_kq, 64, h, t0, b);
-    tma_load_4d(sm.kq + 24576, &map_q, &sm.bar_kq, 64, h, t0, b);
+    tma_load_4d(sm.xt, &map_dv, &sm.bar_kq, 0, h, t0, b);
+    tma_load_4d(sm.xt + 8192, &map_do, &sm.bar_kq, 0, h, t0, b);
+    tma_load_4d(sm.xt + 16384, &map_dv, &sm.bar_kq, 64, h, t0, b);
+    tma_load_4d(sm.xt + 24576, &map_do, &sm.bar_kq, 64, h, t0, b);
     issue_step(0);                                     // the rest of the ring follows once the workers' own loads are back
   }
   if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
@@ -112,17 +117,21 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   // used: the CTA then pays one memory round trip here instead of one per dependent group.
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
   const int tl = min(t, rows - 1);                   // clamped token row of this thread
-  // this thread's row data: K rows dW and U, Q rows dO; columns vh*64 + wg*32 .. +32 for vh = 0, 1 (packed bf16 pairs)
-  uint32_t xw[2][16], uw[2][16];
+  // this thread's row data (packed bf16 pairs): its K row (Q row) over the key columns wg*64 .. +64, and on K rows U over the
+  // value columns vh*64 + wg*32 .. +32 for vh = 0, 1
+  uint32_t kw[32], uw[2][16];
   {
-    const __nv_bfloat16* xsrc = (krow ? p.dV : p.dO) + ((tok + tl) * p.H + h) * HEAD + wg * 32;
+    const __nv_bfloat16* ksrc = (krow ? p.k : p.q) + ((tok + tl) * p.H + h) * HEAD + wg * 64;
     const __nv_bfloat16* usrc = p.U + (item * 64 + t) * HEAD + wg * 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 x = __ldg(reinterpret_cast<const uint4*>(ksrc) + j);
+      kw[4 * j] = x.x; kw[4 * j + 1] = x.y; kw[4 * j + 2] = x.z; kw[4 * j + 3] = x.w;
+    }
 #pragma unroll
     for (int vh = 0; vh < 2; ++vh) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const uint4 x = __ldg(reinterpret_cast<const uint4*>(xsrc + vh * 64) + j);
-        xw[vh][4 * j] = x.x; xw[vh][4 * j + 1] = x.y; xw[vh][4 * j + 2] = x.z; xw[vh][4 * j + 3] = x.w;
         const uint4 u = __ldg(reinterpret_cast<const uint4*>(usrc + vh * 64) + j);
         uw[vh][4 * j] = u.x; uw[vh][4 * j + 1] = u.y; uw[vh][4 * j + 2] = u.z; uw[vh][4 * j + 3] = u.w;
       }
@@ -160,9 +169,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   }
   if (t >= rows) {                                   // token rows past the end of a ragged chunk contribute nothing
 #pragma unroll
-    for (int vh = 0; vh < 2; ++vh)
-#pragma unroll
-      for (int j = 0; j < 16; ++j) xw[vh][j] = 0u;
+    for (int j = 0; j < 32; ++j) kw[j] = 0u;
   }
   if (!krow) {
 #pragma unroll
@@ -177,98 +184,102 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   // Pipeline over the 2E half-slice steps s = 2e + vh.  The MMA warp keeps the tensor core fed: the MMAs of step s go out
-  // as soon as their operands and half-slices are there.  The workers accumulate <h,G> of step s from shared memory while
-  // its MMAs run; once those are complete they take the row sums from the (double-buffered) R tile and build the operands
-  // of step s+2 in the buffer that just became free.  The load warp refills a stage when both of its readers are done.
-  auto build = [&](int e, auto vh_tag) {                 // operands of step (e, vh) into buffer vh
+  // as soon as their operands and half-slices are there.  Once the MMAs of step s are complete the K-row warps build r_e*U
+  // of step s+2 in the buffer that just became free, and after the second step of a slice four warps take the diagonal
+  // of the trace tile and every worker reads its part of the (double-buffered) P_e tile.  The workers never read the
+  // half-slices themselves: with <h_e, G_e> as the trace of a fifth product, shared memory is read by the tensor core only.
+  auto build = [&](int e, auto vh_tag) {                 // r_e*U of step (e, vh) into buffer vh (K-row threads)
     constexpr int vh = decltype(vh_tag)::value;
-    // gate factors rounded to bf16 once, then one packed multiply per pair of elements
-    const __nv_bfloat162 fx = __float2bfloat162_rn(krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e]);
+    if (!krow) return;
+    // gate factor rounded to bf16 once, then one packed multiply per pair of elements
     const __nv_bfloat162 fu = __float2bfloat162_rn(sm.gr[t * ES + e]);
     auto scaled = [](__nv_bfloat162 f, uint32_t x) {
       const __nv_bfloat162 y = __hmul2(f, *reinterpret_cast<const __nv_bfloat162*>(&x));
       return *reinterpret_cast<const uint32_t*>(&y);
     };
-    const uint32_t xbase = smem_u32(sm.xa[vh]) + (row >> 3) * 128 + (row & 7) * 16 + (wg * 4) * 2048;
     const uint32_t vbase = smem_u32(sm.va[vh]) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       uint32_t o[4];
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        o[w] = scaled(fx, xw[vh][4 * j + w]);
-      }
-      st_shared_v4(xbase + j * 2048, o[0], o[1], o[2], o[3]);
-      if (krow) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          o[w] = scaled(fu, uw[vh][4 * j + w]);
-        }
-        st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
-      }
+      for (int w = 0; w < 4; ++w) o[w] = scaled(fu, uw[vh][4 * j + w]);
+      st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
     }
   };
   auto issue_mma = [&](int s, int vh) {                  // one lane of the issuing warp
     const int st = s % NS;
     tc_fence_after();
-    const uint64_t dxa = make_desc(smem_u32(sm.xa[vh]), 2048, 128, LAYOUT_PLAIN);
     const uint64_t dva = make_desc(smem_u32(sm.va[vh]), 1024, 128, LAYOUT_PLAIN);
     const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);   // K = v
     const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
-    const uint64_t dhm = make_desc(smem_u32(sm.hp[st]), 128, 2048, LAYOUT_PLAIN);   // K = d, N = v
-    const uint64_t dkq = make_desc(smem_u32(sm.kq), 16, 1024, LAYOUT_SW128);
+    const uint64_t dxt = make_desc(smem_u32(sm.xt), 16, 1024, LAYOUT_SW128);
     constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
-    constexpr uint32_t id_r = make_idesc(128, 64, 0, 1);
+    const uint32_t tmem_p = tmem + ((s >> 1) & 1) * 128;       // P tile of this slice
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)                            // P_e (+)= [dW ; dO][:, 64 value columns] h_e[:, those columns]^T
+      umma_bf16(tmem_p, desc_advance(dxt, vh * 16384 + kk * 32), desc_advance(dhk, kk * 4096), id_acc, (vh > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk)
-      umma_bf16(tmem, desc_advance(dxa, kk * 4096), desc_advance(dhk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+      umma_bf16(tmem + 256, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
+  };
+  auto issue_trace = [&](int s, int vh) {                // h_e G_e^T over the step's value columns; its diagonal sums to <h_e, G_e>
+    const int st = s % NS;
+    const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);
+    const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
+    constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk)
-      umma_bf16(tmem + 128, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk)
-      umma_bf16(tmem + 256 + vh * 64, desc_advance(dkq, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(dhm, kk * 256), id_r, kk > 0);
+      umma_bf16(tmem + 384, desc_advance(dhk, kk * 4096), desc_advance(dgk, kk * 4096), id_acc, (vh > 0 || kk > 0) ? 1u : 0u);
     umma_commit(&sm.bar_mma[vh]);
   };
-  auto row_sums = [&](auto vh_tag, float& rowsum) {         // R tile of a step whose MMAs are complete
-    constexpr int vh = decltype(vh_tag)::value;
-    float rr[32];
-    tmem_ld<32>(tmem_row + 256 + vh * 64 + wg * 32, rr);
-    tmem_wait_ld();
+  float acc[64];                                         // this row's gate-weighted sum over the slices, key columns wg*64 .. +64
+#pragma unroll
+  for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+  auto take_slice = [&](int e) {                         // P_e complete: row sum against the K (Q) row, and acc += gate * P_e
+    const float gate = krow ? -sm.ga[t * ES + e] : sm.gcq[t * ES + e];
     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;          // independent chains
+    // sixteen columns at a time, the next piece travelling while this one is used
+    const uint32_t src = tmem_row + (e & 1) * 128 + wg * 64;
+    float pv[2][16];
+    tmem_ld<16>(src, pv[0]);
 #pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      a0 = fmaf(bf16_lo(xw[vh][j]), rr[2 * j], a0);
-      a1 = fmaf(bf16_hi(xw[vh][j]), rr[2 * j + 1], a1);
-      a2 = fmaf(bf16_lo(xw[vh][j + 1]), rr[2 * j + 2], a2);
-      a3 = fmaf(bf16_hi(xw[vh][j + 1]), rr[2 * j + 3], a3);
-    }
-    rowsum += (a0 + a1) + (a2 + a3);
-  };
-  auto dot_half = [&](int s, float& dot) {               // <h, G> over the half-slice of step s: 1024 16-byte pieces
-    const uint4* hp4 = reinterpret_cast<const uint4*>(sm.hp[s % NS]);
-    const uint4* gp4 = reinterpret_cast<const uint4*>(sm.gp[s % NS]);
-    float d[4] = {0.f, 0.f, 0.f, 0.f};                     // independent chains
+    for (int c = 0; c < 4; ++c) {
+      tmem_wait_ld();
+      if (c + 1 < 4) tmem_ld<16>(src + (c + 1) * 16, pv[(c + 1) & 1]);
+      const float* pc = pv[c & 1];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint4 a = hp4[j * SG_THREADS + tid], g = gp4[j * SG_THREADS + tid];
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+      for (int j = 0; j < 16; j += 4) {
+        const uint32_t w0 = kw[(c * 16 + j) >> 1], w1 = kw[((c * 16 + j) >> 1) + 1];
+        a0 = fmaf(bf16_lo(w0), pc[j], a0);
+        a1 = fmaf(bf16_hi(w0), pc[j + 1], a1);
+        a2 = fmaf(bf16_lo(w1), pc[j + 2], a2);
+        a3 = fmaf(bf16_hi(w1), pc[j + 3], a3);
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        d[w] = fmaf(bf16_lo(aw[w]), bf16_lo(gw[w]), d[w]);
-        d[w] = fmaf(bf16_hi(aw[w]), bf16_hi(gw[w]), d[w]);
+        for (int i = 0; i < 4; ++i) acc[c * 16 + j + i] = fmaf(gate, pc[j + i], acc[c * 16 + j + i]);
       }
     }
-    dot += (d[0] + d[1]) + (d[2] + d[3]);
+    const float rowsum = (a0 + a1) + (a2 + a3);
+    sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
+  };
+  auto take_diag = [&](int e) {                          // <h_e, G_e> = trace(h_e G_e^T): this warp's 32 diagonal elements
+    float dv[32];
+    tmem_ld<32>(tmem_row + 384 + (warp & 3) * 32, dv);
+    tmem_wait_ld();
+    float d = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) d = (lane == j) ? dv[j] : d;
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (lane == 0) sm.red[e * 4 + (warp & 3)] = d;
   };
   using V0 = std::integral_constant<int, 0>;
   using V1 = std::integral_constant<int, 1>;
 
   // The issuing warp and the workers run decoupled, coupled only by mbarriers:
-  //   bar_built[vh]  workers -> issuer   operands of a step are in buffer vh (and the previous R tile of that parity is read)
-  //   bar_mma[vh]    tensor core -> all  MMAs of a step complete: R tile ready, operand buffer vh reusable
+  //   bar_built[vh]  workers -> issuer   r_e*U of a step is in buffer vh (and the P tile two slices back has been read)
+  //   bar_mma[vh]    tensor core -> all  MMAs of a step complete: buffer vh reusable; after vh = 1 the P tile is ready
   //   bar_load[st]   TMA -> all          half-slices of a step landed in stage st
-  //   bar_read[st]   workers -> loads    <h,G> of a step taken and its MMAs seen complete: stage st may be refilled
+  //   bar_read[st]   workers -> loads    MMAs of a step seen complete: stage st may be refilled
+  //   bar_diag       workers -> issuer   diagonal of the trace tile read: the next slice may overwrite it
   if (worker) {
     build(0, V0{});
     fence_async_smem();
@@ -280,55 +291,47 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.bar_built[1]);
     }
-    float rowsum = 0.f, dot = 0.f;
 #pragma unroll 1
     for (int e = 0; e < E; ++e) {
       // ---- step s = 2e (vh = 0) ----
       {
         const int s = 2 * e;
-        mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
-        dot_half(s, dot);
         mbar_wait(&sm.bar_mma[0], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
         tc_fence_after();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);   // this warp is done with the stage, and so is the tensor core
-        row_sums(V0{}, rowsum);
+        if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);   // the tensor core, the only reader of the stage, is done with it
         if (e + 1 < E) {
           build(e + 1, V0{});
           fence_async_smem();
         }
-        tc_fence_before();
+        tc_fence_before();                                   // orders the reads of P two slices back, which the next step 2e+2 overwrites
         __syncwarp();
         if (e + 1 < E && lane == 0) mbar_arrive(&sm.bar_built[0]);
       }
       // ---- step s = 2e + 1 (vh = 1) ----
       {
         const int s = 2 * e + 1;
-        mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
-        dot_half(s, dot);
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         mbar_wait(&sm.bar_mma[1], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
         tc_fence_after();
         __syncwarp();
-        if (lane == 0) {
-          sm.red[e * (SG_THREADS / 32) + warp] = dot;
-          mbar_arrive(&sm.bar_read[s % NS]);
+        if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);
+        if (wg == 0) {                                       // the trace tile is single: read it first and hand it back
+          take_diag(e);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.bar_diag);
         }
-        dot = 0.f;
-        row_sums(V1{}, rowsum);
-        sm.part[(wg * 128 + row) * ES + e] = krow ? -rowsum : rowsum;
-        rowsum = 0.f;
-        if (e + 1 < E) {
+        if (e + 1 < E) {                                     // the next operands before P_e: the tensor core goes on meanwhile
           build(e + 1, V1{});
           fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.bar_built[1]);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (e + 1 < E && lane == 0) mbar_arrive(&sm.bar_built[1]);
+        take_slice(e);
       }
     }
   } else if (warp_u == SG_THREADS / 32) {                // MMA issue
-    mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);       // the R products read the [K;Q] tile
+    mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);       // the P products read the [dW ; dO] tile
 #pragma unroll 1
     for (int s = 0; s < STEPS; ++s) {
       const int vh = s & 1;
@@ -336,6 +339,13 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
       tc_fence_after();
       if (elect_one()) issue_mma(s, vh);
+      __syncwarp();
+      // the trace tile of the previous slice must have been read before the first step of this one overwrites it
+      if (vh == 0 && s > 0) {
+        mbar_wait(&sm.bar_diag, ((s >> 1) - 1) & 1, ctl, DEV_TIMEOUT_MMA);
+        tc_fence_after();
+      }
+      if (elect_one()) issue_trace(s, vh);
       __syncwarp();
     }
   } else {                                               // bulk loads: step s+NS goes into the stage step s has released
@@ -350,10 +360,10 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       if (p.cmap != nullptr) { t2 = p.cmap[n2]; rows2 = p.cmap[p.NC + n2]; }
       if (rows2 <= 0 || rows2 > CHUNK || t2 < 0 || t2 + rows2 > p.T) return;
       if (lane == 0) {
-        tma_prefetch_4d(&map_k, 0, h2, t2, b2);
-        tma_prefetch_4d(&map_q, 0, h2, t2, b2);
-        tma_prefetch_4d(&map_k, 64, h2, t2, b2);
-        tma_prefetch_4d(&map_q, 64, h2, t2, b2);
+        tma_prefetch_4d(&map_dv, 0, h2, t2, b2);
+        tma_prefetch_4d(&map_do, 0, h2, t2, b2);
+        tma_prefetch_4d(&map_dv, 64, h2, t2, b2);
+        tma_prefetch_4d(&map_do, 64, h2, t2, b2);
         const int64_t slice = static_cast<int64_t>(E) * 32768;
         const uint32_t lead = static_cast<uint32_t>(min(NS, STEPS)) * 16384u;
         bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + item2 * slice, lead);
@@ -364,10 +374,10 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
       const int64_t tok2 = static_cast<int64_t>(b2) * p.T + t2;
       for (int r = lane; r < rows2; r += 32) {
         const int64_t ro = (tok2 + r) * p.H + h2;
-        prefetch_l2(p.dV + ro * HEAD);
-        prefetch_l2(p.dV + ro * HEAD + 64);
-        prefetch_l2(p.dO + ro * HEAD);
-        prefetch_l2(p.dO + ro * HEAD + 64);
+        prefetch_l2(p.k + ro * HEAD);
+        prefetch_l2(p.k + ro * HEAD + 64);
+        prefetch_l2(p.q + ro * HEAD);
+        prefetch_l2(p.q + ro * HEAD + 64);
         prefetch_l2(p.k2 + ro * E);
         prefetch_l2(p.q2 + ro * E);
       }
@@ -389,36 +399,38 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
     warm_successor();                                    // nothing left to wait for: only the last steps and the epilogue remain
   }
   __syncthreads();
-  if (tid < E) {                                       // <h_e, G_e>: the eight warps' partial sums in a fixed order
-    float total = 0.f;
-#pragma unroll
-    for (int w = 0; w < SG_THREADS / 32; ++w) total += sm.red[tid * (SG_THREADS / 32) + w];
-    p.dd[item * E + tid] = total;
-  }
+  if (tid < E)                                         // <h_e, G_e>: the four row blocks' partial traces in a fixed order
+    p.dd[item * E + tid] = (sm.red[tid * 4] + sm.red[tid * 4 + 1]) + (sm.red[tid * 4 + 2] + sm.red[tid * 4 + 3]);
   // row sums: add the two column halves
   for (int idx = tid; idx < 128 * E && worker; idx += SG_THREADS) {
     const int r = idx / E, e = idx % E;
     const float v = sm.part[r * ES + e] + sm.part[(128 + r) * ES + e];
     if (r < 64) p.da[(item * 64 + r) * E + e] = v; else p.dc[(item * 64 + r - 64) * E + e] = v;
   }
-  // accumulators -> dkq, bf16 image [column / 8][row][column % 8]: rows 0..63 = ACC + ACC2 (dK), rows 64..127 = ACC (dQ).
-  // This thread: its row, 64 columns; a warp's 16-byte store covers 32 consecutive rows = 512 contiguous bytes.
+  // dkq, bf16 image [column / 8][row][column % 8]: rows 0..63 = the K rows' sum + (r*U) G^T from tensor memory (dK), rows
+  // 64..127 = the Q rows' sum (dQ).  This thread: its row, 64 columns; a warp's 16-byte store covers 32 consecutive rows =
+  // 512 contiguous bytes.
   tc_fence_after();
-  uint8_t* outp = reinterpret_cast<uint8_t*>(p.dkq) + item * 32768 + row * 16;
+  if (worker) {
+    uint8_t* outp = reinterpret_cast<uint8_t*>(p.dkq) + item * 32768 + row * 16;
+    const bool live_row = t < rows;
 #pragma unroll
-  for (int c0 = 0; c0 < 64 && worker; c0 += 32) {
-    float a[32], a2[32];
-    tmem_ld<32>(tmem_row + wg * 64 + c0, a);
-    tmem_ld<32>(tmem_row + 128 + wg * 64 + c0, a2);
-    tmem_wait_ld();
+    for (int c0 = 0; c0 < 64; c0 += 16) {
+      float a2[16];
+      tmem_ld<16>(tmem_row + 256 + wg * 64 + c0, a2);
+      tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      uint4 u;
-      u.x = pack_bf16(a[j] + (krow ? a2[j] : 0.f), a[j + 1] + (krow ? a2[j + 1] : 0.f));
-      u.y = pack_bf16(a[j + 2] + (krow ? a2[j + 2] : 0.f), a[j + 3] + (krow ? a2[j + 3] : 0.f));
-      u.z = pack_bf16(a[j + 4] + (krow ? a2[j + 4] : 0.f), a[j + 5] + (krow ? a2[j + 5] : 0.f));
-      u.w = pack_bf16(a[j + 6] + (krow ? a2[j + 6] : 0.f), a[j + 7] + (krow ? a2[j + 7] : 0.f));
-      *reinterpret_cast<uint4*>(outp + ((wg * 64 + c0 + j) >> 3) * 2048) = u;
+      for (int j = 0; j < 16; j += 8) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = live_row ? acc[c0 + j + i] + (krow ? a2[j + i] : 0.f) : 0.f;
+        uint4 u;
+        u.x = pack_bf16(v[0], v[1]);
+        u.y = pack_bf16(v[2], v[3]);
+        u.z = pack_bf16(v[4], v[5]);
+        u.w = pack_bf16(v[6], v[7]);
+        *reinterpret_cast<uint4*>(outp + ((wg * 64 + c0 + j) >> 3) * 2048) = u;
+      }
     }
   }
   tc_fence_before();
@@ -431,12 +443,12 @@ sg_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUt
 using namespace tgdn;
 
 template <int E>
-static int launch_sg(const CUtensorMap& mk, const CUtensorMap& mq, const SgParams& p, cudaStream_t s) {
+static int launch_sg(const CUtensorMap& mdv, const CUtensorMap& mdo, const SgParams& p, cudaStream_t s) {
   const int smem = static_cast<int>(sizeof(SgSmem<E>)) + 1024;
   static_assert(sizeof(SgSmem<E>) + 1024 <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(sg_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
-  sg_kernel<E><<<p.B * p.NC * p.H, SG_BLOCK, smem, s>>>(mk, mq, p);
+  sg_kernel<E><<<p.B * p.NC * p.H, SG_BLOCK, smem, s>>>(mdv, mdo, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -450,22 +462,23 @@ extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO
   if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(U) |
        reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkq)) & 15)
     return TGDN_ERR_ALIGN;
-  CUtensorMap mk, mq;
-  if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
-  if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
-  SgParams p{static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
+  if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(q)) & 15) return TGDN_ERR_ALIGN;
+  CUtensorMap mdv, mdo;
+  if ((rc = tgdn_make_token_map(&mdv, dV, B, T, H, 64, 64, 1))) return rc;
+  if ((rc = tgdn_make_token_map(&mdo, dO, B, T, H, 64, 64, 1))) return rc;
+  SgParams p{static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
              static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(h),
              static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, static_cast<__nv_bfloat16*>(dkq), da, dc, dd, chunk_map, B, T, H,
              NC, scale,
              tgdn_status_word(), tgdn_sm_count()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_sg<1>(mk, mq, p, s);
-    case 2: return launch_sg<2>(mk, mq, p, s);
-    case 4: return launch_sg<4>(mk, mq, p, s);
-    case 8: return launch_sg<8>(mk, mq, p, s);
-    case 12: return launch_sg<12>(mk, mq, p, s);
-    case 16: return launch_sg<16>(mk, mq, p, s);
+    case 1: return launch_sg<1>(mdv, mdo, p, s);
+    case 2: return launch_sg<2>(mdv, mdo, p, s);
+    case 4: return launch_sg<4>(mdv, mdo, p, s);
+    case 8: return launch_sg<8>(mdv, mdo, p, s);
+    case 12: return launch_sg<12>(mdv, mdo, p, s);
+    case 16: return launch_sg<16>(mdv, mdo, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

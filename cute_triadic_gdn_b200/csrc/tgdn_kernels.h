@@ -68,6 +68,8 @@ struct RecParams {
 };
 
 struct SgParams {
+  const __nv_bfloat16* k;   // token layout
+  const __nv_bfloat16* q;   // token layout
   const __nv_bfloat16* dO;  // token layout
   const __nv_bfloat16* dV;  // token layout
   const __nv_bfloat16* U;   // chunk layout

@@ -123,16 +123,17 @@ def state_grad_stage(K, Q, dO, fw, rv, rounding):
     a, c, r = (gt[x].transpose(2, 3)[..., None] for x in "acr")                 # (N,NC,E,64,1)
     h, G = fw["h"], rv["ds"]                                                    # (N,NC,E,D,V)
     dW, U = rv["dV"], fw["U"]
-    # the kernel scales its operands with one packed bf16 multiply: the gate factor is rounded to bf16 first, then the
-    # product is rounded once more
-    X1, X2, Vn = rd(rd(-a) * dW[:, :, None]), rd(rd(c) * dO[:, :, None]), rd(rd(r) * U[:, :, None])
+    # P_e = [dW ; dO] h_e^T on the tensor core (bf16 operands, f32 result); the gate-weighted sum over the slices and the
+    # row sums against K and Q are taken from it in f32.  Only r_e*U is scaled per slice: the gate factor is rounded to
+    # bf16 first, then the packed product is rounded once more.
+    P = torch.einsum('nctv,ncedv->ncetd', dW, h)
+    Pq = torch.einsum('nctv,ncedv->ncetd', dO, h)
+    Vn = rd(rd(r) * U[:, :, None])
     # the state parts of dK and dQ are handed to the matrix kernel as bf16
-    dK = rd(torch.einsum('ncetv,ncedv->nctd', X1, h) + torch.einsum('ncetv,ncedv->nctd', Vn, G))
-    dQ = rd(torch.einsum('ncetv,ncedv->nctd', X2, h))
-    R = torch.einsum('nctd,ncedv->ncetv', K, h)
-    Rq = torch.einsum('nctd,ncedv->ncetv', Q, h)
-    da = -torch.einsum('nctv,ncetv->ncte', dW, R)
-    dc = torch.einsum('nctv,ncetv->ncte', dO, Rq)
+    dK = rd((-a * P).sum(2) + torch.einsum('ncetv,ncedv->nctd', Vn, G))
+    dQ = rd((c * Pq).sum(2))
+    da = -torch.einsum('nctd,ncetd->ncte', K, P)
+    dc = torch.einsum('nctd,ncetd->ncte', Q, Pq)
     dd = (h * G).sum((-1, -2))                                                  # (N,NC,E)
     return dict(dK=dK, dQ=dQ, da=da, dc=dc, dd=dd)
 
