@@ -10,9 +10,11 @@
 // axis in two half-slice steps) from the raw [dW ; dO] tile, which TMA loads once: the workers then take both the row
 // sums (da_e[t] = -<K[t], P_e[t]>, dc_e[t] = <Q[t], P_e[t]>: the same numbers as the sums over v above, with the
 // contractions exchanged) and the gate-weighted accumulation over the slices (f32, in registers) from one read of P_e.
-// Against forming R = [K;Q] h_e for the row sums and pre-scaling [dW ; dO] per slice, that halves the MMA instructions
-// (8 instead of 16 per step) and takes 64 KB of operand reads and 16 KB of operand writes per step off the shared
-// memory, which is what bounds this kernel.  Only (r_e*U) G_e^T still runs on operands scaled per slice.
+// Against forming R = [K;Q] h_e for the row sums and pre-scaling [dW ; dO] per slice, that halves these MMA instructions
+// (8 instead of 16 per step), takes 64 KB of operand reads and 16 KB of operand writes per step off the shared memory
+// and keeps the gates in f32.  Only (r_e*U) G_e^T still runs on operands scaled per slice.  dd_e is the trace of a
+// third product, h_e G_e^T (4 more MMAs per step), so that the workers never read the half-slices: the 32 KB per step
+// they used to read for it cost them more time than any other part of their step.
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_state_grads.py:53-449 (sg_kernel).
 #include <type_traits>
@@ -32,9 +34,8 @@ __device__ __forceinline__ float sexp2(float x) {
   return y;
 }
 
-// Number of ring stages: four where the gate tables and row-sum partials of the slice count leave room (E <= 8), else
-// three.  Each stage that holds data already consumed by neither reader is a stage not in flight; the fourth stage is what
-// keeps about two half-slice pairs (64 KB) travelling while two more wait for their MMAs.
+// Four ring stages: about two half-slice pairs (64 KB) travel while two more wait for their MMAs.  Measured at E = 8:
+// three stages are 3% slower, five were slower too.
 template <int E>
 struct SgSmem {
   static constexpr int ES = E | 1;   // row stride of the gate tables and partials (odd: conflict-free)
