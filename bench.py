@@ -56,8 +56,12 @@ KERNEL_U = {
 # full launch is this figure times its items.
 NCU_DRAM_BYTES_PER_ITEM_E8 = {
     "masks": (0.161 + 0.076) * 1e9 / 4096, "fwd": (0.373 + 1.223) * 1e9 / 4096, "rec": (0.479 + 1.221) * 1e9 / 4096,
-    "sg": (2.510 + 0.146) * 1e9 / 4096, "mat": (0.715 + 0.146) * 1e9 / 4096,
+    "sg": (2.511 + 0.214) * 1e9 / 4096, "mat": (0.715 + 0.146) * 1e9 / 4096,
 }
+
+# DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)
+# (profiles/conv_kernels_c4_shape.md; part of the written lines still sat in L2 when the kernel ended).
+NCU_DRAM_BYTES_PER_ELEMENT_CONV = {"fwd": (215.9 + 162.0) * 1e6 / (8192 * 13056), "bwd": (431.6 + 184.2) * 1e6 / (8192 * 13056)}
 
 # Algorithmic HBM bytes per (chunk, head) item: every tensor a kernel must read or write, once (bf16 tiles of 64x128 are
 # 16 KB; a state slice is 32 KB; NV = value blocks of the reverse recurrence).  The saved states make every kernel of this
@@ -402,9 +406,10 @@ def run_conv(args):
             "steps": args.steps, "warmup": 3, "ms_per_step": fwd_ms, "higher_is_better": True, "dtype": "bf16",
             "data": "synthetic", "config": {"workload": f"conv (1,{T},{C}) act={act}, {n_docs} documents"},
             "roofline": {"bound": "hbm", "kernel": "conv_fwd", "achieved": fb / (fwd_ms * 1e-3) / 1e9, "peak": pk["gbs"],
-                         "unit": "GB/s", "frac": fb / (fwd_ms * 1e-3) / 1e9 / pk["gbs"], "traffic": None,
-                         "peak_kind": pk["kind"]},
-            "conv_bwd": {"ms": bwd_ms, "achieved": bb / (bwd_ms * 1e-3) / 1e9, "frac": bb / (bwd_ms * 1e-3) / 1e9 / pk["gbs"]}}
+                         "unit": "GB/s", "frac": fb / (fwd_ms * 1e-3) / 1e9 / pk["gbs"],
+                         "traffic": NCU_DRAM_BYTES_PER_ELEMENT_CONV["fwd"] * T * C, "peak_kind": pk["kind"]},
+            "conv_bwd": {"ms": bwd_ms, "achieved": bb / (bwd_ms * 1e-3) / 1e9, "frac": bb / (bwd_ms * 1e-3) / 1e9 / pk["gbs"],
+                         "traffic": NCU_DRAM_BYTES_PER_ELEMENT_CONV["bwd"] * T * C}}
     print(json.dumps(line))
 
 
