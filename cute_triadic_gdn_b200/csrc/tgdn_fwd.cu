@@ -1,27 +1,36 @@
 // Forward chunk recurrence of the Triadic GDN.
 //
-// One CTA of 512 threads owns one (sequence, head, value block of VC columns) and walks the sequence's 64-token
-// chunks in order, with the E state slices S_e[:, value block] (128 x VC each, f32) in registers.  Per chunk:
-//   (1) R  = [K;Q] S          tcgen05, M=128, N=E*VC, K=128   rows 0..63: K S_e, rows 64..127: Q S_e
+// One CTA owns one (sequence, head, block of VC value columns) and walks the sequence's 64-token chunks in order.  The
+// block is split over NCH independent CHAINS, one per warpgroup (128 threads = the 128 rows of [K;Q]); chain c owns CW value
+// columns of every slice: its E state slices S_e[:, columns] (128 x CW each, f32) live in the registers of its threads.
+// Per chunk a chain runs three dependent MMA groups of its own, with its own accumulators in tensor memory:
+//   (1) R  = [K;Q] S          tcgen05, M=128, N=E*CW, K=128   rows 0..63: K S_e, rows 64..127: Q S_e
 //       W  = V - sum_e a_e*R_e (K rows);   Oq = sum_e c_e*R_e (Q rows)
-//   (2) [U;Oi] = [A;PmA] (beta*W)   tcgen05, M=128, N=VC, K=64
+//   (2) [U;Oi] = [A;PmA] (beta*W)   tcgen05, M=128, N=16 (CW used), K=64
 //       o  = Oq + Oi  ->  bf16;   Vn_e = r_e*U
-//   (3) dS = K^T Vn           tcgen05, M=128, N=E*VC, K=64
+//   (3) dS = K^T Vn           tcgen05, M=128, N=E*CW, K=64
 //       S_e <- d_e S_e + dS_e  (registers), bf16 copy -> shared memory operand of the next (1) and saved state h
 // with a = k2 exp(gc), r = k2 exp(gL-gc), c = scale q2 exp(gc), d = exp(gL).
 //
-// Replaces cute_triadic_gdn/kernels/sm100_joint_fwd.py:66-527 (fwd_kernel); math as cute_triadic_gdn/ops/gdn_joint.py:63-90.
-// K/Q tiles arrive by TMA (128B swizzle) one chunk ahead, the [A;PmA] operand image by a bulk copy; every wait is bounded.
+// The chains of a CTA share only the chunk's K/Q tiles and the [A;PmA] image, which arrive by TMA in a ring of STAGES
+// stages; a stage is refilled by whichever chain is the last to finish with it, so no chain ever waits for another one
+// except through that ring.  Everything else is private to a chain (its columns are independent of all other columns
+// of the problem): its barrier is a named barrier of 128 threads, its MMAs are issued by one of its own lanes and
+// complete on its own mbarrier.  While one chain waits for its MMA or its tensor-memory load, the tensor core and the
+// issue slots work for the others: the dependent chain of a chunk (three MMA -> load -> epilogue round trips) is what
+// bounds this kernel, and the number of independent chains per SM is what hides it.
 //
-// Column order inside the CTA: thread (warpgroup w, row i) owns, for every slice e, the CW = VC/4 value columns
-// w*CW..w*CW+CW-1; its E*CW columns are contiguous in tensor memory and in the operand images:
-// n' = w*(E*CW) + e*CW + c  <->  (slice e, value column w*CW + c of the block).
+// Every thread computes the gate factors of its own row (K rows: a, r, beta; Q rows: c) in registers from the raw
+// k2/q2/gc rows, requested right after its chain's MMA (1) went out, so the loads and the exponentials run under the
+// MMA; there are no shared gate tables and nothing couples the chains but the tile ring.
+//
+// Replaces cute_triadic_gdn/kernels/sm100_joint_fwd.py:66-527 (fwd_kernel); math as cute_triadic_gdn/ops/gdn_joint.py:63-90.
+// Column order inside a chain: n' = e*CW + c  <->  (slice e, value column c of the chain).
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"
 
 namespace tgdn {
-
 
 __device__ __forceinline__ float fexp2(float x) {
   float y;
@@ -29,91 +38,162 @@ __device__ __forceinline__ float fexp2(float x) {
   return y;
 }
 
-// NWG warpgroups (128 threads each) split the VC value columns; STAGES = 2 prefetches the next chunk's tiles and runs
-// one CTA per SM, STAGES = 1 is sized so that two CTAs share an SM and hide each other's dependent-MMA latency.
-template <int E, int VC, int NWG, int STAGES>
+// E floats of one row; rows are E*4 bytes apart from a 16-byte aligned base
+template <int E>
+__device__ __forceinline__ void ld_row(const float* p, float* out) {
+  if constexpr (E % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < E / 4; ++j) {
+      const float4 x = __ldg(reinterpret_cast<const float4*>(p) + j);
+      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+    }
+  } else if constexpr (E == 2) {
+    const float2 x = __ldg(reinterpret_cast<const float2*>(p));
+    out[0] = x.x; out[1] = x.y;
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j) out[j] = __ldg(p + j);
+  }
+}
+
+__device__ __forceinline__ void chain_sync(int chain) {     // the 128 threads of one chain
+  asm volatile("bar.sync %0, 128;" ::"r"(chain + 1) : "memory");
+}
+
+template <int E, int CW, int NCH, int STAGES>
 struct FwdCfg {
-  static constexpr int THREADS = NWG * 128;
-  static constexpr int NCOLS = E * VC;            // columns of R and dS
-  static constexpr int CW = VC / NWG;             // value columns per thread and slice
-  static constexpr int TPC = E * CW;              // state columns per thread
-  static constexpr int ES = E | 1;                // row stride of the gate tables (odd: conflict-free)
-  static constexpr int TMEM_COLS = (NCOLS + VC) <= 64 ? 64 : (NCOLS + VC) <= 128 ? 128 : (NCOLS + VC) <= 256 ? 256 : 512;
-  // shared memory carve-up (bytes); every operand base is 1024-byte aligned
+  static constexpr int THREADS = NCH * 128;
+  static constexpr int VC = CW * NCH;             // value columns of the CTA
+  static constexpr int TPC = E * CW;              // state columns per chain (and per thread)
+  static constexpr int UW = 16;                   // columns of the (2) accumulator (the smallest N of an M=128 MMA)
+  static constexpr int TW = TPC + UW;             // tensor-memory columns per chain
+  static constexpr int TMEM_NEED = NCH * TW;
+  static constexpr int TMEM_COLS = TMEM_NEED <= 32 ? 32 : TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
+  // shared memory carve-up (bytes); the swizzled tiles are 1024-byte aligned
   static constexpr int KQ_BYTES = 32768;
   static constexpr int AP_BYTES = 16384;
-  static constexpr int S_BYTES = NCOLS * 256;     // image (i = d, j = n'), SI = 128, SJ = 2048
-  static constexpr int VN_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
-  static constexpr int BW_BYTES = VC * 128;       // image (i = s, j = v),  SI = 128, SJ = 1024
+  static constexpr int S_BYTES = TPC * 256;       // per chain: image (i = d, j = n'), SI = 128, SJ = 2048
+  static constexpr int VN_BYTES = TPC * 128;      // per chain: image (i = t, j = n'), SI = 128, SJ = 1024
+  static constexpr int BW_BYTES = 2048;           // per chain: image (i = s, j = v), 16 columns, SI = 128, SJ = 1024
   static constexpr int OFF_KQ = 0;
   static constexpr int OFF_AP = OFF_KQ + STAGES * KQ_BYTES;
   static constexpr int OFF_S = OFF_AP + STAGES * AP_BYTES;
-  static constexpr int OFF_VN = OFF_S + S_BYTES;
-  static constexpr int OFF_BW = OFF_VN + VN_BYTES;
-  static constexpr int OFF_GATES = OFF_BW + ((BW_BYTES + 1023) & ~1023);
-  static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 32;     // a, r, c tables, beta, two copies of d
-  static constexpr int OFF_CTRL = OFF_GATES + GATE_FLOATS * 4;
-  static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;       // + control block + alignment slack
+  static constexpr int OFF_VN = OFF_S + NCH * S_BYTES;
+  static constexpr int OFF_BW = OFF_VN + NCH * VN_BYTES;
+  static constexpr int OFF_DT = OFF_BW + NCH * BW_BYTES;      // per chain: exp(gL) of the current chunk, 16 floats
+  static constexpr int OFF_CTRL = OFF_DT + NCH * 64;
+  static constexpr int SMEM_BYTES = OFF_CTRL + 128 + 1024;    // + control block + alignment slack
+  static_assert(CW == 4 || CW == 8 || CW == 16, "a chain owns 4, 8 or 16 value columns");
+  static_assert(TPC % 16 == 0 && TPC <= 64, "columns per chain: a multiple of 16 (MMA N, tensor-memory loads), at most 64 registers of state");
 };
 
 struct FwdCtrl {
   uint64_t bar_load[2];
-  uint64_t bar_mma;
+  uint64_t bar_mma[4];
+  uint32_t released[2];      // chains that have finished with the stage (counts up forever; a multiple of NCH = all)
   uint32_t tmem_base;
   int abort;
 };
 
-template <int E, int VC, int NWG, int STAGES>
-__global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
+template <int E, int CW, int NCH, int STAGES, int MINB>
+__global__ void __launch_bounds__(NCH * 128, MINB)
 fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, FwdParams p) {
-  using C = FwdCfg<E, VC, NWG, STAGES>;
-  constexpr int FWD_THREADS = C::THREADS;
-  constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
+  using C = FwdCfg<E, CW, NCH, STAGES>;
+  constexpr int TPC = C::TPC, VC = C::VC;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* gate_base = reinterpret_cast<float*>(smem + C::OFF_GATES);
   FwdCtrl& ctrl = *reinterpret_cast<FwdCtrl*>(smem + C::OFF_CTRL);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wg = warp >> 2;                         // warpgroup: which CW columns of every slice
+  const int chain = warp >> 2;                      // warpgroup = chain
   const int row = (warp & 3) * 32 + lane;           // tensor-memory lane = operand row
   const bool krow = row < 64;                       // rows 0..63 work on K rows (W, U, Vn), 64..127 on Q rows (o)
   const int t = row & 63;
+  uint8_t* s_img = smem + C::OFF_S + chain * C::S_BYTES;
+  uint8_t* vn_img = smem + C::OFF_VN + chain * C::VN_BYTES;
+  uint8_t* bw_img = smem + C::OFF_BW + chain * C::BW_BYTES;
+  float* dtab = reinterpret_cast<float*>(smem + C::OFF_DT) + chain * 16;
 
   // work item
   constexpr int NV = HEAD / VC;
   const int vb = blockIdx.x % NV, h = (blockIdx.x / NV) % p.H, seq_rank = blockIdx.x / (NV * p.H);
-  int b = seq_rank, first = 0, count = p.NC;
+  int b = seq_rank, first = 0, count = p.NC, seq = seq_rank;
   if (p.cmap != nullptr) {
     const int doc = p.cmap[2 * p.NC + seq_rank];    // longest documents first
     if (doc < 0 || doc >= p.n_seq) return;
     b = 0;
+    seq = doc;
     first = p.offsets[doc];
     count = p.offsets[doc + 1] - first;
     if (first < 0 || count <= 0 || first + count > p.NC) return;
   }
+  const int v0g = vb * VC + chain * CW;             // first value column of this chain in the head
 
   if (tid == 0) {
     mbar_init(&ctrl.bar_load[0], 1);
     mbar_init(&ctrl.bar_load[1], 1);
-    mbar_init(&ctrl.bar_mma, 1);
+    for (int c = 0; c < 4; ++c) mbar_init(&ctrl.bar_mma[c], 1);
     mbar_fence_init();
+    ctrl.released[0] = ctrl.released[1] = 0;
     ctrl.abort = 0;
   }
   if (warp == 0) { tmem_alloc(&ctrl.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
-  // zero state: registers and operand image
+  // state: zero, or the caller's initial state (f32 [seq][H][E][128 d][128 v])
   float S[TPC];
+  if (p.s_in != nullptr) {
+    const float* src = p.s_in + ((static_cast<int64_t>(seq) * p.H + h) * E) * (HEAD * HEAD) + row * HEAD + v0g;
 #pragma unroll
-  for (int j = 0; j < TPC; ++j) S[j] = 0.f;
-  for (int i = tid; i < C::S_BYTES / 16; i += FWD_THREADS) reinterpret_cast<uint4*>(smem + C::OFF_S)[i] = make_uint4(0, 0, 0, 0);
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int c = 0; c < CW; ++c) S[e * CW + c] = __ldg(src + e * (HEAD * HEAD) + c);
+  } else {
+#pragma unroll
+    for (int j = 0; j < TPC; ++j) S[j] = 0.f;
+  }
+  // the second 8-column block of the (2) operand is never written: keep it zero (its products land in unused columns)
+  for (int i = (tid & 127); i < C::BW_BYTES / 16; i += 128) reinterpret_cast<uint4*>(bw_img)[i] = make_uint4(0, 0, 0, 0);
+
+  // saved state / operand image of this thread's S: pieces of 8 columns (one 16-byte store each into the image)
+  auto state_item_ptr = [&](int64_t item) {
+    return reinterpret_cast<uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
+  };
+  auto store_state_slices = [&](uint8_t* hbase, int j0, const uint32_t* packed /* 8 words = 16 columns from j0 */) {
+#pragma unroll
+    for (int j = 0; j < 16; j += CW) {
+      const int e = (j0 + j) / CW;
+      uint8_t* dst = hbase + e * 32768 + (v0g >> 3) * 2048 + row * 16 + (v0g & 7) * 2;
+      if constexpr (CW == 16) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(dst + 2048) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      } else if constexpr (CW == 8) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[j / 2], packed[j / 2 + 1]);
+      }
+    }
+  };
+  {
+    const uint32_t base = smem_u32(s_img) + (row >> 3) * 128 + (row & 7) * 16;
+    uint8_t* hbase = p.h != nullptr ? state_item_ptr((static_cast<int64_t>(b) * p.NC + first) * p.H + h) : nullptr;
+#pragma unroll
+    for (int j0 = 0; j0 < TPC; j0 += 16) {
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) packed[j / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
+      st_shared_v4(base + (j0 >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
+      st_shared_v4(base + ((j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
+      if (hbase != nullptr) store_state_slices(hbase, j0, packed);
+    }
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = __shfl_sync(0xffffffffu, ctrl.tmem_base, 0);
-  const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  const int cwarp_u = __shfl_sync(0xffffffffu, warp & 3, 0);   // warp index inside the chain as a warp-uniform value
+  const uint32_t tmem_c = tmem + chain * C::TW;                  // this chain's columns: [0, TPC) R / dS, [TPC, TPC+16) U / Oi
+  const uint32_t tmem_row = tmem_c + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&ctrl.abort, p.status};
 
   auto chunk_info = [&](int i, int& t0, int& rows) {
@@ -124,10 +204,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       t0 = 0; rows = 0;
     }
   };
-  auto issue_loads = [&](int i) {                   // thread 0: K/Q tiles and the [A;PmA] image of local chunk i
+  auto issue_loads = [&](int i) {                   // one thread: K/Q tiles and the [A;PmA] image of local chunk i
     int t0, rows;
     chunk_info(i, t0, rows);
-    const int st = (STAGES == 2) ? (i & 1) : 0;
+    const int st = i % STAGES;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES);
@@ -137,7 +217,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
     bulk_load(smem + C::OFF_AP + st * C::AP_BYTES, p.AP + item * (128 * 64), C::AP_BYTES, &ctrl.bar_load[st]);
   };
-  auto prefetch_loads = [&](int i) {                // thread 0: pull the next chunk's tiles into L2 while this chunk is worked on
+  auto prefetch_tiles = [&](int i) {                // one thread: pull a later chunk's tiles into L2
     int t0, rows;
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
@@ -147,351 +227,262 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_prefetch_4d(&map_q, 64, h, t0, b);
     bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
   };
-  // saved state of chunk item: this thread's pieces of slice e live at [e][(vb*VC + wg*CW)/8][row][...]
-  auto store_state = [&](int64_t item, const uint32_t* packed /* TPC/2 words */) {
-    if (p.h == nullptr) return;
-    uint8_t* base = reinterpret_cast<uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int v0 = vb * VC + wg * CW;
-      uint8_t* dst = base + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
-      if constexpr (CW == 8) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[e * 4], packed[e * 4 + 1], packed[e * 4 + 2], packed[e * 4 + 3]);
-      } else {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[e * 2], packed[e * 2 + 1]);
-      }
-    }
-  };
-
-  // Gate tables.  The Q-row threads own them.  During the epilogue of (2), where Q rows have little else to do, they load
-  // the next chunk's raw inputs (pulled into L2 one chunk earlier, so the loads are short and nothing is held in
-  // registers across a chunk), turn them into table values and store a, c and beta, which nobody reads after the
-  // epilogue of (1); r, which the K rows still read in (2), and d, which (3) itself uses (two copies), follow at the start
-  // of the epilogue of (3).  Loads are unconditional from clamped (always valid) addresses and masked at use.
-  constexpr int QTHREADS = FWD_THREADS / 2;
-  constexpr int GQ = (64 * E + QTHREADS - 1) / QTHREADS;     // table entries per Q-row thread
-  const int qid = wg * 64 + t;                               // Q-row threads: 0 .. QTHREADS-1
-  struct GateRaw { float gcv[GQ], gl[GQ], k2v[GQ], q2v[GQ], beta; int rows; };
-  struct GateVal { float a[GQ], r[GQ], c[GQ], d[GQ], beta; };
-  float* g_a = gate_base;
-  float* g_r = g_a + 64 * ES;
-  float* g_c = g_r + 64 * ES;
-  float* g_beta = g_c + 64 * ES;
-  float* g_dd = g_beta + 64;                                 // [2][16]
-  auto load_gates = [&](int i) {
-    GateRaw g;
-    int t0, rows;
-    chunk_info(i, t0, rows);
-    g.rows = rows;
-    const int last = max(rows, 1) - 1;
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    const float* gcp = p.gc + item * (64 * E);
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
-      const int r = idx / E, e = idx % E;
-      const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
-      g.gcv[it] = __ldg(gcp + idx);
-      g.gl[it] = __ldg(gcp + 63 * E + e);
-      g.k2v[it] = __ldg(p.k2 + off);
-      g.q2v[it] = __ldg(p.q2 + off);
-    }
-    g.beta = __ldg(p.beta + (tok + min(qid & 63, last)) * p.H + h);
-    return g;
-  };
-  auto gate_values = [&](const GateRaw& g) {
-    GateVal v;
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
-      const bool ok = idx / E < g.rows;
-      const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
-      const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
-      const float eg = fexp2(gcv);
-      v.a[it] = k2v * eg;
-      v.r[it] = k2v * fexp2(gl - gcv);
-      v.c[it] = p.scale * q2v * eg;
-      v.d[it] = fexp2(gl);
-    }
-    v.beta = ((qid & 63) < g.rows) ? g.beta : 0.f;
-    return v;
-  };
-  auto store_gates_early = [&](const GateVal& v) {            // a, c, beta
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = qid + it * QTHREADS;
-      if (idx < 64 * E) {
-        const int r = idx / E, e = idx % E;
-        g_a[r * ES + e] = v.a[it];
-        g_c[r * ES + e] = v.c[it];
-      }
-    }
-    if (qid < 64) g_beta[qid] = v.beta;
-  };
-  auto store_gates_late = [&](const float* vr, float vd, int dbuf) {   // r, d
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = qid + it * QTHREADS;
-      if (idx < 64 * E) g_r[(idx / E) * ES + idx % E] = vr[it];
-    }
-    if (qid < E) g_dd[dbuf * 16 + qid] = vd;                  // entry (row 0, e = qid) is this thread's first
-  };
-  auto prefetch_gates = [&](int i) {                         // Q-row threads: one request per distinct 128-byte line
+  auto prefetch_rows = [&](int i) {                 // this thread's gate rows and value row of a later chunk -> L2
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    if (qid < 64) {
-      const int64_t ro = (tok + min(qid, last)) * p.H + h;
+    const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
+    if (krow) {
       prefetch_l2(p.k2 + ro * E);
-      prefetch_l2(p.q2 + ro * E);
       prefetch_l2(p.beta + ro);
-    }
-    if (qid * 32 < 64 * E) prefetch_l2(p.gc + item * (64 * E) + qid * 32);
-  };
-  auto load_vrow = [&](int i) {                      // this thread's CW value columns of row t (clamped), raw bf16
-    int t0, rows;
-    chunk_info(i, t0, rows);
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    const __nv_bfloat16* vp = p.v + ((tok + min(t, max(rows, 1) - 1)) * p.H + h) * HEAD + vb * VC + wg * CW;
-    uint4 u;
-    if constexpr (CW == 8) {
-      u = __ldg(reinterpret_cast<const uint4*>(vp));
+      prefetch_l2(p.v + ro * HEAD + v0g);
     } else {
-      const uint2 w = __ldg(reinterpret_cast<const uint2*>(vp));
-      u = make_uint4(w.x, w.y, 0u, 0u);
+      prefetch_l2(p.q2 + ro * E);
+      prefetch_l2(p.gc + item * (64 * E) + t * E);
     }
-    return u;
+  };
+  auto load_vrow = [&](int t0, int rows, uint32_t* out /* CW/2 words */) {   // CW value columns of row t (clamped), raw bf16
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const __nv_bfloat16* vp = p.v + ((tok + min(t, max(rows, 1) - 1)) * p.H + h) * HEAD + v0g;
+    if constexpr (CW == 16) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(vp)), u1 = __ldg(reinterpret_cast<const uint4*>(vp) + 1);
+      out[0] = u0.x; out[1] = u0.y; out[2] = u0.z; out[3] = u0.w; out[4] = u1.x; out[5] = u1.y; out[6] = u1.z; out[7] = u1.w;
+    } else if constexpr (CW == 8) {
+      const uint4 u0 = __ldg(reinterpret_cast<const uint4*>(vp));
+      out[0] = u0.x; out[1] = u0.y; out[2] = u0.z; out[3] = u0.w;
+    } else {
+      const uint2 u0 = __ldg(reinterpret_cast<const uint2*>(vp));
+      out[0] = u0.x; out[1] = u0.y;
+    }
+  };
+  auto store_row_global = [&](__nv_bfloat16* ptr, const float* src) {         // CW consecutive bf16
+#pragma unroll
+    for (int c = 0; c < CW; c += 8) {
+      if constexpr (CW >= 8)
+        *reinterpret_cast<uint4*>(ptr + c) = make_uint4(pack_bf16(src[c], src[c + 1]), pack_bf16(src[c + 2], src[c + 3]),
+                                                        pack_bf16(src[c + 4], src[c + 5]), pack_bf16(src[c + 6], src[c + 7]));
+      else
+        *reinterpret_cast<uint2*>(ptr) = make_uint2(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]));
+    }
+  };
+  // CW consecutive columns n0.. of row r of an image whose 8-column blocks are SJ bytes apart
+  auto store_row_image = [&](uint32_t row_base, int n0, uint32_t SJ, const float* src, float f) {
+    if constexpr (CW >= 8) {
+#pragma unroll
+      for (int c = 0; c < CW; c += 8)
+        st_shared_v4(row_base + ((n0 + c) >> 3) * SJ, pack_bf16(f * src[c], f * src[c + 1]), pack_bf16(f * src[c + 2], f * src[c + 3]),
+                     pack_bf16(f * src[c + 4], f * src[c + 5]), pack_bf16(f * src[c + 6], f * src[c + 7]));
+    } else {
+      st_shared_v2(row_base + (n0 >> 3) * SJ + (n0 & 7) * 2, pack_bf16(f * src[0], f * src[1]), pack_bf16(f * src[2], f * src[3]));
+    }
   };
 
-  if (tid == 0) issue_loads(0);
-  uint4 vnext = load_vrow(0);
-  // Where registers allow (small E), the raw inputs are held in registers one chunk ahead instead of only sitting in L2.
-  constexpr bool HOLD_RAW = E <= 4;
-  GateRaw raw_next;
-  float r_next[GQ], d_next = 0.f;                      // Q-row threads: table values that wait for the epilogue of (3)
-  if (!krow) {
-    const GateVal v = gate_values(load_gates(0));
-    store_gates_early(v);
-    store_gates_late(v.r, v.d[0], 0);
-    if (count > 1) {
-      if constexpr (HOLD_RAW) raw_next = load_gates(1); else prefetch_gates(1);
-    }
+  if (tid == 0) {
+    issue_loads(0);
+    if (STAGES == 2 && count > 1) issue_loads(1);
   }
+  if (count > 1) prefetch_rows(1);
   uint32_t mma_phase = 0;
-  {
-    uint32_t zeros[TPC / 2];
-#pragma unroll
-    for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
-    store_state((static_cast<int64_t>(b) * p.NC + first) * p.H + h, zeros);
-  }
-  __syncthreads();                                   // first chunk's gate tables visible
 
   for (int i = 0; i < count; ++i) {
-    const int st = (STAGES == 2) ? (i & 1) : 0;
+    const int st = i % STAGES;
     int t0, rows;
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const bool live = t < rows;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
 
     // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
-    mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (i >> 1) : i) & 1, ctl, DEV_TIMEOUT_LOAD);
-    if (warp_u == 0 && elect_one()) {
+    // Only the chain's first warp polls an mbarrier; the other three sleep in the chain's hardware barrier until it has
+    // seen the flip.  Twelve more spinning warps per SM would take their share of the issue slots from the warps of the
+    // other chains that are in an epilogue at that moment.
+    if (cwarp_u == 0) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    if (cwarp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
-      const uint64_t db = make_desc(smem_u32(smem + C::OFF_S), 128, 2048, LAYOUT_PLAIN);
-      constexpr uint32_t idesc = make_idesc(128, NCOLS, 0, 1);
+      const uint64_t db = make_desc(smem_u32(s_img), 128, 2048, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, TPC, 0, 1);
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)
-        umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
-      umma_commit(&ctrl.bar_mma);
+        umma_bf16(tmem_c, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma[chain]);
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    if (warp_u == 1 && i + 1 < count && elect_one()) {
-      if (STAGES == 2) issue_loads(i + 1);             // the other stage was released by the previous chunk's (3)
-      if (STAGES == 1) prefetch_loads(i + 1);
+    // Under the MMA: this row's raw gate inputs and value row (in L2 since the previous chunk), then the gate factors.
+    float ga[E];                                     // K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
+    float gr[E];                                     // K rows: r_e = k2 exp(gL - gc)
+    float bt = 0.f;
+    uint32_t vraw[CW / 2];
+    {
+      const int tl = min(t, max(rows, 1) - 1);
+      const float* gcp = p.gc + item * (64 * E);
+      const int64_t ro = (tok + tl) * p.H + h;
+      float gcr[E], x2[E];
+      ld_row<E>(gcp + t * E, gcr);
+      ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
+      if (krow) {
+        float gl[E];
+        ld_row<E>(gcp + 63 * E, gl);
+        bt = __ldg(p.beta + ro);
+        load_vrow(t0, rows, vraw);
+        if (t < E) dtab[t] = fexp2(__ldg(gcp + 63 * E + t) * LOG2E);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float k2v = live ? x2[e] : 0.f;
+          ga[e] = k2v * fexp2(gcr[e] * LOG2E);
+          gr[e] = k2v * fexp2((gl[e] - gcr[e]) * LOG2E);
+        }
+        if (!live) bt = 0.f;
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          ga[e] = live ? p.scale * x2[e] * fexp2(gcr[e] * LOG2E) : 0.f;
+          gr[e] = 0.f;
+        }
+      }
+      if (i + 2 < count) prefetch_rows(i + 2);
     }
-    // the load of the next chunk's value row goes out now; it is consumed one iteration later
-    const float* g_d = g_dd + (i & 1) * 16;
-    const uint4 vraw = vnext;
-    if (i + 1 < count) vnext = load_vrow(i + 1);
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    chain_sync(chain);
     ++mma_phase;
     tc_fence_after();
 
     float acc[CW];                                   // K rows: W (starts from V); Q rows: Oq
-    {
-      const uint32_t vw[4] = {vraw.x, vraw.y, vraw.z, vraw.w};
 #pragma unroll
-      for (int c = 0; c < CW; ++c)
-        acc[c] = (krow && t < rows) ? ((c & 1) ? bf16_hi(vw[c >> 1]) : bf16_lo(vw[c >> 1])) : 0.f;
-    }
+    for (int c = 0; c < CW; ++c) acc[c] = (krow && live) ? ((c & 1) ? bf16_hi(vraw[c >> 1]) : bf16_lo(vraw[c >> 1])) : 0.f;
     {
-      const float* tab = krow ? g_a : g_c;
-      constexpr int EP = (TPC % 32 == 0) ? 32 / CW : ((TPC % 16 == 0) ? 16 / CW : E);   // slices per tensor-memory round trip
+      // sixteen columns at a time, the next piece travelling while this one is used
+      float rr[2][16];
+      tmem_ld<16>(tmem_row, rr[0]);
 #pragma unroll
-      for (int e0 = 0; e0 < E; e0 += EP) {
-        float rr[EP * CW];
-        tmem_ld<EP * CW>(tmem_row + wg * TPC + e0 * CW, rr);
+      for (int pc = 0; pc < TPC / 16; ++pc) {
         tmem_wait_ld();
+        if (pc + 1 < TPC / 16) tmem_ld<16>(tmem_row + (pc + 1) * 16, rr[(pc + 1) & 1]);
+        const float* rp = rr[pc & 1];
 #pragma unroll
-        for (int ee = 0; ee < EP; ++ee) {
-          const float gsc = tab[t * ES + e0 + ee];
-          const float sg = krow ? -gsc : gsc;
-#pragma unroll
-          for (int c = 0; c < CW; ++c) acc[c] = fmaf(sg, rr[ee * CW + c], acc[c]);
+        for (int j = 0; j < 16; ++j) {
+          const int e = (pc * 16 + j) / CW, c = (pc * 16 + j) % CW;
+          acc[c] = fmaf(krow ? -ga[e] : ga[e], rp[j], acc[c]);
         }
       }
     }
     if (krow) {
       // W -> saved (bf16), beta*W -> operand image (i = s, j = v)
-      const float bt = g_beta[t];
-      uint32_t wsave[CW / 2], wop[CW / 2];
-#pragma unroll
-      for (int c = 0; c < CW; c += 2) {
-        wsave[c / 2] = pack_bf16(acc[c], acc[c + 1]);
-        wop[c / 2] = pack_bf16(bt * acc[c], bt * acc[c + 1]);
-      }
-      const int v0 = wg * CW;
-      const uint32_t dst = smem_u32(smem + C::OFF_BW) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2;
-      if constexpr (CW == 8) st_shared_v4(dst, wop[0], wop[1], wop[2], wop[3]); else st_shared_v2(dst, wop[0], wop[1]);
-      if (p.W != nullptr) {
-        __nv_bfloat16* wp = p.W + (item * 64 + t) * HEAD + vb * VC + v0;
-        if constexpr (CW == 8) *reinterpret_cast<uint4*>(wp) = make_uint4(wsave[0], wsave[1], wsave[2], wsave[3]);
-        else *reinterpret_cast<uint2*>(wp) = make_uint2(wsave[0], wsave[1]);
-      }
+      store_row_image(smem_u32(bw_img) + (t >> 3) * 128 + (t & 7) * 16, 0, 1024, acc, bt);
+      if (p.W != nullptr) store_row_global(p.W + (item * 64 + t) * HEAD + v0g, acc);
     }
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    chain_sync(chain);
 
     // ---- (2) [U;Oi] = [A;PmA] (beta W) ------------------------------------------------------------------------
-    if (warp_u == 0 && elect_one()) {
+    if (cwarp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(ap), 2048, 128, LAYOUT_PLAIN);
-      const uint64_t db = make_desc(smem_u32(smem + C::OFF_BW), 128, 1024, LAYOUT_PLAIN);
-      constexpr uint32_t idesc = make_idesc(128, VC, 0, 1);
+      const uint64_t db = make_desc(smem_u32(bw_img), 128, 1024, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, C::UW, 0, 1);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
-        umma_bf16(tmem + NCOLS, desc_advance(da, kk * 4096), desc_advance(db, kk * 256), idesc, kk > 0);
-      umma_commit(&ctrl.bar_mma);
+        umma_bf16(tmem_c + TPC, desc_advance(da, kk * 4096), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma[chain]);
     }
-    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    __syncwarp();
+    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    chain_sync(chain);
     ++mma_phase;
     tc_fence_after();
     {
       float u[CW];
-      tmem_ld<CW>(tmem_row + NCOLS + wg * CW, u);
+      tmem_ld<CW>(tmem_row + TPC, u);
       tmem_wait_ld();
       if (krow) {
-        if (p.U != nullptr) {
-          __nv_bfloat16* up = p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW;
-          if constexpr (CW == 8)
-            *reinterpret_cast<uint4*>(up) = make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
-          else
-            *reinterpret_cast<uint2*>(up) = make_uint2(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]));
-        }
+        if (p.U != nullptr) store_row_global(p.U + (item * 64 + t) * HEAD + v0g, u);
         // Vn_e = r_e * U -> operand image (i = t, j = n')
-        const uint32_t base = smem_u32(smem + C::OFF_VN) + (t >> 3) * 128 + (t & 7) * 16;
+        const uint32_t base = smem_u32(vn_img) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float re = g_r[t * ES + e];
-          const int n0 = wg * TPC + e * CW;
-          const uint32_t dst = base + (n0 >> 3) * 1024 + (n0 & 7) * 2;
-          if constexpr (CW == 8)
-            st_shared_v4(dst, pack_bf16(re * u[0], re * u[1]), pack_bf16(re * u[2], re * u[3]),
-                         pack_bf16(re * u[4], re * u[5]), pack_bf16(re * u[6], re * u[7]));
-          else
-            st_shared_v2(dst, pack_bf16(re * u[0], re * u[1]), pack_bf16(re * u[2], re * u[3]));
-        }
-      } else if (t < rows) {
-        __nv_bfloat16* op = p.o + ((tok + t) * p.H + h) * HEAD + vb * VC + wg * CW;
-        if constexpr (CW == 8)
-          *reinterpret_cast<uint4*>(op) = make_uint4(pack_bf16(acc[0] + u[0], acc[1] + u[1]), pack_bf16(acc[2] + u[2], acc[3] + u[3]),
-                                                     pack_bf16(acc[4] + u[4], acc[5] + u[5]), pack_bf16(acc[6] + u[6], acc[7] + u[7]));
-        else
-          *reinterpret_cast<uint2*>(op) = make_uint2(pack_bf16(acc[0] + u[0], acc[1] + u[1]), pack_bf16(acc[2] + u[2], acc[3] + u[3]));
-      }
-      if (!krow && i + 1 < count) {                    // next chunk's tables
-        if constexpr (!HOLD_RAW) raw_next = load_gates(i + 1);
-        const GateVal v = gate_values(raw_next);
-        store_gates_early(v);
+        for (int e = 0; e < E; ++e) store_row_image(base, e * CW, 1024, u, gr[e]);
+      } else if (live) {
+        float ov[CW];
 #pragma unroll
-        for (int it = 0; it < GQ; ++it) r_next[it] = v.r[it];
-        d_next = v.d[0];
-        if (i + 2 < count) {
-          if constexpr (HOLD_RAW) raw_next = load_gates(i + 2); else prefetch_gates(i + 2);
-        }
+        for (int c = 0; c < CW; ++c) ov[c] = acc[c] + u[c];
+        store_row_global(p.o + ((tok + t) * p.H + h) * HEAD + v0g, ov);
       }
     }
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    chain_sync(chain);
 
     // ---- (3) dS = K^T Vn, S <- d S + dS -----------------------------------------------------------------------
-    if (warp_u == 0 && elect_one()) {
+    if (cwarp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
-      const uint64_t db = make_desc(smem_u32(smem + C::OFF_VN), 128, 1024, LAYOUT_PLAIN);
-      constexpr uint32_t idesc = make_idesc(128, NCOLS, 1, 1);
+      const uint64_t db = make_desc(smem_u32(vn_img), 128, 1024, LAYOUT_PLAIN);
+      constexpr uint32_t idesc = make_idesc(128, TPC, 1, 1);
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
-        umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
-      umma_commit(&ctrl.bar_mma);
+        umma_bf16(tmem_c, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
+      umma_commit(&ctrl.bar_mma[chain]);
     }
-    __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    __syncwarp();
+    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    chain_sync(chain);
     ++mma_phase;
     tc_fence_after();
-    if (STAGES == 1 && warp_u == 1 && i + 1 < count && elect_one()) issue_loads(i + 1);   // the only stage is free once (3) has completed
-    if (!krow && i + 1 < count) store_gates_late(r_next, d_next, (i + 1) & 1);   // this chunk's r table is dead by now
+    // This chain is done with the stage's tiles.  The last chain to say so refills the stage with the chunk STAGES ahead.
+    if (cwarp_u == 1 && elect_one()) {
+      __threadfence_block();
+      const uint32_t done = atomicAdd(&ctrl.released[st], 1u) + 1u;
+      if (done % NCH == 0) {
+        if (i + STAGES < count) issue_loads(i + STAGES);
+        if (i + STAGES + 1 < count) prefetch_tiles(i + STAGES + 1);
+      }
+    }
+    __syncwarp();
     {
-      constexpr int PIECE = (TPC % 32 == 0) ? 32 : ((TPC % 16 == 0) ? 16 : TPC);
-      const uint32_t base = smem_u32(smem + C::OFF_S) + (row >> 3) * 128 + (row & 7) * 16;
-      uint8_t* hbase = (p.h != nullptr && i + 1 < count)
-                           ? reinterpret_cast<uint8_t*>(p.h) + (item + p.H) * (static_cast<int64_t>(E) * 32768) : nullptr;
-      const int v0 = vb * VC + wg * CW;
+      float dch[E];                                  // exp(gL) per slice, written by this chain during (1)
 #pragma unroll
-      for (int j0 = 0; j0 < TPC; j0 += PIECE) {
-        float ds[PIECE];
-        tmem_ld<PIECE>(tmem_row + wg * TPC + j0, ds);
+      for (int e = 0; e < E; ++e) dch[e] = dtab[e];
+      const uint32_t base = smem_u32(s_img) + (row >> 3) * 128 + (row & 7) * 16;
+      uint8_t* hbase = (p.h != nullptr && i + 1 < count) ? state_item_ptr(item + p.H) : nullptr;
+      float ds[2][16];
+      tmem_ld<16>(tmem_row, ds[0]);
+#pragma unroll
+      for (int pc = 0; pc < TPC / 16; ++pc) {
+        const int j0 = pc * 16;
         tmem_wait_ld();
-        uint32_t packed[PIECE / 2];
+        if (pc + 1 < TPC / 16) tmem_ld<16>(tmem_row + j0 + 16, ds[(pc + 1) & 1]);
+        const float* dp = ds[pc & 1];
+        uint32_t packed[8];
 #pragma unroll
-        for (int j = 0; j < PIECE; j += 2) {
-          S[j0 + j] = fmaf(g_d[(j0 + j) / CW], S[j0 + j], ds[j]);
-          S[j0 + j + 1] = fmaf(g_d[(j0 + j + 1) / CW], S[j0 + j + 1], ds[j + 1]);
+        for (int j = 0; j < 16; j += 2) {
+          S[j0 + j] = fmaf(dch[(j0 + j) / CW], S[j0 + j], dp[j]);
+          S[j0 + j + 1] = fmaf(dch[(j0 + j + 1) / CW], S[j0 + j + 1], dp[j + 1]);
           packed[j / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
         }
         // operand image (i = d, j = n') for the next chunk's (1)
-#pragma unroll
-        for (int j = 0; j < PIECE; j += 8) {
-          const int n0 = wg * TPC + j0 + j;
-          st_shared_v4(base + (n0 >> 3) * 2048, packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
-        }
+        st_shared_v4(base + (j0 >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(base + ((j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
         // saved state of the next chunk: slice e as [v/8][d][v%8]
-        if (hbase != nullptr) {
-#pragma unroll
-          for (int j = 0; j < PIECE; j += CW) {
-            const int e = (j0 + j) / CW;
-            uint8_t* dst = hbase + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
-            if constexpr (CW == 8)
-              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
-            else
-              *reinterpret_cast<uint2*>(dst) = make_uint2(packed[j / 2], packed[j / 2 + 1]);
-          }
-        }
+        if (hbase != nullptr) store_state_slices(hbase, j0, packed);
       }
     }
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    chain_sync(chain);
   }
+  // final state for the caller (f32, same form as the initial state)
+  if (p.s_out != nullptr) {
+    float* dst = p.s_out + ((static_cast<int64_t>(seq) * p.H + h) * E) * (HEAD * HEAD) + row * HEAD + v0g;
+#pragma unroll
+    for (int e = 0; e < E; ++e)
+#pragma unroll
+      for (int c = 0; c < CW; ++c) dst[e * (HEAD * HEAD) + c] = S[e * CW + c];
+  }
+  tc_fence_before();
+  __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -499,45 +490,69 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
 using namespace tgdn;
 
-template <int E, int VC, int NWG, int STAGES>
+template <int E, int CW, int NCH, int STAGES, int MINB>
 static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const FwdParams& p, cudaStream_t s) {
-  using C = FwdCfg<E, VC, NWG, STAGES>;
-  static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
+  using C = FwdCfg<E, CW, NCH, STAGES>;
+  static_assert(MINB == 1 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
-  cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-  if (e != cudaSuccess) return tgdn_cuda_error(e);
-  const int grid = p.n_seq * p.H * (HEAD / VC);
-  fwd_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  static_assert(MINB * C::TMEM_COLS <= 512, "tensor memory budget of one SM exceeded");
+  static bool configured[64] = {};                  // per device: the attribute is sticky, set it once
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, CW, NCH, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return tgdn_cuda_error(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int grid = p.n_seq * p.H * (HEAD / C::VC);
+  fwd_kernel<E, CW, NCH, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
-extern "C" int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
-                        const float* gc, const void* AP, float scale, const int32_t* doc_offsets,
-                        const int32_t* chunk_map, int n_docs, int B, int T, int H, int E, int NC, void* o, void* W,
-                        void* U, void* h, void* stream) {
+static int tgdn_fwd_variant = 0;
+// Picks an alternative launch configuration of the forward recurrence (0 = default); for configuration sweeps.
+extern "C" void tgdn_tune_fwd(int variant) { tgdn_fwd_variant = variant; }
+
+extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const float* k2, const float* q2,
+                              const float* beta, const float* gc, const void* AP, float scale, const int32_t* doc_offsets,
+                              const int32_t* chunk_map, int n_docs, int B, int T, int H, int E, int NC, void* o, void* W,
+                              void* U, void* h, const float* state_in, float* state_out, void* stream) {
   if (!q || !k || !v || !k2 || !q2 || !beta || !gc || !AP || !o) return TGDN_ERR_NULL;
   const bool packed = chunk_map != nullptr;
   if (packed && (!doc_offsets || n_docs < 1)) return TGDN_ERR_NULL;
   int rc = tgdn_check_core_shape(B, T, H, E, NC, packed);
   if (rc) return rc;
   if ((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(AP) |
-       reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(U) | reinterpret_cast<uintptr_t>(h)) & 15)
+       reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(U) | reinterpret_cast<uintptr_t>(h) |
+       reinterpret_cast<uintptr_t>(k2) | reinterpret_cast<uintptr_t>(q2) | reinterpret_cast<uintptr_t>(gc) |
+       reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) & 15)
     return TGDN_ERR_ALIGN;
   CUtensorMap mk, mq;
   if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
   FwdParams p{static_cast<const __nv_bfloat16*>(v), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<__nv_bfloat16*>(o), static_cast<__nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(U),
-              static_cast<__nv_bfloat16*>(h), doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale,
-              tgdn_status_word()};
+              static_cast<__nv_bfloat16*>(h), state_in, state_out, doc_offsets, chunk_map, B, T, H, NC,
+              packed ? n_docs : B, scale, tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 32, 4, 2>(mk, mq, p, s);
-    case 2: return launch_fwd<2, 32, 4, 2>(mk, mq, p, s);
-    case 4: return launch_fwd<4, 32, 4, 2>(mk, mq, p, s);
-    case 8: return launch_fwd<8, 16, 2, 1>(mk, mq, p, s);
-    case 12: return launch_fwd<12, 16, 4, 2>(mk, mq, p, s);
-    case 16: return launch_fwd<16, 16, 4, 2>(mk, mq, p, s);
+    case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, p, s);
+    case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, p, s);
+    case 4: return launch_fwd<4, 8, 4, 2, 1>(mk, mq, p, s);
+    case 8:
+      if (tgdn_fwd_variant == 1) return launch_fwd<8, 8, 2, 1, 2>(mk, mq, p, s);
+      if (tgdn_fwd_variant == 2) return launch_fwd<8, 8, 2, 2, 1>(mk, mq, p, s);
+      return launch_fwd<8, 8, 4, 2, 1>(mk, mq, p, s);
+    case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, p, s);
+    case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, p, s);
     default: return TGDN_ERR_SHAPE;
   }
+}
+
+extern "C" int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
+                        const float* gc, const void* AP, float scale, const int32_t* doc_offsets,
+                        const int32_t* chunk_map, int n_docs, int B, int T, int H, int E, int NC, void* o, void* W,
+                        void* U, void* h, void* stream) {
+  return tgdn_fwd_state(q, k, v, k2, q2, beta, gc, AP, scale, doc_offsets, chunk_map, n_docs, B, T, H, E, NC, o, W, U, h,
+                        nullptr, nullptr, stream);
 }

@@ -40,6 +40,8 @@ struct FwdParams {
   __nv_bfloat16* W;         // chunk layout; may be nullptr (inference: nothing saved)
   __nv_bfloat16* U;
   __nv_bfloat16* h;
+  const float* s_in;        // f32 [sequence][H][E][128 d][128 v] initial state, or nullptr (zero)
+  float* s_out;             // same form: the state after the last token, or nullptr
   const int32_t* offsets;   // packed: first chunk of every document (n_seq + 1 entries), else nullptr
   const int32_t* cmap;
   int B, T, H, NC, n_seq;   // n_seq = documents (packed) or batch rows (dense)

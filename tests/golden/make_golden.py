@@ -99,11 +99,36 @@ def conv_case(mod, name, B, T, C, act, docs, seed):
     print("wrote conv", name)
 
 
+# packed rows whose chunking the reference's pack_documents pins: (cu_seqlens, T)
+PACKING_CASES = [([0, 70, 133, 400, 640], 640), ([0, 64, 65, 320], 320), ([0, 512], 512),
+                 ([0, 17, 900, 901, 1500, 2999, 3000], 3000), ([0, 1], 1), ([0, 1, 2, 3, 4], 4),
+                 ([0, 63, 127, 128, 192, 1000], 1000)]
+
+
+def packing_cases(ref_pack):
+    """What the reference's pack_documents makes of each offsets vector: `restore` (token -> position in the padded
+    row) and `chunk_starts` (padded chunk begins a document).  Together they fix every chunk's first token and valid rows,
+    and every document's first chunk, which is what the device metadata must reproduce."""
+    out = {}
+    for i, (cu, T) in enumerate(PACKING_CASES):
+        x = torch.zeros(1, T, 1, 1)
+        _, chunk_starts, restore = ref_pack((x,), torch.tensor(cu, dtype=torch.int32))
+        out[f"cu_{i}"] = np.asarray(cu, dtype=np.int64)
+        out[f"restore_{i}"] = restore.numpy().astype(np.int64)
+        out[f"chunk_starts_{i}"] = chunk_starts.numpy().reshape(-1)
+    np.savez_compressed(os.path.join(HERE, "packing_cases.npz"), **out)
+    print("wrote packing_cases", len(PACKING_CASES))
+
+
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    sys.path.insert(0, ref_root)
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    sys.path.insert(0, sys.argv[1])
     from cute_triadic_gdn.ops import gdn_joint, joint_packing
     torch.manual_seed(0)
+    packing_cases(joint_packing.pack_documents)
+    if "--packing-only" in sys.argv:
+        return
     for case in CORE_CASES:
         core_case(gdn_joint._JointTorch, joint_packing.pack_documents, *case)
     try:
