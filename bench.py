@@ -223,9 +223,9 @@ def stage_times(leaves, do, E, reps=2):
         ev[1].record()
         o, h, W, U = gj._run_forward(q, k, v, k2, q2, beta, gc, AP, scale, True)
         ev[2].record()
-        dV, dU, ds, dr = gj._run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale)
+        dV, dU, ds, dkg, dr = gj._run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale)
         ev[3].record()
-        dkq, da, dc, dd = gj._run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale)
+        dkq, da, dc, dd = gj._run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale)
         ev[4].record()
         gj._run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale)
         ev[5].record()
@@ -233,7 +233,7 @@ def stage_times(leaves, do, E, reps=2):
         if rep > 0:
             for i, n in enumerate(names):
                 acc[n] += ev[i].elapsed_time(ev[i + 1])
-        del h, ds, dkq, W, U, dU, o
+        del h, ds, dkg, dkq, W, U, dU, o
     return {n: acc[n] / reps for n in names}
 
 

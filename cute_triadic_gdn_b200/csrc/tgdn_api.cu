@@ -62,6 +62,21 @@ int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H,
   return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
 }
 
+int tgdn_make_gate_map(CUtensorMap* map, const float* base, int B, int T, int H, int E) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return TGDN_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || E % 4) return TGDN_ERR_ALIGN;
+  const cuuint64_t row = static_cast<cuuint64_t>(E) * 4;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(E), static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {row, static_cast<cuuint64_t>(H) * row, static_cast<cuuint64_t>(T) * H * row};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(E), 1, 64, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : TGDN_ERR_DRIVER;
+}
+
 int tgdn_make_rows_map(CUtensorMap* map, const void* base, int C, int T, int B, int64_t stride_t, int64_t stride_b, int box_cols,
                        int box_rows) {
   EncodeTiledFn fn = encode_tiled();

@@ -1,24 +1,39 @@
 // Reverse chunk recurrence of the Triadic GDN backward.
 //
-// One CTA of 512 threads owns one (sequence, head, value block) and walks the chunks from last to first with
+// One CTA owns one (sequence, head, block of VC value columns) and walks the chunks from last to first with
 // G_e = dL/dS_e[:, value block] (f32) in registers.  Per chunk, with dO, U the chunk's rows of the value block:
 //   (a) KG = [K;Q] G                tcgen05 M=128, N=E*VC, K=128   (rows 0..63 are used)
 //       Y  = Pm^T dO                tcgen05 M=128 (64 used), N=VC, K=64
 //       dU = sum_e r_e*KG_e + Y ;   dr_e = sum_v U*KG_e  (per value block, summed later)
 //   (c) Z  = A^T dU                 tcgen05 M=128 (64 used), N=VC, K=64
 //       dW = beta*Z = dV ;  X = [-a_e*dW ; c_e*dO]
+//   (p) P  = G Xu^T                 tcgen05 M=128 (key rows d), N=64 (tokens), K=E*VC     Xu_e = r_e*U
+//       the value block's share of  sum_e (r_e*U) G_e^T, the part of dK that contracts the gradient state over the
+//       value axis; it leaves as a bf16 operand image (16 KB) and the state-gradient kernel adds the blocks up
 //   (d) dG = [K^T | Q^T] X          tcgen05 M=128, N=E*VC, K=128
-//       G_e <- d_e G_e + dG_e ; bf16 copy -> operand of the next (a) and saved ds
+//       G_e <- d_e G_e + dG_e ; bf16 copy -> operand of the next (a)
 //
-// Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:59-533 (rec_kernel).  Same thread/column organisation
-// as the forward recurrence (tgdn_fwd.cu); the operand X and the bf16 image of G share one buffer because they are never
-// live at the same time.
+// Because (p) runs here, where G lives, the gradient state itself never has to travel: the reference writes it to HBM at
+// every chunk (32 KB x E per chunk and head) and reads it back in its state-gradient kernel.  The one other consumer of
+// G_e outside this kernel is dd_e = <h_e, G_e>, the gradient of the chunk decay d_e = exp(gL_e), which enters the result
+// only as d_e*dd_e: slices whose chunk decay is below 2^-24 contribute less than one part in 10^7 of <h_e, G_e> and are
+// skipped there (dd_e = 0); G_e is stored (ds) only for the slices of chunks whose decay is above that threshold.
+//
+// (p) is off the dependent chain of the chunk: it is issued behind (c), completes while the epilogue of (c) reads Z,
+// and is read out of tensor memory while (d) runs.
+//
+// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows (requested under MMA
+// (a)); there are no shared gate tables.
+//
+// Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:59-533 (rec_kernel) and the (r*U) G^T product of
+// cute_triadic_gdn/kernels/sm100_joint_state_grads.py:373-378.  Same thread/column organisation as the forward
+// recurrence before it was split into chains: NWG warpgroups split the VC value columns and move in lockstep; the
+// operand X and the bf16 image of G share one buffer because they are never live at the same time.
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"
 
 namespace tgdn {
-
 
 __device__ __forceinline__ float rexp2(float x) {
   float y;
@@ -26,8 +41,34 @@ __device__ __forceinline__ float rexp2(float x) {
   return y;
 }
 
-// NWG warpgroups split the VC value columns; STAGES = 2 prefetches the next chunk's tiles (one CTA per SM), STAGES = 1 is
-// sized so that two CTAs share an SM and hide each other's dependent-MMA latency.
+template <int E>
+__device__ __forceinline__ void rec_ld_row(const float* p, float* out) {
+  if constexpr (E % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < E / 4; ++j) {
+      const float4 x = __ldg(reinterpret_cast<const float4*>(p) + j);
+      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+    }
+  } else if constexpr (E == 2) {
+    const float2 x = __ldg(reinterpret_cast<const float2*>(p));
+    out[0] = x.x; out[1] = x.y;
+  } else {
+#pragma unroll
+    for (int j = 0; j < E; ++j) out[j] = __ldg(p + j);
+  }
+}
+
+template <int E>
+__device__ __forceinline__ void rec_lds_row(const float* p, float* out) {   // the same from shared memory (E a multiple of 4)
+#pragma unroll
+  for (int j = 0; j < E / 4; ++j) {
+    const float4 x = *(reinterpret_cast<const float4*>(p) + j);
+    out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+  }
+}
+
+// STAGES = 2 prefetches the next chunk's tiles (one CTA per SM), STAGES = 1 is sized so that two CTAs share an SM and
+// hide each other's dependent-MMA latency.
 template <int E, int VC, int NWG, int STAGES>
 struct RecCfg {
   static constexpr int THREADS = NWG * 128;
@@ -35,40 +76,48 @@ struct RecCfg {
   static constexpr int CW = VC / NWG;
   static constexpr int TPC = E * CW;
   static constexpr int ES = E | 1;
-  static constexpr int TMEM_NEED = NCOLS + 2 * VC;
+  static constexpr int TMEM_NEED = NCOLS + 2 * VC + 64;       // KG/dG, Y, Z, P
   static constexpr int TMEM_COLS = TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int KQ_BYTES = 32768;
-  static constexpr int AP_BYTES = 16384;
+  static constexpr int A_BYTES = 8192;            // image (i = t, j = s), SI = 128, SJ = 1024: the A half of [A; Pm A]
   static constexpr int PM_BYTES = 8192;
   static constexpr int GX_BYTES = NCOLS * 256;    // image (i = row 0..127, j = n'), SI = 128, SJ = 2048
+  static constexpr int XU_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
   static constexpr int DO_BYTES = VC * 128;       // image (i = t, j = v), SI = 128, SJ = 1024
   static constexpr int OFF_KQ = 0;
   static constexpr int OFF_GX = OFF_KQ + STAGES * KQ_BYTES;
-  static constexpr int OFF_AP = OFF_GX + GX_BYTES;
-  static constexpr int OFF_PM = OFF_AP + STAGES * AP_BYTES;
-  // the 128-row descriptors over the 64-row Pm image read up to 8 KB past it: keep 8 KB of owned memory behind it
-  static constexpr int OFF_DO = OFF_PM + STAGES * PM_BYTES;
+  // the 128-row descriptors over the 64-row Pm and A images read up to 8 KB past them: Pm is followed by A, A by Xu
+  static constexpr int OFF_PM = OFF_GX + GX_BYTES;
+  static constexpr int OFF_A = OFF_PM + STAGES * PM_BYTES;
+  static constexpr int OFF_XU = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_DO = OFF_XU + (XU_BYTES < 8192 ? 8192 : XU_BYTES);
   static constexpr int OFF_DU = OFF_DO + ((DO_BYTES + 1023) & ~1023);
-  static constexpr int OFF_GATES = OFF_DU + ((DO_BYTES + 1023) & ~1023);
-  static constexpr int GATE_FLOATS = 3 * 64 * ES + 64 + 16;
-  static constexpr int OFF_DRP = OFF_GATES + 2 * GATE_FLOATS * 4;   // two table buffers: next chunk's are built ahead
+  static constexpr int OFF_DRP = OFF_DU + ((DO_BYTES + 1023) & ~1023);
   static constexpr int DRP_FLOATS = NWG * 64 * ES;
-  static constexpr int OFF_PAD = OFF_DRP + DRP_FLOATS * 4;
-  static constexpr int PAD = (OFF_PAD - OFF_DO) >= 8192 ? 0 : 8192 - (OFF_PAD - OFF_DO);
-  static constexpr int OFF_CTRL = OFF_PAD + PAD;
+  static constexpr int OFF_DT = OFF_DRP + DRP_FLOATS * 4;     // exp(gL) of this chunk and the store flags of the next: 2 x 16 words
+  // raw gate rows of the chunk, per stage: gc, k2, q2 as 64 dense rows of E floats each, loaded by TMA where E is a
+  // multiple of 4 and shared memory allows; otherwise every thread loads its own rows from global memory
+  static constexpr int GT_FULL = 64 * E * 4;
+  static constexpr int OFF_GT = (OFF_DT + 128 + 127) & ~127;
+  static constexpr int LIMIT = STAGES == 1 ? 115712 : 232448;
+  static constexpr bool TMA_GATES = E % 4 == 0 && OFF_GT + STAGES * 3 * GT_FULL + 64 + 1024 <= LIMIT;
+  static constexpr int GT_BYTES = TMA_GATES ? GT_FULL : 0;
+  static constexpr int OFF_CTRL = OFF_GT + STAGES * 3 * GT_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;
 };
 
 struct RecCtrl {
   uint64_t bar_load[2];
   uint64_t bar_mma;
+  uint64_t bar_p;
   uint32_t tmem_base;
   int abort;
 };
 
 template <int E, int VC, int NWG, int STAGES>
 __global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
-rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, RecParams p) {
+rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
+           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, RecParams p) {
   using C = RecCfg<E, VC, NWG, STAGES>;
   constexpr int REC_THREADS = C::THREADS;
   constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
@@ -76,8 +125,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* gate_buf = reinterpret_cast<float*>(smem + C::OFF_GATES);
   float* drp = reinterpret_cast<float*>(smem + C::OFF_DRP);
+  float* dtab = reinterpret_cast<float*>(smem + C::OFF_DT);           // [16] exp(gL_e)
+  int* ftab = reinterpret_cast<int*>(smem + C::OFF_DT) + 16;          // [16] store G_e of the next chunk?
   RecCtrl& ctrl = *reinterpret_cast<RecCtrl*>(smem + C::OFF_CTRL);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -101,6 +151,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_init(&ctrl.bar_load[0], 1);
     mbar_init(&ctrl.bar_load[1], 1);
     mbar_init(&ctrl.bar_mma, 1);
+    mbar_init(&ctrl.bar_p, 1);
     mbar_fence_init();
     ctrl.abort = 0;
   }
@@ -116,6 +167,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   const uint32_t tmem = __shfl_sync(0xffffffffu, ctrl.tmem_base, 0);
   const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  constexpr uint32_t TM_Y = NCOLS, TM_Z = NCOLS + VC, TM_P = NCOLS + 2 * VC;
   WaitCtl ctl{&ctrl.abort, p.status};
 
   auto chunk_info = [&](int i, int& t0, int& rows) {
@@ -126,99 +178,28 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       t0 = 0; rows = 0;
     }
   };
-  auto issue_loads = [&](int i, int st) {           // thread 0: K/Q tiles, [A;PmA] image and Pm image of local chunk i
+  auto issue_loads = [&](int i, int st) {           // one thread: K/Q tiles, the A half of [A;PmA] and the Pm image of local chunk i
     int t0, rows;
     chunk_info(i, t0, rows);
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + C::PM_BYTES);
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES);
+    if constexpr (C::TMA_GATES) {
+      uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
+      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
+      tma_load_4d(gt + C::GT_BYTES, &map_k2, &ctrl.bar_load[st], 0, h, t0, b);
+      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, &ctrl.bar_load[st], 0, h, t0, b);
+    }
     tma_load_4d(kq, &map_k, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
     tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
-    bulk_load(smem + C::OFF_AP + st * C::AP_BYTES, p.AP + item * (128 * 64), C::AP_BYTES, &ctrl.bar_load[st]);
+    // [A; Pm A] is an image of 128 rows: per 8-column block (2 KB) the first 1 KB holds the rows of A
+    const __nv_bfloat16* ap = p.AP + item * (128 * 64);
+#pragma unroll
+    for (int jb = 0; jb < 8; ++jb)
+      bulk_load(smem + C::OFF_A + st * C::A_BYTES + jb * 1024, ap + jb * 1024, 1024, &ctrl.bar_load[st]);
     bulk_load(smem + C::OFF_PM + st * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, &ctrl.bar_load[st]);
-  };
-  auto store_state = [&](int64_t item, const uint32_t* packed) {
-    uint8_t* base = reinterpret_cast<uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      const int v0 = vb * VC + wg * CW;
-      uint8_t* dst = base + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
-      if constexpr (CW == 8) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[e * 4], packed[e * 4 + 1], packed[e * 4 + 2], packed[e * 4 + 3]);
-      } else {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[e * 2], packed[e * 2 + 1]);
-      }
-    }
-  };
-  // Prefetched inputs of a chunk, one chunk ahead.  Every thread: its row piece (K-row threads: U, Q-row threads: dO) as
-  // raw bf16.  Q-row threads only: the raw gate inputs of their table entries; they turn them into the next chunk's gate
-  // tables while the K-row threads run the epilogue of (a), in which Q rows have nothing else to do.  Loads are
-  // unconditional from clamped addresses and masked at use.
-  constexpr int QTHREADS = REC_THREADS / 2;
-  constexpr int GQ = (64 * E + QTHREADS - 1) / QTHREADS;     // table entries per Q-row thread
-  const int qid = wg * 64 + t;                               // Q-row threads: 0 .. QTHREADS-1
-  struct GateRaw { float gcv[GQ], gl[GQ], k2v[GQ], q2v[GQ], beta; int rows; };
-  auto load_row = [&](int i) {
-    int t0, rows;
-    chunk_info(i, t0, rows);
-    const int last = max(rows, 1) - 1;
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    const __nv_bfloat16* rp = krow ? p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW
-                                   : p.dO + ((tok + min(t, last)) * p.H + h) * HEAD + vb * VC + wg * CW;
-    if constexpr (CW == 8) {
-      return __ldg(reinterpret_cast<const uint4*>(rp));
-    } else {
-      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
-      return make_uint4(w.x, w.y, 0u, 0u);
-    }
-  };
-  auto load_gates = [&](int i) {                             // Q-row threads
-    GateRaw g;
-    int t0, rows;
-    chunk_info(i, t0, rows);
-    g.rows = rows;
-    const int last = max(rows, 1) - 1;
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    const float* gcp = p.gc + item * (64 * E);
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = min(qid + it * QTHREADS, 64 * E - 1);
-      const int r = idx / E, e = idx % E;
-      const int64_t off = ((tok + min(r, last)) * p.H + h) * E + e;
-      g.gcv[it] = __ldg(gcp + idx);
-      g.gl[it] = __ldg(gcp + 63 * E + e);
-      g.k2v[it] = __ldg(p.k2 + off);
-      g.q2v[it] = __ldg(p.q2 + off);
-    }
-    g.beta = __ldg(p.beta + (tok + min(qid & 63, last)) * p.H + h);
-    return g;
-  };
-  auto write_gates = [&](const GateRaw& g, int buf) {        // Q-row threads
-    float* ga = gate_buf + buf * C::GATE_FLOATS;
-    float* gr = ga + 64 * ES;
-    float* gc_ = gr + 64 * ES;
-    float* gb = gc_ + 64 * ES;
-    float* gd = gb + 64;
-#pragma unroll
-    for (int it = 0; it < GQ; ++it) {
-      const int idx = qid + it * QTHREADS;
-      if (idx < 64 * E) {
-        const int r = idx / E, e = idx % E;
-        const bool ok = r < g.rows;
-        const float k2v = ok ? g.k2v[it] : 0.f, q2v = ok ? g.q2v[it] : 0.f;
-        const float gcv = g.gcv[it] * LOG2E, gl = g.gl[it] * LOG2E;
-        const float eg = rexp2(gcv);
-        ga[r * ES + e] = k2v * eg;
-        gr[r * ES + e] = k2v * rexp2(gl - gcv);
-        gc_[r * ES + e] = p.scale * q2v * eg;
-        if (r == 0) gd[e] = rexp2(gl);
-      }
-    }
-    if (qid < 64) gb[qid] = (qid < g.rows) ? g.beta : 0.f;
   };
   auto prefetch_loads = [&](int i) {                         // one lane: next chunk's tiles into L2 (single-stage configuration)
     int t0, rows;
@@ -228,26 +209,49 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_prefetch_4d(&map_q, 0, h, t0, b);
     tma_prefetch_4d(&map_k, 64, h, t0, b);
     tma_prefetch_4d(&map_q, 64, h, t0, b);
-    bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
+    bulk_prefetch(p.AP + item * (128 * 64), 16384);
     bulk_prefetch(p.Pm + item * (64 * 64), C::PM_BYTES);
   };
-  auto prefetch_gates = [&](int i) {                         // Q-row threads: one request per distinct 128-byte line
+  auto prefetch_rows = [&](int i) {                          // the first warpgroup: what threads load themselves, for a later chunk -> L2
+    if (wg != 0) return;
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    if (qid < 64) {
-      const int64_t ro = (tok + min(qid, last)) * p.H + h;
-      prefetch_l2(p.k2 + ro * E);
-      prefetch_l2(p.q2 + ro * E);
+    const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
+    if (krow) {
+      if (!C::TMA_GATES) prefetch_l2(p.k2 + ro * E);
       prefetch_l2(p.beta + ro);
+    } else if (!C::TMA_GATES) {
+      prefetch_l2(p.q2 + ro * E);
+      prefetch_l2(p.gc + item * (64 * E) + t * E);
     }
-    if (qid * 32 < 64 * E) prefetch_l2(p.gc + item * (64 * E) + qid * 32);
   };
-  // Where registers allow (small E) the raw gate inputs are held in registers one chunk ahead; otherwise they are only
-  // pulled into L2 a chunk ahead and loaded where they are used, by threads that have slack there.
-  constexpr bool HOLD_RAW = E <= 4;
+  // This thread's row pieces of a chunk, one chunk ahead, as raw bf16: U (K-row threads use it for dr, Q-row threads turn
+  // it into the operand Xu) and, for Q-row threads, dO.  Unconditional from clamped addresses and masked at use.
+  auto load_piece = [&](const __nv_bfloat16* rp) {
+    if constexpr (CW == 8) {
+      return __ldg(reinterpret_cast<const uint4*>(rp));
+    } else {
+      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
+      return make_uint4(w.x, w.y, 0u, 0u);
+    }
+  };
+  auto load_u = [&](int i) {
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    return load_piece(p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW);
+  };
+  auto load_do = [&](int i) {
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    return load_piece(p.dO + ((tok + min(t, max(rows, 1) - 1)) * p.H + h) * HEAD + vb * VC + wg * CW);
+  };
+  auto unpack_piece = [&](const uint4& w, bool use, float* out) {
+    const uint32_t rw[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int c = 0; c < CW; ++c) out[c] = use ? ((c & 1) ? bf16_hi(rw[c >> 1]) : bf16_lo(rw[c >> 1])) : 0.f;
+  };
   auto store_row_global = [&](__nv_bfloat16* ptr, const float* src) {
     if constexpr (CW == 8)
       *reinterpret_cast<uint4*>(ptr) = make_uint4(pack_bf16(src[0], src[1]), pack_bf16(src[2], src[3]),
@@ -262,23 +266,51 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     else
       st_shared_v2(dst, pack_bf16(f * src[0], f * src[1]), pack_bf16(f * src[2], f * src[3]));
   };
+  // G_e of one chunk boundary, for the slices the state-gradient kernel will ask for: slice e as [v/8][d][v%8]
+  auto store_state = [&](int64_t item, const uint32_t* packed) {
+    uint8_t* base = reinterpret_cast<uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (!ftab[e]) continue;
+      const int v0 = vb * VC + wg * CW;
+      uint8_t* dst = base + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
+      if constexpr (CW == 8) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[e * 4], packed[e * 4 + 1], packed[e * 4 + 2], packed[e * 4 + 3]);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[e * 2], packed[e * 2 + 1]);
+      }
+    }
+  };
+  auto decay_flag = [&](int64_t item, int e) {      // does d_e*dd_e of this chunk matter?  (same expression in the state-gradient kernel)
+    return __ldg(p.gc + item * (64 * E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
+  };
 
   if (tid == 0) issue_loads(count - 1, 0);
-  uint4 row_cur = load_row(count - 1);
-  GateRaw raw_next;
-  if (!krow) {
-    raw_next = load_gates(count - 1);
-    write_gates(raw_next, 0);
-    if (count > 1) {
-      if constexpr (HOLD_RAW) raw_next = load_gates(count - 2); else prefetch_gates(count - 2);
-    }
-  }
+  uint4 u_next = load_u(count - 1), do_next = make_uint4(0, 0, 0, 0);
+  if (!krow) do_next = load_do(count - 1);
+  if (count > 1) prefetch_rows(count - 2);
   uint32_t mma_phase = 0;
   {
+    // the gradient state at the end of the last chunk is zero
+    if (tid < E) ftab[tid] = decay_flag((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, tid);
+    __syncthreads();
     uint32_t zeros[TPC / 2];
 #pragma unroll
     for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
     store_state((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, zeros);
+    // the dO operand image of the first chunk processed; later ones are written a chunk ahead, by the Q-row threads
+    // while the K-row threads run the epilogue of (a)
+    if (!krow) {
+      int t0, rows;
+      chunk_info(count - 1, t0, rows);
+      float dov[CW];
+      unpack_piece(do_next, t < rows, dov);
+      const int v0 = wg * CW;
+      store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, dov, 1.f);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
   }
 
   for (int kstep = 0; kstep < count; ++kstep) {
@@ -288,31 +320,18 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
+    const bool live = t < rows;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
-    uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
+    uint8_t* am = smem + C::OFF_A + st * C::A_BYTES;
     uint8_t* pm = smem + C::OFF_PM + st * C::PM_BYTES;
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
-    // this chunk's row piece was loaded while the previous one was processed (K-row threads: U, Q-row threads: dO, which
-    // also goes into the dO operand image); its gate tables were built during the previous chunk's (a) epilogue
-    float* g_a = gate_buf + (kstep & 1) * C::GATE_FLOATS;
-    float* g_r = g_a + 64 * ES;
-    float* g_c = g_r + 64 * ES;
-    float* g_beta = g_c + 64 * ES;
-    float* g_d = g_beta + 64;
-    float rowv[CW];
-    {
-      const uint32_t rw[4] = {row_cur.x, row_cur.y, row_cur.z, row_cur.w};
-      const bool live = krow || t < rows;
-#pragma unroll
-      for (int c = 0; c < CW; ++c) rowv[c] = live ? ((c & 1) ? bf16_hi(rw[c >> 1]) : bf16_lo(rw[c >> 1])) : 0.f;
+    // this chunk's row pieces were loaded while the previous one was processed; its dO operand image was written then too
+    const uint4 u_cur = u_next, do_cur = do_next;    // U row piece (all threads), dO row piece (Q-row threads): unpacked where used
+    if (kstep + 1 < count) {                         // consumed during this chunk (dO image) and at the top of the next one
+      u_next = load_u(i - 1);
+      if (!krow) do_next = load_do(i - 1);
     }
-    if (!krow)
-      store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, rowv, 1.f);
-    if (kstep + 1 < count) row_cur = load_row(i - 1);        // consumed at the top of the next iteration
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
@@ -332,7 +351,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_bf16(tmem + NCOLS, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
+          umma_bf16(tmem + TM_Y, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
       }
       umma_commit(&ctrl.bar_mma);
     }
@@ -340,57 +359,140 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     if (warp_u == 1 && kstep + 1 < count && elect_one()) {
       if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
     }
+    __syncwarp();
+    // Under the MMA: this row's gate factors from its raw rows (in L2 since the previous chunk).  The Q-row threads, which
+    // have nothing to do in the epilogue of (a), also form r of their token row and build the operand Xu of (p) from it.
+    float ga[E];                                     // K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
+    float gr[E];                                     // K rows: r_e = k2 exp(gL - gc)
+    float bt = 0.f;
+    {
+      const int tl = min(t, max(rows, 1) - 1);
+      const float* gcp = p.gc + item * (64 * E);
+      const int64_t ro = (tok + tl) * p.H + h;
+      float gcr[E], k2r[E], gl[E];
+      const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
+      if constexpr (C::TMA_GATES) {
+        rec_lds_row<E>(gt + t * E, gcr);
+        rec_lds_row<E>(gt + 64 * E + t * E, k2r);
+        rec_lds_row<E>(gt + 63 * E, gl);
+      } else {
+        rec_ld_row<E>(gcp + t * E, gcr);
+        rec_ld_row<E>(p.k2 + ro * E, k2r);
+        rec_ld_row<E>(gcp + 63 * E, gl);
+      }
+      if (krow) {
+        bt = __ldg(p.beta + ro);
+        if (!live) bt = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float k2v = live ? k2r[e] : 0.f;
+          ga[e] = k2v * rexp2(gcr[e] * LOG2E);
+          gr[e] = k2v * rexp2((gl[e] - gcr[e]) * LOG2E);
+        }
+      } else {
+        // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
+        float uv[CW];
+        unpack_piece(u_cur, true, uv);
+        const uint32_t base = smem_u32(smem + C::OFF_XU) + (t >> 3) * 128 + (t & 7) * 16;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float re = live ? k2r[e] * rexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
+          const int n0 = wg * TPC + e * CW;
+          store_row_image(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, uv, re);
+          gr[e] = 0.f;
+        }
+        // only now the q2 row (a pinned load, which stays behind the stores above): these threads have the whole epilogue
+        // of (a) to wait for it, and the registers of the k2 row are free again
+        float q2r[E];
+        const float* q2p = p.q2 + ro * E;
+        if constexpr (C::TMA_GATES) {
+          rec_lds_row<E>(gt + 128 * E + t * E, q2r);
+        } else if constexpr (E % 4 == 0) {
+#pragma unroll
+          for (int j = 0; j < E / 4; ++j) {
+            const uint4 x = ldg_pinned_v4(q2p + 4 * j);
+            q2r[4 * j] = __uint_as_float(x.x); q2r[4 * j + 1] = __uint_as_float(x.y);
+            q2r[4 * j + 2] = __uint_as_float(x.z); q2r[4 * j + 3] = __uint_as_float(x.w);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < E; ++j) q2r[j] = ldg_pinned_f32(q2p + j);
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) ga[e] = live ? p.scale * q2r[e] * rexp2(gcr[e] * LOG2E) : 0.f;
+      }
+      if (tid < E) {
+        dtab[tid] = rexp2((C::TMA_GATES ? gt[63 * E + tid] : __ldg(gcp + 63 * E + tid)) * LOG2E);
+        if (i > 0) ftab[tid] = decay_flag(item - p.H, tid);          // read after the chunk's last barrier but one
+      }
+      if (kstep + 2 < count) prefetch_rows(i - 2);
+    }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     if (krow) {
-      float du[CW];
-      tmem_ld<CW>(tmem_row + NCOLS + v0, du);
-      tmem_wait_ld();
+      float du[CW], uv[CW];
+      unpack_piece(u_cur, true, uv);
+      constexpr int EP = (8 / CW) < 1 ? 1 : (8 / CW) < E ? (8 / CW) : E;     // slices per piece of eight columns
+      constexpr int NP = E / EP;
+      float kg[2][EP * CW];
+      tmem_ld<CW>(tmem_row + TM_Y + v0, du);
+      tmem_ld<EP * CW>(tmem_row + wg * TPC, kg[0]);
 #pragma unroll
-      for (int e0 = 0; e0 < E; e0 += (16 / CW)) {
-        constexpr int EP = (16 / CW) < E ? (16 / CW) : E;
-        float kg[EP * CW];
-        tmem_ld<EP * CW>(tmem_row + wg * TPC + e0 * CW, kg);
+      for (int pc = 0; pc < NP; ++pc) {                       // the next piece travels while this one is used
         tmem_wait_ld();
+        if (pc + 1 < NP) tmem_ld<EP * CW>(tmem_row + wg * TPC + (pc + 1) * EP * CW, kg[(pc + 1) & 1]);
+        const float* kp = kg[pc & 1];
 #pragma unroll
         for (int ee = 0; ee < EP; ++ee) {
-          const float re = g_r[t * ES + e0 + ee];
+          const float re = gr[pc * EP + ee];
           float dot = 0.f;
 #pragma unroll
           for (int c = 0; c < CW; ++c) {
-            du[c] = fmaf(re, kg[ee * CW + c], du[c]);
-            dot = fmaf(rowv[c], kg[ee * CW + c], dot);
+            du[c] = fmaf(re, kp[ee * CW + c], du[c]);
+            dot = fmaf(uv[c], kp[ee * CW + c], dot);
           }
-          drp[(wg * 64 + t) * ES + e0 + ee] = dot;
+          drp[(wg * 64 + t) * ES + pc * EP + ee] = dot;
         }
       }
       store_row_global(p.dU + (item * 64 + t) * HEAD + vb * VC + v0, du);
       store_row_image(smem_u32(smem + C::OFF_DU) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, du, 1.f);
     } else if (kstep + 1 < count) {
-      if constexpr (!HOLD_RAW) raw_next = load_gates(i - 1);
-      write_gates(raw_next, (kstep + 1) & 1);                // tables of the chunk processed next
-      if (kstep + 2 < count) {
-        if constexpr (HOLD_RAW) raw_next = load_gates(i - 2); else prefetch_gates(i - 2);
-      }
+      // Y has been read out of the dO operand image (its MMA is complete): the next chunk's image can replace it
+      int t0n, rowsn;
+      chunk_info(i - 1, t0n, rowsn);
+      float don[CW];
+      unpack_piece(do_next, t < rowsn, don);
+      store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, don, 1.f);
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
 
-    // ---- (c) Z = A^T dU -----------------------------------------------------------------------------------------
+    // ---- (c) Z = A^T dU, then (p) P = G Xu^T behind it ----------------------------------------------------------
     if (warp_u == 0 && elect_one()) {
       tc_fence_after();
-      const uint64_t da = make_desc(smem_u32(ap), 128, 2048, LAYOUT_PLAIN);         // A^T: MN-major over (i = t, j = s)
-      const uint64_t db = make_desc(smem_u32(smem + C::OFF_DU), 128, 1024, LAYOUT_PLAIN);
-      constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
+      {
+        const uint64_t da = make_desc(smem_u32(am), 128, 1024, LAYOUT_PLAIN);         // A^T: MN-major over (i = t, j = s)
+        const uint64_t db = make_desc(smem_u32(smem + C::OFF_DU), 128, 1024, LAYOUT_PLAIN);
+        constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk)
-        umma_bf16(tmem + NCOLS + VC, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
-      umma_commit(&ctrl.bar_mma);
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tmem + TM_Z, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
+        umma_commit(&ctrl.bar_mma);
+      }
+      {
+        const uint64_t da = make_desc(smem_u32(smem + C::OFF_GX), 2048, 128, LAYOUT_PLAIN);   // G: K-major over (i = d, j = n')
+        const uint64_t db = make_desc(smem_u32(smem + C::OFF_XU), 1024, 128, LAYOUT_PLAIN);   // Xu: K-major over (i = t, j = n')
+        constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < NCOLS / 16; ++kk)
+          umma_bf16(tmem + TM_P, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
+        umma_commit(&ctrl.bar_p);
+      }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    // meanwhile: the value-block partial of dr, summed over the four warpgroups in a fixed order
+    // meanwhile: the value-block partial of dr, summed over the warpgroups in a fixed order
     for (int idx = tid; idx < 64 * E; idx += REC_THREADS) {
       const int r = idx / E, e = idx % E;
       float s4 = 0.f;
@@ -405,22 +507,21 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       float xr[CW];                                  // K rows: dW; Q rows: dO
       if (krow) {
         float z[CW];
-        tmem_ld<CW>(tmem_row + NCOLS + VC + v0, z);
+        tmem_ld<CW>(tmem_row + TM_Z + v0, z);
         tmem_wait_ld();
-        const float bt = g_beta[t];
 #pragma unroll
         for (int c = 0; c < CW; ++c) xr[c] = bt * z[c];
-        if (t < rows) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
+        if (live) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
       } else {
-#pragma unroll
-        for (int c = 0; c < CW; ++c) xr[c] = rowv[c];
+        unpack_piece(do_cur, live, xr);
       }
+      // (p) reads the image of G that X is about to replace
+      mbar_wait_spin(&ctrl.bar_p, kstep & 1, ctl, DEV_TIMEOUT_MMA);
       // X image (i = row, j = n'): rows 0..63 -a_e*dW, rows 64..127 c_e*dO
-      const float* tab = krow ? g_a : g_c;
       const uint32_t base = smem_u32(smem + C::OFF_GX) + (row >> 3) * 128 + (row & 7) * 16;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float f = krow ? -tab[t * ES + e] : tab[t * ES + e];
+        const float f = krow ? -ga[e] : ga[e];
         const int n0 = wg * TPC + e * CW;
         store_row_image(base + (n0 >> 3) * 2048 + (n0 & 7) * 2, xr, f);
       }
@@ -441,33 +542,68 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma);
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
+    // meanwhile: P (128 key rows x 64 tokens, f32) -> bf16 operand image (i = d, j = t), SI = 128, SJ = 2048, of this
+    // value block: a warp's 16-byte stores cover 512 contiguous bytes
+    {
+      tc_fence_after();
+      constexpr int PW = 64 / NWG;                   // token columns per warpgroup
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.dkg) + (item * NV + vb) * 16384 + row * 16;
+#pragma unroll
+      for (int c0 = 0; c0 < PW; c0 += 16) {
+        float pv[16];
+        tmem_ld<16>(tmem_row + TM_P + wg * PW + c0, pv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; j += 8)
+          *reinterpret_cast<uint4*>(dst + ((wg * PW + c0 + j) >> 3) * 2048) =
+              make_uint4(pack_bf16(pv[j], pv[j + 1]), pack_bf16(pv[j + 2], pv[j + 3]), pack_bf16(pv[j + 4], pv[j + 5]),
+                         pack_bf16(pv[j + 6], pv[j + 7]));
+      }
+    }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
     if (STAGES == 1 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
+    __syncwarp();
     {
-      uint32_t packed[TPC / 2];
-#pragma unroll
-      for (int j0 = 0; j0 < TPC; j0 += 16) {
-        constexpr int PIECE = TPC < 16 ? TPC : 16;
-        float dg[PIECE];
-        tmem_ld<PIECE>(tmem_row + wg * TPC + j0, dg);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < PIECE; ++j) {
-          const float de = g_d[(j0 + j) / CW];
-          G[j0 + j] = fmaf(de, G[j0 + j], dg[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < PIECE; j += 2) packed[(j0 + j) / 2] = pack_bf16(G[j0 + j], G[j0 + j + 1]);
-      }
+      constexpr int PIECE = TPC < 16 ? TPC : 16;
       const uint32_t base = smem_u32(smem + C::OFF_GX) + (row >> 3) * 128 + (row & 7) * 16;
+      uint8_t* sbase = i > 0 ? reinterpret_cast<uint8_t*>(p.ds) + (item - p.H) * (static_cast<int64_t>(E) * 32768) : nullptr;
+      const int vg = vb * VC + wg * CW;
+      float dg[2][PIECE];
+      tmem_ld<PIECE>(tmem_row + wg * TPC, dg[0]);
 #pragma unroll
-      for (int j0 = 0; j0 < TPC; j0 += 8) {
-        const int n0 = wg * TPC + j0;
-        st_shared_v4(base + (n0 >> 3) * 2048, packed[j0 / 2], packed[j0 / 2 + 1], packed[j0 / 2 + 2], packed[j0 / 2 + 3]);
+      for (int j0 = 0; j0 < TPC; j0 += PIECE) {               // the next piece travels while this one is used
+        tmem_wait_ld();
+        if (j0 + PIECE < TPC) tmem_ld<PIECE>(tmem_row + wg * TPC + j0 + PIECE, dg[((j0 / PIECE) + 1) & 1]);
+        const float* dp = dg[(j0 / PIECE) & 1];
+        uint32_t packed[PIECE / 2];
+#pragma unroll
+        for (int j = 0; j < PIECE; j += 2) {
+          G[j0 + j] = fmaf(dtab[(j0 + j) / CW], G[j0 + j], dp[j]);
+          G[j0 + j + 1] = fmaf(dtab[(j0 + j + 1) / CW], G[j0 + j + 1], dp[j + 1]);
+          packed[j / 2] = pack_bf16(G[j0 + j], G[j0 + j + 1]);
+        }
+        // operand image (i = d, j = n') of the next (a)
+#pragma unroll
+        for (int j = 0; j < PIECE; j += 8) {
+          const int n0 = wg * TPC + j0 + j;
+          st_shared_v4(base + (n0 >> 3) * 2048, packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
+        }
+        // G_e at the end of the previous chunk, for the slices the state-gradient kernel will ask for: [v/8][d][v%8]
+        if (sbase != nullptr) {
+#pragma unroll
+          for (int j = 0; j < PIECE; j += CW) {
+            const int e = (j0 + j) / CW;
+            if (!ftab[e]) continue;
+            uint8_t* dst = sbase + e * 32768 + (vg >> 3) * 2048 + row * 16 + (vg & 7) * 2;
+            if constexpr (CW == 8)
+              *reinterpret_cast<uint4*>(dst) = make_uint4(packed[j / 2], packed[j / 2 + 1], packed[j / 2 + 2], packed[j / 2 + 3]);
+            else
+              *reinterpret_cast<uint2*>(dst) = make_uint2(packed[j / 2], packed[j / 2 + 1]);
+          }
+        }
       }
-      if (i > 0) store_state(item - p.H, packed);
     }
     fence_async_smem();
     tc_fence_before();
@@ -481,45 +617,62 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 using namespace tgdn;
 
 template <int E, int VC, int NWG, int STAGES>
-static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const RecParams& p, cudaStream_t s) {
+static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
+                      const RecParams& p, cudaStream_t s) {
   using C = RecCfg<E, VC, NWG, STAGES>;
   static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
-  cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  static_assert((STAGES == 1 ? 2 : 1) * C::TMEM_COLS <= 512, "tensor memory budget of one SM exceeded");
+  static_assert(64 % NWG == 0 && (64 / NWG) % 16 == 0, "the readout of P splits 64 token columns over the warpgroups in pieces of 16");
+  static bool configured[64] = {};                  // per device: the attribute is sticky, set it once
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return tgdn_cuda_error(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
 extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2,
                                   const float* beta, const float* gc, const void* AP, const void* Pm, const void* U,
                                   float scale, const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B,
-                                  int T, int H, int E, int NC, void* dV, void* dU, void* ds, float* dr, void* stream) {
-  if (!q || !k || !dO || !k2 || !q2 || !beta || !gc || !AP || !Pm || !U || !dV || !dU || !ds || !dr) return TGDN_ERR_NULL;
+                                  int T, int H, int E, int NC, void* dV, void* dU, void* ds, void* dkg, float* dr,
+                                  void* stream) {
+  if (!q || !k || !dO || !k2 || !q2 || !beta || !gc || !AP || !Pm || !U || !dV || !dU || !ds || !dkg || !dr) return TGDN_ERR_NULL;
   const bool packed = chunk_map != nullptr;
   if (packed && (!doc_offsets || n_docs < 1)) return TGDN_ERR_NULL;
   int rc = tgdn_check_core_shape(B, T, H, E, NC, packed);
   if (rc) return rc;
   if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(AP) | reinterpret_cast<uintptr_t>(Pm) |
        reinterpret_cast<uintptr_t>(U) | reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(dU) |
-       reinterpret_cast<uintptr_t>(ds)) & 15)
+       reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkg) | reinterpret_cast<uintptr_t>(k2) |
+       reinterpret_cast<uintptr_t>(q2) | reinterpret_cast<uintptr_t>(gc)) & 15)
     return TGDN_ERR_ALIGN;
   CUtensorMap mk, mq;
   if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
+  CUtensorMap mk2 = mk, mq2 = mq;                   // placeholders where the gate rows are not loaded by TMA
+  if (E % 4 == 0) {
+    if ((rc = tgdn_make_gate_map(&mk2, k2, B, T, H, E))) return rc;
+    if ((rc = tgdn_make_gate_map(&mq2, q2, B, T, H, E))) return rc;
+  }
   RecParams p{static_cast<const __nv_bfloat16*>(dO), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<const __nv_bfloat16*>(Pm), static_cast<const __nv_bfloat16*>(U),
-              static_cast<__nv_bfloat16*>(dV), static_cast<__nv_bfloat16*>(dU), static_cast<__nv_bfloat16*>(ds), dr,
-              doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale, tgdn_status_word()};
+              static_cast<__nv_bfloat16*>(dV), static_cast<__nv_bfloat16*>(dU), static_cast<__nv_bfloat16*>(ds),
+              static_cast<__nv_bfloat16*>(dkg), dr, doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale,
+              tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, p, s);
-    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, p, s);
-    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, p, s);
-    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, p, s);
-    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, p, s);
-    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, p, s);
+    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
+    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
+    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
+    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, mk2, mq2, p, s);
+    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, mk2, mq2, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

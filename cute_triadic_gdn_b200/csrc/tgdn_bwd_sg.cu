@@ -1,20 +1,21 @@
-// State gradients of the Triadic GDN backward: everything that contracts over the value axis with the saved states.
+// State gradients of the Triadic GDN backward: everything that contracts over the value axis with the saved forward states.
 //
 // One CTA per (batch, chunk, head): 256 worker threads, one warp that only issues the MMAs and one that only issues the bulk loads, so
-// that instruction issue to the tensor core never sits on the workers' path.  With h_e the forward state at the start of the chunk and G_e the
-// gradient state at its end (both 128x128 bf16, streamed from HBM in 16 KB half-slices by bulk copies):
-//   dK_state = sum_e (-a_e*dW) h_e^T + (r_e*U) G_e^T          (64 x 128)
-//   dQ_state = sum_e ( c_e*dO) h_e^T                          (64 x 128)
+// that instruction issue to the tensor core never sits on the workers' path.  With h_e the forward state at the start of the chunk
+// (128x128 bf16, streamed from HBM in 16 KB half-slices by bulk copies):
+//   dK_state = sum_e (-a_e*dW) h_e^T + sum_blocks P_block^T     (64 x 128)
+//   dQ_state = sum_e ( c_e*dO) h_e^T                            (64 x 128)
 //   da_e[t]  = -sum_v dW[t,v] (K h_e)[t,v]     dc_e[t] = sum_v dO[t,v] (Q h_e)[t,v]     dd_e = <h_e, G_e>
+// P_block = sum_e G_e (r_e*U)^T over one block of value columns is formed by the reverse recurrence, where G lives, and
+// arrives as 128/VC bf16 operand images of 16 KB; they are added up, transposed, by the tensor core itself: one product
+// [I;0] P_block^T per image accumulates into the dK tile in tensor memory (exact: every term is a bf16 value times one).
 // The tensor core forms, per slice, P_e = [dW ; dO] h_e^T (128 x 128, f32 in tensor memory, contraction over the value
 // axis in two half-slice steps) from the raw [dW ; dO] tile, which TMA loads once: the workers then take both the row
 // sums (da_e[t] = -<K[t], P_e[t]>, dc_e[t] = <Q[t], P_e[t]>: the same numbers as the sums over v above, with the
 // contractions exchanged) and the gate-weighted accumulation over the slices (f32, in registers) from one read of P_e.
-// Against forming R = [K;Q] h_e for the row sums and pre-scaling [dW ; dO] per slice, that halves these MMA instructions
-// (8 instead of 16 per step), takes 64 KB of operand reads and 16 KB of operand writes per step off the shared memory
-// and keeps the gates in f32.  Only (r_e*U) G_e^T still runs on operands scaled per slice.  dd_e is the trace of a
-// third product, h_e G_e^T (4 more MMAs per step), so that the workers never read the half-slices: the 32 KB per step
-// they used to read for it cost them more time than any other part of their step.
+// dd_e enters the result only as exp(gL_e)*dd_e; it is the trace of one more product, h_e G_e^T, formed only for the
+// slices whose chunk decay exp(gL_e) is at least 2^-24: only for those does the reverse recurrence store G_e, and only
+// those half-slices of G are loaded here (for the others dd_e = 0, an error below 2^-24 of <h_e, G_e>).
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_state_grads.py:53-449 (sg_kernel).
 #include <type_traits>
@@ -42,12 +43,13 @@ struct SgSmem {
   static constexpr int NSTAGE = 4;
   uint8_t xt[32768];            // [dW ; dO] tile, 128B swizzle: two column halves of 128 rows x 64 columns
   uint8_t hp[NSTAGE][16384];    // half-slices of h: image (i = d, j = v), SI = 128, SJ = 2048
-  uint8_t gp[NSTAGE][16384];    // half-slices of G
-  uint8_t va[2][8192];          // r_e*U, image (i = t, j = v), SI = 128, SJ = 1024   (read as 128 rows: more owned memory follows)
-  float ga[64 * ES], gr[64 * ES], gcq[64 * ES];
+  uint8_t gp[NSTAGE][16384];    // first the value-block images of sum_e G_e (r_e U)^T, then half-slices of G (slices with a trace only)
+  uint8_t ident[16384];         // [I;0], image (i = row 0..127, j = k 0..63), SI = 128, SJ = 2048
+  float ga[64 * ES], gcq[64 * ES];
   float part[2 * 128 * ES];     // row sums per half of the key axis
   float red[E * 4];             // per slice and 32-row block: partial trace of h_e G_e^T
-  uint64_t bar_kq, bar_load[NSTAGE], bar_mma[2], bar_built[2], bar_read[NSTAGE], bar_diag;
+  int flag[16];                 // per slice: is exp(gL_e) large enough for dd_e to matter?
+  uint64_t bar_kq, bar_load[NSTAGE], bar_g[NSTAGE], bar_pt[NSTAGE], bar_pfree[NSTAGE], bar_mma[2], bar_pread[2], bar_read[NSTAGE], bar_diag;
   uint32_t tmem_base;
   int abort;
 };
@@ -88,19 +90,34 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
   constexpr int STEPS = 2 * E;
   const uint8_t* hsrc = reinterpret_cast<const uint8_t*>(p.h) + item * (static_cast<int64_t>(E) * 32768);
   const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
-  auto issue_step = [&](int s) {                     // one lane of the issuing warp
+  const uint8_t* psrc = reinterpret_cast<const uint8_t*>(p.dkg) + item * (static_cast<int64_t>(p.NV) * 16384);
+  auto issue_h = [&](int s) {                        // one lane: half-slice s of h
     const int st = s % NS;
-    mbar_expect_tx(&sm.bar_load[st], 32768);
+    mbar_expect_tx(&sm.bar_load[st], 16384);
     bulk_load(sm.hp[st], hsrc + s * 16384, 16384, &sm.bar_load[st]);
-    bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_load[st]);
+  };
+  auto issue_g = [&](int s) {                        // one lane: half-slice s of G (slices with a trace only)
+    const int st = s % NS;
+    mbar_expect_tx(&sm.bar_g[st], 16384);
+    bulk_load(sm.gp[st], gsrc + s * 16384, 16384, &sm.bar_g[st]);
+  };
+  auto issue_block = [&](int u) {                    // one lane: value-block image u of the G part of dK
+    const int st = u % NS;
+    mbar_expect_tx(&sm.bar_pt[st], 16384);
+    bulk_load(sm.gp[st], psrc + u * 16384, 16384, &sm.bar_pt[st]);
   };
   if (issuer) {
     mbar_init(&sm.bar_kq, 1);
-    for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_load[i], 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&sm.bar_load[i], 1);
+      mbar_init(&sm.bar_g[i], 1);
+      mbar_init(&sm.bar_pt[i], 1);
+      mbar_init(&sm.bar_pfree[i], 1);
+    }
     mbar_init(&sm.bar_mma[0], 1);
     mbar_init(&sm.bar_mma[1], 1);
-    mbar_init(&sm.bar_built[0], SG_THREADS / 32);
-    mbar_init(&sm.bar_built[1], SG_THREADS / 32);
+    mbar_init(&sm.bar_pread[0], SG_THREADS / 32);
+    mbar_init(&sm.bar_pread[1], SG_THREADS / 32);
     for (int i = 0; i < NS; ++i) mbar_init(&sm.bar_read[i], SG_THREADS / 32);
     mbar_init(&sm.bar_diag, 4);
     mbar_fence_init();
@@ -110,7 +127,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
     tma_load_4d(sm.xt + 8192, &map_do, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.xt + 16384, &map_dv, &sm.bar_kq, 64, h, t0, b);
     tma_load_4d(sm.xt + 24576, &map_do, &sm.bar_kq, 64, h, t0, b);
-    issue_step(0);                                     // the rest of the ring follows once the workers' own loads are back
+    issue_h(0);                                        // the rest of the ring follows once the workers' own loads are back
+    issue_block(0);
   }
   if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
 
@@ -118,29 +136,20 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
   // used: the CTA then pays one memory round trip here instead of one per dependent group.
   const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
   const int tl = min(t, rows - 1);                   // clamped token row of this thread
-  // this thread's row data (packed bf16 pairs): its K row (Q row) over the key columns wg*64 .. +64, and on K rows U over the
-  // value columns vh*64 + wg*32 .. +32 for vh = 0, 1
-  uint32_t kw[32], uw[2][16];
+  // this thread's row data (packed bf16 pairs): its K row (Q row) over the key columns wg*64 .. +64
+  uint32_t kw[32];
   {
     const __nv_bfloat16* ksrc = (krow ? p.k : p.q) + ((tok + tl) * p.H + h) * HEAD + wg * 64;
-    const __nv_bfloat16* usrc = p.U + (item * 64 + t) * HEAD + wg * 32;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const uint4 x = __ldg(reinterpret_cast<const uint4*>(ksrc) + j);
       kw[4 * j] = x.x; kw[4 * j + 1] = x.y; kw[4 * j + 2] = x.z; kw[4 * j + 3] = x.w;
     }
-#pragma unroll
-    for (int vh = 0; vh < 2; ++vh) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint4 u = __ldg(reinterpret_cast<const uint4*>(usrc + vh * 64) + j);
-        uw[vh][4 * j] = u.x; uw[vh][4 * j + 1] = u.y; uw[vh][4 * j + 2] = u.z; uw[vh][4 * j + 3] = u.w;
-      }
-    }
   }
   // gate tables: raw inputs first, arithmetic after
   constexpr int GATE_ITERS = (64 * E + SG_THREADS - 1) / SG_THREADS;
-  float raw_gc[GATE_ITERS], raw_gl[GATE_ITERS], raw_k2[GATE_ITERS], raw_q2[GATE_ITERS];
+  float raw_gc[GATE_ITERS], raw_k2[GATE_ITERS], raw_q2[GATE_ITERS];
+  float raw_gl = 0.f;
   {
     const float* gcp = p.gc + item * (64 * E);
 #pragma unroll
@@ -149,79 +158,67 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
       const int r = idx / E, e = idx % E;
       const int64_t off = ((tok + min(r, rows - 1)) * p.H + h) * E + e;
       raw_gc[it] = __ldg(gcp + idx);
-      raw_gl[it] = __ldg(gcp + 63 * E + e);
       raw_k2[it] = __ldg(p.k2 + off);
       raw_q2[it] = __ldg(p.q2 + off);
     }
+    if (tid < E) raw_gl = __ldg(gcp + 63 * E + tid);
   }
+  // [I;0]: the operand that adds the value-block images, transposed, into the dK tile
+  if (worker) {
+    for (int i = tid; i < 16384 / 16; i += SG_THREADS) reinterpret_cast<uint4*>(sm.ident)[i] = make_uint4(0, 0, 0, 0);
+  }
+  __syncwarp();
 #pragma unroll
   for (int it = 0; it < GATE_ITERS; ++it) {
     const int idx = tid + it * SG_THREADS;
     if (idx < 64 * E && worker) {
       const int r = idx / E, e = idx % E;
       const bool ok = r < rows;
-      const float gcv = raw_gc[it] * LOG2E, gl = raw_gl[it] * LOG2E;
+      const float gcv = raw_gc[it] * LOG2E;
       const float k2v = ok ? raw_k2[it] : 0.f, q2v = ok ? raw_q2[it] : 0.f;
       const float eg = sexp2(gcv);
       sm.ga[r * ES + e] = k2v * eg;
-      sm.gr[r * ES + e] = k2v * sexp2(gl - gcv);
       sm.gcq[r * ES + e] = p.scale * q2v * eg;
     }
   }
+  if (tid < E) sm.flag[tid] = raw_gl * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
+  if (tid < E * 4) sm.red[tid] = 0.f;
   if (t >= rows) {                                   // token rows past the end of a ragged chunk contribute nothing
 #pragma unroll
     for (int j = 0; j < 32; ++j) kw[j] = 0u;
   }
-  if (!krow) {
-#pragma unroll
-    for (int vh = 0; vh < 2; ++vh)
-#pragma unroll
-      for (int j = 0; j < 16; ++j) uw[vh][j] = 0u;
-  }
+  __syncthreads();                                     // the zeroed operand before its diagonal
+  if (tid < 64) *reinterpret_cast<uint16_t*>(sm.ident + img_off(tid, tid, 128, 2048)) = 0x3F80;   // bf16 1.0
+  fence_async_smem();
   tc_fence_before();
-  __syncthreads();                                     // gate tables, barriers and the tensor-memory address are visible
+  __syncthreads();                                     // gate tables, flags, barriers, operand and the tensor-memory address are visible
   tc_fence_after();
   const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
-  // Pipeline over the 2E half-slice steps s = 2e + vh.  The MMA warp keeps the tensor core fed: the MMAs of step s go out
-  // as soon as their operands and half-slices are there.  Once the MMAs of step s are complete the K-row warps build r_e*U
-  // of step s+2 in the buffer that just became free, and after the second step of a slice four warps take the diagonal
-  // of the trace tile and every worker reads its part of the (double-buffered) P_e tile.  The workers never read the
-  // half-slices themselves: with <h_e, G_e> as the trace of a fifth product, shared memory is read by the tensor core only.
-  auto build = [&](int e, auto vh_tag) {                 // r_e*U of step (e, vh) into buffer vh (K-row threads)
-    constexpr int vh = decltype(vh_tag)::value;
-    if (!krow) return;
-    // gate factor rounded to bf16 once, then one packed multiply per pair of elements
-    const __nv_bfloat162 fu = __float2bfloat162_rn(sm.gr[t * ES + e]);
-    auto scaled = [](__nv_bfloat162 f, uint32_t x) {
-      const __nv_bfloat162 y = __hmul2(f, *reinterpret_cast<const __nv_bfloat162*>(&x));
-      return *reinterpret_cast<const uint32_t*>(&y);
-    };
-    const uint32_t vbase = smem_u32(sm.va[vh]) + (t >> 3) * 128 + (t & 7) * 16 + (wg * 4) * 1024;
+  // Pipeline.  First the value-block images: as each lands in a stage of the G ring the MMA warp adds it into the dK tile
+  // (tensor-memory columns 256..383) and hands the stage back.  Then the 2E half-slice steps s = 2e + vh: the MMAs of
+  // step s go out as soon as its half-slice of h (and of G, for a slice with a trace) is there; after the second step of a
+  // slice four warps take the diagonal of the trace tile and every worker reads its part of the (double-buffered) P_e
+  // tile.  The workers never read the half-slices themselves: shared memory is read by the tensor core only.
+  auto issue_block_mma = [&](int u) {                    // one lane of the issuing warp: dK += [I;0] P_u^T
+    const uint64_t did = make_desc(smem_u32(sm.ident), 2048, 128, LAYOUT_PLAIN);          // K = k
+    const uint64_t dpk = make_desc(smem_u32(sm.gp[u % NS]), 2048, 128, LAYOUT_PLAIN);     // (i = d, j = t): K = t
+    constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint32_t o[4];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) o[w] = scaled(fu, uw[vh][4 * j + w]);
-      st_shared_v4(vbase + j * 1024, o[0], o[1], o[2], o[3]);
-    }
+    for (int kk = 0; kk < 4; ++kk)
+      umma_bf16(tmem + 256, desc_advance(did, kk * 4096), desc_advance(dpk, kk * 4096), id_acc, (u > 0 || kk > 0) ? 1u : 0u);
+    umma_commit(&sm.bar_pfree[u % NS]);
   };
   auto issue_mma = [&](int s, int vh) {                  // one lane of the issuing warp
     const int st = s % NS;
-    tc_fence_after();
-    const uint64_t dva = make_desc(smem_u32(sm.va[vh]), 1024, 128, LAYOUT_PLAIN);
     const uint64_t dhk = make_desc(smem_u32(sm.hp[st]), 2048, 128, LAYOUT_PLAIN);   // K = v
-    const uint64_t dgk = make_desc(smem_u32(sm.gp[st]), 2048, 128, LAYOUT_PLAIN);
     const uint64_t dxt = make_desc(smem_u32(sm.xt), 16, 1024, LAYOUT_SW128);
     constexpr uint32_t id_acc = make_idesc(128, 128, 0, 0);
     const uint32_t tmem_p = tmem + ((s >> 1) & 1) * 128;       // P tile of this slice
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk)                            // P_e (+)= [dW ; dO][:, 64 value columns] h_e[:, those columns]^T
       umma_bf16(tmem_p, desc_advance(dxt, vh * 16384 + kk * 32), desc_advance(dhk, kk * 4096), id_acc, (vh > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk)
-      umma_bf16(tmem + 256, desc_advance(dva, kk * 2048), desc_advance(dgk, kk * 4096), id_acc, (s > 0 || kk > 0) ? 1u : 0u);
   };
   auto issue_trace = [&](int s, int vh) {                // h_e G_e^T over the step's value columns; its diagonal sums to <h_e, G_e>
     const int st = s % NS;
@@ -231,7 +228,6 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk)
       umma_bf16(tmem + 384, desc_advance(dhk, kk * 4096), desc_advance(dgk, kk * 4096), id_acc, (vh > 0 || kk > 0) ? 1u : 0u);
-    umma_commit(&sm.bar_mma[vh]);
   };
   float acc[64];                                         // this row's gate-weighted sum over the slices, key columns wg*64 .. +64
 #pragma unroll
@@ -272,42 +268,26 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
     for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
     if (lane == 0) sm.red[e * 4 + (warp & 3)] = d;
   };
-  using V0 = std::integral_constant<int, 0>;
-  using V1 = std::integral_constant<int, 1>;
 
-  // The issuing warp and the workers run decoupled, coupled only by mbarriers:
-  //   bar_built[vh]  workers -> issuer   r_e*U of a step is in buffer vh (and the P tile two slices back has been read)
-  //   bar_mma[vh]    tensor core -> all  MMAs of a step complete: buffer vh reusable; after vh = 1 the P tile is ready
-  //   bar_load[st]   TMA -> all          half-slices of a step landed in stage st
-  //   bar_read[st]   workers -> loads    MMAs of a step seen complete: stage st may be refilled
-  //   bar_diag       workers -> issuer   diagonal of the trace tile read: the next slice may overwrite it
+  // The issuing warp, the loading warp and the workers run decoupled, coupled only by mbarriers:
+  //   bar_pt[st]     TMA -> issuer       a value-block image landed in stage st of the G ring
+  //   bar_pfree[st]  tensor core -> loads  its product is complete: the stage may be refilled
+  //   bar_load[st]   TMA -> issuer       the half-slice of h of a step landed in stage st
+  //   bar_g[st]      TMA -> issuer       the half-slice of G of a step landed (slices with a trace only)
+  //   bar_mma[vh]    tensor core -> workers  MMAs of a step complete; after vh = 1 the P tile (and the trace tile) is ready
+  //   bar_read[st]   workers -> loads    MMAs of a step seen complete: stage st of both rings may be refilled
+  //   bar_pread[b]   workers -> issuer   P tile b has been read: the slice after next may overwrite it
+  //   bar_diag       workers -> issuer   diagonal of the trace tile read (or not needed): the next slice may overwrite it
+  const int NVB = p.NV;
   if (worker) {
-    build(0, V0{});
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&sm.bar_built[0]);
-    if (STEPS > 1) {
-      build(0, V1{});
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.bar_built[1]);
-    }
 #pragma unroll 1
     for (int e = 0; e < E; ++e) {
       // ---- step s = 2e (vh = 0) ----
       {
         const int s = 2 * e;
         mbar_wait(&sm.bar_mma[0], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
-        tc_fence_after();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);   // the tensor core, the only reader of the stage, is done with it
-        if (e + 1 < E) {
-          build(e + 1, V0{});
-          fence_async_smem();
-        }
-        tc_fence_before();                                   // orders the reads of P two slices back, which the next step 2e+2 overwrites
-        __syncwarp();
-        if (e + 1 < E && lane == 0) mbar_arrive(&sm.bar_built[0]);
       }
       // ---- step s = 2e + 1 (vh = 1) ----
       {
@@ -317,26 +297,36 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.bar_read[s % NS]);
         if (wg == 0) {                                       // the trace tile is single: read it first and hand it back
-          take_diag(e);
+          if (sm.flag[e]) take_diag(e);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm.bar_diag);
         }
-        if (e + 1 < E) {                                     // the next operands before P_e: the tensor core goes on meanwhile
-          build(e + 1, V1{});
-          fence_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.bar_built[1]);
-        }
         take_slice(e);
+        tc_fence_before();                                   // orders the reads of P_e before the MMAs that will overwrite it
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.bar_pread[e & 1]);
       }
     }
   } else if (warp_u == SG_THREADS / 32) {                // MMA issue
+#pragma unroll 1
+    for (int u = 0; u < NVB; ++u) {
+      mbar_wait(&sm.bar_pt[u % NS], (u / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
+      tc_fence_after();
+      if (elect_one()) issue_block_mma(u);
+      __syncwarp();
+    }
     mbar_wait(&sm.bar_kq, 0, ctl, DEV_TIMEOUT_LOAD);       // the P products read the [dW ; dO] tile
+    uint32_t g_uses[NS];                                   // completed loads per stage of the G ring (slices with a trace only)
+#pragma unroll
+    for (int i = 0; i < NS; ++i) g_uses[i] = 0;
 #pragma unroll 1
     for (int s = 0; s < STEPS; ++s) {
-      const int vh = s & 1;
-      mbar_wait(&sm.bar_built[vh], (s >> 1) & 1, ctl, DEV_TIMEOUT_MMA);
+      const int vh = s & 1, e = s >> 1;
+      const bool tr = sm.flag[e] != 0;
+      if (vh == 0 && e >= 2) {                             // P tile (e & 1) was last used by slice e - 2
+        mbar_wait(&sm.bar_pread[e & 1], ((e >> 1) - 1) & 1, ctl, DEV_TIMEOUT_MMA);
+      }
       mbar_wait(&sm.bar_load[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
       tc_fence_after();
       if (elect_one()) issue_mma(s, vh);
@@ -346,10 +336,18 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         mbar_wait(&sm.bar_diag, ((s >> 1) - 1) & 1, ctl, DEV_TIMEOUT_MMA);
         tc_fence_after();
       }
-      if (elect_one()) issue_trace(s, vh);
+      if (tr) {
+#pragma unroll
+        for (int i = 0; i < NS; ++i)
+          if (i == s % NS) { mbar_wait(&sm.bar_g[i], g_uses[i] & 1, ctl, DEV_TIMEOUT_LOAD); ++g_uses[i]; }
+        tc_fence_after();
+        if (elect_one()) issue_trace(s, vh);
+        __syncwarp();
+      }
+      if (elect_one()) umma_commit(&sm.bar_mma[vh]);
       __syncwarp();
     }
-  } else {                                               // bulk loads: step s+NS goes into the stage step s has released
+  } else {                                               // bulk loads
     // Late in this block's life, pull the inputs of the block that will follow it on some SM into L2: its prologue then
     // waits for L2 instead of for an HBM system that the streaming of all the other blocks keeps saturated.
     auto warm_successor = [&]() {
@@ -368,8 +366,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         const int64_t slice = static_cast<int64_t>(E) * 32768;
         const uint32_t lead = static_cast<uint32_t>(min(NS, STEPS)) * 16384u;
         bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + item2 * slice, lead);
-        bulk_prefetch(reinterpret_cast<const uint8_t*>(p.ds) + item2 * slice, lead);
-        bulk_prefetch(p.U + item2 * (64 * HEAD), 64 * HEAD * 2);
+        bulk_prefetch(reinterpret_cast<const uint8_t*>(p.dkg) + item2 * (static_cast<int64_t>(p.NV) * 16384),
+                      static_cast<uint32_t>(min(NS, p.NV)) * 16384u);
         bulk_prefetch(p.gc + item2 * (64 * E), 64 * E * 4);
       }
       const int64_t tok2 = static_cast<int64_t>(b2) * p.T + t2;
@@ -383,18 +381,38 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         prefetch_l2(p.q2 + ro * E);
       }
     };
-    // A worker warp releases a stage only after it has seen the MMAs of that step complete, so bar_read alone says that
-    // both readers of the stage are done; this warp never waits on bar_mma, whose phases it could fall behind.
-    // The first loads of a block compete with the workers' prologue loads, which gate the first MMA; only the tile and
-    // step 0 went out at the start, the rest of the ring is filled now that the prologue values have arrived.
+    // The first loads of a block compete with the workers' prologue loads, which gate the first MMA; only the tile,
+    // step 0 and the first value-block image went out at the start, the rest is sent now that the prologue values have arrived.
     if (elect_one()) {
-      for (int s = 1; s < NS && s < STEPS; ++s) issue_step(s);
+      for (int u = 1; u < NS && u < NVB; ++u) issue_block(u);
+      for (int s = 1; s < NS && s < STEPS; ++s) issue_h(s);
     }
     __syncwarp();
+    // value-block images beyond the first ring round: stage u % NS is free once the product of image u - NS is complete
+#pragma unroll 1
+    for (int u = NS; u < NVB; ++u) {
+      mbar_wait(&sm.bar_pfree[u % NS], ((u / NS) - 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (elect_one()) issue_block(u);
+      __syncwarp();
+    }
+    // half-slices of G for the first ring round of steps: their stage held a value-block image last
+#pragma unroll 1
+    for (int s = 0; s < NS && s < STEPS; ++s) {
+      if (!sm.flag[s >> 1]) continue;
+      const int uses = (NVB - 1 - s % NS) / NS + 1;        // images that went through stage s % NS (0 if none)
+      if (s % NS < NVB) mbar_wait(&sm.bar_pfree[s % NS], (uses - 1) & 1, ctl, DEV_TIMEOUT_LOAD);
+      if (elect_one()) issue_g(s);
+      __syncwarp();
+    }
+    // A worker warp releases a stage only after it has seen the MMAs of that step complete, so bar_read alone says that
+    // both readers of the stage are done; this warp never waits on bar_mma, whose phases it could fall behind.
 #pragma unroll 1
     for (int s = 0; s + NS < STEPS; ++s) {
       mbar_wait(&sm.bar_read[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
-      if (elect_one()) issue_step(s + NS);
+      if (elect_one()) {
+        issue_h(s + NS);
+        if (sm.flag[(s + NS) >> 1]) issue_g(s + NS);
+      }
       __syncwarp();
     }
     warm_successor();                                    // nothing left to wait for: only the last steps and the epilogue remain
@@ -453,24 +471,25 @@ static int launch_sg(const CUtensorMap& mdv, const CUtensorMap& mdo, const SgPar
   return tgdn_cuda_error(cudaGetLastError());
 }
 
-extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U,
-                                    const void* h, const void* ds, const float* k2, const float* q2, const float* gc,
-                                    float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dkq,
+extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV,
+                                    const void* h, const void* ds, const void* dkg, const float* k2, const float* q2,
+                                    const float* gc, float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dkq,
                                     float* da, float* dc, float* dd, void* stream) {
-  if (!q || !k || !dO || !dV || !U || !h || !ds || !k2 || !q2 || !gc || !dkq || !da || !dc || !dd) return TGDN_ERR_NULL;
+  if (!q || !k || !dO || !dV || !h || !ds || !dkg || !k2 || !q2 || !gc || !dkq || !da || !dc || !dd) return TGDN_ERR_NULL;
   int rc = tgdn_check_core_shape(B, T, H, E, NC, chunk_map != nullptr);
   if (rc) return rc;
-  if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dV) | reinterpret_cast<uintptr_t>(U) |
-       reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkq)) & 15)
+  if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dV) |
+       reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkg) |
+       reinterpret_cast<uintptr_t>(dkq)) & 15)
     return TGDN_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(q)) & 15) return TGDN_ERR_ALIGN;
   CUtensorMap mdv, mdo;
   if ((rc = tgdn_make_token_map(&mdv, dV, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mdo, dO, B, T, H, 64, 64, 1))) return rc;
   SgParams p{static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(dV),
-             static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(h),
-             static_cast<const __nv_bfloat16*>(ds), k2, q2, gc, static_cast<__nv_bfloat16*>(dkq), da, dc, dd, chunk_map, B, T, H,
-             NC, scale,
+             static_cast<const __nv_bfloat16*>(h),
+             static_cast<const __nv_bfloat16*>(ds), static_cast<const __nv_bfloat16*>(dkg), k2, q2, gc,
+             static_cast<__nv_bfloat16*>(dkq), da, dc, dd, chunk_map, B, T, H, NC, HEAD / tgdn_value_block(E), scale,
              tgdn_status_word(), tgdn_sm_count()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {

@@ -56,6 +56,15 @@ __device__ __forceinline__ void ld_row(const float* p, float* out) {
   }
 }
 
+template <int E>
+__device__ __forceinline__ void lds_row(const float* p, float* out) {   // the same from shared memory (E a multiple of 4)
+#pragma unroll
+  for (int j = 0; j < E / 4; ++j) {
+    const float4 x = *(reinterpret_cast<const float4*>(p) + j);
+    out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+  }
+}
+
 __device__ __forceinline__ void chain_sync(int chain) {     // the 128 threads of one chain
   asm volatile("bar.sync %0, 128;" ::"r"(chain + 1) : "memory");
 }
@@ -81,7 +90,11 @@ struct FwdCfg {
   static constexpr int OFF_VN = OFF_S + NCH * S_BYTES;
   static constexpr int OFF_BW = OFF_VN + NCH * VN_BYTES;
   static constexpr int OFF_DT = OFF_BW + NCH * BW_BYTES;      // per chain: exp(gL) of the current chunk, 16 floats
-  static constexpr int OFF_CTRL = OFF_DT + NCH * 64;
+  // raw gate rows of the chunk, per stage: gc, k2, q2 as 64 dense rows of E floats each (TMA; E a multiple of 4)
+  static constexpr bool TMA_GATES = E % 4 == 0;
+  static constexpr int GT_BYTES = TMA_GATES ? 64 * E * 4 : 0;
+  static constexpr int OFF_GT = (OFF_DT + NCH * 64 + 127) & ~127;
+  static constexpr int OFF_CTRL = OFF_GT + STAGES * 3 * GT_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 128 + 1024;    // + control block + alignment slack
   static_assert(CW == 4 || CW == 8 || CW == 16, "a chain owns 4, 8 or 16 value columns");
   static_assert(TPC % 16 == 0 && TPC <= 64, "columns per chain: a multiple of 16 (MMA N, tensor-memory loads), at most 64 registers of state");
@@ -97,7 +110,8 @@ struct FwdCtrl {
 
 template <int E, int CW, int NCH, int STAGES, int MINB>
 __global__ void __launch_bounds__(NCH * 128, MINB)
-fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, FwdParams p) {
+fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
+           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
   using C = FwdCfg<E, CW, NCH, STAGES>;
   constexpr int TPC = C::TPC, VC = C::VC;
   constexpr float LOG2E = 1.4426950408889634f;
@@ -210,7 +224,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int st = i % STAGES;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES);
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + 3 * C::GT_BYTES);
+    if constexpr (C::TMA_GATES) {
+      uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
+      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
+      tma_load_4d(gt + C::GT_BYTES, &map_k2, &ctrl.bar_load[st], 0, h, t0, b);
+      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, &ctrl.bar_load[st], 0, h, t0, b);
+    }
     tma_load_4d(kq, &map_k, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
@@ -227,17 +247,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_prefetch_4d(&map_q, 64, h, t0, b);
     bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
   };
-  auto prefetch_rows = [&](int i) {                 // this thread's gate rows and value row of a later chunk -> L2
+  auto prefetch_rows = [&](int i) {                 // what threads still load themselves, for a later chunk -> L2
+    if (C::TMA_GATES && chain != 0) return;           // the value columns of all chains of the CTA share their 128-byte lines
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
     if (krow) {
-      prefetch_l2(p.k2 + ro * E);
+      if (!C::TMA_GATES) prefetch_l2(p.k2 + ro * E);
       prefetch_l2(p.beta + ro);
       prefetch_l2(p.v + ro * HEAD + v0g);
-    } else {
+    } else if (!C::TMA_GATES) {
       prefetch_l2(p.q2 + ro * E);
       prefetch_l2(p.gc + item * (64 * E) + t * E);
     }
@@ -299,7 +320,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     // Only the chain's first warp polls an mbarrier; the other three sleep in the chain's hardware barrier until it has
     // seen the flip.  Twelve more spinning warps per SM would take their share of the issue slots from the warps of the
     // other chains that are in an epilogue at that moment.
-    if (cwarp_u == 0) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    if (cwarp_u == 0 || C::TMA_GATES) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (cwarp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -320,15 +341,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int tl = min(t, max(rows, 1) - 1);
       const float* gcp = p.gc + item * (64 * E);
       const int64_t ro = (tok + tl) * p.H + h;
-      float gcr[E], x2[E];
-      ld_row<E>(gcp + t * E, gcr);
-      ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
+      float gcr[E], x2[E], gl[E];
+      if constexpr (C::TMA_GATES) {
+        const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
+        lds_row<E>(gt + t * E, gcr);
+        lds_row<E>(gt + (krow ? 64 * E : 128 * E) + t * E, x2);
+        if (krow) lds_row<E>(gt + 63 * E, gl);
+      } else {
+        ld_row<E>(gcp + t * E, gcr);
+        ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
+        if (krow) ld_row<E>(gcp + 63 * E, gl);
+      }
       if (krow) {
-        float gl[E];
-        ld_row<E>(gcp + 63 * E, gl);
         bt = __ldg(p.beta + ro);
         load_vrow(t0, rows, vraw);
-        if (t < E) dtab[t] = fexp2(__ldg(gcp + 63 * E + t) * LOG2E);
+        if (t < E) {
+          float glt;
+          if constexpr (C::TMA_GATES) glt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES)[63 * E + t];
+          else glt = __ldg(gcp + 63 * E + t);
+          dtab[t] = fexp2(glt * LOG2E);
+        }
 #pragma unroll
         for (int e = 0; e < E; ++e) {
           const float k2v = live ? x2[e] : 0.f;
@@ -491,7 +523,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 using namespace tgdn;
 
 template <int E, int CW, int NCH, int STAGES, int MINB>
-static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const FwdParams& p, cudaStream_t s) {
+static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
+                      const FwdParams& p, cudaStream_t s) {
   using C = FwdCfg<E, CW, NCH, STAGES>;
   static_assert(MINB == 1 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
@@ -505,7 +538,7 @@ static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const FwdPar
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_seq * p.H * (HEAD / C::VC);
-  fwd_kernel<E, CW, NCH, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, p);
+  fwd_kernel<E, CW, NCH, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -530,21 +563,26 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
   CUtensorMap mk, mq;
   if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
+  CUtensorMap mk2 = mk, mq2 = mq;                   // placeholders where the gate rows are not loaded by TMA (E < 4)
+  if (E % 4 == 0) {
+    if ((rc = tgdn_make_gate_map(&mk2, k2, B, T, H, E))) return rc;
+    if ((rc = tgdn_make_gate_map(&mq2, q2, B, T, H, E))) return rc;
+  }
   FwdParams p{static_cast<const __nv_bfloat16*>(v), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<__nv_bfloat16*>(o), static_cast<__nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(U),
               static_cast<__nv_bfloat16*>(h), state_in, state_out, doc_offsets, chunk_map, B, T, H, NC,
               packed ? n_docs : B, scale, tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, p, s);
-    case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, p, s);
-    case 4: return launch_fwd<4, 8, 4, 2, 1>(mk, mq, p, s);
+    case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 4: return launch_fwd<4, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 8:
-      if (tgdn_fwd_variant == 1) return launch_fwd<8, 8, 2, 1, 2>(mk, mq, p, s);
-      if (tgdn_fwd_variant == 2) return launch_fwd<8, 8, 2, 2, 1>(mk, mq, p, s);
-      return launch_fwd<8, 8, 4, 2, 1>(mk, mq, p, s);
-    case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, p, s);
-    case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, p, s);
+      if (tgdn_fwd_variant == 1) return launch_fwd<8, 8, 2, 1, 2>(mk, mq, mk2, mq2, p, s);
+      if (tgdn_fwd_variant == 2) return launch_fwd<8, 8, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
+      return launch_fwd<8, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

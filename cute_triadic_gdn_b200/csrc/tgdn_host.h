@@ -17,6 +17,10 @@ int* tgdn_status_word();
 // swizzle128 = 1 asks for the 128-byte swizzle (box_cols must then be 64).
 int tgdn_make_token_map(CUtensorMap* map, const void* base, int B, int T, int H, int box_cols, int box_rows, int swizzle128);
 
+// Tensor map over a (B, T, H, E) f32 gate tensor (k2, q2) in token layout, E a multiple of 4: box = [E][1 head][64 tokens][1 row],
+// which lands in shared memory as 64 dense rows of E floats.
+int tgdn_make_gate_map(CUtensorMap* map, const float* base, int B, int T, int H, int E);
+
 // Tensor map over a (B, T, C) bf16 tensor with element strides (stride_b, stride_t, 1): box = [box_cols][box_rows][1], no swizzle.
 int tgdn_make_rows_map(CUtensorMap* map, const void* base, int C, int T, int B, int64_t stride_t, int64_t stride_b, int box_cols,
                        int box_rows);

@@ -15,6 +15,12 @@
 
 namespace tgdn {
 
+// dd_e = <h_e, G_e>, the gradient of the chunk decay d_e = exp(gL_e), enters the result only as d_e * dd_e.  Where
+// log2(d_e) is below this bound the product is under 2^-24 of <h_e, G_e> and is taken as zero: the reverse recurrence
+// then does not store G_e of that chunk and the state-gradient kernel does not read it.  Both kernels evaluate
+// gc[63][e] * log2(e) >= DD_MIN_LOG2_DECAY on the same f32 value.
+constexpr float DD_MIN_LOG2_DECAY = -24.f;
+
 struct MaskParams {
   const float* k2;
   const float* q2;
@@ -60,7 +66,8 @@ struct RecParams {
   const __nv_bfloat16* U;   // chunk layout
   __nv_bfloat16* dV;        // token layout (out): the gradient of v, and the dW the later stages use
   __nv_bfloat16* dU;        // chunk layout (out)
-  __nv_bfloat16* ds;        // chunk layout (out), same form as h: dL/dS at the END of every chunk
+  __nv_bfloat16* ds;        // chunk layout (out), same form as h: dL/dS at the END of a chunk; only slices above DD_MIN_LOG2_DECAY
+  __nv_bfloat16* dkg;       // bf16 image [item][128/VC][t/8][128 d][t%8] (out): per value block, sum_e G_e (r_e U)^T
   float* dr;                // f32 [item][128/VC][64][E] (out): sum_v U*(K G_e) per value block
   const int32_t* offsets;
   const int32_t* cmap;
@@ -74,9 +81,9 @@ struct SgParams {
   const __nv_bfloat16* q;   // token layout
   const __nv_bfloat16* dO;  // token layout
   const __nv_bfloat16* dV;  // token layout
-  const __nv_bfloat16* U;   // chunk layout
   const __nv_bfloat16* h;
-  const __nv_bfloat16* ds;
+  const __nv_bfloat16* ds;  // read only for slices above DD_MIN_LOG2_DECAY
+  const __nv_bfloat16* dkg; // [item][NV][16 KB image] from the reverse recurrence
   const float* k2;
   const float* q2;
   const float* gc;
@@ -85,7 +92,7 @@ struct SgParams {
   float* dc;                // f32 [item][64][E] (out)
   float* dd;                // f32 [item][E] (out)
   const int32_t* cmap;
-  int B, T, H, NC;
+  int B, T, H, NC, NV;
   float scale;
   int* status;
   int ahead;                // block index distance to the block whose inputs this one pulls into L2 (0: none)

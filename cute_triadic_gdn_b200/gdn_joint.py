@@ -106,25 +106,27 @@ def _value_block(E):
 
 
 def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None, token_map=None):
-    """Reverse recurrence: (dV, dU, ds, dr)."""
+    """Reverse recurrence: (dV, dU, ds, dkg, dr).  ds is written only for slices whose chunk decay matters to dg."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
     NV = 128 // _value_block(E)
+    alloc = torch.zeros if token_map is not None else torch.empty     # unused map entries stay defined
     dV = torch.zeros_like(do) if token_map is not None else torch.empty_like(do)
     dU = torch.empty((B, NC, H, CHUNK, 128), dtype=torch.bfloat16, device=dev)
     ds = torch.empty((B, NC, H, E, 16, 128, 8), dtype=torch.bfloat16, device=dev)
+    dkg = alloc((B, NC, H, NV, 8, 128, 8), dtype=torch.bfloat16, device=dev)   # image [token / 8][key row][token % 8] per value block
     dr = torch.empty((B, NC, H, NV, CHUNK, E), dtype=torch.float32, device=dev)
     n_docs = chunk_starts.numel() - 1 if chunk_starts is not None else 0
     with torch.cuda.device(dev):
         _lib.check(_lib.lib.tgdn_bwd_recurrent(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta), _lib.ptr(gc),
             _lib.ptr(AP), _lib.ptr(Pm), _lib.ptr(U), float(scale), _lib.ptr(chunk_starts), _lib.ptr(token_map), n_docs,
-            B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dr), _lib.stream_of(q)),
+            B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dkg), _lib.ptr(dr), _lib.stream_of(q)),
             "tgdn_bwd_recurrent")
-    return dV, dU, ds, dr
+    return dV, dU, ds, dkg, dr
 
 
-def _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map=None):
+def _run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale, token_map=None):
     """State gradients: (dkq, da, dc, dd)."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
@@ -135,7 +137,7 @@ def _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map=None):
     dd = alloc((B, NC, H, E), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib.tgdn_bwd_state_grads(
-            _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(dV), _lib.ptr(U), _lib.ptr(h), _lib.ptr(ds), _lib.ptr(k2),
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(dV), _lib.ptr(h), _lib.ptr(ds), _lib.ptr(dkg), _lib.ptr(k2),
             _lib.ptr(q2), _lib.ptr(gc), float(scale), _lib.ptr(token_map), B, T, H, E, NC, _lib.ptr(dkq), _lib.ptr(da),
             _lib.ptr(dc), _lib.ptr(dd), _lib.stream_of(q)), "tgdn_bwd_state_grads")
     return dkq, da, dc, dd
@@ -159,9 +161,9 @@ def _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do, scale, chun
     """reverse recurrence -> state gradients -> matrix gradients.  Returns (dq, dk, dv, dk2, dq2, dg, dbeta)."""
     if AP is None:      # GJ_SAVE_MASKS=0: the forward's own kernel again, bitwise identical
         _, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
-    dV, dU, ds, dr = _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts, token_map)
-    dkq, da, dc, dd = _run_state_grads(q, k, do, dV, U, h, ds, k2, q2, gc, scale, token_map)
-    del ds
+    dV, dU, ds, dkg, dr = _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts, token_map)
+    dkq, da, dc, dd = _run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale, token_map)
+    del ds, dkg
     dq, dk, dk2, dq2, dg, db = _run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale,
                                            token_map)
     return dq, dk, dV, dk2, dq2, dg, db

@@ -106,27 +106,44 @@ int tgdn_masks(const void* q, const void* k, const float* k2, const float* q2, c
                void* stream);
 
 /* tgdn_fwd: the forward chunk recurrence; writes o and, unless NULL, the tensors the backward needs (W, U, h).
+ * k2, q2 and gc must be 16-byte aligned.
  * Replaces: cute_triadic_gdn/kernels/sm100_joint_fwd.py:569-618 (joint_fwd_sm100). */
 int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
              const float* gc, const void* AP, float scale, const int32_t* doc_offsets, const int32_t* chunk_map,
              int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h, void* stream);
 
+/* tgdn_fwd_state: tgdn_fwd with the recurrent state handed in and out, for inference that continues a sequence:
+ * state_in / state_out are f32 [sequence][H][E][128 key rows][128 value columns] (sequence = batch row, or document of a
+ * packed row), 16-byte aligned; NULL state_in starts from zero, NULL state_out discards the final state.
+ * No counterpart in the reference (its forward always starts from a zero state and drops the final one:
+ * cute_triadic_gdn/kernels/sm100_joint_fwd.py:190-206). */
+int tgdn_fwd_state(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
+                   const float* gc, const void* AP, float scale, const int32_t* doc_offsets, const int32_t* chunk_map,
+                   int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h,
+                   const float* state_in, float* state_out, void* stream);
+
 /* tgdn_bwd_recurrent: the reverse chunk recurrence.  Reads the upstream gradient dO (token layout) and the forward's
- * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), ds (chunk layout, dL/dS at the end of
- * every chunk, same form as h) and dr f32 [item][128/VC][64][E] (VC = 32 for E <= 4, 16 for E >= 8).
- * Replaces: cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:561-609 (joint_bwd_recurrent_sm100, recurrence part). */
+ * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), dr f32 [item][128/VC][64][E]
+ * (VC = 32 for E <= 4, 16 for E >= 8), dkg, per value block the part of dK that contracts the gradient state over the
+ * value axis, sum_e G_e (r_e U)^T, as a bf16 operand image [item][128/VC][token / 8][128 key rows][token % 8] (16 KB per
+ * block), and ds (chunk layout, dL/dS at the end of a chunk, same form as h) for those slices only whose chunk decay
+ * exp(gc[63][e]) is at least 2^-24 (the other slices of ds are left untouched; nothing reads them).
+ * Replaces: cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:561-609 (joint_bwd_recurrent_sm100, recurrence part)
+ * and the (r U) G^T product of cute_triadic_gdn/kernels/sm100_joint_state_grads.py:373-378. */
 int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2, const float* beta,
                        const float* gc, const void* AP, const void* Pm, const void* U, float scale,
                        const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B, int T, int H, int E,
-                       int NC, void* dV, void* dU, void* ds, float* dr, void* stream);
+                       int NC, void* dV, void* dU, void* ds, void* dkg, float* dr, void* stream);
 
-/* tgdn_bwd_state_grads: per (chunk, head), the gradient terms that contract the saved states h (forward, chunk start)
- * and ds (backward, chunk end) over the value axis.  Writes dkq, a bf16 image [item][column / 8][128 rows][column % 8]
- * (32 KB per item; rows 0..63: state part of dK, rows 64..127: of dQ; 16-byte aligned), da, dc f32 [item][64][E] (gradients of the gate tables a = k2 exp(gc), c = scale q2 exp(gc))
- * and dd f32 [item][E] (gradient of the chunk decay exp(gL)).
+/* tgdn_bwd_state_grads: per (chunk, head), the gradient terms that contract the saved forward states h (chunk start)
+ * over the value axis, plus the sum of the value-block images dkg of the reverse recurrence.  Writes dkq, a bf16 image
+ * [item][column / 8][128 rows][column % 8] (32 KB per item; rows 0..63: state part of dK, rows 64..127: of dQ; 16-byte
+ * aligned), da, dc f32 [item][64][E] (gradients of the gate tables a = k2 exp(gc), c = scale q2 exp(gc)) and dd f32
+ * [item][E], the gradient <h_e, G_e> of the chunk decay exp(gL_e), which is zero for slices whose chunk decay is below
+ * 2^-24 (ds is read for the other slices only).
  * Replaces: cute_triadic_gdn/kernels/sm100_joint_state_grads.py:480-520 (joint_state_grads_sm100). */
-int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* U, const void* h,
-                         const void* ds, const float* k2, const float* q2, const float* gc, float scale,
+int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO, const void* dV, const void* h, const void* ds,
+                         const void* dkg, const float* k2, const float* q2, const float* gc, float scale,
                          const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dkq, float* da, float* dc,
                          float* dd, void* stream);
 

@@ -117,25 +117,43 @@ def reverse_stage(K, Q, dO, beta, mk, fw, reset, rounding):
     return dict(dU=st(dU_), dV=st(dV_), ds=st(ds_), dr=st(dr_))
 
 
-def state_grad_stage(K, Q, dO, fw, rv, rounding):
+DD_MIN_LOG2_DECAY = -24.0       # below this log2 of the chunk decay, exp(gL) * <h, G> is taken as zero (see the kernels)
+
+
+def value_block(E):
+    """Value columns one CTA of the reverse recurrence owns."""
+    return 16 if E >= 8 else 32
+
+
+def state_grad_stage(K, Q, dO, fw, rv, mk, rounding):
     rd = _rd(rounding)
     gt = fw["gates"]
     a, c, r = (gt[x].transpose(2, 3)[..., None] for x in "acr")                 # (N,NC,E,64,1)
     h, G = fw["h"], rv["ds"]                                                    # (N,NC,E,D,V)
     dW, U = rv["dV"], fw["U"]
+    E = h.shape[2]
     # P_e = [dW ; dO] h_e^T on the tensor core (bf16 operands, f32 result); the gate-weighted sum over the slices and the
-    # row sums against K and Q are taken from it in f32.  Only r_e*U is scaled per slice: the gate factor is rounded to
-    # bf16 first, then the packed product is rounded once more.
+    # row sums against K and Q are taken from it in f32.
     P = torch.einsum('nctv,ncedv->ncetd', dW, h)
     Pq = torch.einsum('nctv,ncedv->ncetd', dO, h)
-    Vn = rd(rd(r) * U[:, :, None])
+    # The part of dK that contracts the gradient state is formed in the reverse recurrence, per block of value columns,
+    # from r_e*U rounded to bf16, and leaves it rounded to bf16; the blocks are then added up in f32.
+    Vn = rd(r * U[:, :, None])
+    VC = value_block(E)
+    dKg = 0
+    for j in range(128 // VC):
+        sl = slice(j * VC, (j + 1) * VC)
+        dKg = dKg + rd(torch.einsum('ncetv,ncedv->nctd', Vn[..., sl], G[..., sl]))
     # the state parts of dK and dQ are handed to the matrix kernel as bf16
-    dK = rd((-a * P).sum(2) + torch.einsum('ncetv,ncedv->nctd', Vn, G))
+    dK = rd((-a * P).sum(2) + dKg)
     dQ = rd((c * Pq).sum(2))
     da = -torch.einsum('nctd,ncetd->ncte', K, P)
     dc = torch.einsum('nctd,ncetd->ncte', Q, Pq)
     dd = (h * G).sum((-1, -2))                                                  # (N,NC,E)
-    return dict(dK=dK, dQ=dQ, da=da, dc=dc, dd=dd)
+    if rounding:                                                                # slices whose chunk decay cannot matter are skipped
+        gl = mk["gc"][..., -1, :]
+        dd = torch.where(gl * 1.4426950408889634 >= DD_MIN_LOG2_DECAY, dd, torch.zeros_like(dd))
+    return dict(dK=dK, dQ=dQ, da=da, dc=dc, dd=dd, dKg=dKg)
 
 
 def matrix_stage(K, Q, dO, k2, q2, beta, scale, mk, fw, rv, sg, rounding):
@@ -180,7 +198,7 @@ def run_plan(q, k, v, k2, q2, g, beta, do, scale=None, reset=None, rounding=True
     mk = masks_stage(K, Q, k2c, q2c, gch, bc, scale, rounding)
     fw = forward_stage(K, Q, V, k2c, q2c, bc, scale, mk, reset, rounding)
     rv = reverse_stage(K, Q, dO, bc, mk, fw, reset, rounding)
-    sg = state_grad_stage(K, Q, dO, fw, rv, rounding)
+    sg = state_grad_stage(K, Q, dO, fw, rv, mk, rounding)
     mt = matrix_stage(K, Q, dO, k2c, q2c, bc, scale, mk, fw, rv, sg, rounding)
     back = lambda t: from_chunks(t, B, H)
     grads = [back(mt["dq"]), back(mt["dk"]), back(rv["dV"]), back(mt["dk2"]), back(mt["dq2"]), back(mt["dg"]),
