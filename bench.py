@@ -7,7 +7,10 @@ One step = one forward + backward of the whole (B, T, H) problem through `gdn_jo
 JSON line from rank 0.  `value` is timed with the inputs resident in HBM; `e2e` repeats the measurement with the
 inputs in pinned host memory, copied to the device every step, and the output and all seven gradients copied back.
 `roofline` describes the kernel with the largest share of the step; `cpu_baseline` times the CPU oracle (a port of the
-reference's torch path) on a bounded sample.  `--impl reference` times that CPU path alone.
+reference's torch path) on a bounded sample; `parity` compares seeded (batch row | document, head) slices of the
+full-size run with that oracle and fails the run when a tolerance is broken; `aux` carries the second mode of the headline
+configuration (GJ_SAVE_MASKS=0) and the convolution pre-pass; `reference_kernels` is what the reference's own CuTe-DSL
+kernels did on this GPU (baseline/time_reference_kernels.py).  `--impl reference` times the CPU path alone.
 """
 from __future__ import annotations
 
@@ -51,30 +54,44 @@ KERNEL_U = {
     "masks": lambda E: 2, "fwd": lambda E: 2 + 6 * E, "rec": lambda E: 3 + 6 * E, "sg": lambda E: 6 * E, "mat": lambda E: 8,
 }
 
-# DRAM bytes (read + write) per (chunk, head) item and launch at E = 8, from one ncu capture of each kernel on the `prof`
-# workload (4096 items; profiles/core_kernels_prof_workload.md).  Traffic grows in proportion to the item count, so a
-# full launch is this figure times its items.
-NCU_DRAM_BYTES_PER_ITEM_E8 = {
-    "masks": (0.161 + 0.076) * 1e9 / 4096, "fwd": (0.373 + 1.223) * 1e9 / 4096, "rec": (0.479 + 1.221) * 1e9 / 4096,
-    "sg": (2.511 + 0.214) * 1e9 / 4096, "mat": (0.715 + 0.146) * 1e9 / 4096,
+# DRAM bytes (read + write) per (chunk, head) item and launch, from ncu captures of each kernel at E = 8 (the `prof`
+# workload, 4096 items) and at E = 16 (B=2, T=4096, H=16: 2048 items).  Traffic grows in proportion to the item count and,
+# between the two captures, linearly in E (the saved states are E * 32 KB per item), so other E are interpolated.
+NCU_DRAM_BYTES_PER_ITEM = {
+    # kernel: (bytes per item at E = 8, at E = 16); filled from profiles/core_kernels_prof_workload.md
+    "masks": (57.9e3, 64.0e3), "fwd": (389.6e3, 690e3), "rec": (415.0e3, 560e3), "sg": (665.3e3, 1050e3),
+    "mat": (210.2e3, 250e3),
 }
 
 # DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)
-# (profiles/conv_kernels_c4_shape.md; part of the written lines still sat in L2 when the kernel ended).
+# (part of the written lines still sat in L2 when the kernel ended).
 NCU_DRAM_BYTES_PER_ELEMENT_CONV = {"fwd": (215.9 + 162.0) * 1e6 / (8192 * 13056), "bwd": (431.6 + 184.2) * 1e6 / (8192 * 13056)}
 
-# Algorithmic HBM bytes per (chunk, head) item: every tensor a kernel must read or write, once (bf16 tiles of 64x128 are
-# 16 KB; a state slice is 32 KB; NV = value blocks of the reverse recurrence).  The saved states make every kernel of this
-# path nearer to the HBM roofline than to the tensor-core one; both fractions are reported.
+
+def ncu_traffic(name, E, items):
+    lo, hi = NCU_DRAM_BYTES_PER_ITEM[name]
+    return (lo + (hi - lo) * (E - 8) / 8.0) * items
+
+
+# HBM bytes per (chunk, head) item that each kernel of THIS decomposition must read or write once (bf16 tiles of 64x128
+# are 16 KB; a state slice is 32 KB; NV = value blocks of the reverse recurrence).  The saved forward states h (E * 32 KB
+# written by fwd, read by sg) and the value-block images of the reverse recurrence are consequences of the decomposition,
+# not of the algorithm: `io_bytes` below counts only what the algorithm itself must move.
 def kernel_bytes(name, E):
     K, NV, gates = 1024, (8 if E >= 8 else 4), 3 * 64 * E * 4
     return {
         "masks": 32 * K + gates + 256 + 64 * E * 4 + 24 * K,
-        "fwd": 64 * K + 16 * K + gates + 256 + 16 * K + 32 * K * E + 32 * K,
-        "rec": 88 * K + gates + 32 * K + 32 * K * E + NV * 64 * E * 4,
-        "sg": 80 * K + 64 * K * E + gates + 32 * K + 2 * 64 * E * 4 + 4 * E,
-        "mat": 144 * K + gates + 2 * 64 * E * 4 + 4 * E + NV * 64 * E * 4 + 32 * K + gates + 256,
+        "fwd": 48 * K + 16 * K + gates + 256 + 48 * K + 32 * K * E,
+        "rec": 64 * K + 16 * K + gates + 256 + 32 * K + NV * 16 * K + NV * 64 * E * 4,
+        "sg": 64 * K + 32 * K * E + NV * 16 * K + gates + 32 * K + 2 * 64 * E * 4 + 4 * E,
+        "mat": 96 * K + 16 * K + 32 * K + gates + 256 + 2 * 64 * E * 4 + 4 * E + NV * 64 * E * 4 + 32 * K + gates + 256,
     }[name]
+
+
+def io_bytes(E):
+    """Inputs and outputs of the whole forward + backward per (chunk, head): q, k, v, dO, o, dq, dk, dv (bf16 tiles),
+    k2, q2, g and their gradients, beta and its gradient."""
+    return 8 * 16 * 1024 + 6 * 64 * E * 4 + 2 * 256
 
 
 def peaks():
@@ -82,8 +99,9 @@ def peaks():
     if os.path.exists(path):
         with open(path) as fh:
             d = json.load(fh)
-        return {"tflops": d.get("bf16_tflops_sustained", d.get("bf16_tflops")), "gbs": d.get("hbm_gbs"), "kind": "measured (sustained)"}
-    return {"tflops": 1400.0, "gbs": 6650.0, "kind": "fallback"}
+        return {"tflops": d.get("bf16_tflops"), "tflops_sustained": d.get("bf16_tflops_sustained", d.get("bf16_tflops")),
+                "gbs": d.get("hbm_gbs"), "kind": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "gbs": 6650.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -186,6 +204,12 @@ def cpu_reference_rate(B, T, H, E, backward, budget_s=20.0, threads=None):
     return rate, done, threads, per_slice
 
 
+def workload_name(name):
+    B, T, H, E, backward = WORKLOADS[name]
+    packed = ("packed, " + PACKED[name][0] + " documents, ") if name in PACKED else ""
+    return f"{name}: B={B} T={T} H={H} E={E} {packed}{'fwd+bwd' if backward else 'fwd'}"
+
+
 def run_reference(args, rank, world):
     B, T, H, E, backward = WORKLOADS[args.workload]
     if rank != 0:
@@ -202,32 +226,36 @@ def run_reference(args, rank, world):
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * B * T / value, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {'fwd+bwd' if backward else 'fwd'}",
-                       "path": "CPU port of the reference torch path (oracle/triadic_oracle.py)"},
+            "config": {"workload": workload_name(args.workload),
+                       "path": "CPU port of the reference torch path (oracle/triadic_oracle.py); a GPU-over-CPU ratio, not a kernel comparison"},
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def stage_times(leaves, do, E, reps=2):
+def stage_times(leaves, do, E, cu_dev=None, reps=2):
     """Per-kernel device time (ms) of one forward + backward: CUDA events around each C-ABI call on torch's stream."""
     from cute_triadic_gdn_b200 import gdn_joint as gj
     q, k, v, k2, q2, g, beta = [t.detach() for t in leaves]
     scale = 128 ** -0.5
+    cs = tm = None
+    if cu_dev is not None:
+        from cute_triadic_gdn_b200.joint_packing import prepare_documents
+        cs, tm = prepare_documents((q, k, v, k2, q2, g, beta), cu_dev)
     names = ["masks", "fwd", "rec", "sg", "mat"]
     acc = {n: 0.0 for n in names}
     for rep in range(reps + 1):                        # the first repetition warms the allocator and is dropped
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         ev[0].record()
-        gc, AP, Pm = gj._run_masks(q, k, k2, q2, g, beta, scale, None)
+        gc, AP, Pm = gj._run_masks(q, k, k2, q2, g, beta, scale, tm)
         ev[1].record()
-        o, h, W, U = gj._run_forward(q, k, v, k2, q2, beta, gc, AP, scale, True)
+        o, h, W, U = gj._run_forward(q, k, v, k2, q2, beta, gc, AP, scale, True, cs, tm)
         ev[2].record()
-        dV, dU, ds, dkg, dr = gj._run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale)
+        dV, dU, ds, dkg, dr = gj._run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, cs, tm)
         ev[3].record()
-        dkq, da, dc, dd = gj._run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale)
+        dkq, da, dc, dd = gj._run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale, tm)
         ev[4].record()
-        gj._run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale)
+        gj._run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale, tm)
         ev[5].record()
         torch.cuda.synchronize()
         if rep > 0:
@@ -235,6 +263,92 @@ def stage_times(leaves, do, E, reps=2):
                 acc[n] += ev[i].elapsed_time(ev[i + 1])
         del h, ds, dkg, dkq, W, U, dU, o
     return {n: acc[n] / reps for n in names}
+
+
+PARITY_TOL = {"o": 1e-2, "grad": 2e-2}                 # relative L2 against an fp32 run of the reference math
+
+
+def parity_check(ins, do, o_dev, grads_dev, cu_host, seed=0, n_slices=2):
+    """Compares seeded slices of the full-size device result with the CPU oracle (oracle/triadic_oracle.py, the fp32
+    restatement of the reference's torch path).  Dense rows: (batch row, head) slices, which are independent problems.
+    Packed rows: (document, head) slices, the longest document among them.  Returns the worst relative L2 errors."""
+    from oracle import triadic_oracle as orc
+    gen = torch.Generator().manual_seed(int(seed))
+    B, T, H = ins[0].shape[:3]
+    picks = []
+    if cu_host is None:
+        while len(picks) < n_slices:
+            c = (int(torch.randint(B, (1,), generator=gen)), 0, T, int(torch.randint(H, (1,), generator=gen)))
+            if c not in picks:
+                picks.append(c)
+    else:
+        lens = (cu_host[1:] - cu_host[:-1]).tolist()
+        docs = [max(range(len(lens)), key=lambda d: lens[d])]
+        while len(docs) < min(n_slices, len(lens)):
+            d = int(torch.randint(len(lens), (1,), generator=gen))
+            if d not in docs:
+                docs.append(d)
+        picks = [(0, int(cu_host[d]), int(cu_host[d + 1]), int(torch.randint(H, (1,), generator=gen))) for d in docs]
+    worst_o, worst_g, which = 0.0, 0.0, []
+    torch.set_num_threads(os.cpu_count() or 1)
+    for (b, lo, hi, h) in picks:
+        sl = lambda t: t[b:b + 1, lo:hi, h:h + 1].contiguous()
+        cu = None if (hi - lo) % 64 == 0 else torch.tensor([0, hi - lo], dtype=torch.int32)
+        o_ref, g_ref = orc.reference_with_grads(orc.chunk_reference, [sl(t) for t in ins], sl(do), cu_seqlens=cu, dtype=torch.float32)
+        eo = orc.rel_l2(sl(o_dev).float().cpu(), o_ref)
+        eg = max(orc.rel_l2(sl(gd).float().cpu(), gr) for gd, gr in zip(grads_dev, g_ref))
+        worst_o, worst_g = max(worst_o, eo), max(worst_g, eg)
+        which.append({"row": b, "tokens": [lo, hi], "head": h, "o": eo, "max_grad": eg})
+    return {"o": worst_o, "max_grad": worst_g, "slices": which, "tolerance": PARITY_TOL,
+            "against": "oracle/triadic_oracle.py chunk_reference, fp32, same seeded inputs",
+            "ok": worst_o < PARITY_TOL["o"] and worst_g < PARITY_TOL["grad"]}
+
+
+def conv_rates(dev, T=32768, C=13056, act=12288, reps=5):
+    """Achieved GB/s of the convolution pre-pass of configuration 4 at its own size (algorithmic bytes: forward 4*T*C,
+    backward 6*T*C), a few launches outside every other timed region."""
+    from cute_triadic_gdn_b200 import conv_split_act_call
+    from cute_triadic_gdn_b200.conv_split_act import conv_split_act_bwd
+    x = torch.randn(1, T, C, device=dev).to(torch.bfloat16)
+    w = (0.5 * torch.randn(C, 4, device=dev)).to(torch.bfloat16)
+    dy = torch.randn(1, T, C, device=dev).to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, 4096, device=dev, dtype=torch.int32)
+
+    def ev_time(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    with torch.no_grad():
+        f = ev_time(lambda: conv_split_act_call(x, w, act, cu))
+        bw = ev_time(lambda: conv_split_act_bwd(x, dy, w, act, cu))
+    return 4 * T * C / (f * 1e-3) / 1e9, 6 * T * C / (bw * 1e-3) / 1e9, f, bw
+
+
+def reference_kernel_timing(timeout_s=420):
+    """What the reference's own CuTe-DSL kernels do on this GPU, measured by baseline/time_reference_kernels.py in a child
+    process (a compile failure of the DSL must not take the bench down).  Needs the reference installed under
+    baseline/_ref; otherwise, or when the child fails, says why."""
+    script = os.path.join(ROOT, "baseline", "time_reference_kernels.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "cute_triadic_gdn")):
+        return {"ok": False, "unavailable": "baseline/_ref does not hold the reference package"}
+    try:
+        r = subprocess.run([sys.executable, script], capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return {"ok": False, "unavailable": f"no result within {timeout_s} s"}
+    for line in reversed(r.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            out = json.loads(line)["reference_kernels"]
+            out.pop("trace_tail", None)
+            return out
+    return {"ok": False, "unavailable": f"child exited {r.returncode}: {r.stderr[-300:]}"}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -264,6 +378,9 @@ def run_ours(args, rank, world, local_rank):
         Tl, Hl = T, hs.stop - hs.start
         chunks = B * (T // 64)
     ins, do = host_inputs(B, Tl, Hl, E, seed=1000 + rank)
+    # pinned buffers are allocated after the rank has moved to the cores of its GPU's NUMA node (where sysfs says which)
+    from cute_triadic_gdn_b200.host_pipeline import bind_host_to_gpu
+    numa = bind_host_to_gpu(local_rank)
     pinned = [t.pin_memory() for t in ins]
     do_pinned = do.pin_memory()
     leaves = [t.to(dev).requires_grad_(backward) for t in ins]
@@ -327,47 +444,81 @@ def run_ours(args, rank, world, local_rank):
 
     pk = peaks()
     items = chunks * Hl                               # (chunk, head) items of this rank
+    step_s = ms / args.steps * 1e-3
     roof = None
-    if backward and packed:
-        step_tf = algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12
-        roof = {"bound": "tensor", "kernel": "whole step", "achieved": step_tf, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": step_tf / pk["tflops"], "traffic": None, "peak_kind": pk["kind"], "step_achieved": step_tf,
-                "step_frac": step_tf / pk["tflops"]}
-    elif backward:
-        st = stage_times(leaves, do_dev, E)
+    if backward:
+        st = stage_times(leaves, do_dev, E, cu_dev)
         total = sum(st.values())
         top = max(st, key=st.get)
         flops = KERNEL_U[top](E) * U_FLOP * items
         achieved = flops / (st[top] * 1e-3) / 1e12
+        step_tf = algorithmic_flops(E, items * world, True) / step_s / 1e12     # whole job: every rank's items in the max-over-ranks time
+        kb = {k: kernel_bytes(k, E) * items for k in st}
         roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": achieved / pk["tflops"],
-                "traffic": NCU_DRAM_BYTES_PER_ITEM_E8[top] * items if E == 8 else None, "peak_kind": pk["kind"],
+                "frac": achieved / pk["tflops"], "peak_name": "bf16_tflops (burst): the kernel is timed alone",
+                "traffic": ncu_traffic(top, E, items), "peak_kind": pk["kind"],
                 "kernel_ms": {k: round(v, 3) for k, v in st.items()}, "share": round(st[top] / total, 3),
-                "hbm": {"kernel_gbs": kernel_bytes(top, E) * items / (st[top] * 1e-3) / 1e9,
-                        "kernel_frac": kernel_bytes(top, E) * items / (st[top] * 1e-3) / 1e9 / pk["gbs"],
-                        "step_gbs": sum(kernel_bytes(k, E) for k in st) * items / (ms / args.steps * 1e-3) / 1e9,
-                        "step_frac": sum(kernel_bytes(k, E) for k in st) * items / (ms / args.steps * 1e-3) / 1e9 / pk["gbs"],
-                        "peak": pk["gbs"], "unit": "GB/s", "bytes": "algorithmic, per kernel_bytes()"},
-                "step_achieved": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12,
-                "step_frac": algorithmic_flops(E, items, True) / (ms / args.steps * 1e-3) / 1e12 / pk["tflops"]}
+                "step_achieved": step_tf,
+                "step_frac": step_tf / (pk["tflops"] * world), "step_peak_name": "bf16_tflops (burst) x GPUs",
+                "step_frac_sustained": step_tf / (pk["tflops_sustained"] * world),
+                "hbm": {"kernel_gbs": kb[top] / (st[top] * 1e-3) / 1e9, "kernel_frac": kb[top] / (st[top] * 1e-3) / 1e9 / pk["gbs"],
+                        "step_gbs": sum(kb.values()) / step_s / 1e9, "step_frac": sum(kb.values()) / step_s / 1e9 / pk["gbs"],
+                        "step_bytes_this_decomposition": sum(kb.values()), "step_bytes_algorithm_io": io_bytes(E) * items,
+                        "step_traffic_ncu": sum(ncu_traffic(k, E, items) for k in st),
+                        "peak": pk["gbs"], "unit": "GB/s",
+                        "bytes": "kernel_bytes(): what this decomposition must move; io_bytes(): inputs and outputs of the algorithm only"}}
+    # parity at the size that was timed: seeded slices of the last resident step against the CPU oracle
+    parity = None
+    if backward and not args.no_parity:
+        o_dev = step_resident()
+        torch.cuda.synchronize()
+        parity = parity_check(ins, do, o_dev, [t.grad for t in leaves], cu_host, seed=args.steps)
+    # the second mode of the headline configuration and the convolution pre-pass, a few launches each
+    aux = {}
+    if backward and not args.no_aux and world == 1:
+        prev = os.environ.get("GJ_SAVE_MASKS")
+        os.environ["GJ_SAVE_MASKS"] = "0" if prev != "0" else "1"
+        other = os.environ["GJ_SAVE_MASKS"]
+        try:
+            aux[f"save_masks{other}_ms_per_step"] = timed(step_resident, 3, 2) / 3
+        finally:
+            if prev is None:
+                os.environ.pop("GJ_SAVE_MASKS")
+            else:
+                os.environ["GJ_SAVE_MASKS"] = prev
+    del pipe
+    for t in leaves:
+        t.grad = None
+    if world == 1 and not args.no_aux:
+        del leaves, do_dev
+        torch.cuda.empty_cache()
+        fg, bg, fms, bms = conv_rates(dev)
+        aux.update({"conv_fwd_gbs": fg, "conv_bwd_gbs": bg, "conv_fwd_ms": fms, "conv_bwd_ms": bms,
+                    "conv_frac": fg / pk["gbs"], "conv_bwd_frac": bg / pk["gbs"],
+                    "conv_workload": "x (1, 32768, 13056) bf16, 8 documents, SiLU on 12288 channels; bytes 4*T*C forward, 6*T*C backward"})
     cpu_rate, n_slices, threads, per_slice = cpu_reference_rate(B, T, H, E, backward, budget_s=15.0)
+    refk = reference_kernel_timing() if (world == 1 and not args.no_reference_kernels) else None
     line = {"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: B={B} T={T} H={H} E={E} {('packed, ' + PACKED[args.workload][0] + ' documents, ') if packed else ''}"
-                                   f"{'fwd+bwd' if backward else 'fwd'}, GJ_SAVE_MASKS="
-                                   f"{os.environ.get('GJ_SAVE_MASKS', '1')}",
+            "config": {"workload": workload_name(args.workload),
+                       "save_masks": os.environ.get("GJ_SAVE_MASKS", "1"),
                        "parallelism": (f"whole documents, token-balanced, over {world} GPU(s), no collective" if packed
                                        else f"heads sharded over {world} GPU(s), no collective"),
                        "l2": "inputs larger than L2",
                        "api": "gdn_joint_call + backward; e2e: HostPipeline (pinned host tensors, batch slices overlapped on three streams)"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / args.steps,
+                    "h2d_gbs": h2d / (ms_e2e / args.steps * 1e-3) / 1e9, "d2h_gbs": d2h / (ms_e2e / args.steps * 1e-3) / 1e9,
+                    "host_numa": numa},
             "gpu_launches": args.steps * (5 if backward else 2),
-            "clocks": clocks, "roofline": roof, "device_status": status,
+            "clocks": clocks, "roofline": roof, "parity": parity, "aux": aux, "device_status": status,
+            "reference_kernels": refk,
             "cpu_baseline": {"value": cpu_rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": f"{n_slices} of {B * H} (batch row, head) slices of T={min(T, 16384)}, {per_slice:.2f} s each, scaled linearly"}}
     print(json.dumps(line))
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"parity broken at benchmark size: {parity}")
 
 
 def run_conv(args):
@@ -422,6 +573,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=list(WORKLOADS) + ["conv"])
     ap.add_argument("--tokens", type=int, default=0,
                     help="conv workload only: sequence length (multiple of 4096; default 32768); small values size a profiler capture")
+    ap.add_argument("--no-parity", action="store_true", help="skip the comparison of seeded slices with the CPU oracle")
+    ap.add_argument("--no-aux", action="store_true", help="skip the GJ_SAVE_MASKS=0 and convolution side measurements")
+    ap.add_argument("--no-reference-kernels", action="store_true", help="do not time the reference's own kernels (a child process)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="skip the end-to-end, per-kernel and CPU-baseline legs (used for profiler captures)")
     args = ap.parse_args()

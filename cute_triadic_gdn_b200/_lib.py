@@ -11,7 +11,7 @@ import re
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtgdn_b200.so")
-HEADER = os.path.join(_PKG, "..", "include", "tgdn.h")
+HEADERS = [os.path.join(_PKG, "..", "include", n) for n in ("tgdn.h", "tgdn_selftest.h")]
 
 _c = ctypes
 _P, _I, _L, _F = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float
@@ -35,6 +35,7 @@ SIGNATURES = {
     "tgdn_bwd_matrix": (_I, [_P] * 16 + [_F, _P] + [_I] * 5 + [_P] * 7),
     "tgdn_selftest_mma": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "tgdn_selftest_tma": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
+    "tgdn_selftest_wait": (_I, [_c.c_longlong, _P, _P]),
 }
 
 
@@ -43,23 +44,31 @@ class TgdnError(RuntimeError):
 
 
 def declared_symbols():
-    """Names of the functions declared in include/tgdn.h."""
-    with open(HEADER) as fh:
-        text = re.sub(r"/\*.*?\*/", "", fh.read(), flags=re.S)
+    """Names of the functions declared in include/tgdn.h and include/tgdn_selftest.h."""
+    text = ""
+    for path in HEADERS:
+        with open(path) as fh:
+            text += re.sub(r"/\*.*?\*/", "", fh.read(), flags=re.S)
     return sorted(set(re.findall(r"\b(tgdn_[a-z0-9_]+)\s*\(", text)))
 
 
 def _load():
-    # (re)build when a source changed since the library was linked; a no-op otherwise
+    """Builds the library when a source changed since it was linked (a no-op otherwise) and binds the signatures.  Several
+    ranks may import the package at once: the build is serialised by a file lock and the library is moved into place
+    atomically (build.py), so nobody can load a half-written file.  A library that is out of date and cannot be rebuilt
+    is NOT loaded silently: its signatures may no longer match include/tgdn.h."""
     import importlib.util
     spec = importlib.util.spec_from_file_location("_tgdn_build", os.path.join(_PKG, "build.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     try:
         mod.build()
-    except Exception:
+    except Exception as exc:
         if not os.path.exists(LIB_PATH):
             raise
+        if not mod.up_to_date():
+            raise RuntimeError("libtgdn_b200.so is older than its sources and could not be rebuilt "
+                               f"({type(exc).__name__}: {exc}); refusing to bind a stale library") from exc
     lib = ctypes.CDLL(LIB_PATH)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)

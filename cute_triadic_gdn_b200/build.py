@@ -18,8 +18,12 @@ CSRC = os.path.join(PKG, "csrc")
 OUT = os.path.join(PKG, "libtgdn_b200.so")
 BUILD = os.path.join(CSRC, "build")
 
-NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC",
-              "-Xptxas", "-v", "--expt-relaxed-constexpr"]
+# sm_100a (B200) is the target and the default.  TGDN_ARCHS="100a,103a" adds the B300 flavour of the same kernels to the
+# library (the family-specific tcgen05 / TMA instructions need an architecture-specific build per member of the family;
+# the device check of the library admits every compute capability 10.x).  The 103a flavour compiles here; it has not run.
+ARCHS = [a.strip() for a in os.environ.get("TGDN_ARCHS", "100a").split(",") if a.strip()]
+NVCC_FLAGS = [f for a in ARCHS for f in ("-gencode", f"arch=compute_{a},code=sm_{a}")] + \
+             ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
 
 
 def _nvcc():
@@ -43,13 +47,32 @@ def _digest():
     return h.hexdigest()
 
 
-def build(force=False, verbose=False):
-    """Compile every .cu for sm_100a and link the shared library; returns its path."""
+def up_to_date():
+    """True when the library on disk was linked from the sources as they are now."""
     stamp = os.path.join(BUILD, "digest.txt")
-    digest = _digest()
-    if not force and os.path.exists(OUT) and os.path.exists(stamp) and open(stamp).read() == digest:
+    return os.path.exists(OUT) and os.path.exists(stamp) and open(stamp).read() == _digest()
+
+
+def build(force=False, verbose=False):
+    """Compile every .cu for sm_100a and link the shared library; returns its path.  Concurrent callers (one per rank) are
+    serialised by a lock file; whoever comes second finds the work done."""
+    if not force and up_to_date():
         return OUT
     os.makedirs(BUILD, exist_ok=True)
+    import fcntl
+    with open(os.path.join(BUILD, "lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and up_to_date():
+                return OUT
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose):
+    stamp = os.path.join(BUILD, "digest.txt")
+    digest = _digest()
     nvcc = _nvcc()
 
     def compile_one(src):
@@ -66,10 +89,12 @@ def build(force=False, verbose=False):
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, _sources()))
-    cmd = [nvcc, "-shared", "-o", OUT, *objs, "-lcudart"]
+    tmp = OUT + f".tmp{os.getpid()}"
+    cmd = [nvcc, "-shared", "-o", tmp, *objs, "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, OUT)                               # atomic: a concurrent dlopen sees the old or the new file, never half of one
     with open(stamp, "w") as fh:
         fh.write(digest)
     return OUT

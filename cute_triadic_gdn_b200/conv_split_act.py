@@ -15,14 +15,21 @@ from . import _lib
 
 
 def _prep(x, weight, cu_seqlens):
+    """Argument checks and the layout the kernels need: bf16, unit channel stride, 16-byte aligned rows, and a channel count
+    that is a multiple of 8 (a TMA row is a multiple of 16 bytes).  Other channel counts and other weight dtypes, which
+    the reference's Triton kernels take as they are (cute_triadic_gdn/ops/conv_split_act.py:133-140), are served through a
+    zero-padded copy and a cast; `pad` is the number of channels added."""
     if x.ndim != 3 or weight.ndim != 2 or weight.shape[0] != x.shape[2] or weight.shape[1] != 4:
         raise ValueError("x must be (B, T, C) and weight (C, 4)")
-    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
-        raise ValueError("x and weight must be bf16")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("x must be bf16")
     if not x.is_cuda or weight.device != x.device:
         raise ValueError("x and weight must be on the same CUDA device")
-    if x.shape[2] % 8:
-        raise ValueError("the channel count must be a multiple of 8")
+    pad = (-x.shape[2]) % 8
+    weight = weight.to(torch.bfloat16)
+    if pad:
+        x = torch.nn.functional.pad(x, (0, pad))
+        weight = torch.nn.functional.pad(weight, (0, 0, 0, pad))
     if x.stride(2) != 1 or x.stride(1) % 8 or x.stride(0) % 8 or x.data_ptr() % 16:
         x = x.contiguous()
     n_docs = 0
@@ -33,20 +40,20 @@ def _prep(x, weight, cu_seqlens):
             raise ValueError("cu_seqlens must be a vector of at least two offsets on the input device")
         cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
         n_docs = cu_seqlens.numel() - 1
-    return x, weight.contiguous(), cu_seqlens, n_docs
+    return x, weight.contiguous(), cu_seqlens, n_docs, pad
 
 
 @custom_op("tgdn_b200::conv_split_act_fwd", mutates_args=(), device_types="cuda")
 def conv_split_act_fwd(x: torch.Tensor, weight: torch.Tensor, act_channels: int,
                        cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
-    x, weight, cu, n_docs = _prep(x, weight, cu_seqlens)
+    x, weight, cu, n_docs, pad = _prep(x, weight, cu_seqlens)
     B, T, C = x.shape
     y = torch.empty((B, T, C), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib.tgdn_conv_fwd(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(y), _lib.ptr(cu), n_docs, B, T, C,
                                           x.stride(0), x.stride(1), int(act_channels), _lib.stream_of(x)),
                    "tgdn_conv_fwd")
-    return y
+    return y[..., :C - pad].contiguous() if pad else y
 
 
 @conv_split_act_fwd.register_fake
@@ -57,7 +64,10 @@ def _(x, weight, act_channels, cu_seqlens=None):
 @custom_op("tgdn_b200::conv_split_act_bwd", mutates_args=(), device_types="cuda")
 def conv_split_act_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor, act_channels: int,
                        cu_seqlens: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
-    x, weight, cu, n_docs = _prep(x, weight, cu_seqlens)
+    wdtype = weight.dtype
+    x, weight, cu, n_docs, pad = _prep(x, weight, cu_seqlens)
+    if pad:
+        dy = torch.nn.functional.pad(dy, (0, pad))
     if dy.stride(2) != 1 or dy.stride(1) % 8 or dy.stride(0) % 8 or dy.data_ptr() % 16:
         dy = dy.contiguous()
     B, T, C = x.shape
@@ -70,7 +80,9 @@ def conv_split_act_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor, 
                                           _lib.ptr(cu), n_docs, B, T, C, x.stride(0), x.stride(1), dy.stride(0),
                                           dy.stride(1), int(act_channels), _lib.ptr(scratch), nbytes,
                                           _lib.stream_of(x)), "tgdn_conv_bwd")
-    return dx, dw
+    if pad:
+        dx, dw = dx[..., :C - pad].contiguous(), dw[:C - pad].contiguous()
+    return dx, dw.to(wdtype)
 
 
 @conv_split_act_bwd.register_fake
@@ -78,24 +90,26 @@ def _(x, dy, weight, act_channels, cu_seqlens=None):
     return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)
 
 
-def _setup(ctx, inputs, output):
+def _remember(ctx, inputs, output):
+    """What the backward needs: the input, the taps and (for a packed row) the document offsets."""
     x, weight, act_channels, cu_seqlens = inputs
-    ctx.save_for_backward(x, weight, *([cu_seqlens] if cu_seqlens is not None else []))
-    ctx.act_channels = act_channels
-    ctx.has_cu = cu_seqlens is not None
+    keep = [x, weight] + ([] if cu_seqlens is None else [cu_seqlens])
+    ctx.save_for_backward(*keep)
+    ctx.act_channels = int(act_channels)
 
 
-def _backward(ctx, dy):
-    saved = ctx.saved_tensors
-    cu_seqlens = saved[2] if ctx.has_cu else None
-    dx, dw = conv_split_act_bwd(saved[0], dy, saved[1], ctx.act_channels, cu_seqlens)
+def _differentiate(ctx, dy):
+    kept = ctx.saved_tensors                      # read once (activation checkpointing unpacks on every read)
+    offsets = kept[2] if len(kept) == 3 else None
+    dx, dw = conv_split_act_bwd(kept[0], dy, kept[1], ctx.act_channels, offsets)
     return dx, dw, None, None
 
 
-register_autograd("tgdn_b200::conv_split_act_fwd", _backward, setup_context=_setup)
+register_autograd("tgdn_b200::conv_split_act_fwd", _differentiate, setup_context=_remember)
 
 
 def conv_split_act_call(x, weight, act_channels, cu_seqlens=None):
-    """x [B, T, C] bf16, weight [C, 4] bf16; channels [0, act_channels) get SiLU, the rest none.  cu_seqlens: document
-    boundaries of a packed row (the convolution restarts at each document)."""
+    """Width-4 causal depthwise convolution over (B, T, C) bf16 `x` with taps `weight` (C, 4); the first `act_channels`
+    channels pass through SiLU.  With `cu_seqlens` (offsets of the documents of one packed row, B = 1) the window starts
+    afresh at every document.  Same call as the reference's conv_split_act_call (ops/conv_split_act.py:194-197)."""
     return conv_split_act_fwd(x, weight.contiguous(), int(act_channels), cu_seqlens)

@@ -30,8 +30,13 @@ EncodeTiledFn encode_tiled() {
 int tgdn_cuda_error(cudaError_t e) { return e == cudaSuccess ? 0 : -(1000 + static_cast<int>(e)); }
 
 int* tgdn_status_word() {
+  static int* cached[64] = {nullptr};          // per device: the address never changes once the module is loaded
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev >= 0 && dev < 64 && cached[dev] != nullptr) return cached[dev];
   int* p = nullptr;
   if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status_word) != cudaSuccess) return nullptr;
+  if (dev >= 0 && dev < 64) cached[dev] = p;
   return p;
 }
 
@@ -111,9 +116,12 @@ int tgdn_check_core_shape(int B, int T, int H, int E, int NC, int packed) {
 // Number of SMs of the current device.  With one resident CTA per SM and blocks dispatched in index order, block
 // i + count starts about when block i ends, which is what the per-item kernels use to warm L2 for their successor.
 int tgdn_sm_count() {
+  static int cached[64] = {0};
   int dev = 0, n = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
   return n;
 }
 

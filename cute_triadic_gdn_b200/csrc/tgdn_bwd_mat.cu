@@ -198,7 +198,9 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
     const int rr = idx / E, e = idx % E, o = rr * ES + e;
     const float up = sm.gc2[(rr & ~15) * ES + e] - sm.gc2[o];    // >= 0 when gc does not increase
-    if (!(up <= 100.f) || up < 0.f) sm.steep = 1;          // too steep, not monotone, or NaN
+    // too steep, NaN, or not monotone (a log gate above zero makes gc rise from one row to the next: the factorised form,
+    // which clamps its first factor at one, would then be wrong for rows of later blocks)
+    if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[o] > sm.gc2[o - ES])) sm.steep = 1;
     Hd[o] = mexp2(up) * sm.k2[o];
     Xd[o] = mexp2(-up);
   }

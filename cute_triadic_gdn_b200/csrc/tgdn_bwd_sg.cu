@@ -163,36 +163,46 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
     }
     if (tid < E) raw_gl = __ldg(gcp + 63 * E + tid);
   }
+  // The issuing and the loading warp decide per slice whether a trace is taken; they read the chunk decays themselves
+  // (one lane per slice) so that they do not have to wait for the workers' prologue.
+  float my_gl = 0.f;
+  if (!worker && lane < E) my_gl = __ldg(p.gc + item * (64 * E) + 63 * E + lane);
   // [I;0]: the operand that adds the value-block images, transposed, into the dK tile
   if (worker) {
     for (int i = tid; i < 16384 / 16; i += SG_THREADS) reinterpret_cast<uint4*>(sm.ident)[i] = make_uint4(0, 0, 0, 0);
-  }
-  __syncwarp();
-#pragma unroll
-  for (int it = 0; it < GATE_ITERS; ++it) {
-    const int idx = tid + it * SG_THREADS;
-    if (idx < 64 * E && worker) {
-      const int r = idx / E, e = idx % E;
-      const bool ok = r < rows;
-      const float gcv = raw_gc[it] * LOG2E;
-      const float k2v = ok ? raw_k2[it] : 0.f, q2v = ok ? raw_q2[it] : 0.f;
-      const float eg = sexp2(gcv);
-      sm.ga[r * ES + e] = k2v * eg;
-      sm.gcq[r * ES + e] = p.scale * q2v * eg;
-    }
-  }
-  if (tid < E) sm.flag[tid] = raw_gl * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
-  if (tid < E * 4) sm.red[tid] = 0.f;
-  if (t >= rows) {                                   // token rows past the end of a ragged chunk contribute nothing
-#pragma unroll
-    for (int j = 0; j < 32; ++j) kw[j] = 0u;
   }
   __syncthreads();                                     // the zeroed operand before its diagonal
   if (tid < 64) *reinterpret_cast<uint16_t*>(sm.ident + img_off(tid, tid, 128, 2048)) = 0x3F80;   // bf16 1.0
   fence_async_smem();
   tc_fence_before();
-  __syncthreads();                                     // gate tables, flags, barriers, operand and the tensor-memory address are visible
+  __syncthreads();                                     // barriers, operand and the tensor-memory address are visible
   tc_fence_after();
+  // From here the two extra warps run on their own.  The workers' global loads have been travelling since before the two
+  // barriers above; the workers now turn them into the gate tables and meet at a barrier of their own, while the tensor
+  // core is already adding the value-block images and forming the first P tiles (which need no gate).
+  const uint32_t fmask = __ballot_sync(0xffffffffu, !worker && lane < E && my_gl * LOG2E >= DD_MIN_LOG2_DECAY);
+  if (worker) {
+#pragma unroll
+    for (int it = 0; it < GATE_ITERS; ++it) {
+      const int idx = tid + it * SG_THREADS;
+      if (idx < 64 * E) {
+        const int r = idx / E, e = idx % E;
+        const bool ok = r < rows;
+        const float gcv = raw_gc[it] * LOG2E;
+        const float k2v = ok ? raw_k2[it] : 0.f, q2v = ok ? raw_q2[it] : 0.f;
+        const float eg = sexp2(gcv);
+        sm.ga[r * ES + e] = k2v * eg;
+        sm.gcq[r * ES + e] = p.scale * q2v * eg;
+      }
+    }
+    if (tid < E) sm.flag[tid] = raw_gl * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
+    if (tid < E * 4) sm.red[tid] = 0.f;
+    if (t >= rows) {                                   // token rows past the end of a ragged chunk contribute nothing
+#pragma unroll
+      for (int j = 0; j < 32; ++j) kw[j] = 0u;
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");     // the workers only
+  }
   const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
@@ -323,7 +333,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
 #pragma unroll 1
     for (int s = 0; s < STEPS; ++s) {
       const int vh = s & 1, e = s >> 1;
-      const bool tr = sm.flag[e] != 0;
+      const bool tr = (fmask >> e) & 1u;
       if (vh == 0 && e >= 2) {                             // P tile (e & 1) was last used by slice e - 2
         mbar_wait(&sm.bar_pread[e & 1], ((e >> 1) - 1) & 1, ctl, DEV_TIMEOUT_MMA);
       }
@@ -398,7 +408,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
     // half-slices of G for the first ring round of steps: their stage held a value-block image last
 #pragma unroll 1
     for (int s = 0; s < NS && s < STEPS; ++s) {
-      if (!sm.flag[s >> 1]) continue;
+      if (!((fmask >> (s >> 1)) & 1u)) continue;
       const int uses = (NVB - 1 - s % NS) / NS + 1;        // images that went through stage s % NS (0 if none)
       if (s % NS < NVB) mbar_wait(&sm.bar_pfree[s % NS], (uses - 1) & 1, ctl, DEV_TIMEOUT_LOAD);
       if (elect_one()) issue_g(s);
@@ -411,7 +421,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
       mbar_wait(&sm.bar_read[s % NS], (s / NS) & 1, ctl, DEV_TIMEOUT_LOAD);
       if (elect_one()) {
         issue_h(s + NS);
-        if (sm.flag[(s + NS) >> 1]) issue_g(s + NS);
+        if ((fmask >> ((s + NS) >> 1)) & 1u) issue_g(s + NS);
       }
       __syncwarp();
     }

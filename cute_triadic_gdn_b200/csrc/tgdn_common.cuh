@@ -79,7 +79,8 @@ constexpr long long WAIT_LIMIT_CYCLES = 1ll << 31;   // about a second of SM clo
 // Wait for `parity` of `bar`; gives up after WAIT_LIMIT_CYCLES, records `code` and raises the CTA's abort flag.
 // Spins on the non-parking probe: the parking form (try_wait) was measured to wake a waiter up to a microsecond after
 // the barrier flipped, which is as long as a whole pipeline phase here.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code,
+                                          long long limit_cycles = WAIT_LIMIT_CYCLES) {
 #pragma unroll 1
   for (int it = 0; it < 2048; ++it)
     if (mbar_test_wait(bar, parity)) return true;
@@ -88,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_test_wait(bar, parity)) return true;
     if ((it & 63u) == 0u) {
       if (*ctl.abort) return false;
-      if (clock64() - start > WAIT_LIMIT_CYCLES) {
+      if (clock64() - start > limit_cycles) {
         *ctl.abort = 1;
         atomicCAS(ctl.status, DEV_OK, code);
         return false;

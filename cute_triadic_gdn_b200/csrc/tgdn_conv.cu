@@ -14,6 +14,7 @@
 
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
+#include "tgdn_kernels.h"
 
 namespace tgdn {
 
@@ -526,7 +527,7 @@ static int conv_check(const void* x, const void* weight, const void* y, const in
 static void conv_groups(int B, int T, int C, int ctas_per_sm, int waves, int* groups, int* tiles_per_group) {
   const int n_tiles = (T + CONV_TOK - 1) / CONV_TOK;
   const int64_t columns = static_cast<int64_t>((C + CONV_CH - 1) / CONV_CH) * B;      // CTAs per token group
-  int64_t g = static_cast<int64_t>(waves) * ctas_per_sm * 148 / columns;
+  int64_t g = static_cast<int64_t>(waves) * ctas_per_sm * tgdn_sm_count() / columns;   // 148 on a B200 (and without a device)
   if (g > n_tiles / 8) g = n_tiles / 8;
   if (g < 1) g = 1;
   *tiles_per_group = static_cast<int>((n_tiles + g - 1) / g);

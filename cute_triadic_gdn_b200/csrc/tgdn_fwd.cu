@@ -542,9 +542,6 @@ static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
   return tgdn_cuda_error(cudaGetLastError());
 }
 
-static int tgdn_fwd_variant = 0;
-// Picks an alternative launch configuration of the forward recurrence (0 = default); for configuration sweeps.
-extern "C" void tgdn_tune_fwd(int variant) { tgdn_fwd_variant = variant; }
 
 extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const float* k2, const float* q2,
                               const float* beta, const float* gc, const void* AP, float scale, const int32_t* doc_offsets,
@@ -577,10 +574,7 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
     case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 4: return launch_fwd<4, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 8:
-      if (tgdn_fwd_variant == 1) return launch_fwd<8, 8, 2, 1, 2>(mk, mq, mk2, mq2, p, s);
-      if (tgdn_fwd_variant == 2) return launch_fwd<8, 8, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
-      return launch_fwd<8, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 8: return launch_fwd<8, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     default: return TGDN_ERR_SHAPE;

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/tgdn.h"
+#include "../../include/tgdn_selftest.h"
 
 // -(1000 + e) for a CUDA runtime error, 0 for cudaSuccess.
 int tgdn_cuda_error(cudaError_t e);

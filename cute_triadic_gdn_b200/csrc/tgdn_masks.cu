@@ -215,7 +215,9 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
     const int rr = idx / E, e = idx % E;
     const float up = sm.gc2[(rr & ~15) * E + e] - sm.gc2[idx];   // >= 0 when gc does not increase
-    if (!(up <= 100.f) || up < 0.f) sm.steep = 1;                // too steep, not monotone, or NaN
+    // too steep, NaN, or not monotone: a log gate above zero anywhere in the chunk makes gc rise from one row to the
+    // next, and the factorised form (which clamps its first factor at one) would then be wrong for rows of later blocks
+    if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[idx] > sm.gc2[idx - E])) sm.steep = 1;
     sm.hd[idx] = fast_exp2(up) * sm.k2[idx];
   }
 

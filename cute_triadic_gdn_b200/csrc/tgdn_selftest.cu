@@ -114,9 +114,38 @@ __global__ void __launch_bounds__(128) selftest_tma_kernel(const __grid_constant
   for (int i = tid; i < 8192 + bulk_bytes; i += 128) out[i] = smem[i];
 }
 
+// A CTA of two warps waits, with a short limit, for a barrier that nothing will ever arrive at: both warps must give up,
+// the status word must read DEV_TIMEOUT_LOAD, the second warp (which starts waiting later) must see the abort flag of
+// the first, and the kernel must end normally.  This is the path every production kernel takes when a pipeline stalls.
+__global__ void __launch_bounds__(64) selftest_wait_kernel(long long limit_cycles, int* status, int* out) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_s;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); abort_s = 0; }
+  __syncthreads();
+  WaitCtl ctl{&abort_s, status};
+  const long long t0 = clock64();
+  const bool ok = mbar_wait(&bar, 0, ctl, DEV_TIMEOUT_LOAD, limit_cycles);
+  const long long waited = clock64() - t0;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    out[0] = ok ? 1 : 0;                 // 0: the wait gave up
+    out[1] = abort_s;                    // 1: the CTA's abort flag is up
+    out[2] = waited > 0x7fffffffLL ? 0x7fffffff : static_cast<int>(waited);
+  }
+}
+
 }  // namespace tgdn
 
 using namespace tgdn;
+
+extern "C" int tgdn_selftest_wait(long long limit_cycles, int* out3, void* stream) {
+  if (!out3) return TGDN_ERR_NULL;
+  if (limit_cycles < 1 || limit_cycles > (1ll << 28)) return TGDN_ERR_SHAPE;      // a test must not hold a GPU: at most ~0.15 s
+  if (!tgdn_check_device()) return TGDN_ERR_DEVICE;
+  selftest_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, tgdn_status_word(), out3);
+  return tgdn_cuda_error(cudaGetLastError());
+}
+
 
 extern "C" int tgdn_selftest_mma(const void* A, const void* B, void* D, int M, int N, int K, int layout_a, int layout_b,
                                  void* stream) {

@@ -19,24 +19,33 @@ import torch
 from . import _lib
 
 CHUNK = 64
+HEAD_DIM = 128
 SUPPORTED_E = (1, 2, 4, 8, 12, 16)
 
 
 def _check(q, k, v, k2, q2, g, beta, packed=False):
+    """Shapes, dtypes, contiguity and device of the seven inputs; an AssertionError names the first thing that is off (the
+    reference raises the same error class for the same conditions: ops/gdn_joint.py:235-249)."""
+    tensors = dict(q=q, k=k, v=v, k2=k2, q2=q2, g=g, beta=beta)
+    assert q.ndim == 4, f"q: expected (B, T, H, 128), got {tuple(q.shape)}"
     B, T, H, D = q.shape
-    E = k2.shape[-1]
-    assert q.shape == k.shape and v.shape[:3] == q.shape[:3], "q, k, v must be (B, T, H, D)"
-    assert D == 128 and v.shape[-1] == 128, f"head dim must be 128 (got {D}, {v.shape[-1]})"
-    assert T > 0 and (packed or T % CHUNK == 0), f"T must be a multiple of {CHUNK} (got {T})"
-    assert E > 0, f"E must be positive (got E={E})"
-    assert k2.shape == q2.shape == g.shape == (B, T, H, E), "k2, q2, g must be (B, T, H, E)"
-    assert beta.shape == (B, T, H), "beta is one write strength per head: (B, T, H)"
-    for n, t in (("q", q), ("k", k), ("v", v), ("k2", k2), ("q2", q2), ("g", g), ("beta", beta)):
-        assert t.is_contiguous(), f"{n} must be contiguous"
-        assert t.is_cuda and t.device == q.device, f"{n} must be on the same CUDA device as q"
-    assert q.dtype == k.dtype == v.dtype == torch.bfloat16, "q, k, v must be bf16"
-    for n, t in (("k2", k2), ("q2", q2), ("g", g), ("beta", beta)):
-        assert t.dtype == torch.float32, f"{n} must be f32"
+    assert D == HEAD_DIM, f"q: the head dimension must be {HEAD_DIM}, got {D}"
+    for name in ("k", "v"):
+        assert tuple(tensors[name].shape) == (B, T, H, HEAD_DIM), \
+            f"{name}: expected {(B, T, H, HEAD_DIM)} like q, got {tuple(tensors[name].shape)}"
+    assert T >= 1, "the sequence is empty"
+    assert packed or T % CHUNK == 0, f"T = {T}: rows without cu_seqlens must hold whole chunks of {CHUNK} tokens"
+    E = k2.shape[-1] if k2.ndim == 4 else 0
+    assert E >= 1, f"k2: expected (B, T, H, E) with E >= 1, got {tuple(k2.shape)}"
+    for name in ("k2", "q2", "g"):
+        assert tuple(tensors[name].shape) == (B, T, H, E), \
+            f"{name}: expected {(B, T, H, E)}, got {tuple(tensors[name].shape)}"
+    assert tuple(beta.shape) == (B, T, H), f"beta: expected {(B, T, H)} (one write strength per head), got {tuple(beta.shape)}"
+    for name, t in tensors.items():
+        want = torch.bfloat16 if name in ("q", "k", "v") else torch.float32
+        assert t.dtype == want, f"{name}: dtype {t.dtype}, expected {want}"
+        assert t.is_cuda and t.device == q.device, f"{name}: every input must live on q's CUDA device"
+        assert t.is_contiguous(), f"{name}: not contiguous"
 
 
 def _check_device_and_e(q, E):
@@ -72,8 +81,10 @@ def _run_masks(q, k, k2, q2, g, beta, scale, token_map, gc=None):
     return gc_out, AP, Pm
 
 
-def _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, save, chunk_starts=None, token_map=None):
-    """Forward recurrence: (o, h, W, U); h, W, U are None unless save."""
+def _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, save, chunk_starts=None, token_map=None, state_in=None,
+                 state_out=None):
+    """Forward recurrence: (o, h, W, U); h, W, U are None unless save.  state_in / state_out: optional f32
+    (sequences, H, E, 128, 128) tensors holding the recurrent state before the first and after the last token."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
     o = torch.empty_like(v)
@@ -86,10 +97,11 @@ def _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, save, chunk_starts=None, 
         U = torch.empty((B, NC, H, CHUNK, 128), dtype=torch.bfloat16, device=dev)
     n_docs = chunk_starts.numel() - 1 if chunk_starts is not None else 0
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib.tgdn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta),
-                                     _lib.ptr(gc), _lib.ptr(AP), float(scale), _lib.ptr(chunk_starts),
-                                     _lib.ptr(token_map), n_docs, B, T, H, E, NC, _lib.ptr(o), _lib.ptr(W), _lib.ptr(U),
-                                     _lib.ptr(h), _lib.stream_of(q)), "tgdn_fwd")
+        _lib.check(_lib.lib.tgdn_fwd_state(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta),
+                                           _lib.ptr(gc), _lib.ptr(AP), float(scale), _lib.ptr(chunk_starts),
+                                           _lib.ptr(token_map), n_docs, B, T, H, E, NC, _lib.ptr(o), _lib.ptr(W),
+                                           _lib.ptr(U), _lib.ptr(h), _lib.ptr(state_in), _lib.ptr(state_out),
+                                           _lib.stream_of(q)), "tgdn_fwd_state")
     return o, h, W, U
 
 
@@ -202,8 +214,14 @@ class _JointKernels(torch.autograd.Function):
                 *([None] * (len(ctx.needs_input_grad) - 7)))
 
 
-def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, reference=False):
+def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, reference=False, *, initial_state=None,
+                    output_final_state=False):
     """Triadic GDN with autograd for all seven tensor inputs, on the sm_100a kernels.
+
+    Inference that continues a sequence (no counterpart in the reference, whose forward always starts from zero):
+    `initial_state` is an f32 (sequences, H, E, 128, 128) tensor, sequences = batch rows or documents, holding S_e as
+    [key row][value column]; with `output_final_state=True` the call returns (o, final_state) in the same form.  Both are
+    forward-only: they are rejected when a gradient is required.
 
     With cu_seqlens the inputs are one packed row (1, T, ...): contiguous int32/int64 CUDA offsets that start at 0,
     end at T and strictly increase; document lengths are arbitrary and the state resets at every document start.
@@ -220,6 +238,22 @@ def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, refer
         from .joint_packing import prepare_documents
         chunk_starts, token_map = prepare_documents((q, k, v, k2, q2, g, beta), cu_seqlens)
     scale = q.shape[-1] ** -0.5 if scale is None else scale
-    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, k2, q2, g, beta)):
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, k2, q2, g, beta))
+    if initial_state is not None or output_final_state:
+        if needs_grad:
+            raise ValueError("initial_state / output_final_state are forward-only: run them under torch.no_grad()")
+        B, T, H, _ = q.shape
+        E = k2.shape[-1]
+        n_seq = B if cu_seqlens is None else cu_seqlens.numel() - 1
+        shape = (n_seq, H, E, 128, 128)
+        if initial_state is not None:
+            if tuple(initial_state.shape) != shape or initial_state.dtype != torch.float32 or initial_state.device != q.device:
+                raise ValueError(f"initial_state must be an f32 tensor of shape {shape} on the inputs' device")
+            initial_state = initial_state.contiguous()
+        final = torch.empty(shape, dtype=torch.float32, device=q.device) if output_final_state else None
+        gc, AP, _ = _run_masks(q, k, k2, q2, g, beta, float(scale), token_map)
+        o = _run_forward(q, k, v, k2, q2, beta, gc, AP, float(scale), False, chunk_starts, token_map, initial_state, final)[0]
+        return (o, final) if output_final_state else o
+    if needs_grad:
         return _JointKernels.apply(q, k, v, k2, q2, g, beta, float(scale), chunk_starts, token_map)
     return _kernel_forward(q, k, v, k2, q2, g, beta, float(scale), False, chunk_starts, token_map)[0]

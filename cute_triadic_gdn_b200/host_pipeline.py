@@ -13,12 +13,44 @@ same way along its documents, which are just as independent: token-balanced rang
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .joint_torch_ops import gdn_joint_call
 from .sharding import document_ranges
 
 _NAMES = ("q", "k", "v", "k2", "q2", "g", "beta")
+
+
+def bind_host_to_gpu(device_index):
+    """Pins the calling process to the CPU cores of the NUMA node its GPU hangs off, so that pinned buffers allocated
+    afterwards (first touch) and the copy engine's reads stay on that node.  One rank per GPU calls this before it
+    allocates its pinned tensors.  Returns what it found and did: {"bdf", "numa_node", "cpus", "bound"}; a host without
+    that information in sysfs (numa_node -1, containers) is left as it is."""
+    info = {"bdf": None, "numa_node": None, "cpus": None, "bound": False}
+    try:
+        pr = torch.cuda.get_device_properties(device_index)
+        info["bdf"] = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{info['bdf']}/numa_node") as fh:
+            node = int(fh.read().strip())
+        info["numa_node"] = node
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            text = fh.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        info["cpus"] = text
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info["bound"] = True
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        pass
+    return info
 
 
 def _check_host(t, name):
@@ -81,7 +113,12 @@ class HostPipeline:
             (sum(t.numel() * t.element_size() for t in self.grads_host) if self.backward else 0)
 
     def run(self, inputs, do=None):
-        """One step.  Returns (o_host, grads_host or None); the host buffers are reused by the next call."""
+        """One step.  Returns (o_host, grads_host or None), pinned host buffers that the next call reuses.
+
+        The call only ENQUEUES work: when it returns, the downloads into the returned buffers may still be running on the
+        pipeline's own stream.  torch's current stream is made to wait for them, so later GPU work is ordered correctly,
+        but the CPU must call `wait()` (or synchronise the current stream) before it reads the returned tensors, and
+        must be done with them before it calls `run` again."""
         if (do is not None) != self.backward:
             raise ValueError("`do` must be given exactly when the pipeline was built with one")
         dev = self.device
@@ -126,12 +163,19 @@ class HostPipeline:
         done = torch.cuda.Event()
         done.record(self.down)
         compute.wait_event(done)     # the step is complete, in stream order, when the last download is
+        self._done = done
         return self.o_host, self.grads_host
+
+    def wait(self):
+        """Blocks the calling CPU thread until the results of the last `run` are in the host buffers."""
+        done = getattr(self, "_done", None)
+        if done is not None:
+            done.synchronize()
 
 
 def gdn_joint_host(q, k, v, k2, q2, g, beta, do=None, *, scale=None, slices=None, device=None, cu_seqlens=None):
     """One-shot convenience wrapper around `HostPipeline` (allocates its buffers on every call)."""
     pipe = HostPipeline((q, k, v, k2, q2, g, beta), do, scale=scale, slices=slices, device=device, cu_seqlens=cu_seqlens)
     o, grads = pipe.run((q, k, v, k2, q2, g, beta), do)
-    torch.cuda.current_stream(pipe.device).synchronize()
+    pipe.wait()
     return o, grads

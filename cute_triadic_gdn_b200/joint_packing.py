@@ -15,9 +15,11 @@ NC_BUCKET = 16
 
 
 def chunk_capacity(tokens, documents):
-    """sum(ceil(len_i / 64)) <= ceil(tokens / 64) + documents - 1, rounded up to a multiple of 16."""
-    exact = (tokens + CHUNK - 1) // CHUNK + documents - 1
-    return -(-exact // NC_BUCKET) * NC_BUCKET
+    """Entries of the chunk map of a packed row.  N documents over T tokens need at most ceil(T / 64) + N - 1 chunks (every
+    document but one can end in a partial chunk); the count is rounded up to the next multiple of 16 so that it takes few
+    distinct values from batch to batch.  Same number as the reference's (ops/joint_packing.py:16-20) and tgdn_chunk_capacity."""
+    worst = -(-tokens // CHUNK) + documents - 1
+    return NC_BUCKET * (-(-worst // NC_BUCKET))
 
 
 @custom_op("tgdn_b200::joint_metadata", mutates_args=(), device_types="cuda")
@@ -36,32 +38,33 @@ def _metadata(cu_seqlens: torch.Tensor, tokens: int) -> tuple[torch.Tensor, torc
 
 
 @_metadata.register_fake
-def _metadata_fake(cu_seqlens, tokens):
-    documents = cu_seqlens.numel() - 1
-    capacity = chunk_capacity(tokens, documents)
-    return (cu_seqlens.new_empty(documents + 1, dtype=torch.int32),
-            cu_seqlens.new_empty((3, capacity), dtype=torch.int32),
-            cu_seqlens.new_empty(1, dtype=torch.bool))
+def _metadata_shapes(cu_seqlens, tokens):
+    n = cu_seqlens.numel() - 1
+    like = cu_seqlens.new_empty
+    return like(n + 1, dtype=torch.int32), like((3, chunk_capacity(tokens, n)), dtype=torch.int32), like(1, dtype=torch.bool)
 
 
 def _validate(inputs, cu_seqlens):
-    q = inputs[0]
-    if q.shape[0] != 1 or q.shape[1] <= 0:
-        raise ValueError("cu_seqlens requires a nonempty packed row: B=1, T>0")
+    """What can be checked without reading the offsets: a ValueError for the conditions the reference rejects
+    (ops/joint_packing.py:38-49).  The values themselves are checked on the device."""
+    row = inputs[0]
+    if row.shape[0] != 1 or row.shape[1] < 1:
+        raise ValueError(f"a packed row has shape (1, T, ...) with T >= 1; got {tuple(row.shape)}")
     if cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
-        raise ValueError("cu_seqlens must be a vector with at least two offsets")
-    if cu_seqlens.dtype not in (torch.int32, torch.int64):
-        raise ValueError("cu_seqlens must have dtype int32 or int64")
-    if cu_seqlens.device != q.device or not cu_seqlens.is_contiguous():
-        raise ValueError("cu_seqlens must be contiguous and on the input device")
-    if q.shape[1] > 2 ** 31 - 1:
-        raise ValueError("packed token offsets must fit int32")
+        raise ValueError("cu_seqlens: a vector of document offsets, at least [0, T]")
+    if cu_seqlens.dtype != torch.int32 and cu_seqlens.dtype != torch.int64:
+        raise ValueError(f"cu_seqlens: int32 or int64 offsets, got {cu_seqlens.dtype}")
+    if not cu_seqlens.is_contiguous() or cu_seqlens.device != row.device:
+        raise ValueError("cu_seqlens: must be contiguous and live on the device of the inputs")
+    if row.shape[1] >= 2 ** 31:
+        raise ValueError("a packed row is limited to 2^31 - 1 tokens (offsets are 32-bit on the device)")
 
 
 def prepare_documents(inputs, cu_seqlens):
-    """Validate the offsets and build (chunk offsets per document, chunk map) on the device; tokens are not copied."""
+    """(first chunk of every document, chunk map) of a packed row, built on the device from the offsets; no token is
+    copied and nothing is read back.  Offsets that do not start at 0, end at T and strictly increase trip a device-side
+    assertion, as in the reference (ops/joint_packing.py:52-62)."""
     _validate(inputs, cu_seqlens)
-    q = inputs[0]
-    offsets, mapping, valid = _metadata(cu_seqlens, q.shape[1])
+    offsets, mapping, valid = _metadata(cu_seqlens, inputs[0].shape[1])
     torch._assert_async(valid, "cu_seqlens must start at 0, end at T, and strictly increase")
     return offsets, mapping

@@ -48,38 +48,46 @@ def _joint_bwd_fake(saved, do, scale, chunk_starts=None, token_map=None):
             torch.empty_like(g), torch.empty_like(beta)]
 
 
-def _setup(ctx, inputs, output):
-    q, k, v, k2, q2, g, beta, scale, chunk_starts, token_map = inputs
-    _, gc, AP, Pm, h, W, U = output
+def _remember(ctx, inputs, output):
+    """Keeps what the backward op reads.  The op returns the output first and its intermediates after it; those are not
+    differentiable, and autograd is told not to conjure zero gradients for them (each would be a tensor as large as the
+    intermediate itself, on every backward)."""
+    *seven, scale, chunk_starts, token_map = inputs
+    q, k, _, k2, q2, g, beta = seven
+    o, *aux = output
+    gc, AP, Pm, h, W, U = aux
     ctx.save_for_backward(*_save_list(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, chunk_starts, token_map))
     ctx.scale = scale
-    ctx.mark_non_differentiable(*output[1:])
-    # without this autograd materialises a zero gradient for every auxiliary output on each backward
+    ctx.mark_non_differentiable(*aux)
     ctx.set_materialize_grads(False)
 
 
-def _backward(ctx, grads):
-    if grads[0] is None:
-        return (None,) * len(ctx.needs_input_grad)
-    # one read of saved_tensors: activation checkpointing (use_reentrant=False) unpacks each saved tensor exactly once
-    saved = ctx.saved_tensors
-    dq, dk, dv, dk2, dq2, dg, db = joint_bwd(list(saved[:-2]), grads[0].contiguous(), ctx.scale, saved[-2], saved[-1])
-    return (dq, dk, dv, dk2, dq2, dg, db, None, None, None)[:len(ctx.needs_input_grad)]
+def _differentiate(ctx, grads):
+    n_inputs = len(ctx.needs_input_grad)
+    do = grads[0]
+    if do is None:                                   # the output was not used
+        return (None,) * n_inputs
+    # ctx.saved_tensors is read exactly once: under activation checkpointing (use_reentrant=False) every read unpacks, and a
+    # second one would re-run the forward
+    kept = ctx.saved_tensors
+    *tensors, chunk_starts, token_map = kept
+    seven = joint_bwd(list(tensors), do.contiguous(), ctx.scale, chunk_starts, token_map)
+    return (*seven, *([None] * (n_inputs - 7)))
 
 
-register_autograd("tgdn_b200::joint_fwd", _backward, setup_context=_setup)
+register_autograd("tgdn_b200::joint_fwd", _differentiate, setup_context=_remember)
 
 
 def gdn_joint_call(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None):
-    """Traceable Triadic GDN for training; sm_100, E=1/2/4/8/12/16, head dim 128.
-
-    Same inputs and packed-document contract as `chunk_gdn_joint`.  Inputs are made contiguous here; document metadata
-    is built on the device; inputs and outputs are not repacked.
-    """
-    q, k, v, k2, q2, g, beta = (t.contiguous() for t in (q, k, v, k2, q2, g, beta))
-    scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    """Triadic GDN for training, as ONE custom-op node (so that torch.compile does not look inside): same arguments and
+    packed-row rules as `chunk_gdn_joint`.  Unlike that function this one accepts non-contiguous inputs (it makes them
+    contiguous), like the reference's entry of the same name (ops/joint_torch_ops.py:83-95).  sm_100 only,
+    E in {1, 2, 4, 8, 12, 16}, head dimension 128."""
+    seven = [t.contiguous() for t in (q, k, v, k2, q2, g, beta)]
+    if scale is None:
+        scale = seven[0].shape[-1] ** -0.5
     chunk_starts = token_map = None
     if cu_seqlens is not None:
         from .joint_packing import prepare_documents
-        chunk_starts, token_map = prepare_documents((q, k, v, k2, q2, g, beta), cu_seqlens)
-    return joint_fwd(q, k, v, k2, q2, g, beta, scale, chunk_starts, token_map)[0]
+        chunk_starts, token_map = prepare_documents(seven, cu_seqlens)
+    return joint_fwd(*seven, float(scale), chunk_starts, token_map)[0]

@@ -71,7 +71,9 @@ int tgdn_conv_bwd(const void* x, const void* weight, const void* dy, void* dx, v
  * Limit: tgdn_conv_bwd_scratch_bytes(B, T, C) must not exceed that size, otherwise TGDN_ERR_STATIC_LIMIT is returned
  * and nothing is launched.  The first call on each device looks up the array's device address (make it outside any
  * stream capture); the array is shared by all calls on a device, so calls that overlap on the GPU race with each other.
- * Neither this call nor anything under it allocates or frees memory.
+ * After the first call on a device (a warm-up that loads the library's CUDA module with its array and looks the address
+ * up, which the CUDA runtime may answer with allocations of its own), neither this call nor anything under it allocates
+ * or frees memory.
  * No counterpart in the reference (its wrappers always allocate with torch). */
 int tgdn_conv_bwd_static(const void* x, const void* weight, const void* dy, void* dx, void* dw, const int32_t* cu_seqlens,
                          int n_docs, int B, int T, int C, int64_t stride_b, int64_t stride_t, int64_t dy_stride_b,
@@ -157,16 +159,6 @@ int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, const void* dU
                     const void* dkq, const float* da, const float* dc, const float* dd, const float* dr, float scale,
                     const int32_t* chunk_map, int B, int T, int H, int E, int NC, void* dq, void* dk, float* dk2,
                     float* dq2, float* dg, float* dbeta, void* stream);
-
-/* ---- tcgen05 / TMA self-tests (used by the test-suite only) -------------------------------------------------------
- * D (128, N) f32 = A (M, K) * B (K, N) with bf16 operands staged in shared memory in the given layouts
- * (0 = 128B-swizzled K-major, 1 = 128B-swizzled MN-major, 2 = plain K-major, 3 = plain MN-major).
- * No counterpart in the reference. */
-int tgdn_selftest_mma(const void* A, const void* B, void* D, int M, int N, int K, int layout_a, int layout_b, void* stream);
-/* Returns the shared-memory image (8192 bytes) of one 64x64 128B-swizzled tile load of a (B,T,H,128) bf16 tensor at
- * (batch, tok0, head, col0), followed by bulk_bytes copied by a 1-D bulk copy.  No counterpart in the reference. */
-int tgdn_selftest_tma(const void* x, int B, int T, int H, int col0, int head, int tok0, int batch, const void* bulk_src,
-                      int bulk_bytes, void* out, void* stream);
 
 #ifdef __cplusplus
 }

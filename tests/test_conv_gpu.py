@@ -55,6 +55,16 @@ def test_conv_shapes(B, T, C, act, docs):
     _check(x, w, act, dy, cu)
 
 
+def test_conv_at_the_channel_count_of_the_triadic_layer():
+    """C = 32 * (3 * 128 + 2 * 12) = 13056 channels with SiLU on the first 12288, packed documents, a few hundred tokens."""
+    C, act, T = 13056, 12288, 300
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(1, T, C, generator=g).to(torch.bfloat16)
+    w = (0.5 * torch.randn(C, 4, generator=g)).to(torch.bfloat16)
+    dy = torch.randn(1, T, C, generator=g).to(torch.bfloat16)
+    _check(x, w, act, dy, torch.tensor([0, 1, 70, 71, 200, 300], dtype=torch.int32))
+
+
 def test_conv_strided_input_and_linearity():
     g = torch.Generator().manual_seed(3)
     big = torch.randn(2, 300, 512, generator=g).to(torch.bfloat16).cuda()

@@ -109,3 +109,23 @@ def test_steep_decay_takes_the_direct_mask_gradient_path(E):
     o_ker, g_ker = run(chunk_gdn_joint, inputs, do, None)
     assert _lib.device_status() == 0
     compare(o_ker, g_ker, o_ref, g_ref)
+
+
+@pytest.mark.parametrize("E", [2, 8])
+def test_log_gates_above_zero_follow_the_recurrence(E):
+    """The contract, as in the reference, is g <= 0 (the log of a decay).  A gate above zero makes the chunk-local cumulative
+    gate rise from one row to the next; the kernels must then leave their factorised decay tables (which would clamp such
+    a factor at one without a word) and evaluate exp(gc_t - gc_s) as it is, like the reference's kernels, which gives the
+    token-by-token recurrence S_e <- exp(g_te) S_e itself.  (The reference's torch path clamps that factor in its masks,
+    cute_triadic_gdn/ops/gdn_joint.py:54, and so leaves the recurrence for such inputs; the definition is the yardstick here.)"""
+    B, T, H = 1, 128, 2
+    inputs = list(orc.make_inputs(B, T, H, E, seed=950 + E, dist="mild"))
+    g = inputs[5].clone()
+    g[:, 16] = 0.4                                              # the case of a single raised gate at a block boundary
+    g[:, 37, :, 0] = 0.25
+    inputs[5] = g
+    do = orc.make_grad_output((B, T, H, 128), 7)
+    o_ref, g_ref = orc.reference_with_grads(orc.sequential_reference, inputs, do, dtype=torch.float64)
+    o_ker, g_ker = run(chunk_gdn_joint, inputs, do, None)
+    assert _lib.device_status() == 0
+    compare(o_ker, g_ker, o_ref.float(), [x.float() for x in g_ref])

@@ -49,6 +49,29 @@ def test_static_scratch_variant_matches_two_calls_in_a_row():
     assert _lib.device_status() == 0
 
 
+def test_static_scratch_variant_allocates_nothing_after_its_first_call():
+    """The point of the entry: once the first call on the device has loaded the library's module and looked the array up,
+    a call leaves the amount of free device memory exactly as it found it (the caller's own tensors are made before)."""
+    g = torch.Generator().manual_seed(5)
+    B, T, C, act = 1, 700, 256, 128
+    x = torch.randn(B, T, C, generator=g).to(torch.bfloat16).cuda()
+    w = (0.5 * torch.randn(C, 4, generator=g)).to(torch.bfloat16).cuda()
+    dy = torch.randn(B, T, C, generator=g).to(torch.bfloat16).cuda()
+    dx, dw = torch.empty_like(x), torch.empty_like(w)
+    L, p = _lib.lib, _lib.ptr
+    stream = _lib.stream_of(x)
+    call = lambda: L.tgdn_conv_bwd_static(p(x), p(w), p(dy), p(dx), p(dw), None, 0, B, T, C, x.stride(0), x.stride(1),
+                                          dy.stride(0), dy.stride(1), act, stream)
+    assert call() == 0                                        # warm-up: module load and address lookup
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert _lib.device_status() == 0
+
+
 def test_static_scratch_variant_refuses_oversized_problems():
     L = _lib.lib
     fake = ctypes.c_void_p(4096)
