@@ -38,6 +38,7 @@ WORKLOADS = {
     "small": (2, 1024, 4, 8, True),
     "c4": (1, 32768, 32, 12, True),     # the core behind the conv pre-pass: eight documents of 4096 tokens (PACKED below)
     "prof": (2, 8192, 16, 8, True),     # 4096 (chunk, head) items, a few GB: the size used for ncu captures
+    "prof16": (2, 4096, 16, 16, True),  # 2048 items with sixteen slices, a few GB: the second ncu size
 }
 
 
@@ -59,8 +60,8 @@ KERNEL_U = {
 # between the two captures, linearly in E (the saved states are E * 32 KB per item), so other E are interpolated.
 NCU_DRAM_BYTES_PER_ITEM = {
     # kernel: (bytes per item at E = 8, at E = 16); filled from profiles/core_kernels_prof_workload.md
-    "masks": (57.9e3, 64.0e3), "fwd": (389.6e3, 690e3), "rec": (415.0e3, 560e3), "sg": (665.3e3, 1050e3),
-    "mat": (210.2e3, 250e3),
+    "masks": (0.234e9 / 4096, 0.118e9 / 2048), "fwd": (1.540e9 / 4096, 1.569e9 / 2048), "rec": (1.164e9 / 4096, 0.563e9 / 2048),
+    "sg": (2.067e9 / 4096, 1.599e9 / 2048), "mat": (0.857e9 / 4096, 0.507e9 / 2048),
 }
 
 # DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)

@@ -22,8 +22,9 @@
 // (p) is off the dependent chain of the chunk: it is issued behind (c), completes while the epilogue of (c) reads Z,
 // and is read out of tensor memory while (d) runs.
 //
-// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows (requested under MMA
-// (a)); there are no shared gate tables.
+// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows, which arrive with the
+// chunk's tiles by TMA as three dense 64 x E tiles (for E >= 12, where shared memory is full, each thread loads its rows
+// from global memory instead); there are no shared gate tables.
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:59-533 (rec_kernel) and the (r*U) G^T product of
 // cute_triadic_gdn/kernels/sm100_joint_state_grads.py:373-378.  Same thread/column organisation as the forward
@@ -286,8 +287,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   };
 
   if (tid == 0) issue_loads(count - 1, 0);
-  uint4 u_next = load_u(count - 1), do_next = make_uint4(0, 0, 0, 0);
-  if (!krow) do_next = load_do(count - 1);
+  uint4 u_next = make_uint4(0, 0, 0, 0), do_next = make_uint4(0, 0, 0, 0);
+  if (krow) u_next = load_u(count - 1); else do_next = load_do(count - 1);
   if (count > 1) prefetch_rows(count - 2);
   uint32_t mma_phase = 0;
   {
@@ -327,10 +328,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
     // this chunk's row pieces were loaded while the previous one was processed; its dO operand image was written then too
-    const uint4 u_cur = u_next, do_cur = do_next;    // U row piece (all threads), dO row piece (Q-row threads): unpacked where used
+    const uint4 u_cur = u_next, do_cur = do_next;    // U row piece (K-row threads), dO row piece (Q-row threads): unpacked where used
     if (kstep + 1 < count) {                         // consumed during this chunk (dO image) and at the top of the next one
-      u_next = load_u(i - 1);
-      if (!krow) do_next = load_do(i - 1);
+      if (krow) u_next = load_u(i - 1); else do_next = load_do(i - 1);
     }
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
@@ -360,8 +360,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
     }
     __syncwarp();
-    // Under the MMA: this row's gate factors from its raw rows (in L2 since the previous chunk).  The Q-row threads, which
-    // have nothing to do in the epilogue of (a), also form r of their token row and build the operand Xu of (p) from it.
+    // Under the MMA: this row's gate factors from its raw rows, and (K-row threads, which would otherwise only wait for the
+    // MMA) the operand Xu of (p).
     float ga[E];                                     // K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
     float gr[E];                                     // K rows: r_e = k2 exp(gL - gc)
     float bt = 0.f;
@@ -369,57 +369,38 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int tl = min(t, max(rows, 1) - 1);
       const float* gcp = p.gc + item * (64 * E);
       const int64_t ro = (tok + tl) * p.H + h;
-      float gcr[E], k2r[E], gl[E];
       const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
+      float gcr[E], x2[E];
       if constexpr (C::TMA_GATES) {
         rec_lds_row<E>(gt + t * E, gcr);
-        rec_lds_row<E>(gt + 64 * E + t * E, k2r);
-        rec_lds_row<E>(gt + 63 * E, gl);
+        rec_lds_row<E>(gt + (krow ? 64 * E : 128 * E) + t * E, x2);
       } else {
         rec_ld_row<E>(gcp + t * E, gcr);
-        rec_ld_row<E>(p.k2 + ro * E, k2r);
-        rec_ld_row<E>(gcp + 63 * E, gl);
+        rec_ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
       }
       if (krow) {
+        float gl[E];
+        if constexpr (C::TMA_GATES) rec_lds_row<E>(gt + 63 * E, gl); else rec_ld_row<E>(gcp + 63 * E, gl);
         bt = __ldg(p.beta + ro);
         if (!live) bt = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float k2v = live ? k2r[e] : 0.f;
-          ga[e] = k2v * rexp2(gcr[e] * LOG2E);
-          gr[e] = k2v * rexp2((gl[e] - gcr[e]) * LOG2E);
-        }
-      } else {
-        // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
         float uv[CW];
         unpack_piece(u_cur, true, uv);
+        // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
         const uint32_t base = smem_u32(smem + C::OFF_XU) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-          const float re = live ? k2r[e] * rexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
+          const float k2v = live ? x2[e] : 0.f;
+          ga[e] = k2v * rexp2(gcr[e] * LOG2E);
+          gr[e] = k2v * rexp2((gl[e] - gcr[e]) * LOG2E);
           const int n0 = wg * TPC + e * CW;
-          store_row_image(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, uv, re);
+          store_row_image(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, uv, gr[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          ga[e] = live ? p.scale * x2[e] * rexp2(gcr[e] * LOG2E) : 0.f;
           gr[e] = 0.f;
         }
-        // only now the q2 row (a pinned load, which stays behind the stores above): these threads have the whole epilogue
-        // of (a) to wait for it, and the registers of the k2 row are free again
-        float q2r[E];
-        const float* q2p = p.q2 + ro * E;
-        if constexpr (C::TMA_GATES) {
-          rec_lds_row<E>(gt + 128 * E + t * E, q2r);
-        } else if constexpr (E % 4 == 0) {
-#pragma unroll
-          for (int j = 0; j < E / 4; ++j) {
-            const uint4 x = ldg_pinned_v4(q2p + 4 * j);
-            q2r[4 * j] = __uint_as_float(x.x); q2r[4 * j + 1] = __uint_as_float(x.y);
-            q2r[4 * j + 2] = __uint_as_float(x.z); q2r[4 * j + 3] = __uint_as_float(x.w);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < E; ++j) q2r[j] = ldg_pinned_f32(q2p + j);
-        }
-#pragma unroll
-        for (int e = 0; e < E; ++e) ga[e] = live ? p.scale * q2r[e] * rexp2(gcr[e] * LOG2E) : 0.f;
       }
       if (tid < E) {
         dtab[tid] = rexp2((C::TMA_GATES ? gt[63 * E + tid] : __ldg(gcp + 63 * E + tid)) * LOG2E);

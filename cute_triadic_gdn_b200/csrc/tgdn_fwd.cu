@@ -114,6 +114,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
   using C = FwdCfg<E, CW, NCH, STAGES>;
   constexpr int TPC = C::TPC, VC = C::VC;
+  constexpr bool LATE_R = C::TMA_GATES && E >= 12;   // form r_e after the epilogue of (1) (register pressure at many slices)
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -346,7 +347,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
         lds_row<E>(gt + t * E, gcr);
         lds_row<E>(gt + (krow ? 64 * E : 128 * E) + t * E, x2);
-        if (krow) lds_row<E>(gt + 63 * E, gl);
+        if (krow && !LATE_R) lds_row<E>(gt + 63 * E, gl);
       } else {
         ld_row<E>(gcp + t * E, gcr);
         ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
@@ -365,7 +366,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         for (int e = 0; e < E; ++e) {
           const float k2v = live ? x2[e] : 0.f;
           ga[e] = k2v * fexp2(gcr[e] * LOG2E);
-          gr[e] = k2v * fexp2((gl[e] - gcr[e]) * LOG2E);
+          if constexpr (!LATE_R) gr[e] = k2v * fexp2((gl[e] - gcr[e]) * LOG2E);
         }
         if (!live) bt = 0.f;
       } else {
@@ -422,6 +423,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma[chain]);
     }
     __syncwarp();
+    if constexpr (LATE_R) {                          // r_e only now, from the gate tiles that are still in the stage: sixteen
+      if (krow) {                                    // registers fewer are live through the epilogue of (1)
+        const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
+        float gcr[E], k2r[E], gl[E];
+        lds_row<E>(gt + t * E, gcr);
+        lds_row<E>(gt + 64 * E + t * E, k2r);
+        lds_row<E>(gt + 63 * E, gl);
+#pragma unroll
+        for (int e = 0; e < E; ++e) gr[e] = live ? k2r[e] * fexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
+      }
+    }
     if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     chain_sync(chain);
     ++mma_phase;
@@ -573,7 +585,15 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
   switch (E) {
     case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 4: return launch_fwd<4, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 4: {
+      // One CTA per SM: the grid runs in whole waves.  Where a block of 32 value columns needs a second, partly filled wave
+      // and a block of 64 does not, the wider block wins although its chunks take a little longer (B=4, H=16: 256 CTAs on
+      // 148 SMs are two waves, 128 CTAs are one).
+      const long long sms = tgdn_sm_count(), seqs = static_cast<long long>(p.n_seq) * p.H;
+      const long long waves32 = (seqs * 4 + sms - 1) / sms, waves64 = (seqs * 2 + sms - 1) / sms;
+      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+      return launch_fwd<4, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    }
     case 8: return launch_fwd<8, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
