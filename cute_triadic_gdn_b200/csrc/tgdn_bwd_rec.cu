@@ -91,9 +91,13 @@ struct RecCfg {
   static constexpr int OFF_PM = OFF_GX + GX_BYTES;
   static constexpr int OFF_A = OFF_PM + STAGES * PM_BYTES;
   static constexpr int OFF_XU = OFF_A + STAGES * A_BYTES;
+  // per stage: the dO rows of the value block, which TMA writes straight into the operand image of Y, and the U rows,
+  // which TMA writes into the place where the operand image of dU is built later (every thread reads its piece of U
+  // before it overwrites that very piece with dU)
+  static constexpr int DOB = (DO_BYTES + 1023) & ~1023;
   static constexpr int OFF_DO = OFF_XU + (XU_BYTES < 8192 ? 8192 : XU_BYTES);
-  static constexpr int OFF_DU = OFF_DO + ((DO_BYTES + 1023) & ~1023);
-  static constexpr int OFF_DRP = OFF_DU + ((DO_BYTES + 1023) & ~1023);
+  static constexpr int OFF_DU = OFF_DO + STAGES * DOB;
+  static constexpr int OFF_DRP = OFF_DU + STAGES * DOB;
   static constexpr int DRP_FLOATS = NWG * 64 * ES;
   static constexpr int OFF_DT = OFF_DRP + DRP_FLOATS * 4;     // exp(gL) of this chunk and the store flags of the next: 2 x 16 words
   // raw gate rows of the chunk, per stage: gc, k2, q2 as 64 dense rows of E floats each, loaded by TMA where E is a
@@ -118,7 +122,9 @@ struct RecCtrl {
 template <int E, int VC, int NWG, int STAGES>
 __global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
 rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
-           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, RecParams p) {
+           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2,
+           const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_u,
+           const __grid_constant__ CUtensorMap map_du, RecParams p) {
   using C = RecCfg<E, VC, NWG, STAGES>;
   constexpr int REC_THREADS = C::THREADS;
   constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
@@ -184,7 +190,15 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     chunk_info(i, t0, rows);
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES);
+    // the stage's U / dU buffer may still be the source of a store of dU issued by this thread
+    bulk_wait_group_read();
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES + 2 * C::DO_BYTES);
+#pragma unroll
+    for (int jb = 0; jb < VC / 8; ++jb) {            // eight value columns x 64 rows = one 1 KB column block of the image
+      tma_load_4d(smem + C::OFF_DO + st * C::DOB + jb * 1024, &map_do, &ctrl.bar_load[st], vb * VC + jb * 8, h, t0, b);
+      tma_load_4d(smem + C::OFF_DU + st * C::DOB + jb * 1024, &map_u, &ctrl.bar_load[st], vb * VC + jb * 8, 0,
+                  static_cast<int>(item * 64), 0);
+    }
     if constexpr (C::TMA_GATES) {
       uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
       bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
@@ -212,6 +226,11 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_prefetch_4d(&map_q, 64, h, t0, b);
     bulk_prefetch(p.AP + item * (128 * 64), 16384);
     bulk_prefetch(p.Pm + item * (64 * 64), C::PM_BYTES);
+#pragma unroll
+    for (int jb = 0; jb < VC / 8; ++jb) {
+      tma_prefetch_4d(&map_do, vb * VC + jb * 8, h, t0, b);
+      tma_prefetch_4d(&map_u, vb * VC + jb * 8, 0, static_cast<int>(item * 64), 0);
+    }
   };
   auto prefetch_rows = [&](int i) {                          // the first warpgroup: what threads load themselves, for a later chunk -> L2
     if (wg != 0) return;
@@ -228,25 +247,16 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       prefetch_l2(p.gc + item * (64 * E) + t * E);
     }
   };
-  // This thread's row pieces of a chunk, one chunk ahead, as raw bf16: U (K-row threads use it for dr, Q-row threads turn
-  // it into the operand Xu) and, for Q-row threads, dO.  Unconditional from clamped addresses and masked at use.
-  auto load_piece = [&](const __nv_bfloat16* rp) {
+  // This thread's piece of a row of an operand image (i = t, j = v) that TMA filled: CW value columns as raw bf16
+  auto image_piece = [&](const uint8_t* img) {
+    const int v0 = wg * CW;
+    const uint8_t* src = img + (t >> 3) * 128 + (t & 7) * 16 + (v0 >> 3) * 1024 + (v0 & 7) * 2;
     if constexpr (CW == 8) {
-      return __ldg(reinterpret_cast<const uint4*>(rp));
+      return *reinterpret_cast<const uint4*>(src);
     } else {
-      const uint2 w = __ldg(reinterpret_cast<const uint2*>(rp));
+      const uint2 w = *reinterpret_cast<const uint2*>(src);
       return make_uint4(w.x, w.y, 0u, 0u);
     }
-  };
-  auto load_u = [&](int i) {
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    return load_piece(p.U + (item * 64 + t) * HEAD + vb * VC + wg * CW);
-  };
-  auto load_do = [&](int i) {
-    int t0, rows;
-    chunk_info(i, t0, rows);
-    const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
-    return load_piece(p.dO + ((tok + min(t, max(rows, 1) - 1)) * p.H + h) * HEAD + vb * VC + wg * CW);
   };
   auto unpack_piece = [&](const uint4& w, bool use, float* out) {
     const uint32_t rw[4] = {w.x, w.y, w.z, w.w};
@@ -286,9 +296,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     return __ldg(p.gc + item * (64 * E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
   };
 
-  if (tid == 0) issue_loads(count - 1, 0);
-  uint4 u_next = make_uint4(0, 0, 0, 0), do_next = make_uint4(0, 0, 0, 0);
-  if (krow) u_next = load_u(count - 1); else do_next = load_do(count - 1);
+  if (warp_u == 1 && elect_one()) issue_loads(count - 1, 0);   // the lane that issues every load and every store of this CTA
+  __syncwarp();
   if (count > 1) prefetch_rows(count - 2);
   uint32_t mma_phase = 0;
   {
@@ -299,16 +308,6 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
     for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
     store_state((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, zeros);
-    // the dO operand image of the first chunk processed; later ones are written a chunk ahead, by the Q-row threads
-    // while the K-row threads run the epilogue of (a)
-    if (!krow) {
-      int t0, rows;
-      chunk_info(count - 1, t0, rows);
-      float dov[CW];
-      unpack_piece(do_next, t < rows, dov);
-      const int v0 = wg * CW;
-      store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, dov, 1.f);
-    }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -327,11 +326,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* pm = smem + C::OFF_PM + st * C::PM_BYTES;
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
-    // this chunk's row pieces were loaded while the previous one was processed; its dO operand image was written then too
-    const uint4 u_cur = u_next, do_cur = do_next;    // U row piece (K-row threads), dO row piece (Q-row threads): unpacked where used
-    if (kstep + 1 < count) {                         // consumed during this chunk (dO image) and at the top of the next one
-      if (krow) u_next = load_u(i - 1); else do_next = load_do(i - 1);
-    }
+    uint8_t* doimg = smem + C::OFF_DO + st * C::DOB;     // dO rows of the value block: operand image of Y, by TMA
+    uint8_t* duimg = smem + C::OFF_DU + st * C::DOB;     // U rows by TMA, later the operand image of dU
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
@@ -347,7 +343,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       {
         const uint64_t da = make_desc(smem_u32(pm), 128, 1024, LAYOUT_PLAIN);       // Pm^T: MN-major over (i = t, j = s)
-        const uint64_t db = make_desc(smem_u32(smem + C::OFF_DO), 128, 1024, LAYOUT_PLAIN);
+        const uint64_t db = make_desc(smem_u32(doimg), 128, 1024, LAYOUT_PLAIN);
         constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -384,7 +380,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         bt = __ldg(p.beta + ro);
         if (!live) bt = 0.f;
         float uv[CW];
-        unpack_piece(u_cur, true, uv);
+        unpack_piece(image_piece(duimg), true, uv);
         // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
         const uint32_t base = smem_u32(smem + C::OFF_XU) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
@@ -413,7 +409,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_after();
     if (krow) {
       float du[CW], uv[CW];
-      unpack_piece(u_cur, true, uv);
+      unpack_piece(image_piece(duimg), true, uv);
       constexpr int EP = (8 / CW) < 1 ? 1 : (8 / CW) < E ? (8 / CW) : E;     // slices per piece of eight columns
       constexpr int NP = E / EP;
       float kg[2][EP * CW];
@@ -436,15 +432,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           drp[(wg * 64 + t) * ES + pc * EP + ee] = dot;
         }
       }
-      store_row_global(p.dU + (item * 64 + t) * HEAD + vb * VC + v0, du);
-      store_row_image(smem_u32(smem + C::OFF_DU) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, du, 1.f);
-    } else if (kstep + 1 < count) {
-      // Y has been read out of the dO operand image (its MMA is complete): the next chunk's image can replace it
-      int t0n, rowsn;
-      chunk_info(i - 1, t0n, rowsn);
-      float don[CW];
-      unpack_piece(do_next, t < rowsn, don);
-      store_row_image(smem_u32(smem + C::OFF_DO) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, don, 1.f);
+      // dU replaces this thread's piece of U in the image; the image then leaves for global memory by a TMA store
+      store_row_image(smem_u32(duimg) + (t >> 3) * 128 + (v0 >> 3) * 1024 + (t & 7) * 16 + (v0 & 7) * 2, du, 1.f);
     }
     fence_async_smem();
     tc_fence_before();
@@ -455,7 +444,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       tc_fence_after();
       {
         const uint64_t da = make_desc(smem_u32(am), 128, 1024, LAYOUT_PLAIN);         // A^T: MN-major over (i = t, j = s)
-        const uint64_t db = make_desc(smem_u32(smem + C::OFF_DU), 128, 1024, LAYOUT_PLAIN);
+        const uint64_t db = make_desc(smem_u32(duimg), 128, 1024, LAYOUT_PLAIN);
         constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
@@ -473,6 +462,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
+    if (warp_u == 1 && elect_one()) {                // dU (chunk layout) straight from its operand image
+#pragma unroll
+      for (int jb = 0; jb < VC / 8; ++jb)
+        tma_store_4d(&map_du, duimg + jb * 1024, vb * VC + jb * 8, 0, static_cast<int>(item * 64), 0);
+      bulk_commit_group();
+    }
+    __syncwarp();
     // meanwhile: the value-block partial of dr, summed over the warpgroups in a fixed order
     for (int idx = tid; idx < 64 * E; idx += REC_THREADS) {
       const int r = idx / E, e = idx % E;
@@ -494,7 +490,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         for (int c = 0; c < CW; ++c) xr[c] = bt * z[c];
         if (live) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
       } else {
-        unpack_piece(do_cur, live, xr);
+        unpack_piece(image_piece(doimg), live, xr);
       }
       // (p) reads the image of G that X is about to replace
       mbar_wait_spin(&ctrl.bar_p, kstep & 1, ctl, DEV_TIMEOUT_MMA);
@@ -590,6 +586,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
   }
+  if (warp_u == 1 && elect_one()) bulk_wait_group();   // the last store of dU reads shared memory of this CTA
+  __syncwarp();
   if (warp == 0) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
@@ -599,7 +597,7 @@ using namespace tgdn;
 
 template <int E, int VC, int NWG, int STAGES>
 static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
-                      const RecParams& p, cudaStream_t s) {
+                      const CUtensorMap& mdo, const CUtensorMap& mu, const CUtensorMap& mdu, const RecParams& p, cudaStream_t s) {
   using C = RecCfg<E, VC, NWG, STAGES>;
   static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
@@ -614,7 +612,7 @@ static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
+  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, mdo, mu, mdu, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -636,6 +634,13 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
   CUtensorMap mk, mq;
   if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
+  // dO (token layout) and U, dU (chunk layout: item * 64 + t rows of 128 columns) in boxes of 8 columns x 64 rows
+  const int64_t crows = static_cast<int64_t>(B) * NC * H * 64;
+  if (crows > 0x7fffffffLL) return TGDN_ERR_SHAPE;
+  CUtensorMap mdo, mu, mdu;
+  if ((rc = tgdn_make_token_map(&mdo, dO, B, T, H, 8, 64, 0))) return rc;
+  if ((rc = tgdn_make_token_map(&mu, U, 1, static_cast<int>(crows), 1, 8, 64, 0))) return rc;
+  if ((rc = tgdn_make_token_map(&mdu, dU, 1, static_cast<int>(crows), 1, 8, 64, 0))) return rc;
   CUtensorMap mk2 = mk, mq2 = mq;                   // placeholders where the gate rows are not loaded by TMA
   if (E % 4 == 0) {
     if ((rc = tgdn_make_gate_map(&mk2, k2, B, T, H, E))) return rc;
@@ -648,12 +653,12 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
               tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
-    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
-    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mk2, mq2, p, s);
-    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, mk2, mq2, p, s);
-    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, mk2, mq2, p, s);
+    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }
