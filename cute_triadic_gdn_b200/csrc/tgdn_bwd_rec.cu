@@ -85,34 +85,50 @@ struct RecCfg {
   static constexpr int GX_BYTES = NCOLS * 256;    // image (i = row 0..127, j = n'), SI = 128, SJ = 2048
   static constexpr int XU_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
   static constexpr int DO_BYTES = VC * 128;       // image (i = t, j = v), SI = 128, SJ = 1024
+  static constexpr int DOB = (DO_BYTES + 1023) & ~1023;
+  static constexpr int DRP_FLOATS = NWG * 64 * ES;
+  static constexpr int GT_FULL = 64 * E * 4;
+  static constexpr int LIMIT = STAGES == 1 ? 115712 : 232448;
+  // Shared memory of a layout with `nb` copies of Pm, A and the gate rows and the gate rows loaded by TMA or not
+  static constexpr int layout_bytes(int nb, bool gates) {
+    const int xu = XU_BYTES < 8192 ? 8192 : XU_BYTES;
+    const int upto_dt = STAGES * KQ_BYTES + GX_BYTES + nb * (PM_BYTES + A_BYTES) + xu + 2 * STAGES * DOB + DRP_FLOATS * 4;
+    const int off_gt = (upto_dt + 128 + 127) & ~127;
+    return off_gt + (gates ? nb * 3 * GT_FULL : 0) + 64 + 1024;
+  }
+  // With two stages, Pm, A and the gate rows get a second copy too where that fits.  Where it does not (sixteen slices),
+  // they stay single and are requested LATE: each is dead by the end of the epilogue of (c), and the next chunk's copies,
+  // requested right then on a barrier of their own, have the whole of (d) to arrive; only the K/Q tiles and the dO / U
+  // rows, which (d) and its epilogue still read, live in the stage.  Measured: the late scheme costs 12% at E = 4, where
+  // both fit, and gains 7% at E = 16, where it makes room for the gate rows in shared memory.
+  static constexpr bool GATES_OK = E % 4 == 0;
+  static constexpr bool LATE = STAGES == 2 && !(layout_bytes(2, GATES_OK) <= LIMIT);
+  static constexpr int NB = (STAGES == 2 && !LATE) ? 2 : 1;              // copies of Pm, A and the gate rows
+  static constexpr bool TMA_GATES = GATES_OK && layout_bytes(NB, true) <= LIMIT;
+  static constexpr int GT_BYTES = TMA_GATES ? GT_FULL : 0;
   static constexpr int OFF_KQ = 0;
   static constexpr int OFF_GX = OFF_KQ + STAGES * KQ_BYTES;
   // the 128-row descriptors over the 64-row Pm and A images read up to 8 KB past them: Pm is followed by A, A by Xu
   static constexpr int OFF_PM = OFF_GX + GX_BYTES;
-  static constexpr int OFF_A = OFF_PM + STAGES * PM_BYTES;
-  static constexpr int OFF_XU = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_A = OFF_PM + NB * PM_BYTES;
+  static constexpr int OFF_XU = OFF_A + NB * A_BYTES;
   // per stage: the dO rows of the value block, which TMA writes straight into the operand image of Y, and the U rows,
   // which TMA writes into the place where the operand image of dU is built later (every thread reads its piece of U
   // before it overwrites that very piece with dU)
-  static constexpr int DOB = (DO_BYTES + 1023) & ~1023;
   static constexpr int OFF_DO = OFF_XU + (XU_BYTES < 8192 ? 8192 : XU_BYTES);
   static constexpr int OFF_DU = OFF_DO + STAGES * DOB;
   static constexpr int OFF_DRP = OFF_DU + STAGES * DOB;
-  static constexpr int DRP_FLOATS = NWG * 64 * ES;
   static constexpr int OFF_DT = OFF_DRP + DRP_FLOATS * 4;     // exp(gL) of this chunk and the store flags of the next: 2 x 16 words
-  // raw gate rows of the chunk, per stage: gc, k2, q2 as 64 dense rows of E floats each, loaded by TMA where E is a
-  // multiple of 4 and shared memory allows; otherwise every thread loads its own rows from global memory
-  static constexpr int GT_FULL = 64 * E * 4;
+  // raw gate rows of the chunk: gc, k2, q2 as 64 dense rows of E floats each, loaded by TMA where E is a multiple of 4 and
+  // shared memory allows; otherwise every thread loads its own rows from global memory
   static constexpr int OFF_GT = (OFF_DT + 128 + 127) & ~127;
-  static constexpr int LIMIT = STAGES == 1 ? 115712 : 232448;
-  static constexpr bool TMA_GATES = E % 4 == 0 && OFF_GT + STAGES * 3 * GT_FULL + 64 + 1024 <= LIMIT;
-  static constexpr int GT_BYTES = TMA_GATES ? GT_FULL : 0;
-  static constexpr int OFF_CTRL = OFF_GT + STAGES * 3 * GT_BYTES;
+  static constexpr int OFF_CTRL = OFF_GT + NB * 3 * GT_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;
 };
 
 struct RecCtrl {
-  uint64_t bar_load[2];
+  uint64_t bar_load[2];      // K/Q tiles, dO and U rows of a stage (STAGES == 1: everything)
+  uint64_t bar_late;         // late scheme only: Pm, A and the gate rows of the chunk
   uint64_t bar_mma;
   uint64_t bar_p;
   uint32_t tmem_base;
@@ -157,6 +173,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (tid == 0) {
     mbar_init(&ctrl.bar_load[0], 1);
     mbar_init(&ctrl.bar_load[1], 1);
+    mbar_init(&ctrl.bar_late, 1);
     mbar_init(&ctrl.bar_mma, 1);
     mbar_init(&ctrl.bar_p, 1);
     mbar_fence_init();
@@ -185,36 +202,42 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       t0 = 0; rows = 0;
     }
   };
-  auto issue_loads = [&](int i, int st) {           // one thread: K/Q tiles, the A half of [A;PmA] and the Pm image of local chunk i
+  auto issue_late = [&](int i, int nb, uint64_t* bar) {   // one thread: the A half of [A;PmA], the Pm image and the gate rows of local chunk i -> copy nb
+    int t0, rows;
+    chunk_info(i, t0, rows);
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
+    if constexpr (C::TMA_GATES) {
+      uint8_t* gt = smem + C::OFF_GT + nb * 3 * C::GT_BYTES;
+      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, bar);
+      tma_load_4d(gt + C::GT_BYTES, &map_k2, bar, 0, h, t0, b);
+      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, bar, 0, h, t0, b);
+    }
+    // [A; Pm A] is an image of 128 rows: per 8-column block (2 KB) the first 1 KB holds the rows of A
+    const __nv_bfloat16* ap = p.AP + item * (128 * 64);
+#pragma unroll
+    for (int jb = 0; jb < 8; ++jb) bulk_load(smem + C::OFF_A + nb * C::A_BYTES + jb * 1024, ap + jb * 1024, 1024, bar);
+    bulk_load(smem + C::OFF_PM + nb * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, bar);
+  };
+  constexpr uint32_t LATE_TX = C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES;
+  auto issue_loads = [&](int i, int st) {           // one thread: K/Q tiles and the dO / U rows of local chunk i (STAGES == 1: the rest too)
     int t0, rows;
     chunk_info(i, t0, rows);
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     // the stage's U / dU buffer may still be the source of a store of dU issued by this thread
     bulk_wait_group_read();
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES + 2 * C::DO_BYTES);
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + 2 * C::DO_BYTES + (C::LATE ? 0u : LATE_TX));
 #pragma unroll
     for (int jb = 0; jb < VC / 8; ++jb) {            // eight value columns x 64 rows = one 1 KB column block of the image
       tma_load_4d(smem + C::OFF_DO + st * C::DOB + jb * 1024, &map_do, &ctrl.bar_load[st], vb * VC + jb * 8, h, t0, b);
       tma_load_4d(smem + C::OFF_DU + st * C::DOB + jb * 1024, &map_u, &ctrl.bar_load[st], vb * VC + jb * 8, 0,
                   static_cast<int>(item * 64), 0);
     }
-    if constexpr (C::TMA_GATES) {
-      uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
-      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
-      tma_load_4d(gt + C::GT_BYTES, &map_k2, &ctrl.bar_load[st], 0, h, t0, b);
-      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, &ctrl.bar_load[st], 0, h, t0, b);
-    }
     tma_load_4d(kq, &map_k, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
     tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
-    // [A; Pm A] is an image of 128 rows: per 8-column block (2 KB) the first 1 KB holds the rows of A
-    const __nv_bfloat16* ap = p.AP + item * (128 * 64);
-#pragma unroll
-    for (int jb = 0; jb < 8; ++jb)
-      bulk_load(smem + C::OFF_A + st * C::A_BYTES + jb * 1024, ap + jb * 1024, 1024, &ctrl.bar_load[st]);
-    bulk_load(smem + C::OFF_PM + st * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, &ctrl.bar_load[st]);
+    if constexpr (!C::LATE) issue_late(i, C::NB == 2 ? st : 0, &ctrl.bar_load[st]);
   };
   auto prefetch_loads = [&](int i) {                         // one lane: next chunk's tiles into L2 (single-stage configuration)
     int t0, rows;
@@ -296,7 +319,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     return __ldg(p.gc + item * (64 * E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
   };
 
-  if (warp_u == 1 && elect_one()) issue_loads(count - 1, 0);   // the lane that issues every load and every store of this CTA
+  if (warp_u == 1 && elect_one()) {                 // the lane that issues every load and every store of this CTA
+    issue_loads(count - 1, 0);
+    if constexpr (C::LATE) {
+      mbar_expect_tx(&ctrl.bar_late, LATE_TX);
+      issue_late(count - 1, 0, &ctrl.bar_late);
+    }
+  }
   __syncwarp();
   if (count > 1) prefetch_rows(count - 2);
   uint32_t mma_phase = 0;
@@ -322,8 +351,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
     const bool live = t < rows;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
-    uint8_t* am = smem + C::OFF_A + st * C::A_BYTES;
-    uint8_t* pm = smem + C::OFF_PM + st * C::PM_BYTES;
+    const int nbi = C::NB == 2 ? st : 0;             // which copy of Pm, A and the gate rows this chunk uses
+    uint8_t* am = smem + C::OFF_A + nbi * C::A_BYTES;
+    uint8_t* pm = smem + C::OFF_PM + nbi * C::PM_BYTES;
     const int v0 = wg * CW;                          // first value column of this thread inside the block
 
     uint8_t* doimg = smem + C::OFF_DO + st * C::DOB;     // dO rows of the value block: operand image of Y, by TMA
@@ -331,6 +361,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
+    if constexpr (C::LATE) mbar_wait(&ctrl.bar_late, kstep & 1, ctl, DEV_TIMEOUT_LOAD);
     if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       {
@@ -365,7 +396,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int tl = min(t, max(rows, 1) - 1);
       const float* gcp = p.gc + item * (64 * E);
       const int64_t ro = (tok + tl) * p.H + h;
-      const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
+      const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + nbi * 3 * C::GT_BYTES);
       float gcr[E], x2[E];
       if constexpr (C::TMA_GATES) {
         rec_lds_row<E>(gt + t * E, gcr);
@@ -508,6 +539,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (d) dG = [K^T | Q^T] X, G <- d G + dG ------------------------------------------------------------------
+    if constexpr (C::LATE) {                         // Pm, A and the gate rows of this chunk are dead: request the next chunk's
+      if (warp_u == 1 && kstep + 1 < count && elect_one()) {
+        mbar_expect_tx(&ctrl.bar_late, LATE_TX);
+        issue_late(i - 1, 0, &ctrl.bar_late);
+      }
+      __syncwarp();
+    }
     if (warp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
