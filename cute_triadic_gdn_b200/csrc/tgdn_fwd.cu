@@ -65,15 +65,41 @@ __device__ __forceinline__ void lds_row(const float* p, float* out) {   // the s
   }
 }
 
-__device__ __forceinline__ void chain_sync(int chain) {     // the 128 threads of one chain
-  asm volatile("bar.sync %0, 128;" ::"r"(chain + 1) : "memory");
+template <int THREADS>
+__device__ __forceinline__ void chain_sync(int chain) {     // the threads of one chain
+  asm volatile("bar.sync %0, %1;" ::"r"(chain + 1), "n"(THREADS) : "memory");
 }
 
-template <int E, int CW, int NCH, int STAGES>
+// N floats from shared memory; 16-byte loads where N and the address allow, 8-byte loads otherwise (N even)
+template <int N>
+__device__ __forceinline__ void lds_part(const float* p, float* out) {
+  if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < N / 4; ++j) {
+      const float4 x = *(reinterpret_cast<const float4*>(p) + j);
+      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) {
+      const float2 x = *(reinterpret_cast<const float2*>(p) + j);
+      out[2 * j] = x.x; out[2 * j + 1] = x.y;
+    }
+  }
+}
+
+// WPC warpgroups share one chain and split its SLICES (warpgroup w of a chain owns slices w*E/WPC ..): the chain's MMAs
+// then have N = E*CW columns with CW = 8 columns per thread even at twelve and sixteen slices, where a warpgroup alone
+// could hold only four columns of every slice in its registers; the sums over the slices (W, and the state part of o) are
+// completed through shared memory.
+template <int E, int CW, int NCH, int WPC, int STAGES>
 struct FwdCfg {
-  static constexpr int THREADS = NCH * 128;
+  static constexpr int CHAIN_THREADS = WPC * 128;
+  static constexpr int THREADS = NCH * CHAIN_THREADS;
   static constexpr int VC = CW * NCH;             // value columns of the CTA
-  static constexpr int TPC = E * CW;              // state columns per chain (and per thread)
+  static constexpr int TPC = E * CW;              // state columns per chain
+  static constexpr int ET = E / WPC;              // slices per thread
+  static constexpr int TPT = ET * CW;             // state columns per thread
   static constexpr int UW = 16;                   // columns of the (2) accumulator (the smallest N of an M=128 MMA)
   static constexpr int TW = TPC + UW;             // tensor-memory columns per chain
   static constexpr int TMEM_NEED = NCH * TW;
@@ -97,7 +123,10 @@ struct FwdCfg {
   static constexpr int OFF_CTRL = OFF_GT + STAGES * 3 * GT_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 128 + 1024;    // + control block + alignment slack
   static_assert(CW == 4 || CW == 8 || CW == 16, "a chain owns 4, 8 or 16 value columns");
-  static_assert(TPC % 16 == 0 && TPC <= 64, "columns per chain: a multiple of 16 (MMA N, tensor-memory loads), at most 64 registers of state");
+  static_assert(E % WPC == 0 && (WPC == 1 || ET % 2 == 0), "the slices split evenly over the chain's warpgroups");
+  static_assert(TPC % 16 == 0 && TPC <= 256, "columns per chain: a multiple of 16 (MMA N)");
+  static_assert(TPT % 16 == 0 && TPT <= 64, "columns per thread: a multiple of 16 (tensor-memory loads), at most 64 registers of state");
+  static_assert(WPC == 1 || VN_BYTES >= 2 * 64 * CW * 4, "the exchange of partial sums borrows the chain's Vn image");
 };
 
 struct FwdCtrl {
@@ -108,12 +137,12 @@ struct FwdCtrl {
   int abort;
 };
 
-template <int E, int CW, int NCH, int STAGES, int MINB>
-__global__ void __launch_bounds__(NCH * 128, MINB)
+template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
+__global__ void __launch_bounds__(NCH * WPC * 128, MINB)
 fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
            const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
-  using C = FwdCfg<E, CW, NCH, STAGES>;
-  constexpr int TPC = C::TPC, VC = C::VC;
+  using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
+  constexpr int TPC = C::TPC, VC = C::VC, ET = C::ET, TPT = C::TPT, CT = C::CHAIN_THREADS;
   constexpr bool LATE_R = C::TMA_GATES && E >= 12;   // form r_e after the epilogue of (1) (register pressure at many slices)
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -121,7 +150,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   FwdCtrl& ctrl = *reinterpret_cast<FwdCtrl*>(smem + C::OFF_CTRL);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int chain = warp >> 2;                      // warpgroup = chain
+  const int chain = (warp >> 2) / WPC;              // WPC warpgroups form a chain
+  const int sw = (warp >> 2) % WPC;                 // which share of the chain's slices this warpgroup owns
+  const int e0 = sw * ET;                           // first slice of this thread
+  const int col0 = sw * TPT;                        // its first column among the chain's E*CW
   const int row = (warp & 3) * 32 + lane;           // tensor-memory lane = operand row
   const bool krow = row < 64;                       // rows 0..63 work on K rows (W, U, Vn), 64..127 on Q rows (o)
   const int t = row & 63;
@@ -155,19 +187,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (warp == 0) { tmem_alloc(&ctrl.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
   // state: zero, or the caller's initial state (f32 [seq][H][E][128 d][128 v])
-  float S[TPC];
+  float S[TPT];
   if (p.s_in != nullptr) {
-    const float* src = p.s_in + ((static_cast<int64_t>(seq) * p.H + h) * E) * (HEAD * HEAD) + row * HEAD + v0g;
+    const float* src = p.s_in + ((static_cast<int64_t>(seq) * p.H + h) * E + e0) * (HEAD * HEAD) + row * HEAD + v0g;
 #pragma unroll
-    for (int e = 0; e < E; ++e)
+    for (int e = 0; e < ET; ++e)
 #pragma unroll
       for (int c = 0; c < CW; ++c) S[e * CW + c] = __ldg(src + e * (HEAD * HEAD) + c);
   } else {
 #pragma unroll
-    for (int j = 0; j < TPC; ++j) S[j] = 0.f;
+    for (int j = 0; j < TPT; ++j) S[j] = 0.f;
   }
   // the second 8-column block of the (2) operand is never written: keep it zero (its products land in unused columns)
-  for (int i = (tid & 127); i < C::BW_BYTES / 16; i += 128) reinterpret_cast<uint4*>(bw_img)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid % CT; i < C::BW_BYTES / 16; i += CT) reinterpret_cast<uint4*>(bw_img)[i] = make_uint4(0, 0, 0, 0);
 
   // saved state / operand image of this thread's S: pieces of 8 columns (one 16-byte store each into the image)
   auto state_item_ptr = [&](int64_t item) {
@@ -176,7 +208,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   auto store_state_slices = [&](uint8_t* hbase, int j0, const uint32_t* packed /* 8 words = 16 columns from j0 */) {
 #pragma unroll
     for (int j = 0; j < 16; j += CW) {
-      const int e = (j0 + j) / CW;
+      const int e = e0 + (j0 + j) / CW;
       uint8_t* dst = hbase + e * 32768 + (v0g >> 3) * 2048 + row * 16 + (v0g & 7) * 2;
       if constexpr (CW == 16) {
         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -192,12 +224,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const uint32_t base = smem_u32(s_img) + (row >> 3) * 128 + (row & 7) * 16;
     uint8_t* hbase = p.h != nullptr ? state_item_ptr((static_cast<int64_t>(b) * p.NC + first) * p.H + h) : nullptr;
 #pragma unroll
-    for (int j0 = 0; j0 < TPC; j0 += 16) {
+    for (int j0 = 0; j0 < TPT; j0 += 16) {
       uint32_t packed[8];
 #pragma unroll
       for (int j = 0; j < 16; j += 2) packed[j / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
-      st_shared_v4(base + (j0 >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
-      st_shared_v4(base + ((j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
+      st_shared_v4(base + ((col0 + j0) >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
+      st_shared_v4(base + ((col0 + j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
       if (hbase != nullptr) store_state_slices(hbase, j0, packed);
     }
   }
@@ -206,7 +238,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = __shfl_sync(0xffffffffu, ctrl.tmem_base, 0);
-  const int cwarp_u = __shfl_sync(0xffffffffu, warp & 3, 0);   // warp index inside the chain as a warp-uniform value
+  const int cwarp_u = __shfl_sync(0xffffffffu, warp - chain * (CT / 32), 0);   // warp index inside the chain as a warp-uniform value
   const uint32_t tmem_c = tmem + chain * C::TW;                  // this chain's columns: [0, TPC) R / dS, [TPC, TPC+16) U / Oi
   const uint32_t tmem_row = tmem_c + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   WaitCtl ctl{&ctrl.abort, p.status};
@@ -249,7 +281,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
   };
   auto prefetch_rows = [&](int i) {                 // what threads still load themselves, for a later chunk -> L2
-    if (C::TMA_GATES && chain != 0) return;           // the value columns of all chains of the CTA share their 128-byte lines
+    if (sw != 0 || (C::TMA_GATES && chain != 0)) return;   // the value columns of all chains of the CTA share their 128-byte lines
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
@@ -334,36 +366,40 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     // Under the MMA: this row's raw gate inputs and value row (in L2 since the previous chunk), then the gate factors.
-    float ga[E];                                     // K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
-    float gr[E];                                     // K rows: r_e = k2 exp(gL - gc)
+    float ga[ET];                                    // this thread's slices.  K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
+    float gr[ET];                                    // K rows: r_e = k2 exp(gL - gc)
     float bt = 0.f;
     uint32_t vraw[CW / 2];
+#pragma unroll
+    for (int c = 0; c < CW / 2; ++c) vraw[c] = 0u;
     {
       const int tl = min(t, max(rows, 1) - 1);
       const float* gcp = p.gc + item * (64 * E);
       const int64_t ro = (tok + tl) * p.H + h;
-      float gcr[E], x2[E], gl[E];
+      float gcr[ET], x2[ET], gl[ET];
       if constexpr (C::TMA_GATES) {
         const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
-        lds_row<E>(gt + t * E, gcr);
-        lds_row<E>(gt + (krow ? 64 * E : 128 * E) + t * E, x2);
-        if (krow && !LATE_R) lds_row<E>(gt + 63 * E, gl);
+        lds_part<ET>(gt + t * E + e0, gcr);
+        lds_part<ET>(gt + (krow ? 64 * E : 128 * E) + t * E + e0, x2);
+        if (krow && !LATE_R) lds_part<ET>(gt + 63 * E + e0, gl);
       } else {
         ld_row<E>(gcp + t * E, gcr);
         ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
         if (krow) ld_row<E>(gcp + 63 * E, gl);
       }
       if (krow) {
-        bt = __ldg(p.beta + ro);
-        load_vrow(t0, rows, vraw);
-        if (t < E) {
+        if (sw == 0) {                               // the warpgroup that completes W: beta and the value row
+          bt = __ldg(p.beta + ro);
+          load_vrow(t0, rows, vraw);
+        }
+        if (sw == 0 && t < E) {
           float glt;
           if constexpr (C::TMA_GATES) glt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES)[63 * E + t];
           else glt = __ldg(gcp + 63 * E + t);
           dtab[t] = fexp2(glt * LOG2E);
         }
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < ET; ++e) {
           const float k2v = live ? x2[e] : 0.f;
           ga[e] = k2v * fexp2(gcr[e] * LOG2E);
           if constexpr (!LATE_R) gr[e] = k2v * fexp2((gl[e] - gcr[e]) * LOG2E);
@@ -371,7 +407,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         if (!live) bt = 0.f;
       } else {
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < ET; ++e) {
           ga[e] = live ? p.scale * x2[e] * fexp2(gcr[e] * LOG2E) : 0.f;
           gr[e] = 0.f;
         }
@@ -379,21 +415,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       if (i + 2 < count) prefetch_rows(i + 2);
     }
     if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    chain_sync(chain);
+    chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
 
     float acc[CW];                                   // K rows: W (starts from V); Q rows: Oq
 #pragma unroll
-    for (int c = 0; c < CW; ++c) acc[c] = (krow && live) ? ((c & 1) ? bf16_hi(vraw[c >> 1]) : bf16_lo(vraw[c >> 1])) : 0.f;
+    for (int c = 0; c < CW; ++c) acc[c] = (krow && live && sw == 0) ? ((c & 1) ? bf16_hi(vraw[c >> 1]) : bf16_lo(vraw[c >> 1])) : 0.f;
     {
       // sixteen columns at a time, the next piece travelling while this one is used
       float rr[2][16];
-      tmem_ld<16>(tmem_row, rr[0]);
+      tmem_ld<16>(tmem_row + col0, rr[0]);
 #pragma unroll
-      for (int pc = 0; pc < TPC / 16; ++pc) {
+      for (int pc = 0; pc < TPT / 16; ++pc) {
         tmem_wait_ld();
-        if (pc + 1 < TPC / 16) tmem_ld<16>(tmem_row + (pc + 1) * 16, rr[(pc + 1) & 1]);
+        if (pc + 1 < TPT / 16) tmem_ld<16>(tmem_row + col0 + (pc + 1) * 16, rr[(pc + 1) & 1]);
         const float* rp = rr[pc & 1];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -402,14 +438,34 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         }
       }
     }
-    if (krow) {
+    if constexpr (WPC > 1) {
+      // The sums over the slices are split over the chain's warpgroups: the first one completes W (K rows), the last one
+      // the state part of o (Q rows); the others hand their partial sums over through shared memory (the chain's Vn image
+      // is free between the last MMA of the previous chunk and the epilogue of (2)).
+      static_assert(WPC == 2, "the exchange below is written for two warpgroups per chain");
+      float* red = reinterpret_cast<float*>(vn_img) + (krow ? 0 : 64 * CW) + t * CW;
+      const bool owner = krow ? (sw == 0) : (sw == WPC - 1);
+      if (!owner) {
+#pragma unroll
+        for (int c = 0; c < CW; c += 4) *reinterpret_cast<float4*>(red + c) = make_float4(acc[c], acc[c + 1], acc[c + 2], acc[c + 3]);
+      }
+      chain_sync<CT>(chain);
+      if (owner) {
+#pragma unroll
+        for (int c = 0; c < CW; c += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(red + c);
+          acc[c] += x.x; acc[c + 1] += x.y; acc[c + 2] += x.z; acc[c + 3] += x.w;
+        }
+      }
+    }
+    if (krow && sw == 0) {
       // W -> saved (bf16), beta*W -> operand image (i = s, j = v)
       store_row_image(smem_u32(bw_img) + (t >> 3) * 128 + (t & 7) * 16, 0, 1024, acc, bt);
       if (p.W != nullptr) store_row_global(p.W + (item * 64 + t) * HEAD + v0g, acc);
     }
     fence_async_smem();
     tc_fence_before();
-    chain_sync(chain);
+    chain_sync<CT>(chain);
 
     // ---- (2) [U;Oi] = [A;PmA] (beta W) ------------------------------------------------------------------------
     if (cwarp_u == 0 && elect_one()) {
@@ -426,16 +482,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     if constexpr (LATE_R) {                          // r_e only now, from the gate tiles that are still in the stage: sixteen
       if (krow) {                                    // registers fewer are live through the epilogue of (1)
         const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
-        float gcr[E], k2r[E], gl[E];
-        lds_row<E>(gt + t * E, gcr);
-        lds_row<E>(gt + 64 * E + t * E, k2r);
-        lds_row<E>(gt + 63 * E, gl);
+        float gcr[ET], k2r[ET], gl[ET];
+        lds_part<ET>(gt + t * E + e0, gcr);
+        lds_part<ET>(gt + 64 * E + t * E + e0, k2r);
+        lds_part<ET>(gt + 63 * E + e0, gl);
 #pragma unroll
-        for (int e = 0; e < E; ++e) gr[e] = live ? k2r[e] * fexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
+        for (int e = 0; e < ET; ++e) gr[e] = live ? k2r[e] * fexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
       }
     }
     if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    chain_sync(chain);
+    chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
     {
@@ -443,12 +499,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       tmem_ld<CW>(tmem_row + TPC, u);
       tmem_wait_ld();
       if (krow) {
-        if (p.U != nullptr) store_row_global(p.U + (item * 64 + t) * HEAD + v0g, u);
-        // Vn_e = r_e * U -> operand image (i = t, j = n')
+        if (p.U != nullptr && sw == 0) store_row_global(p.U + (item * 64 + t) * HEAD + v0g, u);
+        // Vn_e = r_e * U -> operand image (i = t, j = n'), this thread's slices
         const uint32_t base = smem_u32(vn_img) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-        for (int e = 0; e < E; ++e) store_row_image(base, e * CW, 1024, u, gr[e]);
-      } else if (live) {
+        for (int e = 0; e < ET; ++e) store_row_image(base, (e0 + e) * CW, 1024, u, gr[e]);
+      } else if (live && sw == WPC - 1) {
         float ov[CW];
 #pragma unroll
         for (int c = 0; c < CW; ++c) ov[c] = acc[c] + u[c];
@@ -457,7 +513,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     fence_async_smem();
     tc_fence_before();
-    chain_sync(chain);
+    chain_sync<CT>(chain);
 
     // ---- (3) dS = K^T Vn, S <- d S + dS -----------------------------------------------------------------------
     if (cwarp_u == 0 && elect_one()) {
@@ -472,7 +528,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     __syncwarp();
     if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    chain_sync(chain);
+    chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
     // This chain is done with the stage's tiles.  The last chain to say so refills the stage with the chunk STAGES ahead.
@@ -486,18 +542,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
     __syncwarp();
     {
-      float dch[E];                                  // exp(gL) per slice, written by this chain during (1)
+      float dch[ET];                                 // exp(gL) of this thread's slices, written by this chain during (1)
 #pragma unroll
-      for (int e = 0; e < E; ++e) dch[e] = dtab[e];
+      for (int e = 0; e < ET; ++e) dch[e] = dtab[e0 + e];
       const uint32_t base = smem_u32(s_img) + (row >> 3) * 128 + (row & 7) * 16;
       uint8_t* hbase = (p.h != nullptr && i + 1 < count) ? state_item_ptr(item + p.H) : nullptr;
       float ds[2][16];
-      tmem_ld<16>(tmem_row, ds[0]);
+      tmem_ld<16>(tmem_row + col0, ds[0]);
 #pragma unroll
-      for (int pc = 0; pc < TPC / 16; ++pc) {
+      for (int pc = 0; pc < TPT / 16; ++pc) {
         const int j0 = pc * 16;
         tmem_wait_ld();
-        if (pc + 1 < TPC / 16) tmem_ld<16>(tmem_row + j0 + 16, ds[(pc + 1) & 1]);
+        if (pc + 1 < TPT / 16) tmem_ld<16>(tmem_row + col0 + j0 + 16, ds[(pc + 1) & 1]);
         const float* dp = ds[pc & 1];
         uint32_t packed[8];
 #pragma unroll
@@ -507,21 +563,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           packed[j / 2] = pack_bf16(S[j0 + j], S[j0 + j + 1]);
         }
         // operand image (i = d, j = n') for the next chunk's (1)
-        st_shared_v4(base + (j0 >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
-        st_shared_v4(base + ((j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
+        st_shared_v4(base + ((col0 + j0) >> 3) * 2048, packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(base + ((col0 + j0 + 8) >> 3) * 2048, packed[4], packed[5], packed[6], packed[7]);
         // saved state of the next chunk: slice e as [v/8][d][v%8]
         if (hbase != nullptr) store_state_slices(hbase, j0, packed);
       }
     }
     fence_async_smem();
     tc_fence_before();
-    chain_sync(chain);
+    chain_sync<CT>(chain);
   }
   // final state for the caller (f32, same form as the initial state)
   if (p.s_out != nullptr) {
-    float* dst = p.s_out + ((static_cast<int64_t>(seq) * p.H + h) * E) * (HEAD * HEAD) + row * HEAD + v0g;
+    float* dst = p.s_out + ((static_cast<int64_t>(seq) * p.H + h) * E + e0) * (HEAD * HEAD) + row * HEAD + v0g;
 #pragma unroll
-    for (int e = 0; e < E; ++e)
+    for (int e = 0; e < ET; ++e)
 #pragma unroll
       for (int c = 0; c < CW; ++c) dst[e * (HEAD * HEAD) + c] = S[e * CW + c];
   }
@@ -534,10 +590,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
 using namespace tgdn;
 
-template <int E, int CW, int NCH, int STAGES, int MINB>
+template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
 static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
                       const FwdParams& p, cudaStream_t s) {
-  using C = FwdCfg<E, CW, NCH, STAGES>;
+  using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   static_assert(MINB == 1 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
   static_assert(MINB * C::TMEM_COLS <= 512, "tensor memory budget of one SM exceeded");
@@ -545,12 +601,12 @@ static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, CW, NCH, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(fwd_kernel<E, CW, NCH, WPC, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return tgdn_cuda_error(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_seq * p.H * (HEAD / C::VC);
-  fwd_kernel<E, CW, NCH, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
+  fwd_kernel<E, CW, NCH, WPC, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -583,20 +639,20 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
               packed ? n_docs : B, scale, tgdn_status_word()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 16, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 2: return launch_fwd<2, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 1: return launch_fwd<1, 16, 2, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 2: return launch_fwd<2, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
     case 4: {
       // One CTA per SM: the grid runs in whole waves.  Where a block of 32 value columns needs a second, partly filled wave
       // and a block of 64 does not, the wider block wins although its chunks take a little longer (B=4, H=16: 256 CTAs on
       // 148 SMs are two waves, 128 CTAs are one).
       const long long sms = tgdn_sm_count(), seqs = static_cast<long long>(p.n_seq) * p.H;
       const long long waves32 = (seqs * 4 + sms - 1) / sms, waves64 = (seqs * 2 + sms - 1) / sms;
-      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
-      return launch_fwd<4, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
+      return launch_fwd<4, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
     }
-    case 8: return launch_fwd<8, 8, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 12: return launch_fwd<12, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 16: return launch_fwd<16, 4, 4, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 8: return launch_fwd<8, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 12: return launch_fwd<12, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 16: return launch_fwd<16, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }
