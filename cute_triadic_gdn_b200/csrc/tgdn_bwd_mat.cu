@@ -422,6 +422,43 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       bulk_load(sm.ap, reinterpret_cast<const uint8_t*>(p.dkq) + item * 32768, 32768, &sm.bar_load);
     }
     __syncwarp();
+    // Pull the inputs of the block that will follow this one on some SM into L2: its prologue, which nothing on this SM
+    // overlaps (one block per SM), then waits for L2 instead of for HBM.
+    if (warp_u == 1) {
+      const int64_t item2 = item + p.ahead;
+      if (p.ahead > 0 && item2 < static_cast<int64_t>(gridDim.x)) {
+        const int h2 = static_cast<int>(item2 % p.H), n2 = static_cast<int>((item2 / p.H) % p.NC);
+        const int b2 = static_cast<int>(item2 / (static_cast<int64_t>(p.H) * p.NC));
+        int t2 = n2 * CHUNK, rows2 = CHUNK;
+        if (p.cmap != nullptr) { t2 = p.cmap[n2]; rows2 = p.cmap[p.NC + n2]; }
+        if (rows2 > 0 && rows2 <= CHUNK && t2 >= 0 && t2 + rows2 <= p.T) {
+          if (lane == 0) {
+            const int crow2 = static_cast<int>(item2) * 64;
+            for (int col = 0; col < 128; col += 64) {
+              tma_prefetch_4d(&map_k, col, h2, t2, b2);
+              tma_prefetch_4d(&map_q, col, h2, t2, b2);
+              tma_prefetch_4d(&map_do, col, h2, t2, b2);
+              tma_prefetch_4d(&map_du, col, 0, crow2, 0);
+              tma_prefetch_4d(&map_w, col, 0, crow2, 0);
+              tma_prefetch_4d(&map_u, col, 0, crow2, 0);
+            }
+            bulk_prefetch(p.AP + item2 * (128 * 64), 16384);
+            bulk_prefetch(reinterpret_cast<const uint8_t*>(p.dkq) + item2 * 32768, 32768);
+            bulk_prefetch(p.gc + item2 * (64 * E), 64 * E * 4);
+            bulk_prefetch(p.da + item2 * (64 * E), 64 * E * 4);
+            bulk_prefetch(p.dc + item2 * (64 * E), 64 * E * 4);
+            bulk_prefetch(p.dr + item2 * p.NV * (64 * E), static_cast<uint32_t>(p.NV) * 64 * E * 4);
+          }
+          const int64_t tok2 = static_cast<int64_t>(b2) * p.T + t2;
+          for (int rr = lane; rr < rows2; rr += 32) {
+            const int64_t ro = (tok2 + rr) * p.H + h2;
+            prefetch_l2(p.k2 + ro * E);
+            prefetch_l2(p.q2 + ro * E);
+            if (E > 8) { prefetch_l2(p.k2 + ro * E + 8); prefetch_l2(p.q2 + ro * E + 8); }
+          }
+        }
+      }
+    }
     {
       // key row t, columns s0..s0+15: dL, partial dbeta_row, dm, partial r2, and dPkk + dPkk^T into a5[0..63][0..63]
       float dpr[16];
@@ -674,7 +711,7 @@ extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, con
   if ((rc = tgdn_make_token_map(&maps[5], U, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
   MatParams p{k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP), static_cast<const __nv_bfloat16*>(dkq), da, dc, dd, dr,
               static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), dk2, dq2, dg, dbeta, chunk_map,
-              B, T, H, NC, 128 / tgdn_value_block(E), scale, tgdn_status_word()};
+              B, T, H, NC, 128 / tgdn_value_block(E), scale, tgdn_status_word(), tgdn_sm_count()};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
     case 1: return launch_mat<1>(maps, p, s);

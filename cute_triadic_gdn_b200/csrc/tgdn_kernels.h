@@ -119,6 +119,7 @@ struct MatParams {
   int B, T, H, NC, NV;
   float scale;
   int* status;
+  int ahead;                // block index distance to the block whose inputs this one pulls into L2 (0: none)
 };
 
 }  // namespace tgdn
