@@ -8,7 +8,8 @@
 //       X    = scale*lower(Mp*dPm'),  dmp = scale*lower(Pqk*dPm'),  dA = dA' diag(beta),  dbeta_col = colsum(dA'*A)
 //   G3  Y    = A^T dA          G4  dp = Y A^T,   dL = -strict_lower(dp)
 //       dbeta_row = rowsum(dL*Pkk*M),  dPkk = beta_t dL*M,  dm = beta_t dL*Pkk
-//   G5  [dK;dQ] = [[dPkk+dPkk^T, X^T],[X, 0]] [K;Q]  + state part (from the state-gradient kernel)
+//   G5  [dK;dQ] = [[dPkk+dPkk^T, X^T],[X, 0]] [K;Q]  + state part (from the state-gradient kernel); the operand is P + P^T
+//       with P = [[dPkk, 0],[X, 0]] written by rows: two MMA groups on one image, read K-major and MN-major
 //   mask gradients r1, c1 (from dmp) and r2, c2 (from dm) with the decay factors recomputed, gate-table gradients
 //   folded in, reverse cumulative sum of dgc inside the chunk -> dg.
 // Row and column sums that span the four column quarters go through four-copy partial tables in shared memory and are
@@ -31,10 +32,6 @@ __device__ __forceinline__ float mexp2(float x) {
   return y;
 }
 __device__ __forceinline__ int midx(int i, int j) { return i * 64 + (j ^ (i & 31)); }
-__device__ __forceinline__ void st_shared_b16(uint32_t saddr, float v) {
-  const unsigned short b = __bfloat16_as_ushort(__float2bfloat16_rn(v));
-  asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"(b) : "memory");
-}
 
 template <int E>
 struct MatSmem {
@@ -52,8 +49,12 @@ struct MatSmem {
   uint8_t da[8192];                  // dA image (i = t, j = s), SI = 128, SJ = 1024
   uint8_t y[8192];                   // Y image (i = s', j = t'), SI = 128, SJ = 1024 (read as 128 rows: daa follows)
   float daa[4096];                   // dA' * A, for the column sums
+  // decay tables whose rows are read by whole warps at once (dense rows, 16-byte loads):
+  alignas(16) float hkv[64 * E];     // until the two chains join: exp2(gc[r0(s)] - gc[s]) * k2[s], r0(s) the first row of
+                                     // s's 16-row block; afterwards: k2[t] * exp2(gc[t] - gc[r0(t)])
+  alignas(16) float qxv[64 * E];     // q2[t] * exp2(gc[t] - gc[r0(t)])
   float gc2[64 * ES], k2[64 * ES], q2[64 * ES];
-  float r1[64 * ES], c1[64 * ES], r2[64 * ES], c2[64 * ES], dgc[64 * ES], drr[64 * ES];
+  float r1[64 * ES], c1[64 * ES], r2[64 * ES], dgc[64 * ES], drr[64 * ES];
   float part[2][4][64 * ES];         // per column quarter partial sums
   float browp[4][64];
   float beta[64], brow[64], bcol[64];
@@ -67,7 +68,8 @@ template <int E>
 __global__ void __launch_bounds__(MAT_THREADS, 1)
 mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
            const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_du,
-           const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u, MatParams p) {
+           const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u,
+           const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dq, MatParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   using SM = MatSmem<E>;
   SM& sm = *reinterpret_cast<SM*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -124,7 +126,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   constexpr int GATE_ITERS = (64 * E + MAT_THREADS - 1) / MAT_THREADS;
   constexpr int NV_MAX = 8;                                // value blocks of the reverse recurrence (4 or 8)
   float da_in[GATE_ITERS], dc_in[GATE_ITERS];              // row-sum gradients of the state-gradient kernel, used at the end
-  const float dd_in = __ldg(p.dd + item * E + min(tid, E - 1));
+  const float dd_in = __ldg(p.dd + item * E + min(warp, E - 1));   // warp e adds the chunk-end term of gate column e
   const float beta_in = __ldg(p.beta + (tok + min(tid & 63, rows - 1)) * p.H + h);
   {
     float gc_in[GATE_ITERS], k2_in[GATE_ITERS], q2_in[GATE_ITERS], dr_in[GATE_ITERS][NV_MAX];
@@ -193,16 +195,14 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   // block decays by more than 2^-100 (a flush of the first factor could then hide a product of order one) the whole
   // CTA takes the direct path with one exponential per (t, s, e) instead.
   //   Hd[s][e] = exp2(gc[r0(s)][e] - gc[s][e]) * k2[s][e]          Xd[t][e] = exp2(gc[t][e] - gc[r0(t)][e])
-  float* const Hd = sm.dgc;                                // dgc itself is written much later (gate gradients)
-  float* const Xd = sm.c2;
   for (int idx = tid; idx < 64 * E; idx += MAT_THREADS) {
     const int rr = idx / E, e = idx % E, o = rr * ES + e;
     const float up = sm.gc2[(rr & ~15) * ES + e] - sm.gc2[o];    // >= 0 when gc does not increase
     // too steep, NaN, or not monotone (a log gate above zero makes gc rise from one row to the next: the factorised form,
     // which clamps its first factor at one, would then be wrong for rows of later blocks)
     if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[o] > sm.gc2[o - ES])) sm.steep = 1;
-    Hd[o] = mexp2(up) * sm.k2[o];
-    Xd[o] = mexp2(-up);
+    sm.hkv[idx] = mexp2(up) * sm.k2[o];
+    sm.qxv[idx] = sm.q2[o] * mexp2(-up);
   }
   uint32_t mma_phase = 0;
   mbar_wait_spin(&sm.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
@@ -223,6 +223,19 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mygc[e] = sm.gc2[t * ES + e];
   }
   const bool fast = sm.steep == 0;                         // block-uniform
+  auto table_row = [&](const float* tab, int row, float* out) {   // E floats of a dense table row (the same row for the whole warp)
+    if constexpr (E % 4 == 0) {
+#pragma unroll
+      for (int e = 0; e < E; e += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(tab + row * E + e);
+        out[e] = x.x; out[e + 1] = x.y; out[e + 2] = x.z; out[e + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < E; ++e) out[e] = tab[row * E + e];
+    }
+  };
+  const int warp_tmin = (warp & 1) ? 32 : 0;               // smallest row index t in this warp
   const uint32_t a5 = smem_u32(sm.u1.a5);
   const int warp_tmax = (warp & 1) ? 63 : 31;              // largest row index t in this warp
   // From here to the barrier before G5 the two halves of the CTA run independent chains and synchronise among
@@ -254,12 +267,10 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         float x = 0.f, dmpv = 0.f;
         if (s0 <= warp_tmax) {
           float hk[E];
+          table_row(sm.hkv, s, hk);
           float mp = 0.f;
 #pragma unroll
-          for (int e = 0; e < E; ++e) {
-            hk[e] = Hd[s * ES + e];
-            mp = fmaf(G[e], hk[e], mp);
-          }
+          for (int e = 0; e < E; ++e) mp = fmaf(G[e], hk[e], mp);
           const float in = (s <= t) ? p.scale * gr[j] : 0.f;
           x = in * mp;
           dmpv = live * in * pr[j];
@@ -268,7 +279,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         }
         xrow[j] = x;
         sm.u2.f.dmp[midx(t, s)] = dmpv;
-        st_shared_b16(a5 + (s >> 3) * 128 + ((64 + t) >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, x);   // a5[s][64+t]
       }
 #pragma unroll
       for (int e = 0; e < E; ++e) r1v[e] = F[e] * accr[e];
@@ -292,7 +302,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       xrow[j] = x;
       sm.u2.f.dmp[midx(t, s)] = dmpv;
-      st_shared_b16(a5 + (s >> 3) * 128 + ((64 + t) >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, x);   // a5[s][64+t]
     }
     }
     const uint32_t rowbase = a5 + ((64 + t) >> 3) * 128 + (t & 7) * 16;
@@ -318,10 +327,18 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
       for (int e = 0; e < E; ++e) c1v[e] = 0.f;
       if (fast) {
-        for (int tt = max(s, s0); tt < s0 + 16; ++tt) {
-          const float dv = sm.u2.f.dmp[midx(tt, s)];
+        // the same sixteen rows t' for every lane (dmp is zero above the diagonal); nothing to do where the whole warp
+        // lies below the quarter
+        if (s0 + 15 >= warp_tmin) {
 #pragma unroll
-          for (int e = 0; e < E; ++e) c1v[e] = fmaf(dv * sm.q2[tt * ES + e], Xd[tt * ES + e], c1v[e]);
+          for (int j = 0; j < 16; ++j) {
+            const int tt = s0 + j;
+            const float dv = sm.u2.f.dmp[midx(tt, s)];
+            float qx[E];
+            table_row(sm.qxv, tt, qx);
+#pragma unroll
+            for (int e = 0; e < E; ++e) c1v[e] = fmaf(dv, qx[e], c1v[e]);
+          }
         }
         if (s0 + 15 >= s) {
 #pragma unroll
@@ -469,6 +486,9 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       float r2v[E];
 #pragma unroll
       for (int e = 0; e < E; ++e) r2v[e] = 0.f;
+      float dpk[16];                                       // dPkk, this thread's 16 columns of row t
+#pragma unroll
+      for (int j = 0; j < 16; ++j) dpk[j] = 0.f;
       if (fast) {
         float F[E], G[E], accr[E];
 #pragma unroll
@@ -483,22 +503,16 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           float dmv = 0.f;
           if (s0 <= warp_tmax) {
             float hk[E];
+            table_row(sm.hkv, s, hk);
             float m = 0.f;
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-              hk[e] = Hd[s * ES + e];
-              m = fmaf(G[e], hk[e], m);
-            }
+            for (int e = 0; e < E; ++e) m = fmaf(G[e], hk[e], m);
             const float dl = (s < t) ? -dpr[j] : 0.f;
             brow = fmaf(dl * pr[j], m, brow);
             dmv = bt * dl * pr[j];
-            const float dpk = bt * dl * m;
+            dpk[j] = bt * dl * m;                          // zero on and above the diagonal
 #pragma unroll
             for (int e = 0; e < E; ++e) accr[e] = fmaf(dmv, hk[e], accr[e]);
-            if (s < t) {
-              st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
-              st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
-            }
           }
           sm.u2.f.dm[midx(t, s)] = dmv;
         }
@@ -520,16 +534,20 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           const float dl = -dpr[j];
           brow = fmaf(dl * pr[j], m, brow);
           dmv = bt * dl * pr[j];
-          const float dpk = bt * dl * m;
+          dpk[j] = bt * dl * m;
 #pragma unroll
           for (int e = 0; e < E; ++e) r2v[e] = fmaf(dmv, dec[e], r2v[e]);
-          st_shared_b16(a5 + (t >> 3) * 128 + (s >> 3) * 2048 + (t & 7) * 16 + (s & 7) * 2, dpk);     // a5[t][s]
-          st_shared_b16(a5 + (s >> 3) * 128 + (t >> 3) * 2048 + (s & 7) * 16 + (t & 7) * 2, dpk);     // a5[s][t]
         }
         sm.u2.f.dm[midx(t, s)] = dmv;
       }
       }
-      if (cq == (t >> 4)) st_shared_b16(a5 + (t >> 3) * 128 + (t >> 3) * 2048 + (t & 7) * 16 + (t & 7) * 2, 0.f);   // diagonal
+      const uint32_t rowbase = a5 + (t >> 3) * 128 + (t & 7) * 16;
+#pragma unroll
+      for (int jb = 0; jb < 2; ++jb) {
+        st_shared_v4(rowbase + (2 * cq + jb) * 2048, pack_bf16(dpk[jb * 8], dpk[jb * 8 + 1]), pack_bf16(dpk[jb * 8 + 2], dpk[jb * 8 + 3]),
+                     pack_bf16(dpk[jb * 8 + 4], dpk[jb * 8 + 5]), pack_bf16(dpk[jb * 8 + 6], dpk[jb * 8 + 7]));
+        st_shared_v4(rowbase + (8 + 2 * cq + jb) * 2048, 0u, 0u, 0u, 0u);
+      }
 #pragma unroll
       for (int e = 0; e < E; ++e) sm.part[0][cq][t * ES + e] = r2v[e];
       sm.browp[cq][t] = brow;
@@ -539,14 +557,18 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
 
-  // ---- G5: [dK;dQ] = a5 [K;Q] --------------------------------------------------------------------------------------
+  // ---- G5: [dK;dQ] = (P + P^T) [K;Q] with P = [[dPkk, 0], [X, 0]] ------------------------------------------------------
+  // The image of P is written by rows only; its transpose is the same image read MN-major.
   if (warp_u == 0 && elect_one()) {
     tc_fence_after();
-    const uint64_t da = make_desc(a5, 2048, 128, LAYOUT_PLAIN);
+    const uint64_t da = make_desc(a5, 2048, 128, LAYOUT_PLAIN);                  // P, K-major: only columns 0..63 are not zero
+    const uint64_t dat = make_desc(a5, 128, 2048, LAYOUT_PLAIN);                 // P^T, MN-major
     const uint64_t db = make_desc(smem_u32(sm.kq), 16384, 1024, LAYOUT_SW128);   // (K = token rows, N = d), MN-major
-    constexpr uint32_t idesc = make_idesc(128, 128, 0, 1);
+    constexpr uint32_t idesc = make_idesc(128, 128, 0, 1), idesc_t = make_idesc(128, 128, 1, 1);
 #pragma unroll
-    for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
+    for (int kk = 0; kk < 4; ++kk) umma_bf16(tmem, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem, desc_advance(dat, kk * 256), desc_advance(db, kk * 2048), idesc_t, true);
     umma_commit(&sm.bar_mma);
   }
   __syncwarp();                                           // the other lanes must not run ahead into a spin wait
@@ -555,6 +577,8 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int o = (idx / E) * ES + idx % E;
     sm.r2[o] = (sm.part[0][0][o] + sm.part[0][1][o]) + (sm.part[0][2][o] + sm.part[0][3][o]);
     sm.c1[o] = (sm.part[1][0][o] + sm.part[1][1][o]) + (sm.part[1][2][o] + sm.part[1][3][o]);
+    // the first decay table has been read for the last time: the column sums below want k2[t] exp2(gc[t] - gc[r0(t)])
+    sm.hkv[idx] = sm.k2[o] * mexp2(sm.gc2[o] - sm.gc2[((idx / E) & ~15) * ES + idx % E]);
   }
   if (tid < 64) sm.brow[tid] = (sm.browp[0][tid] + sm.browp[1][tid]) + (sm.browp[2][tid] + sm.browp[3][tid]);
   __syncthreads();
@@ -566,10 +590,16 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     for (int e = 0; e < E; ++e) c2v[e] = 0.f;
     const int lo = s0 + (krow ? 0 : 8);
     if (fast) {
-      for (int tt = max(t + 1, lo); tt < lo + 8; ++tt) {
-        const float dv = sm.u2.f.dm[midx(tt, t)];
+      if (lo + 7 > warp_tmin) {                            // dm is zero on and above the diagonal
 #pragma unroll
-        for (int e = 0; e < E; ++e) c2v[e] = fmaf(dv * sm.k2[tt * ES + e], Xd[tt * ES + e], c2v[e]);
+        for (int j = 0; j < 8; ++j) {
+          const int tt = lo + j;
+          const float dv = sm.u2.f.dm[midx(tt, t)];
+          float kx[E];
+          table_row(sm.hkv, tt, kx);
+#pragma unroll
+          for (int e = 0; e < E; ++e) c2v[e] = fmaf(dv, kx[e], c2v[e]);
+        }
       }
       if (s0 + 15 > t) {
 #pragma unroll
@@ -611,16 +641,15 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   if (tid < 64 && tid < rows) p.dbeta[(tok + tid) * p.H + h] = sm.bcol[tid] + sm.brow[tid];
   __syncthreads();
-  if (tid < E) {                                            // chunk-end terms: sum_t dr*r + dd*exp(gL)
-    float acc = 0.f;
-    for (int tt = 0; tt < 64; ++tt) acc += sm.drr[tt * ES + tid];
-    acc += dd_in * mexp2(sm.gc2[63 * ES + tid]);
-    sm.dgc[63 * ES + tid] += acc;
-  }
-  __syncthreads();
-  // dg = reverse inclusive cumulative sum of dgc over the chunk, one warp per gate column
+  // dg = reverse inclusive cumulative sum of dgc over the chunk, one warp per gate column; the last row first takes the
+  // chunk-end terms sum_t dr*r + dd*exp(gL)
+  static_assert(E <= MAT_THREADS / 32, "one warp per gate column");
   for (int e = warp; e < E; e += MAT_THREADS / 32) {
+    float tot = sm.drr[lane * ES + e] + sm.drr[(lane + 32) * ES + e];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
     float v1 = sm.dgc[(63 - lane) * ES + e], v0 = sm.dgc[(31 - lane) * ES + e];      // lane l: rows 63-l and 31-l
+    if (lane == 0) v1 += tot + dd_in * mexp2(sm.gc2[63 * ES + e]);
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const float a1 = __shfl_up_sync(0xffffffffu, v1, o), a0 = __shfl_up_sync(0xffffffffu, v0, o);
@@ -645,20 +674,35 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     // that it can leave as whole 256-byte rows: a thread owns one row and 32 columns, and storing those directly would
     // scatter every warp store over 32 rows.  16-byte chunks are XOR-swizzled with the row so that neither the staging
     // stores (fixed chunk, 32 rows) nor the row reads (one row, 32 lanes) meet a bank twice.
+    // A whole chunk leaves by TMA instead: four 64 x 64 tiles (dk | dq, column half) staged in the 128-byte swizzle of the
+    // tensor maps.  (A chunk cut short by a document end may not: the rows behind it belong to the next document.)
     const uint32_t xb = smem_u32(sm.ap) + (cq * 4) * 2048 + r * 16;
-    const uint32_t stage = smem_u32(sm.kq) + r * 256;
+    const bool whole = rows == CHUNK;
+    const uint32_t stage = whole ? smem_u32(sm.kq) + ((r >> 6) * 2 + (cq >> 1)) * 8192 + t * 128 : smem_u32(sm.kq) + r * 256;
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       uint32_t x[4];
       asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(xb + (j >> 3) * 2048));
-      st_shared_v4(stage + (((cq * 4 + (j >> 3)) ^ (r & 15)) << 4),
+      st_shared_v4(stage + (whole ? ((((cq & 1) * 4 + (j >> 3)) ^ (t & 7)) << 4) : (((cq * 4 + (j >> 3)) ^ (r & 15)) << 4)),
                    pack_bf16(a[j] + bf16_lo(x[0]), a[j + 1] + bf16_hi(x[0])), pack_bf16(a[j + 2] + bf16_lo(x[1]), a[j + 3] + bf16_hi(x[1])),
                    pack_bf16(a[j + 4] + bf16_lo(x[2]), a[j + 5] + bf16_hi(x[2])), pack_bf16(a[j + 6] + bf16_lo(x[3]), a[j + 7] + bf16_hi(x[3])));
     }
   }
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+  if (rows == CHUNK) {
+    if (warp_u == 1 && elect_one()) {
+      tma_store_4d(&map_dk, sm.kq, 0, h, t0, b);
+      tma_store_4d(&map_dk, sm.kq + 8192, 64, h, t0, b);
+      tma_store_4d(&map_dq, sm.kq + 16384, 0, h, t0, b);
+      tma_store_4d(&map_dq, sm.kq + 24576, 64, h, t0, b);
+      bulk_commit_group();
+      bulk_wait_group_read();                              // the staging buffer must outlive the copies
+    }
+    return;
+  }
   // rows 0..63 -> dk, rows 64..127 -> dq; warp w stores rows w, w + 16, ...: one coalesced 256-byte row per instruction
   for (int rr = warp; rr < 128; rr += MAT_THREADS / 32) {
     const int tt = rr & 63;
@@ -682,7 +726,7 @@ static int launch_mat(const CUtensorMap* maps, const MatParams& p, cudaStream_t 
   static_assert(sizeof(MatSmem<E>) + 1024 <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(mat_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
-  mat_kernel<E><<<p.B * p.NC * p.H, MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  mat_kernel<E><<<p.B * p.NC * p.H, MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -701,7 +745,7 @@ extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, con
     return TGDN_ERR_ALIGN;
   const long long crows = static_cast<long long>(B) * NC * H * 64;
   if (crows > 0x7fffffffLL) return TGDN_ERR_SHAPE;
-  CUtensorMap maps[6];
+  CUtensorMap maps[8];
   if ((rc = tgdn_make_token_map(&maps[0], k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[1], q, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[2], dO, B, T, H, 64, 64, 1))) return rc;
@@ -709,6 +753,8 @@ extern "C" int tgdn_bwd_matrix(const void* q, const void* k, const void* dO, con
   if ((rc = tgdn_make_token_map(&maps[3], dU, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[4], W, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&maps[5], U, 1, static_cast<int>(crows), 1, 64, 64, 1))) return rc;
+  if ((rc = tgdn_make_token_map(&maps[6], dk, B, T, H, 64, 64, 1))) return rc;
+  if ((rc = tgdn_make_token_map(&maps[7], dq, B, T, H, 64, 64, 1))) return rc;
   MatParams p{k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP), static_cast<const __nv_bfloat16*>(dkq), da, dc, dd, dr,
               static_cast<__nv_bfloat16*>(dq), static_cast<__nv_bfloat16*>(dk), dk2, dq2, dg, dbeta, chunk_map,
               B, T, H, NC, 128 / tgdn_value_block(E), scale, tgdn_status_word(), tgdn_sm_count()};

@@ -34,6 +34,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // "lanes along a column" accesses are conflict-free.
 __device__ __forceinline__ int mat_idx(int i, int j) { return i * 64 + (j ^ (i & 31)); }
 __device__ __forceinline__ int t_idx(int k, int j) { return k * 32 + ((j ^ k) & 31); }
+__device__ __forceinline__ void st_shared_b16(uint32_t saddr, float v) {      // v is a bf16 value held as f32
+  const unsigned short b = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(saddr), "h"(b) : "memory");
+}
 
 // ---- warp-level TF32 products with a 3-term split --------------------------------------------------------------------
 __device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
@@ -76,13 +80,20 @@ struct MaskSmem {
   float gc2[64 * E];       // log2-domain cumulative gate
   float k2[64 * E];
   float q2[64 * E];
-  float hd[64 * E];        // exp2(gc[first row of s's 16-row block] - gc[s]) * k2[s]
   float pad[(3 * 64 * E * 4 >= 8192) ? 1 : (8192 - 3 * 64 * E * 4) / 4];
   float beta[64];
   uint64_t bar_load, bar_mma;
   uint32_t tmem_base;
   int abort;
   int steep;               // a 16-row block decays by more than 2^-100 (or gc is not monotone): direct decay path
+  // Operands of the mask-sum products (see the kernel), in buffers that are written only after those products are done:
+  //   G images: four blocks of (128 rows x KP) bf16, image (i = row, j = k), SI = 128, SJ = 2048, over Pm, T, img_ap
+  //   H images: two of (64 rows x KP) bf16, image (i = s, j = k), SI = 128, SJ = 1024, over img_pm
+  static constexpr int KP = 2 * E <= 16 ? 16 : 32;         // [hi | lo] halves of the E factors, padded to the MMA's K = 16
+  static constexpr int G_BYTES = KP / 8 * 2048, H_BYTES = KP / 8 * 1024;
+  __device__ uint8_t* img_g() { return reinterpret_cast<uint8_t*>(Pm); }
+  __device__ uint8_t* img_h() { return img_pm; }
+  static_assert(4 * G_BYTES <= 16384 + 4096 + 16384 && 2 * H_BYTES <= 8192, "operand images fit the buffers they borrow");
 };
 
 // X21 = -X22 (L21 X11) for the diagonal blocks of size 2n (n = 16: two blocks, n = 32: one), one 16x8 tile per warp.
@@ -160,6 +171,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   }
   __syncwarp();
   if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 128); tmem_relinquish(); }
+  for (int i = tid; i < 2 * SM::H_BYTES / 16; i += MASK_THREADS) reinterpret_cast<uint4*>(sm.img_h())[i] = make_uint4(0, 0, 0, 0);
 
   // gates of the chunk: rows past the document end count as g = 0, k2 = q2 = beta = 0.  All loads are requested first, from
   // clamped (always valid) addresses, and masked when stored: the block pays one memory round trip, not one per iteration.
@@ -207,21 +219,66 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
     sm.gc2[(lane + 32) * E + e] = v1 * LOG2E;
   }
   __syncthreads();
-  // Decay table for the mask sums.  With r0(s) the first row of s's 16-row block,
-  //   exp2(gc[t] - gc[s]) = exp2(gc[t] - gc[r0(s)]) * exp2(gc[r0(s)] - gc[s])        for every t >= s:
-  // the first factor costs E exponentials per thread and column block, the second is this table.  Its exponent is
-  // positive but bounded by the decay inside one block; when a block decays by more than 2^-100 (a flush of the first
-  // factor could then hide a product of order one) the CTA takes one exponential per (t, s, e) instead.
-  for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
-    const int rr = idx / E, e = idx % E;
-    const float up = sm.gc2[(rr & ~15) * E + e] - sm.gc2[idx];   // >= 0 when gc does not increase
-    // too steep, NaN, or not monotone: a log gate above zero anywhere in the chunk makes gc rise from one row to the
-    // next, and the factorised form (which clamps its first factor at one) would then be wrong for rows of later blocks
-    if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[idx] > sm.gc2[idx - E])) sm.steep = 1;
-    sm.hd[idx] = fast_exp2(up) * sm.k2[idx];
+  // Mask sums on the tensor core.  With r0(s) the first row of s's 16-row block,
+  //   exp2(gc[t] - gc[s]) = exp2(gc[t] - gc[r0(s)]) * exp2(gc[r0(s)] - gc[s])        for every t >= s,
+  // so that for the 16 columns of block i
+  //   M[t, s] = sum_e G_i[t, e] H[s, e],   G_i[t, e] = x2[t, e] exp2(min(gc[t, e] - gc[16 i, e], 0)),
+  //                                         H[s, e]  = k2[s, e] exp2(gc[r0(s), e] - gc[s, e])
+  // (x2 = k2 for key rows, q2 for query rows): four products of (128 x E)(E x 16).  Both factors go in as a bf16 pair
+  // hi + lo; with K laid out as [hi | lo] two MMAs per block give hi*hi + lo*hi + hi*lo, an error of 2^-16 per term.
+  // The exponent of H is positive but bounded by the decay inside one block; when a block decays by more than 2^-100 (a
+  // flush of the first factor could then hide a product of order one) the CTA takes one exponential per (t, s, e) instead.
+  constexpr int KP = SM::KP;
+  {
+    const uint32_t hb = smem_u32(sm.img_h());
+    for (int idx = tid; idx < 64 * E; idx += MASK_THREADS) {
+      const int rr = idx / E, e = idx % E;
+      const float up = sm.gc2[(rr & ~15) * E + e] - sm.gc2[idx];   // >= 0 when gc does not increase
+      // too steep, NaN, or not monotone: a log gate above zero anywhere in the chunk makes gc rise from one row to the
+      // next, and the factorised form (which clamps its first factor at one) would then be wrong for rows of later blocks
+      if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[idx] > sm.gc2[idx - E])) sm.steep = 1;
+      const float hv = fast_exp2(up) * sm.k2[idx];
+      const float hi = round_bf16(hv), lo = hv - hi;
+      const uint32_t row = hb + (rr >> 3) * 128 + (rr & 7) * 16;
+      st_shared_b16(row + (e >> 3) * 1024 + (e & 7) * 2, hi);                                    // first image:  [hi | hi]
+      st_shared_b16(row + ((E + e) >> 3) * 1024 + ((E + e) & 7) * 2, hi);
+      st_shared_b16(row + SM::H_BYTES + (e >> 3) * 1024 + (e & 7) * 2, lo);                      // second image: [lo | 0]
+    }
   }
+  const int t = r & 63;
+  const bool isq = r >= 64;
+  {
+    float my2[E], mygc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      my2[e] = isq ? sm.q2[t * E + e] : sm.k2[t * E + e];
+      mygc[e] = sm.gc2[t * E + e];
+    }
+#pragma unroll
+    for (int ii = 0; ii < 2; ++ii) {
+      const int i = 2 * ch + ii;                              // the two column halves of a row share the four blocks
+      float vals[KP];
+#pragma unroll
+      for (int k = 0; k < KP; ++k) vals[k] = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float g = my2[e] * fast_exp2(fminf(mygc[e] - sm.gc2[(16 * i) * E + e], 0.f));   // rows above the block are masked later
+        vals[e] = round_bf16(g);
+        vals[E + e] = g - vals[e];
+      }
+      const uint32_t row = smem_u32(sm.img_g()) + i * SM::G_BYTES + (r >> 3) * 128 + (r & 7) * 16;
+#pragma unroll
+      for (int kb = 0; kb < KP / 8; ++kb)
+        st_shared_v4(row + kb * 2048, pack_bf16(vals[8 * kb], vals[8 * kb + 1]), pack_bf16(vals[8 * kb + 2], vals[8 * kb + 3]),
+                     pack_bf16(vals[8 * kb + 4], vals[8 * kb + 5]), pack_bf16(vals[8 * kb + 6], vals[8 * kb + 7]));
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
-  // Gram product [K;Q] K^T
+  // Gram product [K;Q] K^T, then the four mask-sum products
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
   const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
   const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -234,28 +291,26 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
       const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
       umma_bf16(tmem, desc_advance(desc, off), desc_advance(desc, off), idesc, kk > 0);
     }
+    constexpr uint32_t idm = make_idesc(128, 16, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t da = make_desc(smem_u32(sm.img_g()) + i * SM::G_BYTES, 2048, 128, LAYOUT_PLAIN);
+      const uint64_t db = make_desc(smem_u32(sm.img_h()) + i * 256, 1024, 128, LAYOUT_PLAIN);
+#pragma unroll
+      for (int kk = 0; kk < KP / 16; ++kk)
+        umma_bf16(tmem + 64 + 16 * i, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idm, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < KP / 16; ++kk)
+        umma_bf16(tmem + 64 + 16 * i, desc_advance(da, kk * 4096), desc_advance(db, SM::H_BYTES + kk * 2048), idm, 1);
+    }
     umma_commit(&sm.bar_mma);
   }
   __syncwarp();                                           // the other lanes must not run ahead into a spin wait
   mbar_wait_spin(&sm.bar_mma, 0, ctl, DEV_TIMEOUT_MMA);
   tc_fence_after();
-  float pr[32];                                             // this thread's 4 blocks of 8 columns of its row
-#pragma unroll
-  for (int i = 0; i < 4; ++i) tmem_ld8(tmem_row + 16 * i + 8 * ch, pr + 8 * i);
-  tmem_wait_ld();
-  tc_fence_before();
-  __syncthreads();                                          // the KQ tile is dead from here: L and X take its place
-
-  // mask sums: rows 0..63 -> M (strictly lower) -> L, rows 64..127 -> Mp (lower) -> Pm
+  // The KQ tile and the operand images are dead from here (every thread has seen the products complete): L, X, Pm take
+  // their places.  Rows 0..63 -> M (strictly lower) -> L, rows 64..127 -> Mp (lower) -> Pm.
   {
-    const int t = r & 63;
-    const bool isq = r >= 64;
-    float my2[E], mygc[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      my2[e] = isq ? sm.q2[t * E + e] : sm.k2[t * E + e];
-      mygc[e] = sm.gc2[t * E + e];
-    }
     const float rowscale = isq ? p.scale : sm.beta[t];
     float* dst = isq ? sm.Pm : sm.u.m.L;
     const int tmax = (warp & 1) ? 63 : 31;                  // largest row of this warp
@@ -263,88 +318,83 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int sb = 16 * i + 8 * ch;
-        float G[E];                                           // my2[e] * exp2(gc[t][e] - gc[16 i][e]); rows above the block are masked
-#pragma unroll
-        for (int e = 0; e < E; ++e) G[e] = my2[e] * fast_exp2(fminf(mygc[e] - sm.gc2[(16 * i) * E + e], 0.f));
+        float pr8[8], m8[8];
+        if (sb <= tmax) {                                   // warp-uniform: blocks above the warp's rows are all zero
+          tmem_ld8(tmem_row + sb, pr8);
+          tmem_ld8(tmem_row + 64 + sb, m8);
+          tmem_wait_ld();
+        }
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int s = sb + c;
-          float val = 0.f;
-          if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
-            float acc = 0.f;
-            if constexpr (E % 4 == 0) {
-#pragma unroll
-              for (int e = 0; e < E; e += 4) {
-                const float4 h4 = *reinterpret_cast<const float4*>(&sm.hd[s * E + e]);
-                acc = fmaf(G[e], h4.x, acc);
-                acc = fmaf(G[e + 1], h4.y, acc);
-                acc = fmaf(G[e + 2], h4.z, acc);
-                acc = fmaf(G[e + 3], h4.w, acc);
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < E; ++e) acc = fmaf(G[e], sm.hd[s * E + e], acc);
-            }
-            val = rowscale * pr[8 * i + c] * acc;
-          }
-          dst[mat_idx(t, s)] = val;
+          const bool in = sb <= tmax && (isq ? (s <= t) : (s < t));
+          dst[mat_idx(t, s)] = in ? rowscale * pr8[c] * m8[c] : 0.f;
+          if (!isq) sm.u.m.X[mat_idx(t, s)] = 0.f;        // the inverse fills in the blocks on and below the diagonal
         }
       }
     } else {
+      float my2[E], mygc[E];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        my2[e] = isq ? sm.q2[t * E + e] : sm.k2[t * E + e];
+        mygc[e] = sm.gc2[t * E + e];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int sb = 16 * i + 8 * ch;
+        float pr8[8];
+        tmem_ld8(tmem_row + sb, pr8);
+        tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           const int s = sb + c;
           float val = 0.f;
           if (sb <= tmax && (isq ? (s <= t) : (s < t))) {
             float acc = 0.f;
-            if constexpr (E % 4 == 0) {
 #pragma unroll
-              for (int e = 0; e < E; e += 4) {
-                const float4 g4 = *reinterpret_cast<const float4*>(&sm.gc2[s * E + e]);
-                const float4 k4 = *reinterpret_cast<const float4*>(&sm.k2[s * E + e]);
-                acc = fmaf(my2[e] * k4.x, fast_exp2(mygc[e] - g4.x), acc);
-                acc = fmaf(my2[e + 1] * k4.y, fast_exp2(mygc[e + 1] - g4.y), acc);
-                acc = fmaf(my2[e + 2] * k4.z, fast_exp2(mygc[e + 2] - g4.z), acc);
-                acc = fmaf(my2[e + 3] * k4.w, fast_exp2(mygc[e + 3] - g4.w), acc);
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < E; ++e)
-                acc = fmaf(my2[e] * sm.k2[s * E + e], fast_exp2(mygc[e] - sm.gc2[s * E + e]), acc);
-            }
-            val = rowscale * pr[8 * i + c] * acc;
+            for (int e = 0; e < E; ++e)
+              acc = fmaf(my2[e] * sm.k2[s * E + e], fast_exp2(mygc[e] - sm.gc2[s * E + e]), acc);
+            val = rowscale * pr8[c] * acc;
           }
           dst[mat_idx(t, s)] = val;
+          if (!isq) sm.u.m.X[mat_idx(t, s)] = 0.f;
         }
       }
     }
   }
+  tc_fence_before();
   __syncthreads();
 
   // triangular inverse X = (I + L)^-1: 16x16 diagonal blocks by forward substitution, then two merge levels
   float* L = sm.u.m.L;
   float* X = sm.u.m.X;
+  // 8x8 diagonal blocks by forward substitution (one column per thread)
   if (tid < 64) {
-    const int r0 = (tid >> 4) * 16, j = tid & 15;
-    float x[16];
+    const int r0 = (tid >> 3) * 8, j = tid & 7;
+    float x[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
       float acc = 0.f;
 #pragma unroll
       for (int k = 0; k < i; ++k) acc = fmaf(L[mat_idx(r0 + i, r0 + k)], x[k], acc);
       x[i] = (i == j) ? 1.f : (i < j ? 0.f : -acc);
     }
 #pragma unroll
-    for (int i = 0; i < 16; ++i) X[mat_idx(r0 + i, r0 + j)] = x[i];
-  } else {
-    // zero the blocks above the block diagonal, which the merges never write
-    for (int idx = tid - 64; idx < 4096; idx += MASK_THREADS - 64) {
-      const int i = idx >> 6, j = idx & 63;
-      if ((j >> 4) > (i >> 4)) X[mat_idx(i, j)] = 0.f;
-    }
+    for (int i = 0; i < 8; ++i) X[mat_idx(r0 + i, r0 + j)] = x[i];
+  }
+  __syncthreads();
+  // 8 -> 16: X21 = -X22 (L21 X11), one element per thread and step
+  {
+    const int r0 = (tid >> 6) * 16, i = (tid >> 3) & 7, j = tid & 7;
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc = fmaf(L[mat_idx(r0 + 8 + i, r0 + k)], X[mat_idx(r0 + k, r0 + j)], acc);
+    sm.T[tid] = acc;
+    __syncthreads();
+    float acc2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc2 = fmaf(X[mat_idx(r0 + 8 + i, r0 + 8 + k)], sm.T[(tid & ~63) + k * 8 + j], acc2);
+    X[mat_idx(r0 + 8 + i, r0 + j)] = -acc2;
   }
   __syncthreads();
   tri_merge_mma<16>(L, X, sm.T, warp, lane);
