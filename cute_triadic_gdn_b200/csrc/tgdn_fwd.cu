@@ -365,6 +365,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma[chain]);
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
+    // The chain finished with the previous chunk's tiles when its third MMA group completed.  It says so now, under this
+    // MMA, where its warps have time to spare; the last chain to say so refills that stage with the chunk STAGES ahead.
+    if (i > 0 && cwarp_u == 1 && elect_one()) {
+      const uint32_t done = atomicAdd(&ctrl.released[(i - 1) % STAGES], 1u) + 1u;
+      if (done % NCH == 0) {
+        if (i - 1 + STAGES < count) issue_loads(i - 1 + STAGES);
+        if (i + STAGES < count) prefetch_tiles(i + STAGES);
+      }
+    }
+    __syncwarp();
     // Under the MMA: this row's raw gate inputs and value row (in L2 since the previous chunk), then the gate factors.
     float ga[ET];                                    // this thread's slices.  K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
     float gr[ET];                                    // K rows: r_e = k2 exp(gL - gc)
@@ -533,16 +543,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
-    // This chain is done with the stage's tiles.  The last chain to say so refills the stage with the chunk STAGES ahead.
-    if (cwarp_u == 1 && elect_one()) {
-      __threadfence_block();
-      const uint32_t done = atomicAdd(&ctrl.released[st], 1u) + 1u;
-      if (done % NCH == 0) {
-        if (i + STAGES < count) issue_loads(i + STAGES);
-        if (i + STAGES + 1 < count) prefetch_tiles(i + STAGES + 1);
-      }
-    }
-    __syncwarp();
     {
       float dch[ET];                                 // exp(gL) of this thread's slices, written by this chain during (1)
 #pragma unroll
