@@ -120,7 +120,16 @@ struct FwdCfg {
   static constexpr bool TMA_GATES = E % 4 == 0;
   static constexpr int GT_BYTES = TMA_GATES ? 64 * E * 4 : 0;
   static constexpr int OFF_GT = (OFF_DT + NCH * 64 + 127) & ~127;
-  static constexpr int OFF_CTRL = OFF_GT + STAGES * 3 * GT_BYTES;
+  // per stage: the value rows of the CTA's columns, one box of 64 rows x CW columns per chain (TMA; a row of a box is at
+  // least 16 bytes), and the beta rows of the chunk for the four heads h & ~3 .. (TMA when H is a multiple of 4)
+  static constexpr bool TMA_V = CW >= 8;
+  static constexpr int VBOX_BYTES = 64 * CW * 2;
+  static constexpr int VT_BYTES = TMA_V ? NCH * VBOX_BYTES : 0;
+  static constexpr int OFF_VT = OFF_GT + STAGES * 3 * GT_BYTES;
+  static constexpr int OFF_BT = OFF_VT + STAGES * VT_BYTES;
+  static constexpr bool TMA_BETA = OFF_BT + STAGES * 1024 + 128 + 1024 <= 232448;   // where the beta rows still fit
+  static constexpr int BT_BYTES = TMA_BETA ? 1024 : 0;
+  static constexpr int OFF_CTRL = OFF_BT + STAGES * BT_BYTES;
   static constexpr int SMEM_BYTES = OFF_CTRL + 128 + 1024;    // + control block + alignment slack
   static_assert(CW == 4 || CW == 8 || CW == 16, "a chain owns 4, 8 or 16 value columns");
   static_assert(E % WPC == 0 && (WPC == 1 || ET % 2 == 0), "the slices split evenly over the chain's warpgroups");
@@ -139,10 +148,12 @@ struct FwdCtrl {
 
 template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
 __global__ void __launch_bounds__(NCH * WPC * 128, MINB)
-fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
+fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_beta,
+           const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
            const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
   using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   constexpr int TPC = C::TPC, VC = C::VC, ET = C::ET, TPT = C::TPT, CT = C::CHAIN_THREADS;
+  const bool beta_tma = C::TMA_BETA && p.beta_tma;
   constexpr bool LATE_R = C::TMA_GATES && E >= 12;   // form r_e after the epilogue of (1) (register pressure at many slices)
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -257,7 +268,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int st = i % STAGES;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + 3 * C::GT_BYTES);
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + 3 * C::GT_BYTES + C::VT_BYTES + (beta_tma ? C::BT_BYTES : 0));
+    if constexpr (C::TMA_V) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+        tma_load_4d(smem + C::OFF_VT + st * C::VT_BYTES + c * C::VBOX_BYTES, &map_v, &ctrl.bar_load[st], vb * VC + c * CW, h, t0, b);
+    }
+    if (beta_tma) tma_load_4d(smem + C::OFF_BT + st * C::BT_BYTES, &map_beta, &ctrl.bar_load[st], 0, h >> 2, t0, b);
     if constexpr (C::TMA_GATES) {
       uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
       bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
@@ -289,8 +306,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
     if (krow) {
       if (!C::TMA_GATES) prefetch_l2(p.k2 + ro * E);
-      prefetch_l2(p.beta + ro);
-      prefetch_l2(p.v + ro * HEAD + v0g);
+      if (!beta_tma) prefetch_l2(p.beta + ro);
+      if (!C::TMA_V) prefetch_l2(p.v + ro * HEAD + v0g);
     } else if (!C::TMA_GATES) {
       prefetch_l2(p.q2 + ro * E);
       prefetch_l2(p.gc + item * (64 * E) + t * E);
@@ -350,10 +367,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     uint8_t* ap = smem + C::OFF_AP + st * C::AP_BYTES;
 
     // ---- (1) R = [K;Q] S --------------------------------------------------------------------------------------
-    // Only the chain's first warp polls an mbarrier; the other three sleep in the chain's hardware barrier until it has
-    // seen the flip.  Twelve more spinning warps per SM would take their share of the issue slots from the warps of the
-    // other chains that are in an epilogue at that moment.
-    if (cwarp_u == 0 || C::TMA_GATES) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    // Every thread reads rows of the stage (gates, value row, beta) under the MMA, so every warp waits for the loads itself.
+    // (The MMA completions below are polled by the chain's first warp only: the other three sleep in the chain's hardware
+    // barrier, where they take no issue slots from the chains that are in an epilogue at that moment.)
+    if (cwarp_u == 0 || C::TMA_GATES || C::TMA_V) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (cwarp_u == 0 && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -401,8 +418,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       if (krow) {
         if (sw == 0) {                               // the warpgroup that completes W: beta and the value row
-          bt = __ldg(p.beta + ro);
-          load_vrow(t0, rows, vraw);
+          if (beta_tma) bt = reinterpret_cast<const float*>(smem + C::OFF_BT + st * C::BT_BYTES)[t * 4 + (h & 3)];
+          else bt = __ldg(p.beta + ro);
+          if constexpr (C::TMA_V) {
+            const uint32_t va = smem_u32(smem + C::OFF_VT + st * C::VT_BYTES + chain * C::VBOX_BYTES) + t * (CW * 2);
+#pragma unroll
+            for (int c = 0; c < CW / 2; c += 4)
+              asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(vraw[c]), "=r"(vraw[c + 1]), "=r"(vraw[c + 2]), "=r"(vraw[c + 3]) : "r"(va + c * 4));
+          } else {
+            load_vrow(t0, rows, vraw);
+          }
         }
         if (sw == 0 && t < E) {
           float glt;
@@ -594,7 +619,7 @@ using namespace tgdn;
 
 template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
 static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
-                      const FwdParams& p, cudaStream_t s) {
+                      const void* v, const FwdParams& p, cudaStream_t s) {
   using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   static_assert(MINB == 1 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
@@ -607,8 +632,17 @@ static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
     if (e != cudaSuccess) return tgdn_cuda_error(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
+  CUtensorMap mv = mk, mb = mk;                     // placeholders where the rows are not loaded by TMA
+  if (C::TMA_V) {
+    const int rc = tgdn_make_token_map(&mv, v, p.B, p.T, p.H, CW, 64, 0);
+    if (rc) return rc;
+  }
+  if (C::TMA_BETA && p.beta_tma) {
+    const int rc = tgdn_make_gate_map(&mb, p.beta, p.B, p.T, p.H / 4, 4);    // (B, T, H) read as (B, T, H/4, 4)
+    if (rc) return rc;
+  }
   const int grid = p.n_seq * p.H * (HEAD / C::VC);
-  fwd_kernel<E, CW, NCH, WPC, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, p);
+  fwd_kernel<E, CW, NCH, WPC, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mv, mb, mk, mq, mk2, mq2, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -638,24 +672,25 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
   FwdParams p{static_cast<const __nv_bfloat16*>(v), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<__nv_bfloat16*>(o), static_cast<__nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(U),
               static_cast<__nv_bfloat16*>(h), state_in, state_out, doc_offsets, chunk_map, B, T, H, NC,
-              packed ? n_docs : B, scale, tgdn_status_word()};
+              packed ? n_docs : B, scale, tgdn_status_word(),
+              (H % 4 == 0 && (reinterpret_cast<uintptr_t>(beta) & 15) == 0) ? 1 : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 16, 2, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 2: return launch_fwd<2, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 1: return launch_fwd<1, 16, 2, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+    case 2: return launch_fwd<2, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
     case 4: {
       // One CTA per SM: the grid runs in whole waves.  Where a block of 32 value columns needs a second, partly filled wave
       // and a block of 64 does not, the wider block wins although its chunks take a little longer (B=4, H=16: 256 CTAs on
       // 148 SMs are two waves, 128 CTAs are one).
       const long long sms = tgdn_sm_count(), seqs = static_cast<long long>(p.n_seq) * p.H;
       const long long waves32 = (seqs * 4 + sms - 1) / sms, waves64 = (seqs * 2 + sms - 1) / sms;
-      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
-      return launch_fwd<4, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
+      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+      return launch_fwd<4, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
     }
     // (two warpgroups per chain at E = 8, sixteen columns per thread, measured 17% slower than four one-warpgroup chains)
-    case 8: return launch_fwd<8, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 12: return launch_fwd<12, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
-    case 16: return launch_fwd<16, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, p, s);
+    case 8: return launch_fwd<8, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+    case 12: return launch_fwd<12, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+    case 16: return launch_fwd<16, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, v, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

@@ -53,6 +53,7 @@ struct FwdParams {
   int B, T, H, NC, n_seq;   // n_seq = documents (packed) or batch rows (dense)
   float scale;
   int* status;
+  int beta_tma;             // beta rows of a chunk arrive by TMA (H a multiple of 4, base 16-byte aligned), else by global loads
 };
 
 struct RecParams {
