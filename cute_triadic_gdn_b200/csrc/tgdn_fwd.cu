@@ -153,6 +153,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
            const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
   using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   constexpr int TPC = C::TPC, VC = C::VC, ET = C::ET, TPT = C::TPT, CT = C::CHAIN_THREADS;
+  // Roles inside a chain: its key-row warps (0, 1) have the longer epilogues (gate factors r_e, the operand images of W
+  // and of r_e U), so the query-row warps take the extra work: warp 2 issues the MMAs and polls their barrier, warp 3
+  // hands stages back and issues the loads.
+  constexpr int ISSUE_WARP = 2, REFILL_WARP = 3;
   const bool beta_tma = C::TMA_BETA && p.beta_tma;
   constexpr bool LATE_R = C::TMA_GATES && E >= 12;   // form r_e after the epilogue of (1) (register pressure at many slices)
   constexpr float LOG2E = 1.4426950408889634f;
@@ -370,8 +374,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     // Every thread reads rows of the stage (gates, value row, beta) under the MMA, so every warp waits for the loads itself.
     // (The MMA completions below are polled by the chain's first warp only: the other three sleep in the chain's hardware
     // barrier, where they take no issue slots from the chains that are in an epilogue at that moment.)
-    if (cwarp_u == 0 || C::TMA_GATES || C::TMA_V) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
-    if (cwarp_u == 0 && elect_one()) {
+    if (cwarp_u == ISSUE_WARP || C::TMA_GATES || C::TMA_V) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    if (cwarp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(s_img), 128, 2048, LAYOUT_PLAIN);
@@ -384,7 +388,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     // The chain finished with the previous chunk's tiles when its third MMA group completed.  It says so now, under this
     // MMA, where its warps have time to spare; the last chain to say so refills that stage with the chunk STAGES ahead.
-    if (i > 0 && cwarp_u == 1 && elect_one()) {
+    if (i > 0 && cwarp_u == REFILL_WARP && elect_one()) {
       const uint32_t done = atomicAdd(&ctrl.released[(i - 1) % STAGES], 1u) + 1u;
       if (done % NCH == 0) {
         if (i - 1 + STAGES < count) issue_loads(i - 1 + STAGES);
@@ -451,7 +455,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       }
       if (i + 2 < count) prefetch_rows(i + 2);
     }
-    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    if (cwarp_u == ISSUE_WARP) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
@@ -505,7 +509,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     chain_sync<CT>(chain);
 
     // ---- (2) [U;Oi] = [A;PmA] (beta W) ------------------------------------------------------------------------
-    if (cwarp_u == 0 && elect_one()) {
+    if (cwarp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(ap), 2048, 128, LAYOUT_PLAIN);
       const uint64_t db = make_desc(smem_u32(bw_img), 128, 1024, LAYOUT_PLAIN);
@@ -527,7 +531,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
         for (int e = 0; e < ET; ++e) gr[e] = live ? k2r[e] * fexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
       }
     }
-    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    if (cwarp_u == ISSUE_WARP) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
@@ -553,7 +557,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     chain_sync<CT>(chain);
 
     // ---- (3) dS = K^T Vn, S <- d S + dS -----------------------------------------------------------------------
-    if (cwarp_u == 0 && elect_one()) {
+    if (cwarp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(vn_img), 128, 1024, LAYOUT_PLAIN);
@@ -564,7 +568,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma[chain]);
     }
     __syncwarp();
-    if (cwarp_u == 0) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    if (cwarp_u == ISSUE_WARP) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     chain_sync<CT>(chain);
     ++mma_phase;
     tc_fence_after();
