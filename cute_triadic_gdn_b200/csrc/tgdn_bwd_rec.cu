@@ -179,6 +179,10 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_fence_init();
     ctrl.abort = 0;
   }
+  // Roles: the key-row warps (0, 1 of a warpgroup) build the gate factors r_e and the operand of (p) under the first MMA
+  // group, so two query-row warps of the first warpgroup take the extra work: warp 2 issues the MMAs, warp 3 every load and
+  // store of the CTA.
+  constexpr int ISSUE_WARP = 2, COPY_WARP = 3;
   if (warp == 0) { tmem_alloc(&ctrl.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
   float G[TPC];
 #pragma unroll
@@ -319,7 +323,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     return __ldg(p.gc + item * (64 * E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
   };
 
-  if (warp_u == 1 && elect_one()) {                 // the lane that issues every load and every store of this CTA
+  if (warp_u == COPY_WARP && elect_one()) {                 // the lane that issues every load and every store of this CTA
     issue_loads(count - 1, 0);
     if constexpr (C::LATE) {
       mbar_expect_tx(&ctrl.bar_late, LATE_TX);
@@ -362,7 +366,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     // ---- (a) KG = [K;Q] G and Y = Pm^T dO -----------------------------------------------------------------------
     mbar_wait(&ctrl.bar_load[st], (STAGES == 2 ? (kstep >> 1) : kstep) & 1, ctl, DEV_TIMEOUT_LOAD);
     if constexpr (C::LATE) mbar_wait(&ctrl.bar_late, kstep & 1, ctl, DEV_TIMEOUT_LOAD);
-    if (warp_u == 0 && elect_one()) {
+    if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       {
         const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -383,7 +387,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma);
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    if (warp_u == 1 && kstep + 1 < count && elect_one()) {
+    if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
       if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
     }
     __syncwarp();
@@ -471,7 +475,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (c) Z = A^T dU, then (p) P = G Xu^T behind it ----------------------------------------------------------
-    if (warp_u == 0 && elect_one()) {
+    if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       {
         const uint64_t da = make_desc(smem_u32(am), 128, 1024, LAYOUT_PLAIN);         // A^T: MN-major over (i = t, j = s)
@@ -493,7 +497,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
-    if (warp_u == 1 && elect_one()) {                // dU (chunk layout) straight from its operand image
+    if (warp_u == COPY_WARP && elect_one()) {                // dU (chunk layout) straight from its operand image
 #pragma unroll
       for (int jb = 0; jb < VC / 8; ++jb)
         tma_store_4d(&map_du, duimg + jb * 1024, vb * VC + jb * 8, 0, static_cast<int>(item * 64), 0);
@@ -540,13 +544,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
     // ---- (d) dG = [K^T | Q^T] X, G <- d G + dG ------------------------------------------------------------------
     if constexpr (C::LATE) {                         // Pm, A and the gate rows of this chunk are dead: request the next chunk's
-      if (warp_u == 1 && kstep + 1 < count && elect_one()) {
+      if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
         mbar_expect_tx(&ctrl.bar_late, LATE_TX);
         issue_late(i - 1, 0, &ctrl.bar_late);
       }
       __syncwarp();
     }
-    if (warp_u == 0 && elect_one()) {
+    if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_GX), 128, 2048, LAYOUT_PLAIN);
@@ -578,7 +582,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
-    if (STAGES == 1 && warp_u == 1 && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
+    if (STAGES == 1 && warp_u == COPY_WARP && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
     __syncwarp();
     {
       constexpr int PIECE = TPC < 16 ? TPC : 16;
@@ -624,7 +628,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
   }
-  if (warp_u == 1 && elect_one()) bulk_wait_group();   // the last store of dU reads shared memory of this CTA
+  if (warp_u == COPY_WARP && elect_one()) bulk_wait_group();   // the last store of dU reads shared memory of this CTA
   __syncwarp();
   if (warp == 0) tmem_dealloc(tmem, C::TMEM_COLS);
 }
