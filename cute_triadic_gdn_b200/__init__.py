@@ -8,13 +8,16 @@ Same names, signatures, shapes and dtypes as cute_triadic_gdn/__init__.py:7-11 o
 
 Beyond the reference's surface:
 
+    gdn_joint_decode                one token per sequence on a resident state (continues what
+                                    chunk_gdn_joint(..., output_final_state=True) hands out)
     HostPipeline / gdn_joint_host   inputs and results in pinned host memory; uploads, kernels and downloads of
                                     successive batch slices overlap on three streams (host_pipeline.py)
 """
 from .conv_split_act import conv_split_act_call
-from .gdn_joint import chunk_gdn_joint
+from .gdn_joint import chunk_gdn_joint, gdn_joint_decode
 from .host_pipeline import HostPipeline, gdn_joint_host
 from .joint_torch_ops import gdn_joint_call
 
-__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call", "HostPipeline", "gdn_joint_host"]
+__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call", "gdn_joint_decode", "HostPipeline",
+           "gdn_joint_host"]
 __version__ = "0.1.0"

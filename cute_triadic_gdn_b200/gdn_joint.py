@@ -257,3 +257,38 @@ def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, refer
     if needs_grad:
         return _JointKernels.apply(q, k, v, k2, q2, g, beta, float(scale), chunk_starts, token_map)
     return _kernel_forward(q, k, v, k2, q2, g, beta, float(scale), False, chunk_starts, token_map)[0]
+
+
+def gdn_joint_decode(q, k, v, k2, q2, g, beta, state, scale=None):
+    """One token per sequence on a resident state (decode).  No counterpart in the reference.
+
+    q, k, v: bf16 (B, 1, H, 128) or (B, H, 128); k2, q2, g: f32 (B, 1, H, E) or (B, H, E); beta: f32 (B, 1, H) or (B, H);
+    `state`: contiguous f32 (B, H, E, 128, 128), the form `chunk_gdn_joint(..., output_final_state=True)` returns; it is
+    updated IN PLACE.  Returns o in the shape of v.  Forward only."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, k2, q2, g, beta, state)):
+        raise ValueError("gdn_joint_decode is forward-only: run it under torch.no_grad()")
+    squeeze = q.dim() == 4
+    if squeeze:
+        if q.shape[1] != 1:
+            raise ValueError("gdn_joint_decode takes one token per sequence: T must be 1")
+        q, k, v, k2, q2, g, beta = (t[:, 0] for t in (q, k, v, k2, q2, g, beta))
+    if q.dim() != 3 or q.shape[-1] != HEAD_DIM or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError("q, k, v must be (B, H, 128) (or (B, 1, H, 128)) and agree")
+    B, H, _ = q.shape
+    E = k2.shape[-1]
+    if tuple(k2.shape) != (B, H, E) or q2.shape != k2.shape or g.shape != k2.shape or tuple(beta.shape) != (B, H):
+        raise ValueError("k2, q2, g must be (B, H, E) and beta (B, H)")
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v)) or any(t.dtype != torch.float32 for t in (k2, q2, g, beta)):
+        raise ValueError("q, k, v must be bfloat16 and k2, q2, g, beta float32")
+    _check_device_and_e(q, E)
+    if tuple(state.shape) != (B, H, E, 128, 128) or state.dtype != torch.float32 or state.device != q.device \
+            or not state.is_contiguous():
+        raise ValueError(f"state must be a contiguous f32 tensor of shape {(B, H, E, 128, 128)} on the inputs' device")
+    scale = HEAD_DIM ** -0.5 if scale is None else scale
+    q, k, v, k2, q2, g, beta = (t.contiguous() for t in (q, k, v, k2, q2, g, beta))
+    o = torch.empty_like(v)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib.tgdn_decode_step(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(g),
+                                             _lib.ptr(beta), float(scale), B, H, E, _lib.ptr(state), _lib.ptr(o),
+                                             _lib.stream_of(q)), "tgdn_decode_step")
+    return o[:, None] if squeeze else o

@@ -124,6 +124,13 @@ int tgdn_fwd_state(const void* q, const void* k, const void* v, const float* k2,
                    int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h,
                    const float* state_in, float* state_out, void* stream);
 
+/* tgdn_decode_step: one token of the recurrence on a resident state (decode).  q, k, v bf16 (B, H, 128); k2, q2, g f32
+ * (B, H, E); beta f32 (B, H); state f32 (B, H, E, 128 key rows, 128 value columns), 16-byte aligned, updated in place (the
+ * form tgdn_fwd_state hands out); o bf16 (B, H, 128).  Token-by-token definition of
+ * cute_triadic_gdn/ops/gdn_joint.py:45-90; the reference itself has no decode entry. */
+int tgdn_decode_step(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* g,
+                     const float* beta, float scale, int B, int H, int E, float* state, void* o, void* stream);
+
 /* tgdn_bwd_recurrent: the reverse chunk recurrence.  Reads the upstream gradient dO (token layout) and the forward's
  * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), dr f32 [item][128/VC][64][E]
  * (VC = 32 for E <= 4, 16 for E >= 8), dkg, per value block the part of dK that contracts the gradient state over the
