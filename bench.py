@@ -79,7 +79,7 @@ def ncu_traffic(name, E, items):
 # written by fwd, read by sg) and the value-block images of the reverse recurrence are consequences of the decomposition,
 # not of the algorithm: `io_bytes` below counts only what the algorithm itself must move.
 def kernel_bytes(name, E):
-    K, NV, gates = 1024, (8 if E >= 8 else 4), 3 * 64 * E * 4
+    K, NV, gates = 1024, (8 if E > 8 else 4), 3 * 64 * E * 4
     return {
         "masks": 32 * K + gates + 256 + 64 * E * 4 + 24 * K,
         "fwd": 48 * K + 16 * K + gates + 256 + 48 * K + 32 * K * E,
@@ -335,6 +335,30 @@ def conv_rates(dev, T=32768, C=13056, act=12288, reps=5):
     return 4 * T * C / (f * 1e-3) / 1e9, 6 * T * C / (bw * 1e-3) / 1e9, f, bw
 
 
+def decode_rate(dev, B=8, H=32, E=8, reps=10):
+    """Achieved GB/s of the one-token decode step at the head count and slice count of configuration 2: the state
+    (B*H*E*64 KB f32, larger than L2) is read once and written once per token; everything else is a few KB."""
+    from cute_triadic_gdn_b200 import gdn_joint_decode
+    gen = torch.Generator(device=dev).manual_seed(3)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    q, k, v = (rn(B, H, 128).to(torch.bfloat16) for _ in range(3))
+    k2, q2 = rn(B, H, E), rn(B, H, E)
+    g, beta = -torch.nn.functional.softplus(rn(B, H, E)), torch.sigmoid(rn(B, H))
+    state = torch.zeros(B, H, E, 128, 128, device=dev)
+    with torch.no_grad():
+        for _ in range(3):
+            gdn_joint_decode(q, k, v, k2, q2, g, beta, state)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            gdn_joint_decode(q, k, v, k2, q2, g, beta, state)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return 2 * state.numel() * 4 / (ms * 1e-3) / 1e9, ms
+
+
 def reference_kernel_timing(timeout_s=420):
     """What the reference's own CuTe-DSL kernels do on this GPU, measured by baseline/time_reference_kernels.py in a child
     process (a compile failure of the DSL must not take the bench down).  Needs the reference installed under
@@ -530,6 +554,9 @@ def run_ours(args, rank, world, local_rank):
         aux.update({"conv_fwd_gbs": fg, "conv_bwd_gbs": bg, "conv_fwd_ms": fms, "conv_bwd_ms": bms,
                     "conv_frac": fg / pk["gbs"], "conv_bwd_frac": bg / pk["gbs"],
                     "conv_workload": "x (1, 32768, 13056) bf16, 8 documents, SiLU on 12288 channels; bytes 4*T*C forward, 6*T*C backward"})
+        dg, dms = decode_rate(dev)
+        aux.update({"decode_gbs": dg, "decode_us_per_token": dms * 1e3, "decode_frac": dg / pk["gbs"],
+                    "decode_workload": "one token, B=8 H=32 E=8: state 268 MB f32 read and written once"})
     cpu_rate, n_slices, threads, per_slice = cpu_reference_rate(B, T, H, E, backward, budget_s=15.0)
     refk = reference_kernel_timing() if (world == 1 and not args.no_reference_kernels) else None
     line = {"metric": "fwd+bwd tokens/s" if backward else "fwd tokens/s", "value": value, "unit": "tokens/s",

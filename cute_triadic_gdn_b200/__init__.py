@@ -8,16 +8,18 @@ Same names, signatures, shapes and dtypes as cute_triadic_gdn/__init__.py:7-11 o
 
 Beyond the reference's surface:
 
+    conv_split_norm_call            the convolution with the layer glue fused in: x -> (q, k, v, k2, q2) as the core
+                                    takes them (SiLU / softplus, l2 norms), differentiable
     gdn_joint_decode                one token per sequence on a resident state (continues what
                                     chunk_gdn_joint(..., output_final_state=True) hands out)
     HostPipeline / gdn_joint_host   inputs and results in pinned host memory; uploads, kernels and downloads of
                                     successive batch slices overlap on three streams (host_pipeline.py)
 """
-from .conv_split_act import conv_split_act_call
+from .conv_split_act import conv_split_act_call, conv_split_norm_call
 from .gdn_joint import chunk_gdn_joint, gdn_joint_decode
 from .host_pipeline import HostPipeline, gdn_joint_host
 from .joint_torch_ops import gdn_joint_call
 
-__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call", "gdn_joint_decode", "HostPipeline",
+__all__ = ["chunk_gdn_joint", "gdn_joint_call", "conv_split_act_call", "conv_split_norm_call", "gdn_joint_decode", "HostPipeline",
            "gdn_joint_host"]
 __version__ = "0.1.0"

@@ -113,3 +113,92 @@ def conv_split_act_call(x, weight, act_channels, cu_seqlens=None):
     channels pass through SiLU.  With `cu_seqlens` (offsets of the documents of one packed row, B = 1) the window starts
     afresh at every document.  Same call as the reference's conv_split_act_call (ops/conv_split_act.py:194-197)."""
     return conv_split_act_fwd(x, weight.contiguous(), int(act_channels), cu_seqlens)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# The layer glue fused into the convolution (beyond the reference's surface; it describes the glue at
+# cute_triadic_gdn/ops/conv_split_act.py:3-5 and leaves it to its caller)
+# ----------------------------------------------------------------------------------------------------------------------
+def _glue_dims(x, H, E):
+    C = x.shape[2]
+    if H <= 0 or C != H * (3 * 128 + 2 * E) or E not in (1, 2, 4, 8, 12, 16):
+        raise ValueError(f"conv_split_norm: C={C} is not H*(3*128 + 2*E) for H={H}, E={E} (E in 1, 2, 4, 8, 12, 16)")
+    if C % 8:
+        raise ValueError("conv_split_norm: the channel count must be a multiple of 8")
+
+
+@custom_op("tgdn_b200::conv_split_norm_fwd", mutates_args=(), device_types="cuda")
+def conv_split_norm_fwd(x: torch.Tensor, weight: torch.Tensor, heads: int, slices: int, eps: float,
+                        cu_seqlens: Optional[torch.Tensor] = None
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    _glue_dims(x, heads, slices)
+    x, weight, cu, n_docs, _ = _prep(x, weight, cu_seqlens)
+    B, T, C = x.shape
+    q, k, v = (torch.empty((B, T, heads, 128), dtype=torch.bfloat16, device=x.device) for _ in range(3))
+    k2, q2 = (torch.empty((B, T, heads, slices), dtype=torch.float32, device=x.device) for _ in range(2))
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib.tgdn_glue_fwd(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(cu), n_docs, B, T, C, x.stride(0),
+                                          x.stride(1), heads, slices, float(eps), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+                                          _lib.ptr(k2), _lib.ptr(q2), _lib.stream_of(x)), "tgdn_glue_fwd")
+    return q, k, v, k2, q2
+
+
+@conv_split_norm_fwd.register_fake
+def _(x, weight, heads, slices, eps, cu_seqlens=None):
+    B, T, _ = x.shape
+    qkv = [x.new_empty((B, T, heads, 128)) for _ in range(3)]
+    gates = [x.new_empty((B, T, heads, slices), dtype=torch.float32) for _ in range(2)]
+    return (*qkv, *gates)
+
+
+@custom_op("tgdn_b200::conv_split_norm_bwd", mutates_args=(), device_types="cuda")
+def conv_split_norm_bwd(x: torch.Tensor, weight: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor,
+                        dk2: torch.Tensor, dq2: torch.Tensor, heads: int, slices: int, eps: float,
+                        cu_seqlens: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
+    wdtype = weight.dtype
+    x, weight, cu, n_docs, _ = _prep(x, weight, cu_seqlens)
+    B, T, C = x.shape
+    dq, dk, dv = (t.to(torch.bfloat16).contiguous() for t in (dq, dk, dv))
+    dk2, dq2 = (t.to(torch.float32).contiguous() for t in (dk2, dq2))
+    dy = torch.empty((B, T, C), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib.tgdn_glue_bwd_norm(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(cu), n_docs, B, T, C, x.stride(0),
+                                               x.stride(1), heads, slices, float(eps), _lib.ptr(dq), _lib.ptr(dk),
+                                               _lib.ptr(dv), _lib.ptr(dk2), _lib.ptr(dq2), _lib.ptr(dy),
+                                               _lib.stream_of(x)), "tgdn_glue_bwd_norm")
+    dx, dw = conv_split_act_bwd(x, dy, weight, 3 * heads * 128, cu)
+    return dx, dw.to(wdtype)
+
+
+@conv_split_norm_bwd.register_fake
+def _(x, weight, dq, dk, dv, dk2, dq2, heads, slices, eps, cu_seqlens=None):
+    return torch.empty_like(x, memory_format=torch.contiguous_format), torch.empty_like(weight)
+
+
+def _glue_remember(ctx, inputs, output):
+    x, weight, heads, slices, eps, cu_seqlens = inputs
+    ctx.save_for_backward(*([x, weight] + ([] if cu_seqlens is None else [cu_seqlens])))
+    ctx.glue = (int(heads), int(slices), float(eps))
+
+
+def _glue_differentiate(ctx, dq, dk, dv, dk2, dq2):
+    kept = ctx.saved_tensors
+    offsets = kept[2] if len(kept) == 3 else None
+    heads, slices, eps = ctx.glue
+    dx, dw = conv_split_norm_bwd(kept[0], kept[1], dq, dk, dv, dk2, dq2, heads, slices, eps, offsets)
+    return dx, dw, None, None, None, None
+
+
+register_autograd("tgdn_b200::conv_split_norm_fwd", _glue_differentiate, setup_context=_glue_remember)
+
+
+def conv_split_norm_call(x, weight, heads, slices, cu_seqlens=None, eps=1e-6):
+    """The convolution pre-pass with the layer glue fused in: x (B, T, C) bf16 with C = heads*(3*128 + 2*slices) channels
+    laid out [q | k | v | k2 | q2] goes straight to what `gdn_joint_call` takes,
+
+        q, k = l2norm(SiLU(conv(x)))  bf16 (B, T, heads, 128)      v = SiLU(conv(x))  bf16 (B, T, heads, 128)
+        k2, q2 = l2norm(softplus(conv(x)))  f32 (B, T, heads, slices),     l2norm(s) = s * rsqrt(sum s^2 + eps),
+
+    without the convolution's output ever being written.  Differentiable in x and weight; packed rows as in
+    `conv_split_act_call`."""
+    return conv_split_norm_fwd(x, weight.contiguous(), int(heads), int(slices), float(eps), cu_seqlens)

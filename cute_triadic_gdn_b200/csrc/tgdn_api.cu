@@ -125,7 +125,7 @@ int tgdn_sm_count() {
   return n;
 }
 
-int tgdn_value_block(int E) { return E >= 8 ? 16 : 32; }   // must match the dispatch in tgdn_bwd_rec.cu
+int tgdn_value_block(int E) { return E > 8 ? 16 : 32; }   // must match the dispatch in tgdn_bwd_rec.cu
 
 extern "C" const char* tgdn_error_string(int code) {
   static thread_local char buf[160];

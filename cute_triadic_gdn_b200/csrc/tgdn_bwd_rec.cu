@@ -698,7 +698,10 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
     case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 8: return launch_rec<8, 16, 2, 1>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    // E = 8: four warpgroups on 32 value columns with a two-stage ring, one CTA per SM, measured 9% faster than two CTAs
+    // per SM of two warpgroups on 16 columns each (5.26 -> 4.77 ms at B=8, T=8192, H=32), and the state-gradient kernel
+    // then adds four value-block images per item instead of eight.
+    case 8: return launch_rec<8, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     case 12: return launch_rec<12, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     case 16: return launch_rec<16, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     default: return TGDN_ERR_SHAPE;

@@ -10,6 +10,7 @@
 // forward for it), so x and dy are read once and dx written once; the weight gradient is accumulated in registers
 // over all tiles of the CTA, reduced across its warps in shared memory and written as one f32 partial per CTA; a
 // second small kernel sums the partials in a fixed order.
+#include <algorithm>
 #include <mutex>
 
 #include "tgdn_common.cuh"
@@ -656,4 +657,267 @@ extern "C" int tgdn_conv_bwd_static(const void* x, const void* weight, const voi
   if ((rc = conv_static_scratch(&scratch))) return rc;
   return conv_bwd_launch(x, weight, dy, dx, dw, cu_seqlens, n_docs, B, T, C, stride_b, stride_t, dy_stride_b, dy_stride_t,
                          act_channels, scratch, static_cast<cudaStream_t>(stream));
+}
+
+// ----------------------------------------------------------------------------------------------------------------------
+// The layer glue around the convolution, fused: x (B, T, C) with C = H (3*128 + 2E) channels laid out as
+// [q: H x 128 | k: H x 128 | v: H x 128 | k2: H x E | q2: H x E] goes straight to the tensors the core takes:
+//   q, k  = l2norm(SiLU(conv))   bf16 (B, T, H, 128)         v = SiLU(conv)   bf16 (B, T, H, 128)
+//   k2, q2 = l2norm(softplus(conv))   f32 (B, T, H, E)        l2norm(s) = s * rsqrt(sum s^2 + eps)
+// which the reference only describes (cute_triadic_gdn/ops/conv_split_act.py:3-5: "q, k, v (SiLU) and its second key and
+// query (no activation, softplus afterwards)"); its callers run the split, the activations and the norms as separate
+// elementwise passes over (T, C).  Here nothing of the convolution's output is written in between.
+//
+// Main kernel (both directions): the forward's tiling, a warp owning one head's 128 channels of 8 token rows, so that a
+// head's norm is a sum over the 32 lanes.  Forward: writes q, k, v.  Backward: recomputes s = SiLU(conv) from the same x
+// window, takes the gradients of q, k, v and writes the gradient of s, which is what the convolution's own backward takes:
+//   ds = r dy - r^3 <s, dy> s,   r = rsqrt(sum s^2 + eps)              (v: ds = dv)
+// Gate kernel (both directions): one thread per (token, head, k2 | q2), E channels each, straight from global memory (the
+// gate channels are 2E of 384 + 2E per head).  Backward writes dc = du * sigmoid(c) with du as above for u = softplus(c).
+// ----------------------------------------------------------------------------------------------------------------------
+namespace tgdn {
+
+struct GlueArgs {
+  const __nv_bfloat16* weight;
+  const int32_t* cu;
+  int n_docs, T, C, H, E, tiles_per_group;
+  float eps;
+  // forward: outputs; backward: the gradients of the same tensors
+  __nv_bfloat16 *q, *k, *v;      // (B, T, H, 128) each
+  float *k2, *q2;                // (B, T, H, E) each
+  __nv_bfloat16* dy;             // backward: (B, T, C) gradient for the convolution's backward
+  const __nv_bfloat16* x;        // gate kernel: the input itself (element strides below)
+  int64_t stride_b, stride_t;
+  int* status;
+};
+
+template <bool BWD>
+__global__ void __launch_bounds__(CONV_THREADS, BWD ? 3 : 4)
+glue_main_kernel(const __grid_constant__ CUtensorMap map_x, GlueArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  constexpr int STAGE_BYTES = CONV_FWD_ROWS * CONV_CH * 2;
+  __shared__ uint64_t full[CONV_FWD_STAGES];
+  __shared__ int abort_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int half = warp & 1, rg = warp >> 1;
+  const int cbase = blockIdx.x * CONV_CH, c0 = cbase + half * 128 + lane * CONV_VEC, b = blockIdx.z;
+  const int n_tiles = (a.T + CONV_TOK - 1) / CONV_TOK;
+  const int tile_lo = blockIdx.y * a.tiles_per_group, tile_hi = min(n_tiles, tile_lo + a.tiles_per_group);
+  if (tile_lo >= tile_hi) return;
+  if (tid == 0) {
+    for (int s = 0; s < CONV_FWD_STAGES; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+    abort_s = 0;
+  }
+  __syncthreads();
+  WaitCtl ctl{&abort_s, a.status};
+  auto issue = [&](int tile) {                         // thread 0
+    const int s = (tile - tile_lo) % CONV_FWD_STAGES;
+    mbar_expect_tx(&full[s], STAGE_BYTES);
+    tma_load_3d(smem + s * STAGE_BYTES, &map_x, &full[s], cbase, tile * CONV_TOK - 3, b);
+  };
+  if (tid == 0)
+    for (int i = 0; i < CONV_FWD_STAGES && tile_lo + i < tile_hi; ++i) issue(tile_lo + i);
+
+  // this warp's head: unit = which 128-channel block of [q heads | k heads | v heads]
+  const int unit = (cbase + half * 128) >> 7;
+  const bool live = unit < 3 * a.H;                    // a last, half-filled channel tile
+  const int region = live ? unit / a.H : 0, head = live ? unit % a.H : 0;
+  const bool normed = region < 2;
+  float2 w2[2][CONV_W];
+  load_weights(a.weight, c0, live ? a.C : 0, w2);
+  __nv_bfloat16* tb = (region == 0 ? a.q : region == 1 ? a.k : a.v) + ((static_cast<int64_t>(b) * a.T) * a.H + head) * HEAD + lane * CONV_VEC;
+  __nv_bfloat16* dyb = BWD ? a.dy + (static_cast<int64_t>(b) * a.T) * a.C + c0 : nullptr;
+  const int col_off = half * 256 + lane * 8;
+  const int64_t trow = static_cast<int64_t>(a.H) * HEAD;    // elements between token rows of q, k, v
+
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int k = tile - tile_lo, s = k % CONV_FWD_STAGES;
+    mbar_wait(&full[s], (k / CONV_FWD_STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    const uint8_t* st = smem + s * STAGE_BYTES + col_off;
+    const int t_first = tile * CONV_TOK + rg * 8;
+    DocCursor doc;
+    doc.init(a.cu, a.n_docs, min(t_first, a.T - 1), a.T);
+    Vec4 xm[3];                                           // x[t-1], x[t-2], x[t-3]
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      const int tj = t_first - 1 - j;
+      xm[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
+    }
+    const int n_rows = live ? min(8, a.T - t_first) : 0;
+    // the gradient rows of this warp's eight tokens are asked for before the arithmetic needs them
+    uint2 gin[8];
+    if constexpr (BWD) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        gin[i] = (i < n_rows) ? __ldg(reinterpret_cast<const uint2*>(tb + (t_first + i) * trow)) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i >= n_rows) break;                              // warp-uniform
+      if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
+      const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
+      Vec4 sv;
+      float ss = 0.f;
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+        float2 acc = __fmul2_rn(xm[2].p[p], w2[p][0]);
+        acc = __ffma2_rn(xm[1].p[p], w2[p][1], acc);
+        acc = __ffma2_rn(xm[0].p[p], w2[p][2], acc);
+        acc = __ffma2_rn(x0.p[p], w2[p][3], acc);
+        sv.p[p] = make_float2(silu(acc.x), silu(acc.y));
+        ss = fmaf(sv.p[p].x, sv.p[p].x, fmaf(sv.p[p].y, sv.p[p].y, ss));
+      }
+      if constexpr (!BWD) {
+        float r = 1.f;
+        if (normed) {
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          r = rsqrtf(ss + a.eps);
+        }
+        Vec4 out;
+        out.p[0] = make_float2(sv.p[0].x * r, sv.p[0].y * r);
+        out.p[1] = make_float2(sv.p[1].x * r, sv.p[1].y * r);
+        store4(tb + (t_first + i) * trow, out);
+      } else {
+        Vec4 g = unpack4(gin[i]);
+        if (normed) {
+          float dot = fmaf(sv.p[0].x, g.p[0].x, fmaf(sv.p[0].y, g.p[0].y, fmaf(sv.p[1].x, g.p[1].x, sv.p[1].y * g.p[1].y)));
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          }
+          const float r = rsqrtf(ss + a.eps), f = r * r * r * dot;
+#pragma unroll
+          for (int p = 0; p < 2; ++p) g.p[p] = make_float2(fmaf(r, g.p[p].x, -f * sv.p[p].x), fmaf(r, g.p[p].y, -f * sv.p[p].y));
+        }
+        store4(dyb + static_cast<int64_t>(t_first + i) * a.C, g);
+      }
+      xm[2] = xm[1]; xm[1] = xm[0]; xm[0] = x0;
+    }
+    __syncthreads();                                      // every warp is done with this stage
+    if (tid == 0 && tile + CONV_FWD_STAGES < tile_hi) issue(tile + CONV_FWD_STAGES);
+  }
+}
+
+template <int E, bool BWD>
+__global__ void __launch_bounds__(256)
+glue_gate_kernel(GlueArgs a, int B) {
+  const int64_t n = static_cast<int64_t>(B) * a.T * 2 * a.H;
+  const int gbase = 3 * a.H * HEAD;                    // first gate channel
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < n;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int u = static_cast<int>(idx % (2 * a.H));    // which * H + head: consecutive threads, consecutive channel groups
+    const int64_t bt = idx / (2 * a.H);
+    const int t = static_cast<int>(bt % a.T), b = static_cast<int>(bt / a.T);
+    const int which = u / a.H, head = u % a.H;
+    const int c0 = gbase + u * E;
+    int start = 0;                                      // first token of t's document
+    if (a.cu != nullptr) {
+      int lo = 0, hi = a.n_docs - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(a.cu + mid) <= t) lo = mid; else hi = mid - 1;
+      }
+      start = __ldg(a.cu + lo);
+    }
+    float c[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) c[e] = 0.f;
+    const __nv_bfloat16* xb = a.x + b * a.stride_b + c0;
+#pragma unroll
+    for (int j = 0; j < CONV_W; ++j) {
+      const int tj = t - 3 + j;
+      if (tj < start) continue;
+      const __nv_bfloat16* xr = xb + tj * a.stride_t;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        c[e] = fmaf(__bfloat162float(xr[e]), __bfloat162float(a.weight[static_cast<int64_t>(c0 + e) * CONV_W + j]), c[e]);
+    }
+    float uu[E], ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      uu[e] = c[e] > 20.f ? c[e] : log1pf(__expf(c[e]));          // softplus
+      ss = fmaf(uu[e], uu[e], ss);
+    }
+    const float r = rsqrtf(ss + a.eps);
+    float* gp = (which == 0 ? a.k2 : a.q2) + ((static_cast<int64_t>(b) * a.T + t) * a.H + head) * E;
+    if constexpr (!BWD) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) gp[e] = uu[e] * r;
+    } else {
+      float g[E], dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        g[e] = gp[e];
+        dot = fmaf(uu[e], g[e], dot);
+      }
+      const float f = r * r * r * dot;
+      __nv_bfloat16* dyr = a.dy + (static_cast<int64_t>(b) * a.T + t) * a.C + c0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float du = fmaf(r, g[e], -f * uu[e]);
+        dyr[e] = __float2bfloat16_rn(du * fast_sigmoid(c[e]));      // d softplus = sigmoid
+      }
+    }
+  }
+}
+
+}  // namespace tgdn
+
+using namespace tgdn;
+
+template <bool BWD>
+static int glue_launch(const void* x, const void* weight, const int32_t* cu, int n_docs, int B, int T, int C, int64_t stride_b,
+                       int64_t stride_t, int H, int E, float eps, void* q, void* k, void* v, float* k2, float* q2, void* dy,
+                       cudaStream_t s) {
+  if (!q || !k || !v || !k2 || !q2 || (BWD && !dy)) return TGDN_ERR_NULL;
+  int rc = conv_check(x, weight, q, cu, n_docs, B, T, C, stride_b, stride_t);
+  if (rc) return rc;
+  if (H <= 0 || C != H * (3 * HEAD + 2 * E)) return TGDN_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(dy)) & 15) return TGDN_ERR_ALIGN;
+  if (!tgdn_check_device()) return TGDN_ERR_DEVICE;
+  CUtensorMap mx;
+  if ((rc = tgdn_make_rows_map(&mx, x, C, T, B, stride_t, stride_b, CONV_CH, CONV_FWD_ROWS))) return rc;
+  const int main_channels = 3 * H * HEAD;
+  int groups, tpg;
+  conv_groups(B, T, main_channels, 4, CONV_FWD_WAVES, &groups, &tpg);
+  GlueArgs a{static_cast<const __nv_bfloat16*>(weight), cu, n_docs, T, C, H, E, tpg, eps,
+             static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), k2, q2,
+             static_cast<__nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), stride_b, stride_t, tgdn_status_word()};
+  const int smem = CONV_FWD_STAGES * CONV_FWD_ROWS * CONV_CH * 2 + 128;
+  cudaError_t e = cudaFuncSetAttribute(glue_main_kernel<BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return tgdn_cuda_error(e);
+  dim3 grid((main_channels + CONV_CH - 1) / CONV_CH, groups, B);
+  glue_main_kernel<BWD><<<grid, CONV_THREADS, smem, s>>>(mx, a);
+  if ((e = cudaGetLastError()) != cudaSuccess) return tgdn_cuda_error(e);
+  const int64_t n = static_cast<int64_t>(B) * T * 2 * H;
+  const int blocks = static_cast<int>(std::min<int64_t>((n + 255) / 256, static_cast<int64_t>(tgdn_sm_count()) * 16));
+  switch (E) {
+    case 1: glue_gate_kernel<1, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    case 2: glue_gate_kernel<2, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    case 4: glue_gate_kernel<4, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    case 8: glue_gate_kernel<8, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    case 12: glue_gate_kernel<12, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    case 16: glue_gate_kernel<16, BWD><<<blocks, 256, 0, s>>>(a, B); break;
+    default: return TGDN_ERR_SHAPE;
+  }
+  return tgdn_cuda_error(cudaGetLastError());
+}
+
+extern "C" int tgdn_glue_fwd(const void* x, const void* weight, const int32_t* cu_seqlens, int n_docs, int B, int T, int C,
+                             int64_t stride_b, int64_t stride_t, int H, int E, float eps, void* q, void* k, void* v, float* k2,
+                             float* q2, void* stream) {
+  return glue_launch<false>(x, weight, cu_seqlens, n_docs, B, T, C, stride_b, stride_t, H, E, eps, q, k, v, k2, q2, nullptr,
+                            static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tgdn_glue_bwd_norm(const void* x, const void* weight, const int32_t* cu_seqlens, int n_docs, int B, int T, int C,
+                                  int64_t stride_b, int64_t stride_t, int H, int E, float eps, const void* dq, const void* dk,
+                                  const void* dv, const float* dk2, const float* dq2, void* dy, void* stream) {
+  return glue_launch<true>(x, weight, cu_seqlens, n_docs, B, T, C, stride_b, stride_t, H, E, eps, const_cast<void*>(dq),
+                           const_cast<void*>(dk), const_cast<void*>(dv), const_cast<float*>(dk2), const_cast<float*>(dq2), dy,
+                           static_cast<cudaStream_t>(stream));
 }

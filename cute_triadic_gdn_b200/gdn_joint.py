@@ -114,7 +114,7 @@ def _kernel_forward(q, k, v, k2, q2, g, beta, scale, save, chunk_starts=None, to
 
 def _value_block(E):
     """Width of the value-axis block one CTA of the recurrences owns (fixed by the library per E)."""
-    return 16 if E >= 8 else 32
+    return 16 if E > 8 else 32
 
 
 def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None, token_map=None):

@@ -124,6 +124,20 @@ int tgdn_fwd_state(const void* q, const void* k, const void* v, const float* k2,
                    int n_docs, int B, int T, int H, int E, int NC, void* o, void* W, void* U, void* h,
                    const float* state_in, float* state_out, void* stream);
 
+/* tgdn_glue_fwd: the convolution with the layer glue that follows it fused in.  x bf16 (B, T, C) with element strides
+ * (stride_b, stride_t, 1), C = H (3*128 + 2E) channels laid out [q: H x 128 | k: H x 128 | v: H x 128 | k2: H x E | q2: H x E];
+ * weight bf16 (C, 4); writes q, k = l2norm(SiLU(conv)) and v = SiLU(conv) as bf16 (B, T, H, 128) and k2, q2 =
+ * l2norm(softplus(conv)) as f32 (B, T, H, E), l2norm(s) = s * rsqrt(sum s^2 + eps) over the last axis.  Packed rows as in
+ * tgdn_conv_fwd.  The reference describes this glue (cute_triadic_gdn/ops/conv_split_act.py:3-5) and leaves it to the caller.
+ * tgdn_glue_bwd_norm: the backward of that glue up to the convolution: from the gradients of q, k, v, k2, q2 (same layouts)
+ * it writes dy bf16 (B, T, C) contiguous, the gradient tgdn_conv_bwd takes with act_channels = 3*H*128. */
+int tgdn_glue_fwd(const void* x, const void* weight, const int32_t* cu_seqlens, int n_docs, int B, int T, int C,
+                  int64_t stride_b, int64_t stride_t, int H, int E, float eps, void* q, void* k, void* v, float* k2, float* q2,
+                  void* stream);
+int tgdn_glue_bwd_norm(const void* x, const void* weight, const int32_t* cu_seqlens, int n_docs, int B, int T, int C,
+                       int64_t stride_b, int64_t stride_t, int H, int E, float eps, const void* dq, const void* dk,
+                       const void* dv, const float* dk2, const float* dq2, void* dy, void* stream);
+
 /* tgdn_decode_step: one token of the recurrence on a resident state (decode).  q, k, v bf16 (B, H, 128); k2, q2, g f32
  * (B, H, E); beta f32 (B, H); state f32 (B, H, E, 128 key rows, 128 value columns), 16-byte aligned, updated in place (the
  * form tgdn_fwd_state hands out); o bf16 (B, H, 128).  Token-by-token definition of
@@ -133,7 +147,7 @@ int tgdn_decode_step(const void* q, const void* k, const void* v, const float* k
 
 /* tgdn_bwd_recurrent: the reverse chunk recurrence.  Reads the upstream gradient dO (token layout) and the forward's
  * gc, AP, Pm, U; writes dV (token layout; the gradient of v), dU (chunk layout), dr f32 [item][128/VC][64][E]
- * (VC = 32 for E <= 4, 16 for E >= 8), dkg, per value block the part of dK that contracts the gradient state over the
+ * (VC = 32 for E <= 8, 16 for E = 12 and 16), dkg, per value block the part of dK that contracts the gradient state over the
  * value axis, sum_e G_e (r_e U)^T, as a bf16 operand image [item][128/VC][token / 8][128 key rows][token % 8] (16 KB per
  * block), and ds (chunk layout, dL/dS at the end of a chunk, same form as h) for those slices only whose chunk decay
  * exp(gc[63][e]) is at least 2^-24 (the other slices of ds are left untouched; nothing reads them).

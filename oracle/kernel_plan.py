@@ -122,7 +122,7 @@ DD_MIN_LOG2_DECAY = -24.0       # below this log2 of the chunk decay, exp(gL) * 
 
 def value_block(E):
     """Value columns one CTA of the reverse recurrence owns."""
-    return 16 if E >= 8 else 32
+    return 16 if E > 8 else 32
 
 
 def state_grad_stage(K, Q, dO, fw, rv, mk, rounding):

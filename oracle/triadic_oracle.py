@@ -252,3 +252,25 @@ def conv_reference_backward(x, weight, act_channels, dy, cu_seqlens=None):
             dx[:, lo:hi - sh] += dyf[:, lo + sh:hi] * wf[:, w]
             dw[:, w] += (dyf[:, lo + sh:hi] * xf[:, lo:hi - sh]).sum((0, 1))
     return dx.to(x.dtype), dw.to(weight.dtype)
+
+
+def glue_reference(x, weight, heads, slices, cu_seqlens=None, eps=1e-6):
+    """The layer glue the reference describes around its convolution (cute_triadic_gdn/ops/conv_split_act.py:3-5: "q, k, v
+    (SiLU) and its second key and query (no activation, softplus afterwards)"), in f32 and differentiable in x and weight
+    (pass float tensors that require grad): channels [q | k | v | k2 | q2] -> q, k = l2norm(SiLU(conv)), v = SiLU(conv) as
+    (B, T, heads, 128); k2, q2 = l2norm(softplus(conv)) as (B, T, heads, slices); l2norm(s) = s * rsqrt(sum s^2 + eps).
+    Nothing is rounded."""
+    B, T, C = x.shape
+    W = weight.shape[1]
+    xf, wf = x.float(), weight.float()
+    rows = []
+    for (lo, hi) in _documents(T, cu_seqlens):
+        seg = F.pad(xf[:, lo:hi].transpose(1, 2), (W - 1, 0))
+        rows.append(F.conv1d(seg, wf[:, None, :], groups=C).transpose(1, 2))
+    y = torch.cat(rows, 1)
+    hd = heads * 128
+    q, k, v, k2, q2 = y.split([hd, hd, hd, heads * slices, heads * slices], dim=-1)
+    l2 = lambda t: t * torch.rsqrt((t * t).sum(-1, keepdim=True) + eps)
+    q, k, v = (F.silu(t).view(B, T, heads, 128) for t in (q, k, v))
+    k2, q2 = (F.softplus(t).view(B, T, heads, slices) for t in (k2, q2))
+    return l2(q), l2(k), v, l2(k2), l2(q2)
