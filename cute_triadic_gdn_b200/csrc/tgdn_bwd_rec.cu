@@ -68,15 +68,37 @@ __device__ __forceinline__ void rec_lds_row(const float* p, float* out) {   // t
   }
 }
 
+// N floats of a gate row in shared memory; 16-byte loads where N allows (the offsets used are then 16-byte aligned too),
+// 8-byte loads otherwise (N even)
+template <int N>
+__device__ __forceinline__ void rec_lds_part(const float* p, float* out) {
+  if constexpr (N % 4 == 0) {
+    rec_lds_row<N>(p, out);
+  } else {
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) {
+      const float2 x = *(reinterpret_cast<const float2*>(p) + j);
+      out[2 * j] = x.x; out[2 * j + 1] = x.y;
+    }
+  }
+}
+
 // STAGES = 2 prefetches the next chunk's tiles (one CTA per SM), STAGES = 1 is sized so that two CTAs share an SM and
 // hide each other's dependent-MMA latency.
-template <int E, int VC, int NWG, int STAGES>
+// NSG > 1 splits the SLICES of a column group over NSG warpgroups (warpgroup w = slice group * NCG + column group): at
+// twelve and sixteen slices a thread then holds eight value columns of half the slices instead of four columns of all of
+// them, which restores the 16-byte accesses of the E = 8 kernel; the one sum over all slices (dU) is completed through
+// shared memory.
+template <int E, int VC, int NWG, int STAGES, int NSG = 1>
 struct RecCfg {
   static constexpr int THREADS = NWG * 128;
   static constexpr int NCOLS = E * VC;
-  static constexpr int CW = VC / NWG;
-  static constexpr int TPC = E * CW;
+  static constexpr int NCG = NWG / NSG;           // column groups
+  static constexpr int CW = VC / NCG;             // value columns per thread
+  static constexpr int EL = E / NSG;              // slices per thread
+  static constexpr int TPC = EL * CW;             // state columns per thread
   static constexpr int ES = E | 1;
+  static_assert(NWG % NSG == 0 && E % NSG == 0 && (NSG == 1 || EL % 2 == 0), "slice groups split the slices evenly");
   static constexpr int TMEM_NEED = NCOLS + 2 * VC + 64;       // KG/dG, Y, Z, P
   static constexpr int TMEM_COLS = TMEM_NEED <= 64 ? 64 : TMEM_NEED <= 128 ? 128 : TMEM_NEED <= 256 ? 256 : 512;
   static constexpr int KQ_BYTES = 32768;
@@ -86,7 +108,7 @@ struct RecCfg {
   static constexpr int XU_BYTES = NCOLS * 128;    // image (i = t, j = n'), SI = 128, SJ = 1024
   static constexpr int DO_BYTES = VC * 128;       // image (i = t, j = v), SI = 128, SJ = 1024
   static constexpr int DOB = (DO_BYTES + 1023) & ~1023;
-  static constexpr int DRP_FLOATS = NWG * 64 * ES;
+  static constexpr int DRP_FLOATS = NCG * 64 * ES + (NSG > 1 ? 64 * VC : 0);   // dr partials per column group; partial dU of the other slice group
   static constexpr int GT_FULL = 64 * E * 4;
   static constexpr int LIMIT = STAGES == 1 ? 115712 : 232448;
   // Shared memory of a layout with `nb` copies of Pm, A and the gate rows and the gate rows loaded by TMA or not
@@ -105,6 +127,7 @@ struct RecCfg {
   static constexpr bool LATE = STAGES == 2 && !(layout_bytes(2, GATES_OK) <= LIMIT);
   static constexpr int NB = (STAGES == 2 && !LATE) ? 2 : 1;              // copies of Pm, A and the gate rows
   static constexpr bool TMA_GATES = GATES_OK && layout_bytes(NB, true) <= LIMIT;
+  static_assert(NSG == 1 || TMA_GATES, "slice groups read their part of the gate rows from shared memory");
   static constexpr int GT_BYTES = TMA_GATES ? GT_FULL : 0;
   static constexpr int OFF_KQ = 0;
   static constexpr int OFF_GX = OFF_KQ + STAGES * KQ_BYTES;
@@ -135,26 +158,30 @@ struct RecCtrl {
   int abort;
 };
 
-template <int E, int VC, int NWG, int STAGES>
+template <int E, int VC, int NWG, int STAGES, int NSG>
 __global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
 rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
            const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2,
            const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_u,
            const __grid_constant__ CUtensorMap map_du, RecParams p) {
-  using C = RecCfg<E, VC, NWG, STAGES>;
+  using C = RecCfg<E, VC, NWG, STAGES, NSG>;
   constexpr int REC_THREADS = C::THREADS;
-  constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES;
+  constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES, NCG = C::NCG, EL = C::EL;
   constexpr int NV = HEAD / VC;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* drp = reinterpret_cast<float*>(smem + C::OFF_DRP);
+  float* dured = drp + NCG * 64 * ES;                                 // NSG > 1: [64 rows][VC] partial dU
   float* dtab = reinterpret_cast<float*>(smem + C::OFF_DT);           // [16] exp(gL_e)
   int* ftab = reinterpret_cast<int*>(smem + C::OFF_DT) + 16;          // [16] store G_e of the next chunk?
   RecCtrl& ctrl = *reinterpret_cast<RecCtrl*>(smem + C::OFF_CTRL);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wg = warp >> 2;
+  const int cgp = NSG == 1 ? wg : wg % NCG;         // column group: value columns cgp*CW .. of the block
+  const int sgp = NSG == 1 ? 0 : wg / NCG;          // slice group: slices sgp*EL ..
+  const int e0 = sgp * EL;
   const int row = (warp & 3) * 32 + lane;
   const bool krow = row < 64;
   const int t = row & 63;
@@ -276,7 +303,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   };
   // This thread's piece of a row of an operand image (i = t, j = v) that TMA filled: CW value columns as raw bf16
   auto image_piece = [&](const uint8_t* img) {
-    const int v0 = wg * CW;
+    const int v0 = cgp * CW;
     const uint8_t* src = img + (t >> 3) * 128 + (t & 7) * 16 + (v0 >> 3) * 1024 + (v0 & 7) * 2;
     if constexpr (CW == 8) {
       return *reinterpret_cast<const uint4*>(src);
@@ -308,10 +335,10 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   auto store_state = [&](int64_t item, const uint32_t* packed) {
     uint8_t* base = reinterpret_cast<uint8_t*>(p.ds) + item * (static_cast<int64_t>(E) * 32768);
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
-      if (!ftab[e]) continue;
-      const int v0 = vb * VC + wg * CW;
-      uint8_t* dst = base + e * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
+    for (int e = 0; e < EL; ++e) {
+      if (!ftab[e0 + e]) continue;
+      const int v0 = vb * VC + cgp * CW;
+      uint8_t* dst = base + (e0 + e) * 32768 + (v0 >> 3) * 2048 + row * 16 + (v0 & 7) * 2;
       if constexpr (CW == 8) {
         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[e * 4], packed[e * 4 + 1], packed[e * 4 + 2], packed[e * 4 + 3]);
       } else {
@@ -358,7 +385,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int nbi = C::NB == 2 ? st : 0;             // which copy of Pm, A and the gate rows this chunk uses
     uint8_t* am = smem + C::OFF_A + nbi * C::A_BYTES;
     uint8_t* pm = smem + C::OFF_PM + nbi * C::PM_BYTES;
-    const int v0 = wg * CW;                          // first value column of this thread inside the block
+    const int v0 = cgp * CW;                         // first value column of this thread inside the block
 
     uint8_t* doimg = smem + C::OFF_DO + st * C::DOB;     // dO rows of the value block: operand image of Y, by TMA
     uint8_t* duimg = smem + C::OFF_DU + st * C::DOB;     // U rows by TMA, later the operand image of dU
@@ -393,25 +420,25 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncwarp();
     // Under the MMA: this row's gate factors from its raw rows, and (K-row threads, which would otherwise only wait for the
     // MMA) the operand Xu of (p).
-    float ga[E];                                     // K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
-    float gr[E];                                     // K rows: r_e = k2 exp(gL - gc)
+    float ga[EL];                                    // this thread's slices.  K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
+    float gr[EL];                                    // K rows: r_e = k2 exp(gL - gc)
     float bt = 0.f;
     {
       const int tl = min(t, max(rows, 1) - 1);
       const float* gcp = p.gc + item * (64 * E);
       const int64_t ro = (tok + tl) * p.H + h;
       const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + nbi * 3 * C::GT_BYTES);
-      float gcr[E], x2[E];
+      float gcr[EL], x2[EL];
       if constexpr (C::TMA_GATES) {
-        rec_lds_row<E>(gt + t * E, gcr);
-        rec_lds_row<E>(gt + (krow ? 64 * E : 128 * E) + t * E, x2);
+        rec_lds_part<EL>(gt + t * E + e0, gcr);
+        rec_lds_part<EL>(gt + (krow ? 64 * E : 128 * E) + t * E + e0, x2);
       } else {
         rec_ld_row<E>(gcp + t * E, gcr);
         rec_ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
       }
       if (krow) {
-        float gl[E];
-        if constexpr (C::TMA_GATES) rec_lds_row<E>(gt + 63 * E, gl); else rec_ld_row<E>(gcp + 63 * E, gl);
+        float gl[EL];
+        if constexpr (C::TMA_GATES) rec_lds_part<EL>(gt + 63 * E + e0, gl); else rec_ld_row<E>(gcp + 63 * E, gl);
         bt = __ldg(p.beta + ro);
         if (!live) bt = 0.f;
         float uv[CW];
@@ -419,7 +446,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
         const uint32_t base = smem_u32(smem + C::OFF_XU) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < EL; ++e) {
           const float k2v = live ? x2[e] : 0.f;
           ga[e] = k2v * rexp2(gcr[e] * LOG2E);
           gr[e] = k2v * rexp2((gl[e] - gcr[e]) * LOG2E);
@@ -428,7 +455,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
+        for (int e = 0; e < EL; ++e) {
           ga[e] = live ? p.scale * x2[e] * rexp2(gcr[e] * LOG2E) : 0.f;
           gr[e] = 0.f;
         }
@@ -442,13 +469,19 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
+    float du[CW];                                    // K rows: dU of this thread's columns (NSG > 1: its slice group's part)
     if (krow) {
-      float du[CW], uv[CW];
+      float uv[CW];
       unpack_piece(image_piece(duimg), true, uv);
-      constexpr int EP = (8 / CW) < 1 ? 1 : (8 / CW) < E ? (8 / CW) : E;     // slices per piece of eight columns
-      constexpr int NP = E / EP;
+      constexpr int EP = (8 / CW) < 1 ? 1 : (8 / CW) < EL ? (8 / CW) : EL;   // slices per piece of eight columns
+      constexpr int NP = EL / EP;
       float kg[2][EP * CW];
-      tmem_ld<CW>(tmem_row + TM_Y + v0, du);
+      if (sgp == 0) {
+        tmem_ld<CW>(tmem_row + TM_Y + v0, du);
+      } else {
+#pragma unroll
+        for (int c = 0; c < CW; ++c) du[c] = 0.f;
+      }
       tmem_ld<EP * CW>(tmem_row + wg * TPC, kg[0]);
 #pragma unroll
       for (int pc = 0; pc < NP; ++pc) {                       // the next piece travels while this one is used
@@ -464,7 +497,25 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
             du[c] = fmaf(re, kp[ee * CW + c], du[c]);
             dot = fmaf(uv[c], kp[ee * CW + c], dot);
           }
-          drp[(wg * 64 + t) * ES + pc * EP + ee] = dot;
+          drp[(cgp * 64 + t) * ES + e0 + pc * EP + ee] = dot;
+        }
+      }
+      if constexpr (NSG > 1) {
+        static_assert(NSG <= 2 && (NSG == 1 || CW % 4 == 0), "the exchange below is written for two slice groups");
+        if (sgp != 0) {
+#pragma unroll
+          for (int c = 0; c < CW; c += 4)
+            *reinterpret_cast<float4*>(dured + t * VC + v0 + c) = make_float4(du[c], du[c + 1], du[c + 2], du[c + 3]);
+        }
+      }
+    }
+    if constexpr (NSG > 1) __syncthreads();          // the other slice group's part of dU; every reader of the U piece is done
+    if (krow && sgp == 0) {
+      if constexpr (NSG > 1) {
+#pragma unroll
+        for (int c = 0; c < CW; c += 4) {
+          const float4 x = *reinterpret_cast<const float4*>(dured + t * VC + v0 + c);
+          du[c] += x.x; du[c + 1] += x.y; du[c + 2] += x.z; du[c + 3] += x.w;
         }
       }
       // dU replaces this thread's piece of U in the image; the image then leaves for global memory by a TMA store
@@ -509,7 +560,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int r = idx / E, e = idx % E;
       float s4 = 0.f;
 #pragma unroll
-      for (int w = 0; w < NWG; ++w) s4 += drp[(w * 64 + r) * ES + e];
+      for (int w = 0; w < NCG; ++w) s4 += drp[(w * 64 + r) * ES + e];
       p.dr[((item * NV + vb) * 64 + r) * E + e] = s4;
     }
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
@@ -523,7 +574,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < CW; ++c) xr[c] = bt * z[c];
-        if (live) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
+        if (live && sgp == 0) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
       } else {
         unpack_piece(image_piece(doimg), live, xr);
       }
@@ -532,7 +583,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       // X image (i = row, j = n'): rows 0..63 -a_e*dW, rows 64..127 c_e*dO
       const uint32_t base = smem_u32(smem + C::OFF_GX) + (row >> 3) * 128 + (row & 7) * 16;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
+      for (int e = 0; e < EL; ++e) {
         const float f = krow ? -ga[e] : ga[e];
         const int n0 = wg * TPC + e * CW;
         store_row_image(base + (n0 >> 3) * 2048 + (n0 & 7) * 2, xr, f);
@@ -588,7 +639,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       constexpr int PIECE = TPC < 16 ? TPC : 16;
       const uint32_t base = smem_u32(smem + C::OFF_GX) + (row >> 3) * 128 + (row & 7) * 16;
       uint8_t* sbase = i > 0 ? reinterpret_cast<uint8_t*>(p.ds) + (item - p.H) * (static_cast<int64_t>(E) * 32768) : nullptr;
-      const int vg = vb * VC + wg * CW;
+      const int vg = vb * VC + cgp * CW;
       float dg[2][PIECE];
       tmem_ld<PIECE>(tmem_row + wg * TPC, dg[0]);
 #pragma unroll
@@ -599,8 +650,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         uint32_t packed[PIECE / 2];
 #pragma unroll
         for (int j = 0; j < PIECE; j += 2) {
-          G[j0 + j] = fmaf(dtab[(j0 + j) / CW], G[j0 + j], dp[j]);
-          G[j0 + j + 1] = fmaf(dtab[(j0 + j + 1) / CW], G[j0 + j + 1], dp[j + 1]);
+          G[j0 + j] = fmaf(dtab[e0 + (j0 + j) / CW], G[j0 + j], dp[j]);
+          G[j0 + j + 1] = fmaf(dtab[e0 + (j0 + j + 1) / CW], G[j0 + j + 1], dp[j + 1]);
           packed[j / 2] = pack_bf16(G[j0 + j], G[j0 + j + 1]);
         }
         // operand image (i = d, j = n') of the next (a)
@@ -613,7 +664,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         if (sbase != nullptr) {
 #pragma unroll
           for (int j = 0; j < PIECE; j += CW) {
-            const int e = (j0 + j) / CW;
+            const int e = e0 + (j0 + j) / CW;
             if (!ftab[e]) continue;
             uint8_t* dst = sbase + e * 32768 + (vg >> 3) * 2048 + row * 16 + (vg & 7) * 2;
             if constexpr (CW == 8)
@@ -637,10 +688,10 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
 using namespace tgdn;
 
-template <int E, int VC, int NWG, int STAGES>
+template <int E, int VC, int NWG, int STAGES, int NSG = 1>
 static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
                       const CUtensorMap& mdo, const CUtensorMap& mu, const CUtensorMap& mdu, const RecParams& p, cudaStream_t s) {
-  using C = RecCfg<E, VC, NWG, STAGES>;
+  using C = RecCfg<E, VC, NWG, STAGES, NSG>;
   static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
   static_assert((STAGES == 1 ? 2 : 1) * C::TMEM_COLS <= 512, "tensor memory budget of one SM exceeded");
@@ -649,12 +700,12 @@ static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC, NWG, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(rec_kernel<E, VC, NWG, STAGES, NSG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return tgdn_cuda_error(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  rec_kernel<E, VC, NWG, STAGES><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, mdo, mu, mdu, p);
+  rec_kernel<E, VC, NWG, STAGES, NSG><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, mdo, mu, mdu, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -702,8 +753,8 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
     // per SM of two warpgroups on 16 columns each (5.26 -> 4.77 ms at B=8, T=8192, H=32), and the state-gradient kernel
     // then adds four value-block images per item instead of eight.
     case 8: return launch_rec<8, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 12: return launch_rec<12, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 16: return launch_rec<16, 16, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 12: return launch_rec<12, 16, 4, 2, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 16: return launch_rec<16, 16, 4, 2, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }
