@@ -57,11 +57,12 @@ KERNEL_U = {
 
 # DRAM bytes (read + write) per (chunk, head) item and launch, from ncu captures of each kernel at E = 8 (the `prof`
 # workload, 4096 items) and at E = 16 (B=2, T=4096, H=16: 2048 items).  Traffic grows in proportion to the item count and,
-# between the two captures, linearly in E (the saved states are E * 32 KB per item), so other E are interpolated.
+# between the two captures, linearly in E (the saved states are E * 32 KB per item), so other E are interpolated (E = 12
+# shares the eight value blocks of E = 16 where E = 8 has four: its rec and sg figures come out about 64 KB per item low).
 NCU_DRAM_BYTES_PER_ITEM = {
     # kernel: (bytes per item at E = 8, at E = 16); filled from profiles/core_kernels_prof_workload.md
-    "masks": (0.234e9 / 4096, 0.118e9 / 2048), "fwd": (1.540e9 / 4096, 1.569e9 / 2048), "rec": (1.145e9 / 4096, 0.548e9 / 2048),
-    "sg": (2.067e9 / 4096, 1.599e9 / 2048), "mat": (0.857e9 / 4096, 0.507e9 / 2048),
+    "masks": (0.234e9 / 4096, 0.116e9 / 2048), "fwd": (1.531e9 / 4096, 1.283e9 / 2048), "rec": (0.750e9 / 4096, 0.550e9 / 2048),
+    "sg": (1.791e9 / 4096, 1.599e9 / 2048), "mat": (0.829e9 / 4096, 0.499e9 / 2048),
 }
 
 # DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)
