@@ -336,6 +336,48 @@ def conv_rates(dev, T=32768, C=13056, act=12288, reps=5):
     return 4 * T * C / (f * 1e-3) / 1e9, 6 * T * C / (bw * 1e-3) / 1e9, f, bw
 
 
+def glue_rates(dev, T=32768, H=32, E=12, reps=5):
+    """Achieved GB/s of the convolution with the layer glue fused in, at the shape of configuration 4 (C = 13056).
+    Algorithmic bytes: forward x in, q, k, v (bf16) and k2, q2 (f32) out; backward x and the five gradients in, dx out
+    (the gradient of the convolution's output, which the backward writes and reads once in between, is not counted)."""
+    from cute_triadic_gdn_b200 import conv_split_norm_call
+    from cute_triadic_gdn_b200.conv_split_act import conv_split_norm_bwd
+    C = H * (3 * 128 + 2 * E)
+    x = torch.randn(1, T, C, device=dev).to(torch.bfloat16)
+    w = (0.5 * torch.randn(C, 4, device=dev)).to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, 4096, device=dev, dtype=torch.int32)
+    grads = [torch.randn(1, T, H, 128, device=dev).to(torch.bfloat16) for _ in range(3)] + \
+            [torch.randn(1, T, H, E, device=dev) for _ in range(2)]
+
+    def ev_time(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def unfused():                     # what a caller of the plain convolution runs after it: split, activations, norms
+        from cute_triadic_gdn_b200 import conv_split_act_call
+        y = conv_split_act_call(x, w, 3 * H * 128, cu)
+        yq, yk, yv, yk2, yq2 = y.split([H * 128, H * 128, H * 128, H * E, H * E], dim=-1)
+        l2 = lambda t: t * torch.rsqrt((t * t).sum(-1, keepdim=True) + 1e-6)
+        q, k = (l2(t.float().view(1, T, H, 128)).to(torch.bfloat16) for t in (yq, yk))
+        k2, q2 = (l2(torch.nn.functional.softplus(t.float()).view(1, T, H, E)) for t in (yk2, yq2))
+        return q, k, yv.reshape(1, T, H, 128).contiguous(), k2, q2
+
+    with torch.no_grad():
+        f = ev_time(lambda: conv_split_norm_call(x, w, H, E, cu))
+        bw = ev_time(lambda: conv_split_norm_bwd(x, w, *grads, H, E, 1e-6, cu))
+        uf = ev_time(unfused)
+    out_bytes = T * H * (3 * 128 * 2 + 2 * E * 4)
+    return (2 * T * C + out_bytes) / (f * 1e-3) / 1e9, (4 * T * C + out_bytes) / (bw * 1e-3) / 1e9, f, bw, uf
+
+
 def decode_rate(dev, B=8, H=32, E=8, reps=10):
     """Achieved GB/s of the one-token decode step at the head count and slice count of configuration 2: the state
     (B*H*E*64 KB f32, larger than L2) is read once and written once per token; everything else is a few KB."""
@@ -555,6 +597,11 @@ def run_ours(args, rank, world, local_rank):
         aux.update({"conv_fwd_gbs": fg, "conv_bwd_gbs": bg, "conv_fwd_ms": fms, "conv_bwd_ms": bms,
                     "conv_frac": fg / pk["gbs"], "conv_bwd_frac": bg / pk["gbs"],
                     "conv_workload": "x (1, 32768, 13056) bf16, 8 documents, SiLU on 12288 channels; bytes 4*T*C forward, 6*T*C backward"})
+        gf, gb, gfms, gbms, ufms = glue_rates(dev)
+        aux.update({"glue_fwd_gbs": gf, "glue_bwd_gbs": gb, "glue_fwd_ms": gfms, "glue_bwd_ms": gbms,
+                    "unfused_glue_fwd_ms": ufms,
+                    "glue_fwd_frac": gf / pk["gbs"], "glue_bwd_frac": gb / pk["gbs"],
+                    "glue_workload": "conv_split_norm_call at x (1, 32768, 13056), H=32, E=12, 8 documents: x -> q, k, v, k2, q2"})
         dg, dms = decode_rate(dev)
         aux.update({"decode_gbs": dg, "decode_us_per_token": dms * 1e3, "decode_frac": dg / pk["gbs"],
                     "decode_workload": "one token, B=8 H=32 E=8: state 268 MB f32 read and written once"})

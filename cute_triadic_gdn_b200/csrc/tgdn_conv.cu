@@ -746,6 +746,9 @@ glue_main_kernel(const __grid_constant__ CUtensorMap map_x, GlueArgs a) {
       xm[j] = (tj >= doc.start) ? unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 2 - j) * (CONV_CH * 2))) : zero4();
     }
     const int n_rows = live ? min(8, a.T - t_first) : 0;
+    // Interior of a document and of the sequence (almost every tile): no document starts among the warp's eight rows or
+    // their three halo rows and all eight rows exist, so the rows need no cursor and no bounds.
+    const bool interior = live && t_first + 8 <= a.T && doc.next >= t_first + 8 && doc.start <= max(t_first - 3, 0);
     // the gradient rows of this warp's eight tokens are asked for before the arithmetic needs them
     uint2 gin[8];
     if constexpr (BWD) {
@@ -755,8 +758,10 @@ glue_main_kernel(const __grid_constant__ CUtensorMap map_x, GlueArgs a) {
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      if (i >= n_rows) break;                              // warp-uniform
-      if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
+      if (!interior) {                                     // warp-uniform
+        if (i >= n_rows) break;
+        if (i > 0 && doc.advance(t_first + i)) { xm[0] = zero4(); xm[1] = zero4(); xm[2] = zero4(); }   // a document starts here
+      }
       const Vec4 x0 = unpack4(*reinterpret_cast<const uint2*>(st + (rg * 8 + 3 + i) * (CONV_CH * 2)));
       Vec4 sv;
       float ss = 0.f;
@@ -827,19 +832,36 @@ glue_gate_kernel(GlueArgs a, int B) {
 #pragma unroll
     for (int e = 0; e < E; ++e) c[e] = 0.f;
     const __nv_bfloat16* xb = a.x + b * a.stride_b + c0;
+    // taps of the E channels: four bf16 = one 8-byte load per channel (c0 * 4 taps * 2 bytes is a multiple of 8)
+    float w[E][CONV_W];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const uint2 u2 = __ldg(reinterpret_cast<const uint2*>(a.weight + static_cast<int64_t>(c0 + e) * CONV_W));
+      w[e][0] = bf16_lo(u2.x); w[e][1] = bf16_hi(u2.x); w[e][2] = bf16_lo(u2.y); w[e][3] = bf16_hi(u2.y);
+    }
 #pragma unroll
     for (int j = 0; j < CONV_W; ++j) {
       const int tj = t - 3 + j;
       if (tj < start) continue;
       const __nv_bfloat16* xr = xb + tj * a.stride_t;
+      if constexpr (E % 4 == 0) {                       // rows and c0 are multiples of 4 channels: 8-byte loads
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        c[e] = fmaf(__bfloat162float(xr[e]), __bfloat162float(a.weight[static_cast<int64_t>(c0 + e) * CONV_W + j]), c[e]);
+        for (int e = 0; e < E; e += 4) {
+          const uint2 u2 = __ldg(reinterpret_cast<const uint2*>(xr + e));
+          c[e] = fmaf(bf16_lo(u2.x), w[e][j], c[e]);
+          c[e + 1] = fmaf(bf16_hi(u2.x), w[e + 1][j], c[e + 1]);
+          c[e + 2] = fmaf(bf16_lo(u2.y), w[e + 2][j], c[e + 2]);
+          c[e + 3] = fmaf(bf16_hi(u2.y), w[e + 3][j], c[e + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) c[e] = fmaf(__bfloat162float(xr[e]), w[e][j], c[e]);
+      }
     }
     float uu[E], ss = 0.f;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
-      uu[e] = c[e] > 20.f ? c[e] : log1pf(__expf(c[e]));          // softplus
+      uu[e] = c[e] > 15.f ? c[e] : __logf(1.f + __expf(c[e]));     // softplus; absolute error below 1e-7 at either end
       ss = fmaf(uu[e], uu[e], ss);
     }
     const float r = rsqrtf(ss + a.eps);
