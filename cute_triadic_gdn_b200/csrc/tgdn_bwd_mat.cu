@@ -81,28 +81,43 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   const bool krow = r < 64;
   const int t = r & 63;
   const int s0 = cq * 16;
-  const int h = blockIdx.x % p.H, n = (blockIdx.x / p.H) % p.NC, b = blockIdx.x / (p.H * p.NC);
-  const int64_t item = blockIdx.x;
-
-  int t0 = n * CHUNK, rows = CHUNK;
-  if (p.cmap != nullptr) {
-    t0 = p.cmap[n];
-    rows = p.cmap[p.NC + n];
-    if (rows <= 0) return;
-    if (t0 < 0 || rows > CHUNK || t0 + rows > p.T) {
-      if (tid == 0) atomicCAS(p.status, DEV_OK, DEV_BAD_CHUNK_MAP);
-      return;
-    }
-  }
-  // One thread of the second warp sets the barriers up and sends the tile loads off at once; the first warp allocates
-  // tensor memory meanwhile; everybody else is already requesting its global inputs.  One CTA barrier ends all three.
+  // The CTA is persistent (one per SM): it walks the items blockIdx.x, blockIdx.x + gridDim.x, ... and keeps its barriers
+  // and its tensor memory.  Both barriers complete an even number of phases per item (two loads, four MMA groups), so
+  // every item starts at parity zero.
+  const int64_t n_items = static_cast<int64_t>(p.B) * p.NC * p.H;
   const int warp_u = __shfl_sync(0xffffffffu, warp, 0);   // warp index as a warp-uniform value
-  const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
   if (warp_u == 1 && elect_one()) {
     mbar_init(&sm.bar_load, 1);
     mbar_init(&sm.bar_mma, 1);
     mbar_fence_init();
     sm.abort = 0;
+  }
+  __syncwarp();
+  if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
+  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  WaitCtl ctl{&sm.abort, p.status};
+
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+  const int h = static_cast<int>(item % p.H), n = static_cast<int>((item / p.H) % p.NC);
+  const int b = static_cast<int>(item / (static_cast<int64_t>(p.H) * p.NC));
+  int t0 = n * CHUNK, rows = CHUNK;
+  if (p.cmap != nullptr) {
+    t0 = p.cmap[n];
+    rows = p.cmap[p.NC + n];
+    if (rows <= 0) continue;                               // unused tail of the chunk map (the same for every thread)
+    if (t0 < 0 || rows > CHUNK || t0 + rows > p.T) {
+      if (tid == 0) atomicCAS(p.status, DEV_OK, DEV_BAD_CHUNK_MAP);
+      continue;
+    }
+  }
+  // One thread of the second warp sends the tile loads off at once; everybody else is already requesting its global
+  // inputs.  (The previous item's stores from these buffers were waited for by the same thread.)
+  const int crow = static_cast<int>(item) * 64;           // first row of this item in the chunk-layout tensors
+  if (warp_u == 1 && elect_one()) {
     sm.steep = 0;
     mbar_expect_tx(&sm.bar_load, 3 * 32768 + 16384);
     for (int half = 0; half < 2; ++half) {
@@ -117,8 +132,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     bulk_load(sm.ap, p.AP + item * (128 * 64), 16384, &sm.bar_load);
   }
   __syncwarp();
-  if (warp_u == 0) { tmem_alloc(&sm.tmem_base, 512); tmem_relinquish(); }
-  WaitCtl ctl{&sm.abort, p.status};
   // Every global value this thread needs later is requested here, in one batch, from clamped (always valid) addresses,
   // and masked when it is used: a load that waits until its consumer is reached costs a full memory round trip, which
   // under the streaming load of the other blocks is microseconds.
@@ -164,8 +177,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = __shfl_sync(0xffffffffu, sm.tmem_base, 0);
-  const uint32_t tmem_row = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
 
   // ---- G1, G2 ----------------------------------------------------------------------------------------------------
   mbar_wait(&sm.bar_load, 0, ctl, DEV_TIMEOUT_LOAD);
@@ -439,11 +450,11 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       bulk_load(sm.ap, reinterpret_cast<const uint8_t*>(p.dkq) + item * 32768, 32768, &sm.bar_load);
     }
     __syncwarp();
-    // Pull the inputs of the block that will follow this one on some SM into L2: its prologue, which nothing on this SM
-    // overlaps (one block per SM), then waits for L2 instead of for HBM.
+    // Pull the inputs of this CTA's next item into L2: its prologue, which nothing on this SM overlaps, then waits for L2
+    // instead of for HBM.
     if (warp_u == 1) {
-      const int64_t item2 = item + p.ahead;
-      if (p.ahead > 0 && item2 < static_cast<int64_t>(gridDim.x)) {
+      const int64_t item2 = item + gridDim.x;              // this CTA's next item
+      if (item2 < n_items) {
         const int h2 = static_cast<int>(item2 % p.H), n2 = static_cast<int>((item2 / p.H) % p.NC);
         const int b2 = static_cast<int>(item2 / (static_cast<int64_t>(p.H) * p.NC));
         int t2 = n2 * CHUNK, rows2 = CHUNK;
@@ -691,7 +702,6 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
   if (rows == CHUNK) {
     if (warp_u == 1 && elect_one()) {
       tma_store_4d(&map_dk, sm.kq, 0, h, t0, b);
@@ -699,21 +709,27 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       tma_store_4d(&map_dq, sm.kq + 16384, 0, h, t0, b);
       tma_store_4d(&map_dq, sm.kq + 24576, 64, h, t0, b);
       bulk_commit_group();
-      bulk_wait_group_read();                              // the staging buffer must outlive the copies
+      bulk_wait_group_read();                              // the staging buffer must outlive the copies: the next item loads into it
     }
-    return;
-  }
-  // rows 0..63 -> dk, rows 64..127 -> dq; warp w stores rows w, w + 16, ...: one coalesced 256-byte row per instruction
-  for (int rr = warp; rr < 128; rr += MAT_THREADS / 32) {
-    const int tt = rr & 63;
-    if (tt < rows) {
-      const uint32_t src = smem_u32(sm.kq) + rr * 256 + ((((lane >> 1) ^ (rr & 15)) << 4) | ((lane & 1) << 3));
-      uint2 v;
-      asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(src));
-      __nv_bfloat16* dst = (rr < 64 ? p.dk : p.dq) + ((tok + tt) * p.H + h) * HEAD + lane * 4;
-      *reinterpret_cast<uint2*>(dst) = v;
+    __syncwarp();
+  } else {
+    // rows 0..63 -> dk, rows 64..127 -> dq; warp w stores rows w, w + 16, ...: one coalesced 256-byte row per instruction
+    for (int rr = warp; rr < 128; rr += MAT_THREADS / 32) {
+      const int tt = rr & 63;
+      if (tt < rows) {
+        const uint32_t src = smem_u32(sm.kq) + rr * 256 + ((((lane >> 1) ^ (rr & 15)) << 4) | ((lane & 1) << 3));
+        uint2 v;
+        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(src));
+        __nv_bfloat16* dst = (rr < 64 ? p.dk : p.dq) + ((tok + tt) * p.H + h) * HEAD + lane * 4;
+        *reinterpret_cast<uint2*>(dst) = v;
+      }
     }
+    __syncthreads();                                       // the staging buffer is read: the next item may load into it
   }
+  }   // items
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 }  // namespace tgdn
@@ -726,7 +742,8 @@ static int launch_mat(const CUtensorMap* maps, const MatParams& p, cudaStream_t 
   static_assert(sizeof(MatSmem<E>) + 1024 <= 232448, "shared memory budget of one CTA exceeded");
   cudaError_t e = cudaFuncSetAttribute(mat_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return tgdn_cuda_error(e);
-  mat_kernel<E><<<p.B * p.NC * p.H, MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p);
+  const long long items = static_cast<long long>(p.B) * p.NC * p.H;
+  mat_kernel<E><<<static_cast<int>(items < p.ahead ? items : p.ahead), MAT_THREADS, smem, s>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], maps[6], maps[7], p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 

@@ -120,7 +120,7 @@ struct MatParams {
   int B, T, H, NC, NV;
   float scale;
   int* status;
-  int ahead;                // block index distance to the block whose inputs this one pulls into L2 (0: none)
+  int ahead;                // CTAs to launch (the SM count): the kernel is persistent, CTA c takes items c, c + ahead, ...
 };
 
 }  // namespace tgdn
