@@ -151,7 +151,8 @@ struct RecCfg {
 
 struct RecCtrl {
   uint64_t bar_load[2];      // K/Q tiles, dO and U rows of a stage (STAGES == 1: everything)
-  uint64_t bar_late;         // late scheme only: Pm, A and the gate rows of the chunk
+  uint64_t bar_late;         // late scheme only: Pm and the gate rows of the chunk
+  uint64_t bar_a;            // late scheme only: A of the chunk
   uint64_t bar_mma;
   uint64_t bar_p;
   uint32_t tmem_base;
@@ -201,6 +202,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_init(&ctrl.bar_load[0], 1);
     mbar_init(&ctrl.bar_load[1], 1);
     mbar_init(&ctrl.bar_late, 1);
+    mbar_init(&ctrl.bar_a, 1);
     mbar_init(&ctrl.bar_mma, 1);
     mbar_init(&ctrl.bar_p, 1);
     mbar_fence_init();
@@ -233,7 +235,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       t0 = 0; rows = 0;
     }
   };
-  auto issue_late = [&](int i, int nb, uint64_t* bar) {   // one thread: the A half of [A;PmA], the Pm image and the gate rows of local chunk i -> copy nb
+  auto issue_gates_pm = [&](int i, int nb, uint64_t* bar) {   // one thread: the Pm image and the gate rows of local chunk i -> copy nb
     int t0, rows;
     chunk_info(i, t0, rows);
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
@@ -243,13 +245,17 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       tma_load_4d(gt + C::GT_BYTES, &map_k2, bar, 0, h, t0, b);
       tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, bar, 0, h, t0, b);
     }
+    bulk_load(smem + C::OFF_PM + nb * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, bar);
+  };
+  auto issue_a = [&](int i, int nb, uint64_t* bar) {          // one thread: the A half of [A;PmA] of local chunk i -> copy nb
+    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     // [A; Pm A] is an image of 128 rows: per 8-column block (2 KB) the first 1 KB holds the rows of A
     const __nv_bfloat16* ap = p.AP + item * (128 * 64);
 #pragma unroll
     for (int jb = 0; jb < 8; ++jb) bulk_load(smem + C::OFF_A + nb * C::A_BYTES + jb * 1024, ap + jb * 1024, 1024, bar);
-    bulk_load(smem + C::OFF_PM + nb * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, bar);
   };
-  constexpr uint32_t LATE_TX = C::A_BYTES + C::PM_BYTES + 3 * C::GT_BYTES;
+  constexpr uint32_t GATES_PM_TX = C::PM_BYTES + 3 * C::GT_BYTES;
+  constexpr uint32_t LATE_TX = C::A_BYTES + GATES_PM_TX;
   auto issue_loads = [&](int i, int st) {           // one thread: K/Q tiles and the dO / U rows of local chunk i (STAGES == 1: the rest too)
     int t0, rows;
     chunk_info(i, t0, rows);
@@ -268,7 +274,10 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
     tma_load_4d(kq + 24576, &map_q, &ctrl.bar_load[st], 64, h, t0, b);
-    if constexpr (!C::LATE) issue_late(i, C::NB == 2 ? st : 0, &ctrl.bar_load[st]);
+    if constexpr (!C::LATE) {
+      issue_gates_pm(i, C::NB == 2 ? st : 0, &ctrl.bar_load[st]);
+      issue_a(i, C::NB == 2 ? st : 0, &ctrl.bar_load[st]);
+    }
   };
   auto prefetch_loads = [&](int i) {                         // one lane: next chunk's tiles into L2 (single-stage configuration)
     int t0, rows;
@@ -353,8 +362,10 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (warp_u == COPY_WARP && elect_one()) {                 // the lane that issues every load and every store of this CTA
     issue_loads(count - 1, 0);
     if constexpr (C::LATE) {
-      mbar_expect_tx(&ctrl.bar_late, LATE_TX);
-      issue_late(count - 1, 0, &ctrl.bar_late);
+      mbar_expect_tx(&ctrl.bar_late, GATES_PM_TX);
+      issue_gates_pm(count - 1, 0, &ctrl.bar_late);
+      mbar_expect_tx(&ctrl.bar_a, C::A_BYTES);
+      issue_a(count - 1, 0, &ctrl.bar_a);
     }
   }
   __syncwarp();
@@ -373,8 +384,16 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
   }
 
+  // The chunk decays of the chunk below decide whether its gradient state is stored; they are read a whole chunk before they
+  // are looked at (the warp that reads them must not arrive late at the chunk's first barrier).
+  auto decay_of = [&](int i) {                       // local chunk i, slice tid (tid < E)
+    return __ldg(p.gc + ((static_cast<int64_t>(b) * p.NC + first + i) * p.H + h) * (64 * E) + 63 * E + tid);
+  };
+  float gl_below = (tid < E && count > 1) ? decay_of(count - 2) : 0.f;
   for (int kstep = 0; kstep < count; ++kstep) {
     const int i = count - 1 - kstep;
+    const float gl_use = gl_below;
+    if (tid < E && i > 1) gl_below = decay_of(i - 2);
     const int st = (STAGES == 2) ? (kstep & 1) : 0;
     int t0, rows;
     chunk_info(i, t0, rows);
@@ -462,7 +481,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       if (tid < E) {
         dtab[tid] = rexp2((C::TMA_GATES ? gt[63 * E + tid] : __ldg(gcp + 63 * E + tid)) * LOG2E);
-        if (i > 0) ftab[tid] = decay_flag(item - p.H, tid);          // read after the chunk's last barrier but one
+        if (i > 0) ftab[tid] = gl_use * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;   // read after the chunk's last barrier but one
       }
       if (kstep + 2 < count) prefetch_rows(i - 2);
     }
@@ -526,6 +545,17 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (c) Z = A^T dU, then (p) P = G Xu^T behind it ----------------------------------------------------------
+    if constexpr (C::LATE) {
+      // Pm was last read by the MMAs of (a) and the gate rows by the gate factors before the barrier above: the next chunk's
+      // copies are asked for now and have the rest of the chunk to arrive.  A, which (c) is about to read, has its own
+      // barrier and was asked for when the previous chunk's (c) had completed.
+      if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
+        mbar_expect_tx(&ctrl.bar_late, GATES_PM_TX);
+        issue_gates_pm(i - 1, 0, &ctrl.bar_late);
+      }
+      __syncwarp();
+      if (warp_u == ISSUE_WARP) mbar_wait(&ctrl.bar_a, kstep & 1, ctl, DEV_TIMEOUT_LOAD);
+    }
     if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       {
@@ -566,6 +596,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     ++mma_phase;
     tc_fence_after();
+    if constexpr (C::LATE) {                         // (c) has read A: the next chunk's copy may land
+      if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
+        mbar_expect_tx(&ctrl.bar_a, C::A_BYTES);
+        issue_a(i - 1, 0, &ctrl.bar_a);
+      }
+      __syncwarp();
+    }
     {
       float xr[CW];                                  // K rows: dW; Q rows: dO
       if (krow) {
@@ -594,13 +631,6 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     __syncthreads();
 
     // ---- (d) dG = [K^T | Q^T] X, G <- d G + dG ------------------------------------------------------------------
-    if constexpr (C::LATE) {                         // Pm, A and the gate rows of this chunk are dead: request the next chunk's
-      if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
-        mbar_expect_tx(&ctrl.bar_late, LATE_TX);
-        issue_late(i - 1, 0, &ctrl.bar_late);
-      }
-      __syncwarp();
-    }
     if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
