@@ -34,6 +34,7 @@ SIGNATURES = {
     "tgdn_glue_bwd_norm": (_I, [_P, _P, _P, _I, _I, _I, _I, _L, _L, _I, _I, _F, _P, _P, _P, _P, _P, _P, _P]),
     "tgdn_decode_step": (_I, [_P] * 7 + [_F, _I, _I, _I, _P, _P, _P]),
     "tgdn_bwd_recurrent": (_I, [_P] * 10 + [_F, _P, _P] + [_I] * 6 + [_P] * 6),
+    "tgdn_bwd_recurrent_state": (_I, [_P] * 10 + [_F, _P, _P] + [_I] * 6 + [_P] * 8),
     "tgdn_bwd_state_grads": (_I, [_P] * 10 + [_F, _P] + [_I] * 5 + [_P] * 5),
     "tgdn_bwd_matrix": (_I, [_P] * 16 + [_F, _P] + [_I] * 5 + [_P] * 7),
     "tgdn_selftest_mma": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P]),

@@ -188,11 +188,12 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   const int t = row & 63;
 
   const int vb = blockIdx.x % NV, h = (blockIdx.x / NV) % p.H, seq_rank = blockIdx.x / (NV * p.H);
-  int b = seq_rank, first = 0, count = p.NC;
+  int b = seq_rank, first = 0, count = p.NC, seq = seq_rank;
   if (p.cmap != nullptr) {
     const int doc = p.cmap[2 * p.NC + seq_rank];
     if (doc < 0 || doc >= p.n_seq) return;
     b = 0;
+    seq = doc;
     first = p.offsets[doc];
     count = p.offsets[doc + 1] - first;
     if (first < 0 || count <= 0 || first + count > p.NC) return;
@@ -213,10 +214,29 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   // store of the CTA.
   constexpr int ISSUE_WARP = 2, COPY_WARP = 3;
   if (warp == 0) { tmem_alloc(&ctrl.tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+  // The gradient state after the last token: zero, or what a later segment of the same sequence handed over
+  // (f32 [sequence][H][E][128 d][128 v]); its bf16 image is the operand of the first chunk's products.
   float G[TPC];
+  if (p.g_in != nullptr) {
+    static_assert(CW % 4 == 0 && TPC % 8 == 0, "state hand-off: whole 16-byte pieces per thread");
+    const float* src = p.g_in + ((static_cast<int64_t>(seq) * p.H + h) * E + e0) * (HEAD * HEAD) + row * HEAD + vb * VC + cgp * CW;
 #pragma unroll
-  for (int j = 0; j < TPC; ++j) G[j] = 0.f;
-  for (int i = tid; i < C::GX_BYTES / 16; i += REC_THREADS) reinterpret_cast<uint4*>(smem + C::OFF_GX)[i] = make_uint4(0, 0, 0, 0);
+    for (int e = 0; e < EL; ++e)
+#pragma unroll
+      for (int c = 0; c < CW; c += 4) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(src + e * (HEAD * HEAD) + c));
+        G[e * CW + c] = x.x; G[e * CW + c + 1] = x.y; G[e * CW + c + 2] = x.z; G[e * CW + c + 3] = x.w;
+      }
+    const uint32_t base = smem_u32(smem + C::OFF_GX) + (row >> 3) * 128 + (row & 7) * 16;
+#pragma unroll
+    for (int j = 0; j < TPC; j += 8)
+      st_shared_v4(base + ((wg * TPC + j) >> 3) * 2048, pack_bf16(G[j], G[j + 1]), pack_bf16(G[j + 2], G[j + 3]),
+                   pack_bf16(G[j + 4], G[j + 5]), pack_bf16(G[j + 6], G[j + 7]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < TPC; ++j) G[j] = 0.f;
+    for (int i = tid; i < C::GX_BYTES / 16; i += REC_THREADS) reinterpret_cast<uint4*>(smem + C::OFF_GX)[i] = make_uint4(0, 0, 0, 0);
+  }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -372,13 +392,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   if (count > 1) prefetch_rows(count - 2);
   uint32_t mma_phase = 0;
   {
-    // the gradient state at the end of the last chunk is zero
+    // the gradient state at the end of the last chunk (zero unless handed in)
     if (tid < E) ftab[tid] = decay_flag((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, tid);
     __syncthreads();
-    uint32_t zeros[TPC / 2];
+    uint32_t packed0[TPC / 2];
 #pragma unroll
-    for (int j = 0; j < TPC / 2; ++j) zeros[j] = 0u;
-    store_state((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, zeros);
+    for (int j = 0; j < TPC / 2; ++j) packed0[j] = pack_bf16(G[2 * j], G[2 * j + 1]);
+    store_state((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, packed0);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -709,6 +729,15 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
   }
+  // dL/dS before the first token, for an earlier segment of the same sequence
+  if (p.g_out != nullptr) {
+    float* dst = p.g_out + ((static_cast<int64_t>(seq) * p.H + h) * E + e0) * (HEAD * HEAD) + row * HEAD + vb * VC + cgp * CW;
+#pragma unroll
+    for (int e = 0; e < EL; ++e)
+#pragma unroll
+      for (int c = 0; c < CW; c += 4)
+        *reinterpret_cast<float4*>(dst + e * (HEAD * HEAD) + c) = make_float4(G[e * CW + c], G[e * CW + c + 1], G[e * CW + c + 2], G[e * CW + c + 3]);
+  }
   if (warp_u == COPY_WARP && elect_one()) bulk_wait_group();   // the last store of dU reads shared memory of this CTA
   __syncwarp();
   if (warp == 0) tmem_dealloc(tmem, C::TMEM_COLS);
@@ -739,11 +768,12 @@ static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
   return tgdn_cuda_error(cudaGetLastError());
 }
 
-extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2,
-                                  const float* beta, const float* gc, const void* AP, const void* Pm, const void* U,
-                                  float scale, const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B,
-                                  int T, int H, int E, int NC, void* dV, void* dU, void* ds, void* dkg, float* dr,
-                                  void* stream) {
+extern "C" int tgdn_bwd_recurrent_state(const void* q, const void* k, const void* dO, const float* k2, const float* q2,
+                                        const float* beta, const float* gc, const void* AP, const void* Pm, const void* U,
+                                        float scale, const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B,
+                                        int T, int H, int E, int NC, void* dV, void* dU, void* ds, void* dkg, float* dr,
+                                        const float* grad_state_in, float* grad_state_out, void* stream) {
+  if ((reinterpret_cast<uintptr_t>(grad_state_in) | reinterpret_cast<uintptr_t>(grad_state_out)) & 15) return TGDN_ERR_ALIGN;
   if (!q || !k || !dO || !k2 || !q2 || !beta || !gc || !AP || !Pm || !U || !dV || !dU || !ds || !dkg || !dr) return TGDN_ERR_NULL;
   const bool packed = chunk_map != nullptr;
   if (packed && (!doc_offsets || n_docs < 1)) return TGDN_ERR_NULL;
@@ -773,7 +803,7 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
               static_cast<const __nv_bfloat16*>(Pm), static_cast<const __nv_bfloat16*>(U),
               static_cast<__nv_bfloat16*>(dV), static_cast<__nv_bfloat16*>(dU), static_cast<__nv_bfloat16*>(ds),
               static_cast<__nv_bfloat16*>(dkg), dr, doc_offsets, chunk_map, B, T, H, NC, packed ? n_docs : B, scale,
-              tgdn_status_word()};
+              tgdn_status_word(), grad_state_in, grad_state_out};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
     case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
@@ -787,4 +817,13 @@ extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, 
     case 16: return launch_rec<16, 16, 4, 2, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
     default: return TGDN_ERR_SHAPE;
   }
+}
+
+extern "C" int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float* k2, const float* q2,
+                                  const float* beta, const float* gc, const void* AP, const void* Pm, const void* U,
+                                  float scale, const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B,
+                                  int T, int H, int E, int NC, void* dV, void* dU, void* ds, void* dkg, float* dr,
+                                  void* stream) {
+  return tgdn_bwd_recurrent_state(q, k, dO, k2, q2, beta, gc, AP, Pm, U, scale, doc_offsets, chunk_map, n_docs, B, T, H, E, NC,
+                                  dV, dU, ds, dkg, dr, nullptr, nullptr, stream);
 }

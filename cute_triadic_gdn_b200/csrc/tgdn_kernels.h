@@ -75,6 +75,8 @@ struct RecParams {
   int B, T, H, NC, n_seq;
   float scale;
   int* status;
+  const float* g_in;        // f32 [sequence][H][E][128 d][128 v]: dL/dS after the last token (a later segment's hand-off), or nullptr (zero)
+  float* g_out;             // same form: dL/dS before the first token, or nullptr
 };
 
 struct SgParams {

@@ -117,8 +117,11 @@ def _value_block(E):
     return 16 if E > 8 else 32
 
 
-def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None, token_map=None):
-    """Reverse recurrence: (dV, dU, ds, dkg, dr).  ds is written only for slices whose chunk decay matters to dg."""
+def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None, token_map=None, grad_state_in=None,
+                 grad_state_out=None):
+    """Reverse recurrence: (dV, dU, ds, dkg, dr).  ds is written only for slices whose chunk decay matters to dg.
+    grad_state_in / grad_state_out: optional f32 (sequences, H, E, 128, 128) tensors, dL/dS after the last and before the
+    first token (the hand-off between segments of one sequence)."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
     NV = 128 // _value_block(E)
@@ -130,11 +133,11 @@ def _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts=None
     dr = torch.empty((B, NC, H, NV, CHUNK, E), dtype=torch.float32, device=dev)
     n_docs = chunk_starts.numel() - 1 if chunk_starts is not None else 0
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib.tgdn_bwd_recurrent(
+        _lib.check(_lib.lib.tgdn_bwd_recurrent_state(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(do), _lib.ptr(k2), _lib.ptr(q2), _lib.ptr(beta), _lib.ptr(gc),
             _lib.ptr(AP), _lib.ptr(Pm), _lib.ptr(U), float(scale), _lib.ptr(chunk_starts), _lib.ptr(token_map), n_docs,
-            B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dkg), _lib.ptr(dr), _lib.stream_of(q)),
-            "tgdn_bwd_recurrent")
+            B, T, H, E, NC, _lib.ptr(dV), _lib.ptr(dU), _lib.ptr(ds), _lib.ptr(dkg), _lib.ptr(dr),
+            _lib.ptr(grad_state_in), _lib.ptr(grad_state_out), _lib.stream_of(q)), "tgdn_bwd_recurrent_state")
     return dV, dU, ds, dkg, dr
 
 
@@ -169,11 +172,13 @@ def _run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, s
     return dq, dk, dk2, dq2, dg, db
 
 
-def _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do, scale, chunk_starts=None, token_map=None):
+def _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do, scale, chunk_starts=None, token_map=None,
+                     grad_state_in=None, grad_state_out=None):
     """reverse recurrence -> state gradients -> matrix gradients.  Returns (dq, dk, dv, dk2, dq2, dg, dbeta)."""
     if AP is None:      # GJ_SAVE_MASKS=0: the forward's own kernel again, bitwise identical
         _, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, token_map)
-    dV, dU, ds, dkg, dr = _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts, token_map)
+    dV, dU, ds, dkg, dr = _run_reverse(q, k, do, k2, q2, beta, gc, AP, Pm, U, scale, chunk_starts, token_map,
+                                       grad_state_in, grad_state_out)
     dkq, da, dc, dd = _run_state_grads(q, k, do, dV, h, ds, dkg, k2, q2, gc, scale, token_map)
     del ds, dkg
     dq, dk, dk2, dq2, dg, db = _run_matrix(q, k, do, dU, W, U, AP, k2, q2, beta, gc, dkq, da, dc, dd, dr, scale,
@@ -212,6 +217,54 @@ class _JointKernels(torch.autograd.Function):
                                  chunk_starts, token_map)
         return (*(gr if need else None for gr, need in zip(grads, ctx.needs_input_grad)),
                 *([None] * (len(ctx.needs_input_grad) - 7)))
+
+
+class _JointKernelsState(torch.autograd.Function):
+    """The kernel pipeline on ONE SEGMENT of longer sequences: the recurrent state comes in and goes out, and so does its
+    gradient in the backward (f32 (B, H, E, 128, 128) each).  Dense rows only.  No counterpart in the reference, whose
+    sequences always start from a zero state inside one call."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k2, q2, g, beta, state_in, scale):
+        B, T, H, _ = q.shape
+        E = k2.shape[-1]
+        gc, AP, Pm = _run_masks(q, k, k2, q2, g, beta, scale, None)
+        state_out = torch.empty((B, H, E, 128, 128), dtype=torch.float32, device=q.device)
+        o, h, W, U = _run_forward(q, k, v, k2, q2, beta, gc, AP, scale, True, None, None,
+                                  None if state_in is None else state_in.contiguous(), state_out)
+        ctx.save_for_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U)
+        ctx.scale = scale
+        ctx.has_state = state_in is not None
+        ctx.set_materialize_grads(False)              # an unused state_out arrives as None, not as a tensor of zeros
+        return o, state_out
+
+    @staticmethod
+    def backward(ctx, do, dstate_out):
+        q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U = ctx.saved_tensors
+        B, T, H, _ = q.shape
+        E = k2.shape[-1]
+        dstate_in = torch.empty((B, H, E, 128, 128), dtype=torch.float32, device=q.device) if ctx.has_state else None
+        g_in = None if dstate_out is None else dstate_out.to(torch.float32).contiguous()
+        do = torch.zeros((B, T, H, 128), dtype=torch.bfloat16, device=q.device) if do is None else do.contiguous()
+        grads = _kernel_backward(q, k, k2, q2, g, beta, gc, AP, Pm, h, W, U, do, ctx.scale, None, None, g_in, dstate_in)
+        return (*grads, dstate_in, None)
+
+
+def chunk_gdn_joint_segment(q, k, v, k2, q2, g, beta, state_in=None, scale=None):
+    """One segment of longer sequences, differentiable through the state: returns (o, state_out).  `state_in` (None:
+    zero) and `state_out` are f32 (B, H, E, 128, 128), S_e as [key row][value column]; gradients flow into `state_in`
+    and out of `state_out`, so that segments chained by their states (on one GPU or, with the states sent between
+    ranks, on several: `context_parallel.py`) give the outputs and gradients of the unsplit sequences.  T must be a
+    multiple of 64; dense rows only."""
+    _check(q, k, v, k2, q2, g, beta, packed=False)
+    _check_device_and_e(q, k2.shape[-1])
+    B, T, H, _ = q.shape
+    E = k2.shape[-1]
+    if state_in is not None and (tuple(state_in.shape) != (B, H, E, 128, 128) or state_in.dtype != torch.float32
+                                 or state_in.device != q.device):
+        raise ValueError(f"state_in must be an f32 tensor of shape {(B, H, E, 128, 128)} on the inputs' device")
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    return _JointKernelsState.apply(q, k, v, k2, q2, g, beta, state_in, float(scale))
 
 
 def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, reference=False, *, initial_state=None,

@@ -158,6 +158,16 @@ int tgdn_bwd_recurrent(const void* q, const void* k, const void* dO, const float
                        const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B, int T, int H, int E,
                        int NC, void* dV, void* dU, void* ds, void* dkg, float* dr, void* stream);
 
+/* tgdn_bwd_recurrent_state: tgdn_bwd_recurrent with the gradient of the recurrent state handed in and out, for sequences
+ * that are processed in segments (context parallelism): grad_state_in is dL/dS after the segment's last token (NULL: zero),
+ * grad_state_out receives dL/dS before its first token (NULL: discarded); both f32 [sequence][H][E][128][128], 16-byte
+ * aligned, the form of tgdn_fwd_state's states.  No counterpart in the reference. */
+int tgdn_bwd_recurrent_state(const void* q, const void* k, const void* dO, const float* k2, const float* q2,
+                             const float* beta, const float* gc, const void* AP, const void* Pm, const void* U, float scale,
+                             const int32_t* doc_offsets, const int32_t* chunk_map, int n_docs, int B, int T, int H, int E,
+                             int NC, void* dV, void* dU, void* ds, void* dkg, float* dr, const float* grad_state_in,
+                             float* grad_state_out, void* stream);
+
 /* tgdn_bwd_state_grads: per (chunk, head), the gradient terms that contract the saved forward states h (chunk start)
  * over the value axis, plus the sum of the value-block images dkg of the reverse recurrence.  Writes dkq, a bf16 image
  * [item][column / 8][128 rows][column % 8] (32 KB per item; rows 0..63: state part of dK, rows 64..127: of dQ; 16-byte
