@@ -587,6 +587,15 @@ def run_ours(args, rank, world, local_rank):
                 os.environ.pop("GJ_SAVE_MASKS")
             else:
                 os.environ["GJ_SAVE_MASKS"] = prev
+    if backward and not args.no_aux and world == 1 and not packed:
+        # backward state recomputation: only the state every 2048 tokens is kept, every segment's forward runs twice
+        from cute_triadic_gdn_b200 import chunk_gdn_joint
+
+        def step_checkpointed():
+            for t in leaves:
+                t.grad = None
+            chunk_gdn_joint(*leaves, checkpoint_tokens=2048).backward(do_dev)
+        aux["checkpoint2048_ms_per_step"] = timed(step_checkpointed, 3, 2) / 3
     del pipe
     for t in leaves:
         t.grad = None

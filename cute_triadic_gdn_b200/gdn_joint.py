@@ -250,6 +250,53 @@ class _JointKernelsState(torch.autograd.Function):
         return (*grads, dstate_in, None)
 
 
+class _JointKernelsCheckpointed(torch.autograd.Function):
+    """Backward state recomputation: the forward keeps only the inputs and the f32 state at every segment boundary
+    (E*64 KB per head, sequence and segment) instead of the per-chunk tensors (h: E*32 KB per head and CHUNK of 64 tokens,
+    W, U, the chunk operators); the backward walks the segments from the last to the first, runs each segment's forward
+    again with everything saved, then its backward, and hands the gradient of the state to the segment before.  Results
+    are bitwise those of the plain function; the price is one more masks + forward pass.  Dense rows only."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k2, q2, g, beta, scale, seg_tokens):
+        B, T, H, _ = q.shape
+        E = k2.shape[-1]
+        cuts = list(range(0, T, seg_tokens)) + [T]
+        states, outs, state = [], [], None
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            part = [t[:, lo:hi].contiguous() for t in (q, k, v, k2, q2, g, beta)]
+            states.append(state)
+            gc, AP, _ = _run_masks(part[0], part[1], part[3], part[4], part[5], part[6], scale, None)
+            nxt = torch.empty((B, H, E, 128, 128), dtype=torch.float32, device=q.device) if hi < T else None
+            outs.append(_run_forward(part[0], part[1], part[2], part[3], part[4], part[6], gc, AP, scale, False, None, None,
+                                     state, nxt)[0])
+            state = nxt
+        ctx.save_for_backward(q, k, v, k2, q2, g, beta, *[s for s in states if s is not None])
+        ctx.scale, ctx.cuts = scale, cuts
+        return torch.cat(outs, 1)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, k2, q2, g, beta, *bounds = ctx.saved_tensors
+        states = [None] + list(bounds)
+        B, T, H, _ = q.shape
+        E = k2.shape[-1]
+        grads = [torch.empty_like(t) for t in (q, k, v, k2, q2, g, beta)]
+        g_state = None
+        for i in reversed(range(len(ctx.cuts) - 1)):
+            lo, hi = ctx.cuts[i], ctx.cuts[i + 1]
+            pq, pk, pv, pk2, pq2, pg, pb = (t[:, lo:hi].contiguous() for t in (q, k, v, k2, q2, g, beta))
+            gc, AP, Pm = _run_masks(pq, pk, pk2, pq2, pg, pb, ctx.scale, None)
+            _, h, W, U = _run_forward(pq, pk, pv, pk2, pq2, pb, gc, AP, ctx.scale, True, None, None, states[i], None)
+            g_prev = torch.empty((B, H, E, 128, 128), dtype=torch.float32, device=q.device) if i > 0 else None
+            part = _kernel_backward(pq, pk, pk2, pq2, pg, pb, gc, AP, Pm, h, W, U, do[:, lo:hi].contiguous(), ctx.scale,
+                                    None, None, g_state, g_prev)
+            for dst, src in zip(grads, part):
+                dst[:, lo:hi] = src
+            g_state = g_prev
+        return (*grads, None, None)
+
+
 def chunk_gdn_joint_segment(q, k, v, k2, q2, g, beta, state_in=None, scale=None):
     """One segment of longer sequences, differentiable through the state: returns (o, state_out).  `state_in` (None:
     zero) and `state_out` are f32 (B, H, E, 128, 128), S_e as [key row][value column]; gradients flow into `state_in`
@@ -268,7 +315,7 @@ def chunk_gdn_joint_segment(q, k, v, k2, q2, g, beta, state_in=None, scale=None)
 
 
 def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, reference=False, *, initial_state=None,
-                    output_final_state=False):
+                    output_final_state=False, checkpoint_tokens=None):
     """Triadic GDN with autograd for all seven tensor inputs, on the sm_100a kernels.
 
     Inference that continues a sequence (no counterpart in the reference, whose forward always starts from zero):
@@ -278,6 +325,9 @@ def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, refer
 
     With cu_seqlens the inputs are one packed row (1, T, ...): contiguous int32/int64 CUDA offsets that start at 0,
     end at T and strictly increase; document lengths are arbitrary and the state resets at every document start.
+    `checkpoint_tokens=S` (training, dense rows): backward state recomputation.  Only the inputs and the f32 state every
+    S tokens are kept; the backward recomputes each segment's forward before differentiating it (bitwise the same results,
+    one more forward pass, the per-chunk saved tensors of one segment at a time instead of the whole sequence).
     `reference=True` asked the reference package for its torch pipeline; this package ships kernels only (its CPU
     restatement of that pipeline lives with the tests), so the flag is rejected instead of silently running something else.
     """
@@ -307,6 +357,14 @@ def chunk_gdn_joint(q, k, v, k2, q2, g, beta, scale=None, cu_seqlens=None, refer
         gc, AP, _ = _run_masks(q, k, k2, q2, g, beta, float(scale), token_map)
         o = _run_forward(q, k, v, k2, q2, beta, gc, AP, float(scale), False, chunk_starts, token_map, initial_state, final)[0]
         return (o, final) if output_final_state else o
+    if needs_grad and checkpoint_tokens is not None:
+        if cu_seqlens is not None:
+            raise ValueError("checkpoint_tokens: dense rows only (a packed row is already cut at its documents)")
+        seg = int(checkpoint_tokens)
+        if seg <= 0 or seg % CHUNK:
+            raise ValueError(f"checkpoint_tokens must be a positive multiple of {CHUNK}")
+        if seg < q.shape[1]:
+            return _JointKernelsCheckpointed.apply(q, k, v, k2, q2, g, beta, float(scale), seg)
     if needs_grad:
         return _JointKernels.apply(q, k, v, k2, q2, g, beta, float(scale), chunk_starts, token_map)
     return _kernel_forward(q, k, v, k2, q2, g, beta, float(scale), False, chunk_starts, token_map)[0]

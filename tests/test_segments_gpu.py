@@ -66,3 +66,32 @@ def test_gradient_reaches_the_initial_state_and_leaves_the_final_one():
     assert orc.rel_l2(s_in.grad.cpu().double(), S0.grad) < 2e-2
     for name, a, b in zip("q k v k2 q2 g beta".split(), leaves, (q, k, v, k2, q2, g, beta)):
         assert orc.rel_l2(a.grad.float().cpu(), b.grad.float()) < 2e-2, name
+
+
+@pytest.mark.parametrize("E", [4, 8, 16])
+def test_checkpointed_backward_is_bitwise_and_saves_memory(E):
+    """`checkpoint_tokens`: the backward recomputes each segment from the state at its start; same bits, less memory."""
+    from cute_triadic_gdn_b200 import chunk_gdn_joint
+    B, T, H = 2, 1024, 4
+    ins = orc.make_inputs(B, T, H, E, seed=60 + E, dist="mild")
+    do = orc.make_grad_output((B, T, H, 128), 61).cuda()
+
+    def run(**kw):
+        leaves = [t.cuda().requires_grad_(True) for t in ins]
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        o = chunk_gdn_joint(*leaves, **kw)
+        held = torch.cuda.memory_allocated() - base           # what the forward keeps for the backward (plus o)
+        o.backward(do)
+        return o.detach(), [t.grad for t in leaves], held
+
+    o_ref, g_ref, held_ref = run()
+    o_ck, g_ck, held_ck = run(checkpoint_tokens=256)
+    assert _lib.device_status() == 0
+    assert torch.equal(o_ck, o_ref)
+    for a, b in zip(g_ck, g_ref):
+        assert torch.equal(a, b)
+    assert held_ck < 0.6 * held_ref, (held_ck, held_ref)
+    with pytest.raises(ValueError):
+        chunk_gdn_joint(*[t.cuda().requires_grad_(True) for t in ins], checkpoint_tokens=100)
