@@ -22,14 +22,17 @@
 // (p) is off the dependent chain of the chunk: it is issued behind (c), completes while the epilogue of (c) reads Z,
 // and is read out of tensor memory while (d) runs.
 //
-// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows, which arrive with the
-// chunk's tiles by TMA as three dense 64 x E tiles (for E >= 12, where shared memory is full, each thread loads its rows
-// from global memory instead); there are no shared gate tables.
+// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows, which arrive by TMA as
+// three dense 64 x E tiles (E a multiple of 4; otherwise each thread loads its rows from global memory); there are no
+// shared gate tables.  The gradient state can be handed in (dL/dS after the last token) and out (before the first), so
+// that sequences can be processed in segments (tgdn_bwd_recurrent_state).
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:59-533 (rec_kernel) and the (r*U) G^T product of
 // cute_triadic_gdn/kernels/sm100_joint_state_grads.py:373-378.  Same thread/column organisation as the forward
-// recurrence before it was split into chains: NWG warpgroups split the VC value columns and move in lockstep; the
-// operand X and the bf16 image of G share one buffer because they are never live at the same time.
+// recurrence before it was split into chains: NWG warpgroups split the VC value columns (and, with NSG = 2, the slices) and
+// move in lockstep; the operand X and the bf16 image of G share one buffer because they are never live at the same time.
+// Two query-row warps of the first warpgroup issue the MMAs and the copies; the key-row warps, which build the gate
+// factors and the operand of (p) under the first MMA group, carry no extra role.
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"

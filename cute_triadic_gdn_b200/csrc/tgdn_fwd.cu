@@ -1,8 +1,9 @@
 // Forward chunk recurrence of the Triadic GDN.
 //
 // One CTA owns one (sequence, head, block of VC value columns) and walks the sequence's 64-token chunks in order.  The
-// block is split over NCH independent CHAINS, one per warpgroup (128 threads = the 128 rows of [K;Q]); chain c owns CW value
-// columns of every slice: its E state slices S_e[:, columns] (128 x CW each, f32) live in the registers of its threads.
+// block is split over NCH independent CHAINS of WPC warpgroups (a warpgroup = 128 threads = the 128 rows of [K;Q]); chain c
+// owns CW value columns of every slice: its E state slices S_e[:, columns] (128 x CW each, f32) live in the registers of its
+// threads (WPC = 2, at twelve and sixteen slices: each of the chain's two warpgroups holds half of the slices).
 // Per chunk a chain runs three dependent MMA groups of its own, with its own accumulators in tensor memory:
 //   (1) R  = [K;Q] S          tcgen05, M=128, N=E*CW, K=128   rows 0..63: K S_e, rows 64..127: Q S_e
 //       W  = V - sum_e a_e*R_e (K rows);   Oq = sum_e c_e*R_e (Q rows)
@@ -12,17 +13,19 @@
 //       S_e <- d_e S_e + dS_e  (registers), bf16 copy -> shared memory operand of the next (1) and saved state h
 // with a = k2 exp(gc), r = k2 exp(gL-gc), c = scale q2 exp(gc), d = exp(gL).
 //
-// The chains of a CTA share only the chunk's K/Q tiles and the [A;PmA] image, which arrive by TMA in a ring of STAGES
-// stages; a stage is refilled by whichever chain is the last to finish with it, so no chain ever waits for another one
-// except through that ring.  Everything else is private to a chain (its columns are independent of all other columns
-// of the problem): its barrier is a named barrier of 128 threads, its MMAs are issued by one of its own lanes and
-// complete on its own mbarrier.  While one chain waits for its MMA or its tensor-memory load, the tensor core and the
+// The chains of a CTA share only the chunk's tiles (K/Q, the [A;PmA] image, the raw gate rows, the value rows of the block
+// and the beta rows), which arrive by TMA in a ring of STAGES stages; a stage is refilled by whichever chain is the last to
+// hand it back, so no chain ever waits for another one except through that ring.  Everything else is private to a chain
+// (its columns are independent of all other columns of the problem): its barrier is a named barrier of its own threads,
+// its MMAs are issued by one of its own lanes and complete on its own mbarrier.  While one chain waits for its MMA or its tensor-memory load, the tensor core and the
 // issue slots work for the others: the dependent chain of a chunk (three MMA -> load -> epilogue round trips) is what
 // bounds this kernel, and the number of independent chains per SM is what hides it.
 //
 // Every thread computes the gate factors of its own row (K rows: a, r, beta; Q rows: c) in registers from the raw
-// k2/q2/gc rows, requested right after its chain's MMA (1) went out, so the loads and the exponentials run under the
-// MMA; there are no shared gate tables and nothing couples the chains but the tile ring.
+// k2/q2/gc rows of the stage, right after its chain's MMA (1) went out, so the exponentials run under the MMA; there are
+// no shared gate tables and nothing couples the chains but the tile ring.  The key-row warps have the longer phases (two
+// gate factors per slice, the operand images of beta*W and r_e*U), so the chain's extra roles sit on its query-row
+// warps: one issues the MMAs and polls their barrier, one hands stages back and issues the loads.
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_fwd.py:66-527 (fwd_kernel); math as cute_triadic_gdn/ops/gdn_joint.py:63-90.
 // Column order inside a chain: n' = e*CW + c  <->  (slice e, value column c of the chain).
