@@ -3,8 +3,10 @@
 Follows cute_triadic_gdn/kernels/sm90_joint_packed.py:64-99 (metadata_kernel) and
 cute_triadic_gdn/ops/joint_packing.py:16-20 (chunk_capacity): per document the index of its first 64-token chunk,
 per chunk its first token and its number of valid rows, and the documents ordered longest first (ties in document order).
-Parity pinned by reading: the reference's kernel needs a GPU and its DSL; the golden packed cases in tests/golden
-exercise the same chunking through the reference's torch path.
+Parity pinned: the reference's device kernel needs a GPU and its DSL, but its host statement of the same chunking,
+pack_documents (cute_triadic_gdn/ops/joint_packing.py:65-90), runs anywhere; what it makes of the packed cases is stored
+in tests/golden/packing_cases.npz (written by tests/golden/make_golden.py) and tests/test_packing_oracle.py holds this
+restatement to it.
 """
 import numpy as np
 
