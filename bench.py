@@ -336,7 +336,7 @@ def conv_rates(dev, T=32768, C=13056, act=12288, reps=5):
     return 4 * T * C / (f * 1e-3) / 1e9, 6 * T * C / (bw * 1e-3) / 1e9, f, bw
 
 
-def glue_rates(dev, T=32768, H=32, E=12, reps=5):
+def glue_rates(dev, T=32768, H=32, E=12, reps=5, unfused_too=True):
     """Achieved GB/s of the convolution with the layer glue fused in, at the shape of configuration 4 (C = 13056).
     Algorithmic bytes: forward x in, q, k, v (bf16) and k2, q2 (f32) out; backward x and the five gradients in, dx out
     (the gradient of the convolution's output, which the backward writes and reads once in between, is not counted)."""
@@ -373,7 +373,7 @@ def glue_rates(dev, T=32768, H=32, E=12, reps=5):
     with torch.no_grad():
         f = ev_time(lambda: conv_split_norm_call(x, w, H, E, cu))
         bw = ev_time(lambda: conv_split_norm_bwd(x, w, *grads, H, E, 1e-6, cu))
-        uf = ev_time(unfused)
+        uf = ev_time(unfused) if unfused_too else None
     out_bytes = T * H * (3 * 128 * 2 + 2 * E * 4)
     return (2 * T * C + out_bytes) / (f * 1e-3) / 1e9, (4 * T * C + out_bytes) / (bw * 1e-3) / 1e9, f, bw, uf
 
@@ -682,13 +682,38 @@ def run_conv(args):
     print(json.dumps(line))
 
 
+def run_glue_decode(args):
+    """Secondary workloads: the convolution with the layer glue fused in (`--workload glue`, x (1, T, 13056), T = 32768
+    unless --tokens says otherwise) and the one-token decode step (`--workload decode`, B=8, H=32, E=8); HBM rooflines."""
+    dev = torch.device("cuda", 0)
+    pk = peaks()
+    if args.workload == "glue":
+        T = args.tokens or 32768
+        if T % 4096:
+            raise SystemExit("--tokens must be a multiple of 4096 (documents of 4096 tokens)")
+        gf, gb, fms, bms, _ = glue_rates(dev, T=T, reps=args.steps, unfused_too=False)
+        line = {"metric": "conv_split_norm GB/s", "value": gf, "unit": "GB/s", "ms_per_step": fms,
+                "config": {"workload": f"conv_split_norm (1,{T},13056) H=32 E=12, {T // 4096} documents"},
+                "roofline": {"bound": "hbm", "kernel": "glue_main + glue_gate (forward)", "achieved": gf, "peak": pk["gbs"],
+                             "unit": "GB/s", "frac": gf / pk["gbs"], "traffic": None, "peak_kind": pk["kind"]},
+                "backward": {"ms": bms, "achieved": gb, "frac": gb / pk["gbs"]}}
+    else:
+        dg, dms = decode_rate(dev, reps=args.steps)
+        line = {"metric": "decode GB/s", "value": dg, "unit": "GB/s", "ms_per_step": dms,
+                "config": {"workload": "one token, B=8 H=32 E=8: 268 MB of f32 state read and written"},
+                "roofline": {"bound": "hbm", "kernel": "decode_kernel", "achieved": dg, "peak": pk["gbs"], "unit": "GB/s",
+                             "frac": dg / pk["gbs"], "traffic": None, "peak_kind": pk["kind"]}}
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic"})
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=list(WORKLOADS) + ["conv"])
+    ap.add_argument("--workload", default="c2", choices=list(WORKLOADS) + ["conv", "glue", "decode"])
     ap.add_argument("--tokens", type=int, default=0,
                     help="conv workload only: sequence length (multiple of 4096; default 32768); small values size a profiler capture")
     ap.add_argument("--no-parity", action="store_true", help="skip the comparison of seeded slices with the CPU oracle")
@@ -705,6 +730,9 @@ def main():
         return
     if args.workload == "conv":
         run_conv(args)
+        return
+    if args.workload in ("glue", "decode"):
+        run_glue_decode(args)
         return
     if world > 1:
         import torch.distributed as dist
