@@ -27,6 +27,7 @@ SIGNATURES = {
     "tgdn_conv_bwd_static": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _L, _I, _P]),
     "tgdn_chunk_capacity": (_I, [_I, _I]),
     "tgdn_metadata": (_I, [_P, _I, _I, _I, _P, _P, _I, _P, _P]),
+    "tgdn_gate_item_floats": (_I, [_I]),
     "tgdn_masks": (_I, [_P, _P, _P, _P, _P, _P, _F, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "tgdn_fwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "tgdn_fwd_state": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),

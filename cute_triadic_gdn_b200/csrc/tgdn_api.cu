@@ -148,7 +148,8 @@ extern "C" const char* tgdn_error_string(int code) {
   return buf;
 }
 
-extern "C" int tgdn_abi_version(void) { return 100; }
+extern "C" int tgdn_abi_version(void) { return 101; }
+extern "C" int tgdn_gate_item_floats(int E) { return tgdn::gate_item_floats(E); }
 
 extern "C" int tgdn_device_status(int* host_status) {
   if (!host_status) return TGDN_ERR_NULL;

@@ -148,7 +148,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       const int idx = min(tid + it * MAT_THREADS, 64 * E - 1);
       const int rr = idx / E, e = idx % E;
       const int64_t off = ((tok + min(rr, rows - 1)) * p.H + h) * E + e;
-      gc_in[it] = __ldg(p.gc + item * (64 * E) + idx);
+      gc_in[it] = __ldg(p.gc + item * gate_item_floats(E) + idx);
       k2_in[it] = __ldg(p.k2 + off);
       q2_in[it] = __ldg(p.q2 + off);
       da_in[it] = __ldg(p.da + item * (64 * E) + idx);
@@ -472,7 +472,7 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
             }
             bulk_prefetch(p.AP + item2 * (128 * 64), 16384);
             bulk_prefetch(reinterpret_cast<const uint8_t*>(p.dkq) + item2 * 32768, 32768);
-            bulk_prefetch(p.gc + item2 * (64 * E), 64 * E * 4);
+            bulk_prefetch(p.gc + item2 * gate_item_floats(E), 64 * E * 4);
             bulk_prefetch(p.da + item2 * (64 * E), 64 * E * 4);
             bulk_prefetch(p.dc + item2 * (64 * E), 64 * E * 4);
             bulk_prefetch(p.dr + item2 * p.NV * (64 * E), static_cast<uint32_t>(p.NV) * 64 * E * 4);

@@ -22,61 +22,34 @@
 // (p) is off the dependent chain of the chunk: it is issued behind (c), completes while the epilogue of (c) reads Z,
 // and is read out of tensor memory while (d) runs.
 //
-// Every thread computes the gate factors of its own row in registers from the raw k2/q2/gc rows, which arrive by TMA as
-// three dense 64 x E tiles (E a multiple of 4; otherwise each thread loads its rows from global memory); there are no
-// shared gate tables.  The gradient state can be handed in (dL/dS after the last token) and out (before the first), so
+// The gate factors (a, r, c per row and slice, d per slice) were formed by the masks kernel and arrive with one bulk copy
+// per chunk; every thread reads those of its own row from shared memory.  The gradient state can be handed in (dL/dS after the last token) and out (before the first), so
 // that sequences can be processed in segments (tgdn_bwd_recurrent_state).
 //
 // Replaces cute_triadic_gdn/kernels/sm100_joint_bwd_recurrent.py:59-533 (rec_kernel) and the (r*U) G^T product of
 // cute_triadic_gdn/kernels/sm100_joint_state_grads.py:373-378.  Same thread/column organisation as the forward
 // recurrence before it was split into chains: NWG warpgroups split the VC value columns (and, with NSG = 2, the slices) and
 // move in lockstep; the operand X and the bf16 image of G share one buffer because they are never live at the same time.
-// Two query-row warps of the first warpgroup issue the MMAs and the copies; the key-row warps, which build the gate
-// factors and the operand of (p) under the first MMA group, carry no extra role.
+// Two query-row warps of the first warpgroup issue the MMAs and the copies; the key-row warps, which build the operand
+// of (p) under the first MMA group, carry no extra role.
 #include "tgdn_common.cuh"
 #include "tgdn_host.h"
 #include "tgdn_kernels.h"
 
 namespace tgdn {
 
-__device__ __forceinline__ float rexp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-template <int E>
-__device__ __forceinline__ void rec_ld_row(const float* p, float* out) {
-  if constexpr (E % 4 == 0) {
-#pragma unroll
-    for (int j = 0; j < E / 4; ++j) {
-      const float4 x = __ldg(reinterpret_cast<const float4*>(p) + j);
-      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
-    }
-  } else if constexpr (E == 2) {
-    const float2 x = __ldg(reinterpret_cast<const float2*>(p));
-    out[0] = x.x; out[1] = x.y;
-  } else {
-#pragma unroll
-    for (int j = 0; j < E; ++j) out[j] = __ldg(p + j);
-  }
-}
-
-template <int E>
-__device__ __forceinline__ void rec_lds_row(const float* p, float* out) {   // the same from shared memory (E a multiple of 4)
-#pragma unroll
-  for (int j = 0; j < E / 4; ++j) {
-    const float4 x = *(reinterpret_cast<const float4*>(p) + j);
-    out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
-  }
-}
-
 // N floats of a gate row in shared memory; 16-byte loads where N allows (the offsets used are then 16-byte aligned too),
 // 8-byte loads otherwise (N even)
 template <int N>
 __device__ __forceinline__ void rec_lds_part(const float* p, float* out) {
-  if constexpr (N % 4 == 0) {
-    rec_lds_row<N>(p, out);
+  if constexpr (N == 1) {
+    out[0] = p[0];
+  } else if constexpr (N % 4 == 0) {
+#pragma unroll
+    for (int j = 0; j < N / 4; ++j) {
+      const float4 x = *(reinterpret_cast<const float4*>(p) + j);
+      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+    }
   } else {
 #pragma unroll
     for (int j = 0; j < N / 2; ++j) {
@@ -112,26 +85,26 @@ struct RecCfg {
   static constexpr int DO_BYTES = VC * 128;       // image (i = t, j = v), SI = 128, SJ = 1024
   static constexpr int DOB = (DO_BYTES + 1023) & ~1023;
   static constexpr int DRP_FLOATS = NCG * 64 * ES + (NSG > 1 ? 64 * VC : 0);   // dr partials per column group; partial dU of the other slice group
-  static constexpr int GT_FULL = 64 * E * 4;
+  // the gate factors of a chunk as the masks kernel stored them: a, r, c as 64 dense rows of E floats each, then d
+  static constexpr int GT_BYTES = gate_factor_bytes(E);
+  static constexpr int GT_STRIDE = (GT_BYTES + 127) & ~127;
+  static constexpr int GF_R = 64 * E, GF_C = 128 * E, GF_D = 192 * E;   // float offsets of r, c, d behind a
   static constexpr int LIMIT = STAGES == 1 ? 115712 : 232448;
-  // Shared memory of a layout with `nb` copies of Pm, A and the gate rows and the gate rows loaded by TMA or not
-  static constexpr int layout_bytes(int nb, bool gates) {
+  // Shared memory of a layout with `nb` copies of Pm, A and the gate factors
+  static constexpr int layout_bytes(int nb) {
     const int xu = XU_BYTES < 8192 ? 8192 : XU_BYTES;
     const int upto_dt = STAGES * KQ_BYTES + GX_BYTES + nb * (PM_BYTES + A_BYTES) + xu + 2 * STAGES * DOB + DRP_FLOATS * 4;
     const int off_gt = (upto_dt + 128 + 127) & ~127;
-    return off_gt + (gates ? nb * 3 * GT_FULL : 0) + 64 + 1024;
+    return off_gt + nb * GT_STRIDE + 64 + 1024;
   }
-  // With two stages, Pm, A and the gate rows get a second copy too where that fits.  Where it does not (sixteen slices),
+  // With two stages, Pm, A and the gate factors get a second copy too where that fits.  Where it does not (sixteen slices),
   // they stay single and are requested LATE: each is dead by the end of the epilogue of (c), and the next chunk's copies,
   // requested right then on a barrier of their own, have the whole of (d) to arrive; only the K/Q tiles and the dO / U
   // rows, which (d) and its epilogue still read, live in the stage.  Measured: the late scheme costs 12% at E = 4, where
-  // both fit, and gains 7% at E = 16, where it makes room for the gate rows in shared memory.
-  static constexpr bool GATES_OK = E % 4 == 0;
-  static constexpr bool LATE = STAGES == 2 && !(layout_bytes(2, GATES_OK) <= LIMIT);
-  static constexpr int NB = (STAGES == 2 && !LATE) ? 2 : 1;              // copies of Pm, A and the gate rows
-  static constexpr bool TMA_GATES = GATES_OK && layout_bytes(NB, true) <= LIMIT;
-  static_assert(NSG == 1 || TMA_GATES, "slice groups read their part of the gate rows from shared memory");
-  static constexpr int GT_BYTES = TMA_GATES ? GT_FULL : 0;
+  // both fit, and gains 7% at E = 16, where it makes room for the gate factors in shared memory.
+  static constexpr bool LATE = STAGES == 2 && !(layout_bytes(2) <= LIMIT);
+  static constexpr int NB = (STAGES == 2 && !LATE) ? 2 : 1;              // copies of Pm, A and the gate factors
+  static_assert(layout_bytes(NB) <= LIMIT, "shared memory budget of one CTA exceeded");
   static constexpr int OFF_KQ = 0;
   static constexpr int OFF_GX = OFF_KQ + STAGES * KQ_BYTES;
   // the 128-row descriptors over the 64-row Pm and A images read up to 8 KB past them: Pm is followed by A, A by Xu
@@ -145,10 +118,8 @@ struct RecCfg {
   static constexpr int OFF_DU = OFF_DO + STAGES * DOB;
   static constexpr int OFF_DRP = OFF_DU + STAGES * DOB;
   static constexpr int OFF_DT = OFF_DRP + DRP_FLOATS * 4;     // exp(gL) of this chunk and the store flags of the next: 2 x 16 words
-  // raw gate rows of the chunk: gc, k2, q2 as 64 dense rows of E floats each, loaded by TMA where E is a multiple of 4 and
-  // shared memory allows; otherwise every thread loads its own rows from global memory
   static constexpr int OFF_GT = (OFF_DT + 128 + 127) & ~127;
-  static constexpr int OFF_CTRL = OFF_GT + NB * 3 * GT_BYTES;
+  static constexpr int OFF_CTRL = OFF_GT + NB * GT_STRIDE;
   static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;
 };
 
@@ -165,14 +136,13 @@ struct RecCtrl {
 template <int E, int VC, int NWG, int STAGES, int NSG>
 __global__ void __launch_bounds__(NWG * 128, STAGES == 1 ? 2 : 1)
 rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
-           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2,
            const __grid_constant__ CUtensorMap map_do, const __grid_constant__ CUtensorMap map_u,
            const __grid_constant__ CUtensorMap map_du, RecParams p) {
   using C = RecCfg<E, VC, NWG, STAGES, NSG>;
   constexpr int REC_THREADS = C::THREADS;
   constexpr int NCOLS = C::NCOLS, CW = C::CW, TPC = C::TPC, ES = C::ES, NCG = C::NCG, EL = C::EL;
   constexpr int NV = HEAD / VC;
-  constexpr float LOG2E = 1.4426950408889634f;
+  constexpr float LOG2E = 1.4426950408889634f;   // the decay threshold below is in the log2 domain
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* drp = reinterpret_cast<float*>(smem + C::OFF_DRP);
@@ -212,7 +182,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_fence_init();
     ctrl.abort = 0;
   }
-  // Roles: the key-row warps (0, 1 of a warpgroup) build the gate factors r_e and the operand of (p) under the first MMA
+  // Roles: the key-row warps (0, 1 of a warpgroup) build the operand of (p) under the first MMA
   // group, so two query-row warps of the first warpgroup take the extra work: warp 2 issues the MMAs, warp 3 every load and
   // store of the CTA.
   constexpr int ISSUE_WARP = 2, COPY_WARP = 3;
@@ -258,16 +228,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       t0 = 0; rows = 0;
     }
   };
-  auto issue_gates_pm = [&](int i, int nb, uint64_t* bar) {   // one thread: the Pm image and the gate rows of local chunk i -> copy nb
-    int t0, rows;
-    chunk_info(i, t0, rows);
+  auto issue_gates_pm = [&](int i, int nb, uint64_t* bar) {   // one thread: the Pm image and the gate factors of local chunk i -> copy nb
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    if constexpr (C::TMA_GATES) {
-      uint8_t* gt = smem + C::OFF_GT + nb * 3 * C::GT_BYTES;
-      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, bar);
-      tma_load_4d(gt + C::GT_BYTES, &map_k2, bar, 0, h, t0, b);
-      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, bar, 0, h, t0, b);
-    }
+    bulk_load(smem + C::OFF_GT + nb * C::GT_STRIDE, p.gc + item * gate_item_floats(E) + 64 * E, C::GT_BYTES, bar);
     bulk_load(smem + C::OFF_PM + nb * C::PM_BYTES, p.Pm + item * (64 * 64), C::PM_BYTES, bar);
   };
   auto issue_a = [&](int i, int nb, uint64_t* bar) {          // one thread: the A half of [A;PmA] of local chunk i -> copy nb
@@ -277,7 +240,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
     for (int jb = 0; jb < 8; ++jb) bulk_load(smem + C::OFF_A + nb * C::A_BYTES + jb * 1024, ap + jb * 1024, 1024, bar);
   };
-  constexpr uint32_t GATES_PM_TX = C::PM_BYTES + 3 * C::GT_BYTES;
+  constexpr uint32_t GATES_PM_TX = C::PM_BYTES + C::GT_BYTES;
   constexpr uint32_t LATE_TX = C::A_BYTES + GATES_PM_TX;
   auto issue_loads = [&](int i, int st) {           // one thread: K/Q tiles and the dO / U rows of local chunk i (STAGES == 1: the rest too)
     int t0, rows;
@@ -312,6 +275,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tma_prefetch_4d(&map_q, 64, h, t0, b);
     bulk_prefetch(p.AP + item * (128 * 64), 16384);
     bulk_prefetch(p.Pm + item * (64 * 64), C::PM_BYTES);
+    bulk_prefetch(p.gc + item * gate_item_floats(E) + 64 * E, C::GT_BYTES);
 #pragma unroll
     for (int jb = 0; jb < VC / 8; ++jb) {
       tma_prefetch_4d(&map_do, vb * VC + jb * 8, h, t0, b);
@@ -323,15 +287,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
-    if (krow) {
-      if (!C::TMA_GATES) prefetch_l2(p.k2 + ro * E);
-      prefetch_l2(p.beta + ro);
-    } else if (!C::TMA_GATES) {
-      prefetch_l2(p.q2 + ro * E);
-      prefetch_l2(p.gc + item * (64 * E) + t * E);
-    }
+    if (krow) prefetch_l2(p.beta + ro);
   };
   // This thread's piece of a row of an operand image (i = t, j = v) that TMA filled: CW value columns as raw bf16
   auto image_piece = [&](const uint8_t* img) {
@@ -379,7 +336,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     }
   };
   auto decay_flag = [&](int64_t item, int e) {      // does d_e*dd_e of this chunk matter?  (same expression in the state-gradient kernel)
-    return __ldg(p.gc + item * (64 * E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
+    return __ldg(p.gc + item * gate_item_floats(E) + 63 * E + e) * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;
   };
 
   if (warp_u == COPY_WARP && elect_one()) {                 // the lane that issues every load and every store of this CTA
@@ -410,7 +367,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   // The chunk decays of the chunk below decide whether its gradient state is stored; they are read a whole chunk before they
   // are looked at (the warp that reads them must not arrive late at the chunk's first barrier).
   auto decay_of = [&](int i) {                       // local chunk i, slice tid (tid < E)
-    return __ldg(p.gc + ((static_cast<int64_t>(b) * p.NC + first + i) * p.H + h) * (64 * E) + 63 * E + tid);
+    return __ldg(p.gc + ((static_cast<int64_t>(b) * p.NC + first + i) * p.H + h) * gate_item_floats(E) + 63 * E + tid);
   };
   float gl_below = (tid < E && count > 1) ? decay_of(count - 2) : 0.f;
   for (int kstep = 0; kstep < count; ++kstep) {
@@ -460,28 +417,17 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
     }
     __syncwarp();
-    // Under the MMA: this row's gate factors from its raw rows, and (K-row threads, which would otherwise only wait for the
-    // MMA) the operand Xu of (p).
+    // Under the MMA: this row's gate factors, and (K-row threads, which would otherwise only wait for the MMA) the operand
+    // Xu of (p).
     float ga[EL];                                    // this thread's slices.  K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
     float gr[EL];                                    // K rows: r_e = k2 exp(gL - gc)
     float bt = 0.f;
     {
-      const int tl = min(t, max(rows, 1) - 1);
-      const float* gcp = p.gc + item * (64 * E);
-      const int64_t ro = (tok + tl) * p.H + h;
-      const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + nbi * 3 * C::GT_BYTES);
-      float gcr[EL], x2[EL];
-      if constexpr (C::TMA_GATES) {
-        rec_lds_part<EL>(gt + t * E + e0, gcr);
-        rec_lds_part<EL>(gt + (krow ? 64 * E : 128 * E) + t * E + e0, x2);
-      } else {
-        rec_ld_row<E>(gcp + t * E, gcr);
-        rec_ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
-      }
+      const float* gf = reinterpret_cast<const float*>(smem + C::OFF_GT + nbi * C::GT_STRIDE);
+      rec_lds_part<EL>(gf + (krow ? 0 : C::GF_C) + t * E + e0, ga);
       if (krow) {
-        float gl[EL];
-        if constexpr (C::TMA_GATES) rec_lds_part<EL>(gt + 63 * E + e0, gl); else rec_ld_row<E>(gcp + 63 * E, gl);
-        bt = __ldg(p.beta + ro);
+        rec_lds_part<EL>(gf + C::GF_R + t * E + e0, gr);
+        bt = __ldg(p.beta + (tok + min(t, max(rows, 1) - 1)) * p.H + h);
         if (!live) bt = 0.f;
         float uv[CW];
         unpack_piece(image_piece(duimg), true, uv);
@@ -489,21 +435,15 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         const uint32_t base = smem_u32(smem + C::OFF_XU) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
         for (int e = 0; e < EL; ++e) {
-          const float k2v = live ? x2[e] : 0.f;
-          ga[e] = k2v * rexp2(gcr[e] * LOG2E);
-          gr[e] = k2v * rexp2((gl[e] - gcr[e]) * LOG2E);
           const int n0 = wg * TPC + e * CW;
           store_row_image(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, uv, gr[e]);
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < EL; ++e) {
-          ga[e] = live ? p.scale * x2[e] * rexp2(gcr[e] * LOG2E) : 0.f;
-          gr[e] = 0.f;
-        }
+        for (int e = 0; e < EL; ++e) gr[e] = 0.f;
       }
       if (tid < E) {
-        dtab[tid] = rexp2((C::TMA_GATES ? gt[63 * E + tid] : __ldg(gcp + 63 * E + tid)) * LOG2E);
+        dtab[tid] = gf[C::GF_D + tid];
         if (i > 0) ftab[tid] = gl_use * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;   // read after the chunk's last barrier but one
       }
       if (kstep + 2 < count) prefetch_rows(i - 2);
@@ -751,7 +691,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 using namespace tgdn;
 
 template <int E, int VC, int NWG, int STAGES, int NSG = 1>
-static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
+static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq,
                       const CUtensorMap& mdo, const CUtensorMap& mu, const CUtensorMap& mdu, const RecParams& p, cudaStream_t s) {
   using C = RecCfg<E, VC, NWG, STAGES, NSG>;
   static_assert(STAGES == 2 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
@@ -767,7 +707,7 @@ static int launch_rec(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = p.n_seq * p.H * (HEAD / VC);
-  rec_kernel<E, VC, NWG, STAGES, NSG><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mk2, mq2, mdo, mu, mdu, p);
+  rec_kernel<E, VC, NWG, STAGES, NSG><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mk, mq, mdo, mu, mdu, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -797,11 +737,6 @@ extern "C" int tgdn_bwd_recurrent_state(const void* q, const void* k, const void
   if ((rc = tgdn_make_token_map(&mdo, dO, B, T, H, 8, 64, 0))) return rc;
   if ((rc = tgdn_make_token_map(&mu, U, 1, static_cast<int>(crows), 1, 8, 64, 0))) return rc;
   if ((rc = tgdn_make_token_map(&mdu, dU, 1, static_cast<int>(crows), 1, 8, 64, 0))) return rc;
-  CUtensorMap mk2 = mk, mq2 = mq;                   // placeholders where the gate rows are not loaded by TMA
-  if (E % 4 == 0) {
-    if ((rc = tgdn_make_gate_map(&mk2, k2, B, T, H, E))) return rc;
-    if ((rc = tgdn_make_gate_map(&mq2, q2, B, T, H, E))) return rc;
-  }
   RecParams p{static_cast<const __nv_bfloat16*>(dO), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<const __nv_bfloat16*>(Pm), static_cast<const __nv_bfloat16*>(U),
               static_cast<__nv_bfloat16*>(dV), static_cast<__nv_bfloat16*>(dU), static_cast<__nv_bfloat16*>(ds),
@@ -809,15 +744,15 @@ extern "C" int tgdn_bwd_recurrent_state(const void* q, const void* k, const void
               tgdn_status_word(), grad_state_in, grad_state_out};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 1: return launch_rec<1, 32, 4, 2>(mk, mq, mdo, mu, mdu, p, s);
+    case 2: return launch_rec<2, 32, 4, 2>(mk, mq, mdo, mu, mdu, p, s);
+    case 4: return launch_rec<4, 32, 4, 2>(mk, mq, mdo, mu, mdu, p, s);
     // E = 8: four warpgroups on 32 value columns with a two-stage ring, one CTA per SM, measured 9% faster than two CTAs
     // per SM of two warpgroups on 16 columns each (5.26 -> 4.77 ms at B=8, T=8192, H=32), and the state-gradient kernel
     // then adds four value-block images per item instead of eight.
-    case 8: return launch_rec<8, 32, 4, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 12: return launch_rec<12, 16, 4, 2, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
-    case 16: return launch_rec<16, 16, 4, 2, 2>(mk, mq, mk2, mq2, mdo, mu, mdu, p, s);
+    case 8: return launch_rec<8, 32, 4, 2>(mk, mq, mdo, mu, mdu, p, s);
+    case 12: return launch_rec<12, 16, 4, 2, 2>(mk, mq, mdo, mu, mdu, p, s);
+    case 16: return launch_rec<16, 16, 4, 2, 2>(mk, mq, mdo, mu, mdu, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

@@ -30,12 +30,6 @@ namespace tgdn {
 constexpr int SG_THREADS = 256;      // eight worker warps ...
 constexpr int SG_BLOCK = SG_THREADS + 64;   // ... plus one warp that only issues MMAs and one that only issues bulk loads
 
-__device__ __forceinline__ float sexp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 // Four ring stages: about two half-slice pairs (64 KB) travel while two more wait for their MMAs.  Measured at E = 8:
 // three stages are 3% slower, five were slower too.
 template <int E>
@@ -179,7 +173,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
 
   // chunk decays of an item, one lane per slice of the two extra warps: they decide per slice whether a trace is taken
   auto load_gl = [&](int64_t it) {
-    return (!worker && lane < E && it < n_items) ? __ldg(p.gc + it * (64 * E) + 63 * E + lane) : 0.f;
+    return (!worker && lane < E && it < n_items) ? __ldg(p.gc + it * gate_item_floats(E) + 63 * E + lane) : 0.f;
   };
   float my_gl = load_gl(item);
 
@@ -203,18 +197,17 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         const uint4 x = __ldg(reinterpret_cast<const uint4*>(ksrc) + j);
         kw[4 * j] = x.x; kw[4 * j + 1] = x.y; kw[4 * j + 2] = x.z; kw[4 * j + 3] = x.w;
       }
+      // the gate factors a = k2 exp(gc) and c = scale q2 exp(gc) of the chunk, as the masks kernel stored them (zero in rows
+      // past a document end)
       constexpr int GATE_ITERS = (64 * E + SG_THREADS - 1) / SG_THREADS;
-      float raw_gc[GATE_ITERS], raw_k2[GATE_ITERS], raw_q2[GATE_ITERS];
+      float raw_a[GATE_ITERS], raw_c[GATE_ITERS];
       float raw_gl = 0.f;
-      const float* gcp = p.gc + item * (64 * E);
+      const float* gcp = p.gc + item * gate_item_floats(E);
 #pragma unroll
       for (int it = 0; it < GATE_ITERS; ++it) {
         const int idx = min(tid + it * SG_THREADS, 64 * E - 1);
-        const int r = idx / E, e = idx % E;
-        const int64_t off = ((tok + min(r, rows - 1)) * p.H + h) * E + e;
-        raw_gc[it] = __ldg(gcp + idx);
-        raw_k2[it] = __ldg(p.k2 + off);
-        raw_q2[it] = __ldg(p.q2 + off);
+        raw_a[it] = __ldg(gcp + 64 * E + idx);
+        raw_c[it] = __ldg(gcp + 192 * E + idx);
       }
       if (tid < E) raw_gl = __ldg(gcp + 63 * E + tid);
 #pragma unroll
@@ -222,12 +215,8 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         const int idx = tid + it * SG_THREADS;
         if (idx < 64 * E) {
           const int r = idx / E, e = idx % E;
-          const bool ok = r < rows;
-          const float gcv = raw_gc[it] * LOG2E;
-          const float k2v = ok ? raw_k2[it] : 0.f, q2v = ok ? raw_q2[it] : 0.f;
-          const float eg = sexp2(gcv);
-          sm.ga[r * ES + e] = k2v * eg;
-          sm.gcq[r * ES + e] = p.scale * q2v * eg;
+          sm.ga[r * ES + e] = raw_a[it];
+          sm.gcq[r * ES + e] = raw_c[it];
         }
       }
       if (tid < E) sm.flag[tid] = raw_gl * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;

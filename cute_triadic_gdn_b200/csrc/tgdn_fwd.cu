@@ -13,7 +13,7 @@
 //       S_e <- d_e S_e + dS_e  (registers), bf16 copy -> shared memory operand of the next (1) and saved state h
 // with a = k2 exp(gc), r = k2 exp(gL-gc), c = scale q2 exp(gc), d = exp(gL).
 //
-// The chains of a CTA share only the chunk's tiles (K/Q, the [A;PmA] image, the raw gate rows, the value rows of the block
+// The chains of a CTA share only the chunk's tiles (K/Q, the [A;PmA] image, the gate factors, the value rows of the block
 // and the beta rows), which arrive by TMA in a ring of STAGES stages; a stage is refilled by whichever chain is the last to
 // hand it back, so no chain ever waits for another one except through that ring.  Everything else is private to a chain
 // (its columns are independent of all other columns of the problem): its barrier is a named barrier of its own threads,
@@ -21,9 +21,9 @@
 // issue slots work for the others: the dependent chain of a chunk (three MMA -> load -> epilogue round trips) is what
 // bounds this kernel, and the number of independent chains per SM is what hides it.
 //
-// Every thread computes the gate factors of its own row (K rows: a, r, beta; Q rows: c) in registers from the raw
-// k2/q2/gc rows of the stage, right after its chain's MMA (1) went out, so the exponentials run under the MMA; there are
-// no shared gate tables and nothing couples the chains but the tile ring.  The key-row warps have the longer phases (two
+// The gate factors of a chunk (a, r, c per row and slice, d per slice) were formed by the masks kernel and arrive in the
+// stage with one bulk copy; every thread reads those of its own row (K rows: a, r, beta; Q rows: c) right after its
+// chain's MMA (1) went out.  Nothing couples the chains but the tile ring.  The key-row warps have the longer phases (two
 // gate factors per slice, the operand images of beta*W and r_e*U), so the chain's extra roles sit on its query-row
 // warps: one issues the MMAs and polls their barrier, one hands stages back and issues the loads.
 //
@@ -35,48 +35,17 @@
 
 namespace tgdn {
 
-__device__ __forceinline__ float fexp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// E floats of one row; rows are E*4 bytes apart from a 16-byte aligned base
-template <int E>
-__device__ __forceinline__ void ld_row(const float* p, float* out) {
-  if constexpr (E % 4 == 0) {
-#pragma unroll
-    for (int j = 0; j < E / 4; ++j) {
-      const float4 x = __ldg(reinterpret_cast<const float4*>(p) + j);
-      out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
-    }
-  } else if constexpr (E == 2) {
-    const float2 x = __ldg(reinterpret_cast<const float2*>(p));
-    out[0] = x.x; out[1] = x.y;
-  } else {
-#pragma unroll
-    for (int j = 0; j < E; ++j) out[j] = __ldg(p + j);
-  }
-}
-
-template <int E>
-__device__ __forceinline__ void lds_row(const float* p, float* out) {   // the same from shared memory (E a multiple of 4)
-#pragma unroll
-  for (int j = 0; j < E / 4; ++j) {
-    const float4 x = *(reinterpret_cast<const float4*>(p) + j);
-    out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
-  }
-}
-
 template <int THREADS>
 __device__ __forceinline__ void chain_sync(int chain) {     // the threads of one chain
   asm volatile("bar.sync %0, %1;" ::"r"(chain + 1), "n"(THREADS) : "memory");
 }
 
-// N floats from shared memory; 16-byte loads where N and the address allow, 8-byte loads otherwise (N even)
+// N floats from shared memory; 16-byte loads where N and the address allow, else 8-byte loads (N even) or one float
 template <int N>
 __device__ __forceinline__ void lds_part(const float* p, float* out) {
-  if constexpr (N % 4 == 0) {
+  if constexpr (N == 1) {
+    out[0] = p[0];
+  } else if constexpr (N % 4 == 0) {
 #pragma unroll
     for (int j = 0; j < N / 4; ++j) {
       const float4 x = *(reinterpret_cast<const float4*>(p) + j);
@@ -118,17 +87,18 @@ struct FwdCfg {
   static constexpr int OFF_S = OFF_AP + STAGES * AP_BYTES;
   static constexpr int OFF_VN = OFF_S + NCH * S_BYTES;
   static constexpr int OFF_BW = OFF_VN + NCH * VN_BYTES;
-  static constexpr int OFF_DT = OFF_BW + NCH * BW_BYTES;      // per chain: exp(gL) of the current chunk, 16 floats
-  // raw gate rows of the chunk, per stage: gc, k2, q2 as 64 dense rows of E floats each (TMA; E a multiple of 4)
-  static constexpr bool TMA_GATES = E % 4 == 0;
-  static constexpr int GT_BYTES = TMA_GATES ? 64 * E * 4 : 0;
-  static constexpr int OFF_GT = (OFF_DT + NCH * 64 + 127) & ~127;
+  // per stage: the gate factors of the chunk as the masks kernel stored them, a, r, c as 64 dense rows of E floats each,
+  // then d (one bulk copy)
+  static constexpr int GT_BYTES = gate_factor_bytes(E);
+  static constexpr int GT_STRIDE = (GT_BYTES + 127) & ~127;
+  static constexpr int GF_R = 64 * E, GF_C = 128 * E, GF_D = 192 * E;   // float offsets of r, c, d behind a
+  static constexpr int OFF_GT = (OFF_BW + NCH * BW_BYTES + 127) & ~127;
   // per stage: the value rows of the CTA's columns, one box of 64 rows x CW columns per chain (TMA; a row of a box is at
   // least 16 bytes), and the beta rows of the chunk for the four heads h & ~3 .. (TMA when H is a multiple of 4)
   static constexpr bool TMA_V = CW >= 8;
   static constexpr int VBOX_BYTES = 64 * CW * 2;
   static constexpr int VT_BYTES = TMA_V ? NCH * VBOX_BYTES : 0;
-  static constexpr int OFF_VT = OFF_GT + STAGES * 3 * GT_BYTES;
+  static constexpr int OFF_VT = OFF_GT + STAGES * GT_STRIDE;
   static constexpr int OFF_BT = OFF_VT + STAGES * VT_BYTES;
   static constexpr bool TMA_BETA = OFF_BT + STAGES * 1024 + 128 + 1024 <= 232448;   // where the beta rows still fit
   static constexpr int BT_BYTES = TMA_BETA ? 1024 : 0;
@@ -152,8 +122,7 @@ struct FwdCtrl {
 template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
 __global__ void __launch_bounds__(NCH * WPC * 128, MINB)
 fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_beta,
-           const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q,
-           const __grid_constant__ CUtensorMap map_k2, const __grid_constant__ CUtensorMap map_q2, FwdParams p) {
+           const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_q, FwdParams p) {
   using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   constexpr int TPC = C::TPC, VC = C::VC, ET = C::ET, TPT = C::TPT, CT = C::CHAIN_THREADS;
   // Roles inside a chain: its key-row warps (0, 1) have the longer epilogues (gate factors r_e, the operand images of W
@@ -161,8 +130,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
   // hands stages back and issues the loads.
   constexpr int ISSUE_WARP = 2, REFILL_WARP = 3;
   const bool beta_tma = C::TMA_BETA && p.beta_tma;
-  constexpr bool LATE_R = C::TMA_GATES && E >= 12;   // form r_e after the epilogue of (1) (register pressure at many slices)
-  constexpr float LOG2E = 1.4426950408889634f;
+  constexpr bool LATE_R = E >= 12;                   // read r_e after the epilogue of (1) (register pressure at many slices)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   FwdCtrl& ctrl = *reinterpret_cast<FwdCtrl*>(smem + C::OFF_CTRL);
@@ -178,7 +146,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
   uint8_t* s_img = smem + C::OFF_S + chain * C::S_BYTES;
   uint8_t* vn_img = smem + C::OFF_VN + chain * C::VN_BYTES;
   uint8_t* bw_img = smem + C::OFF_BW + chain * C::BW_BYTES;
-  float* dtab = reinterpret_cast<float*>(smem + C::OFF_DT) + chain * 16;
 
   // work item
   constexpr int NV = HEAD / VC;
@@ -275,19 +242,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     const int st = i % STAGES;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
     const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
-    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + 3 * C::GT_BYTES + C::VT_BYTES + (beta_tma ? C::BT_BYTES : 0));
+    mbar_expect_tx(&ctrl.bar_load[st], C::KQ_BYTES + C::AP_BYTES + C::GT_BYTES + C::VT_BYTES + (beta_tma ? C::BT_BYTES : 0));
     if constexpr (C::TMA_V) {
 #pragma unroll
       for (int c = 0; c < NCH; ++c)
         tma_load_4d(smem + C::OFF_VT + st * C::VT_BYTES + c * C::VBOX_BYTES, &map_v, &ctrl.bar_load[st], vb * VC + c * CW, h, t0, b);
     }
     if (beta_tma) tma_load_4d(smem + C::OFF_BT + st * C::BT_BYTES, &map_beta, &ctrl.bar_load[st], 0, h >> 2, t0, b);
-    if constexpr (C::TMA_GATES) {
-      uint8_t* gt = smem + C::OFF_GT + st * 3 * C::GT_BYTES;
-      bulk_load(gt, p.gc + item * (64 * E), C::GT_BYTES, &ctrl.bar_load[st]);
-      tma_load_4d(gt + C::GT_BYTES, &map_k2, &ctrl.bar_load[st], 0, h, t0, b);
-      tma_load_4d(gt + 2 * C::GT_BYTES, &map_q2, &ctrl.bar_load[st], 0, h, t0, b);
-    }
+    bulk_load(smem + C::OFF_GT + st * C::GT_STRIDE, p.gc + item * gate_item_floats(E) + 64 * E, C::GT_BYTES, &ctrl.bar_load[st]);
     tma_load_4d(kq, &map_k, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 8192, &map_q, &ctrl.bar_load[st], 0, h, t0, b);
     tma_load_4d(kq + 16384, &map_k, &ctrl.bar_load[st], 64, h, t0, b);
@@ -303,22 +265,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     tma_prefetch_4d(&map_k, 64, h, t0, b);
     tma_prefetch_4d(&map_q, 64, h, t0, b);
     bulk_prefetch(p.AP + item * (128 * 64), C::AP_BYTES);
+    bulk_prefetch(p.gc + item * gate_item_floats(E) + 64 * E, C::GT_BYTES);
   };
   auto prefetch_rows = [&](int i) {                 // what threads still load themselves, for a later chunk -> L2
-    if (sw != 0 || (C::TMA_GATES && chain != 0)) return;   // the value columns of all chains of the CTA share their 128-byte lines
+    if (sw != 0 || chain != 0 || !krow) return;      // the value columns of all chains of the CTA share their 128-byte lines
     int t0, rows;
     chunk_info(i, t0, rows);
     const int last = max(rows, 1) - 1;
-    const int64_t item = (static_cast<int64_t>(b) * p.NC + first + i) * p.H + h;
     const int64_t ro = (static_cast<int64_t>(b) * p.T + t0 + min(t, last)) * p.H + h;
-    if (krow) {
-      if (!C::TMA_GATES) prefetch_l2(p.k2 + ro * E);
-      if (!beta_tma) prefetch_l2(p.beta + ro);
-      if (!C::TMA_V) prefetch_l2(p.v + ro * HEAD + v0g);
-    } else if (!C::TMA_GATES) {
-      prefetch_l2(p.q2 + ro * E);
-      prefetch_l2(p.gc + item * (64 * E) + t * E);
-    }
+    if (!beta_tma) prefetch_l2(p.beta + ro);
+    if (!C::TMA_V) prefetch_l2(p.v + ro * HEAD + v0g);
   };
   auto load_vrow = [&](int t0, int rows, uint32_t* out /* CW/2 words */) {   // CW value columns of row t (clamped), raw bf16
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
@@ -377,7 +333,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     // Every thread reads rows of the stage (gates, value row, beta) under the MMA, so every warp waits for the loads itself.
     // (The MMA completions below are polled by the chain's first warp only: the other three sleep in the chain's hardware
     // barrier, where they take no issue slots from the chains that are in an epilogue at that moment.)
-    if (cwarp_u == ISSUE_WARP || C::TMA_GATES || C::TMA_V) mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
+    mbar_wait(&ctrl.bar_load[st], (i / STAGES) & 1, ctl, DEV_TIMEOUT_LOAD);
     if (cwarp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
@@ -399,7 +355,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       }
     }
     __syncwarp();
-    // Under the MMA: this row's raw gate inputs and value row (in L2 since the previous chunk), then the gate factors.
+    // Under the MMA: this row's gate factors, value row and beta from the stage.
+    const float* gf = reinterpret_cast<const float*>(smem + C::OFF_GT + st * C::GT_STRIDE);
     float ga[ET];                                    // this thread's slices.  K rows: a_e = k2 exp(gc); Q rows: c_e = scale q2 exp(gc)
     float gr[ET];                                    // K rows: r_e = k2 exp(gL - gc)
     float bt = 0.f;
@@ -409,24 +366,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       for (int c = 0; c < CW / 2; ++c) vraw[c] = 0u;
     }
     {
-      const int tl = min(t, max(rows, 1) - 1);
-      const float* gcp = p.gc + item * (64 * E);
-      const int64_t ro = (tok + tl) * p.H + h;
-      float gcr[ET], x2[ET], gl[ET];
-      if constexpr (C::TMA_GATES) {
-        const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
-        lds_part<ET>(gt + t * E + e0, gcr);
-        lds_part<ET>(gt + (krow ? 64 * E : 128 * E) + t * E + e0, x2);
-        if (krow && !LATE_R) lds_part<ET>(gt + 63 * E + e0, gl);
-      } else {
-        ld_row<E>(gcp + t * E, gcr);
-        ld_row<E>((krow ? p.k2 : p.q2) + ro * E, x2);
-        if (krow) ld_row<E>(gcp + 63 * E, gl);
-      }
+      lds_part<ET>(gf + (krow ? 0 : C::GF_C) + t * E + e0, ga);
       if (krow) {
+        if constexpr (!LATE_R) lds_part<ET>(gf + C::GF_R + t * E + e0, gr);
         if (sw == 0) {                               // the warpgroup that completes W: beta and the value row
-          if (beta_tma) bt = reinterpret_cast<const float*>(smem + C::OFF_BT + st * C::BT_BYTES)[t * 4 + (h & 3)];
-          else bt = __ldg(p.beta + ro);
+          if (beta_tma) {
+            bt = reinterpret_cast<const float*>(smem + C::OFF_BT + st * C::BT_BYTES)[t * 4 + (h & 3)];
+          } else {
+            bt = __ldg(p.beta + (tok + min(t, max(rows, 1) - 1)) * p.H + h);
+          }
           if constexpr (C::TMA_V) {
             const uint32_t va = smem_u32(smem + C::OFF_VT + st * C::VT_BYTES + chain * C::VBOX_BYTES) + t * (CW * 2);
 #pragma unroll
@@ -436,25 +384,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
             load_vrow(t0, rows, vraw);
           }
         }
-        if (sw == 0 && t < E) {
-          float glt;
-          if constexpr (C::TMA_GATES) glt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES)[63 * E + t];
-          else glt = __ldg(gcp + 63 * E + t);
-          dtab[t] = fexp2(glt * LOG2E);
-        }
-#pragma unroll
-        for (int e = 0; e < ET; ++e) {
-          const float k2v = live ? x2[e] : 0.f;
-          ga[e] = k2v * fexp2(gcr[e] * LOG2E);
-          if constexpr (!LATE_R) gr[e] = k2v * fexp2((gl[e] - gcr[e]) * LOG2E);
-        }
         if (!live) bt = 0.f;
       } else {
 #pragma unroll
-        for (int e = 0; e < ET; ++e) {
-          ga[e] = live ? p.scale * x2[e] * fexp2(gcr[e] * LOG2E) : 0.f;
-          gr[e] = 0.f;
-        }
+        for (int e = 0; e < ET; ++e) gr[e] = 0.f;
       }
       if (i + 2 < count) prefetch_rows(i + 2);
     }
@@ -523,16 +456,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       umma_commit(&ctrl.bar_mma[chain]);
     }
     __syncwarp();
-    if constexpr (LATE_R) {                          // r_e only now, from the gate tiles that are still in the stage: sixteen
-      if (krow) {                                    // registers fewer are live through the epilogue of (1)
-        const float* gt = reinterpret_cast<const float*>(smem + C::OFF_GT + st * 3 * C::GT_BYTES);
-        float gcr[ET], k2r[ET], gl[ET];
-        lds_part<ET>(gt + t * E + e0, gcr);
-        lds_part<ET>(gt + 64 * E + t * E + e0, k2r);
-        lds_part<ET>(gt + 63 * E + e0, gl);
-#pragma unroll
-        for (int e = 0; e < ET; ++e) gr[e] = live ? k2r[e] * fexp2((gl[e] - gcr[e]) * LOG2E) : 0.f;
-      }
+    if constexpr (LATE_R) {                          // r_e only now, from the stage: sixteen registers fewer are live
+      if (krow) lds_part<ET>(gf + C::GF_R + t * E + e0, gr);   // through the epilogue of (1)
     }
     if (cwarp_u == ISSUE_WARP) mbar_wait(&ctrl.bar_mma[chain], mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
     chain_sync<CT>(chain);
@@ -576,9 +501,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
     ++mma_phase;
     tc_fence_after();
     {
-      float dch[ET];                                 // exp(gL) of this thread's slices, written by this chain during (1)
-#pragma unroll
-      for (int e = 0; e < ET; ++e) dch[e] = dtab[e0 + e];
+      float dch[ET];                                 // exp(gL) of this thread's slices
+      lds_part<ET>(gf + C::GF_D + e0, dch);
       const uint32_t base = smem_u32(s_img) + (row >> 3) * 128 + (row & 7) * 16;
       uint8_t* hbase = (p.h != nullptr && i + 1 < count) ? state_item_ptr(item + p.H) : nullptr;
       float ds[2][16];
@@ -625,8 +549,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
 using namespace tgdn;
 
 template <int E, int CW, int NCH, int WPC, int STAGES, int MINB>
-static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtensorMap& mk2, const CUtensorMap& mq2,
-                      const void* v, const FwdParams& p, cudaStream_t s) {
+static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const void* v, const FwdParams& p, cudaStream_t s) {
   using C = FwdCfg<E, CW, NCH, WPC, STAGES>;
   static_assert(MINB == 1 || C::SMEM_BYTES <= 115712, "two CTAs per SM need at most 113 KB each");
   static_assert(C::SMEM_BYTES <= 232448, "shared memory budget of one CTA exceeded");
@@ -649,7 +572,7 @@ static int launch_fwd(const CUtensorMap& mk, const CUtensorMap& mq, const CUtens
     if (rc) return rc;
   }
   const int grid = p.n_seq * p.H * (HEAD / C::VC);
-  fwd_kernel<E, CW, NCH, WPC, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mv, mb, mk, mq, mk2, mq2, p);
+  fwd_kernel<E, CW, NCH, WPC, STAGES, MINB><<<grid, C::THREADS, C::SMEM_BYTES, s>>>(mv, mb, mk, mq, p);
   return tgdn_cuda_error(cudaGetLastError());
 }
 
@@ -671,11 +594,6 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
   CUtensorMap mk, mq;
   if ((rc = tgdn_make_token_map(&mk, k, B, T, H, 64, 64, 1))) return rc;
   if ((rc = tgdn_make_token_map(&mq, q, B, T, H, 64, 64, 1))) return rc;
-  CUtensorMap mk2 = mk, mq2 = mq;                   // placeholders where the gate rows are not loaded by TMA (E < 4)
-  if (E % 4 == 0) {
-    if ((rc = tgdn_make_gate_map(&mk2, k2, B, T, H, E))) return rc;
-    if ((rc = tgdn_make_gate_map(&mq2, q2, B, T, H, E))) return rc;
-  }
   FwdParams p{static_cast<const __nv_bfloat16*>(v), k2, q2, beta, gc, static_cast<const __nv_bfloat16*>(AP),
               static_cast<__nv_bfloat16*>(o), static_cast<__nv_bfloat16*>(W), static_cast<__nv_bfloat16*>(U),
               static_cast<__nv_bfloat16*>(h), state_in, state_out, doc_offsets, chunk_map, B, T, H, NC,
@@ -683,21 +601,21 @@ extern "C" int tgdn_fwd_state(const void* q, const void* k, const void* v, const
               (H % 4 == 0 && (reinterpret_cast<uintptr_t>(beta) & 15) == 0) ? 1 : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (E) {
-    case 1: return launch_fwd<1, 16, 2, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
-    case 2: return launch_fwd<2, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+    case 1: return launch_fwd<1, 16, 2, 1, 2, 1>(mk, mq, v, p, s);
+    case 2: return launch_fwd<2, 8, 4, 1, 2, 1>(mk, mq, v, p, s);
     case 4: {
       // One CTA per SM: the grid runs in whole waves.  Where a block of 32 value columns needs a second, partly filled wave
       // and a block of 64 does not, the wider block wins although its chunks take a little longer (B=4, H=16: 256 CTAs on
       // 148 SMs are two waves, 128 CTAs are one).
       const long long sms = tgdn_sm_count(), seqs = static_cast<long long>(p.n_seq) * p.H;
       const long long waves32 = (seqs * 4 + sms - 1) / sms, waves64 = (seqs * 2 + sms - 1) / sms;
-      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
-      return launch_fwd<4, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+      if (waves64 * 5 < waves32 * 4) return launch_fwd<4, 16, 4, 1, 2, 1>(mk, mq, v, p, s);
+      return launch_fwd<4, 8, 4, 1, 2, 1>(mk, mq, v, p, s);
     }
     // (two warpgroups per chain at E = 8, sixteen columns per thread, measured 17% slower than four one-warpgroup chains)
-    case 8: return launch_fwd<8, 8, 4, 1, 2, 1>(mk, mq, mk2, mq2, v, p, s);
-    case 12: return launch_fwd<12, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, v, p, s);
-    case 16: return launch_fwd<16, 8, 2, 2, 2, 1>(mk, mq, mk2, mq2, v, p, s);
+    case 8: return launch_fwd<8, 8, 4, 1, 2, 1>(mk, mq, v, p, s);
+    case 12: return launch_fwd<12, 8, 2, 2, 2, 1>(mk, mq, v, p, s);
+    case 16: return launch_fwd<16, 8, 2, 2, 2, 1>(mk, mq, v, p, s);
     default: return TGDN_ERR_SHAPE;
   }
 }

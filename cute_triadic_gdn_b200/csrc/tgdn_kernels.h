@@ -1,7 +1,11 @@
 // Parameter blocks of the Triadic GDN kernels and the layouts of the tensors that travel between them.
 //
 // Chunk-layout tensors are indexed by item = (b * NC + n) * H + h (b batch row, n chunk, h head):
-//   gc   f32  [item][64][E]              cumulative log gate of the chunk
+//   gc   f32  [item][GATE_ITEM_FLOATS(E)]  the gates of the chunk, five blocks (rows past a document end: a = r = c = 0):
+//          [0, 64E)        gc[t][e]  cumulative log gate
+//          [64E, 128E)     a[t][e] = k2 exp(gc)                [128E, 192E)   r[t][e] = k2 exp(gL - gc),  gL = gc[63]
+//          [192E, 256E)    c[t][e] = scale q2 exp(gc)          [256E, 256E+16)  d[e] = exp(gL), padded to 16 floats
+//        The masks kernel forms the factors once; the recurrences fetch [64E, 256E+16) with one bulk copy per chunk.
 //   AP   bf16 [item][16 KB image]        [A; Pm A] stacked, image (i = row 0..127, j = column 0..63), SI = 128, SJ = 2048
 //   Pm   bf16 [item][ 8 KB image]        image (i = t, j = s), SI = 128, SJ = 1024
 //   W, U, dU  bf16 [item][64][128]       row-major token rows of the chunk (rows past a document end are zero)
@@ -20,6 +24,10 @@ namespace tgdn {
 // then does not store G_e of that chunk and the state-gradient kernel does not read it.  Both kernels evaluate
 // gc[63][e] * log2(e) >= DD_MIN_LOG2_DECAY on the same f32 value.
 constexpr float DD_MIN_LOG2_DECAY = -24.f;
+
+// Floats per item of the gate tensor, and where its blocks start.
+__host__ __device__ constexpr int gate_item_floats(int E) { return 256 * E + 16; }
+__host__ __device__ constexpr int gate_factor_bytes(int E) { return (192 * E + 16) * 4; }   // a, r, c, d: one bulk copy
 
 struct MaskParams {
   const float* k2;

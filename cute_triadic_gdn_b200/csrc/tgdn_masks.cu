@@ -5,8 +5,10 @@
 //   M[t,s]   = sum_e k2[t,e] k2[s,e] exp(gc[t,e]-gc[s,e]) (s <  t),  Mp[t,s] = sum_e q2[t,e] k2[s,e] exp(.) (s <= t)
 //   A        = (I + strict_lower(beta_t (K K^T)[t,s] M[t,s]))^-1
 //   Pm       = scale * lower(Q K^T * Mp),   PA = Pm A
-// and stores gc (f32), the stacked operand image [A; PA] (bf16, 128x64) that the forward recurrence multiplies with
-// beta*W, and the Pm image (bf16, 64x64) that the reverse recurrence needs.
+// and stores gc (f32) followed by the gate factors a = k2 exp(gc), r = k2 exp(gL - gc), c = scale q2 exp(gc), d = exp(gL)
+// that the recurrences multiply their rows with (layout in tgdn_kernels.h), the stacked operand image [A; PA] (bf16,
+// 128x64) that the forward recurrence multiplies with beta*W, and the Pm image (bf16, 64x64) that the reverse recurrence
+// needs.
 //
 // Replaces cute_triadic_gdn/kernels/sm90_joint_scan.py:21-80 (scan_kernel, forward direction) and
 // cute_triadic_gdn/kernels/sm100_joint_masks.py:34-267 (masks_kernel); math as in
@@ -204,7 +206,7 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
   __syncthreads();                                          // gate values, barriers and the tensor-memory address are visible
   tc_fence_after();
   // inclusive scan over the 64 rows, one warp per gate column
-  float* gc_out = p.gc + ((static_cast<int64_t>(b) * p.NC + n) * p.H + h) * (64 * E);
+  float* gc_out = p.gc + ((static_cast<int64_t>(b) * p.NC + n) * p.H + h) * gate_item_floats(E);
   for (int e = warp; e < E; e += MASK_THREADS / 32) {
     float v0 = sm.gc2[lane * E + e], v1 = sm.gc2[(lane + 32) * E + e];
 #pragma unroll
@@ -237,6 +239,14 @@ masks_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ 
       // too steep, NaN, or not monotone: a log gate above zero anywhere in the chunk makes gc rise from one row to the
       // next, and the factorised form (which clamps its first factor at one) would then be wrong for rows of later blocks
       if (!(up <= 100.f) || up < 0.f || (rr > 0 && sm.gc2[idx] > sm.gc2[idx - E])) sm.steep = 1;
+      // the gate factors of the recurrences, formed here once instead of by every value block of every recurrence
+      {
+        const float eg = fast_exp2(sm.gc2[idx]), k2v = sm.k2[idx];
+        gc_out[64 * E + idx] = k2v * eg;
+        gc_out[128 * E + idx] = k2v * fast_exp2(sm.gc2[63 * E + e] - sm.gc2[idx]);
+        gc_out[192 * E + idx] = p.scale * sm.q2[idx] * eg;
+        if (idx < 16) gc_out[256 * E + idx] = idx < E ? fast_exp2(sm.gc2[63 * E + idx]) : 0.f;
+      }
       const float hv = fast_exp2(up) * sm.k2[idx];
       const float hi = round_bf16(hv), lo = hv - hi;
       const uint32_t row = hb + (rr >> 3) * 128 + (rr & 7) * 16;

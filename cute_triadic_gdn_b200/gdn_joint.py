@@ -67,11 +67,22 @@ def _dims(q, k2, token_map):
     return B, T, H, E, NC
 
 
+def gate_item_floats(E):
+    """Floats per (batch row, chunk, head) of the gate tensor: gc, a, r, c as 64 x E blocks, then d padded to 16 (include/tgdn.h)."""
+    return 4 * CHUNK * E + 16
+
+
+def chunk_gates(gc, E):
+    """The cumulative log gate (B, NC, H, 64, E) as a view of the gate tensor that tgdn_masks writes."""
+    return gc[..., :CHUNK * E].unflatten(-1, (CHUNK, E))
+
+
 def _run_masks(q, k, k2, q2, g, beta, scale, token_map, gc=None):
-    """(gc, AP, Pm) of every chunk.  AP = [A; Pm A] operand image, Pm image; see include/tgdn.h."""
+    """(gc, AP, Pm) of every chunk.  gc holds the cumulative log gate and the gate factors, AP = [A; Pm A] operand image,
+    Pm image; see include/tgdn.h."""
     B, T, H, E, NC = _dims(q, k2, token_map)
     dev = q.device
-    gc_out = torch.empty((B, NC, H, CHUNK, E), dtype=torch.float32, device=dev)
+    gc_out = torch.empty((B, NC, H, gate_item_floats(E)), dtype=torch.float32, device=dev)
     AP = torch.empty((B, NC, H, 128 * 64), dtype=torch.bfloat16, device=dev)
     Pm = torch.empty((B, NC, H, 64 * 64), dtype=torch.bfloat16, device=dev)
     with torch.cuda.device(dev):

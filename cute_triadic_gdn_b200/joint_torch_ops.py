@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 from torch.library import custom_op, register_autograd
 
-from .gdn_joint import (CHUNK, _check, _check_device_and_e, _kernel_backward, _kernel_forward, _save_list, _unpack_saved)
+from .gdn_joint import (CHUNK, gate_item_floats, _check, _check_device_and_e, _kernel_backward, _kernel_forward, _save_list, _unpack_saved)
 
 
 @custom_op("tgdn_b200::joint_fwd", mutates_args=(), device_types="cuda")
@@ -28,7 +28,7 @@ def _joint_fwd_fake(q, k, v, k2, q2, g, beta, scale, chunk_starts=None, token_ma
     B, T, H, D = q.shape
     E = k2.shape[-1]
     NC = token_map.shape[1] if token_map is not None else T // CHUNK
-    return [torch.empty_like(v), g.new_empty(B, NC, H, CHUNK, E), q.new_empty(B, NC, H, 128 * 64),
+    return [torch.empty_like(v), g.new_empty(B, NC, H, gate_item_floats(E)), q.new_empty(B, NC, H, 128 * 64),
             q.new_empty(B, NC, H, 64 * 64), q.new_empty(B, NC, H, E, 16, 128, 8), v.new_empty(B, NC, H, CHUNK, 128),
             v.new_empty(B, NC, H, CHUNK, 128)]
 

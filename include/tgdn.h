@@ -97,12 +97,17 @@ int tgdn_metadata(const void* cu_seqlens, int cu_is_int64, int n_docs, int T, in
  * Dense rows: T % 64 == 0, NC = T/64, chunk_map = doc_offsets = NULL.  Packed rows: B = 1, NC = chunk-map capacity,
  * chunk_map / doc_offsets from tgdn_metadata, n_docs documents; the state restarts at every document.
  * Chunk-layout intermediates, indexed by item = (b*NC + n)*H + h:
- *   gc f32 [item][64][E];  AP bf16 [item][128*64] ([A; Pm A] operand image);  Pm bf16 [item][64*64];
+ *   gc f32 [item][tgdn_gate_item_floats(E) = 256 E + 16]: the gates of the chunk in five blocks, with gL = gc[63] and
+ *      zeros in rows past a document end: [0, 64E) gc[t][e] cumulative log gate; [64E, 128E) a = k2 exp(gc);
+ *      [128E, 192E) r = k2 exp(gL - gc); [192E, 256E) c = scale q2 exp(gc); [256E, 256E + 16) d[e] = exp(gL), zero padded;
+ *   AP bf16 [item][128*64] ([A; Pm A] operand image);  Pm bf16 [item][64*64];
  *   W, U, dU bf16 [item][64][128];  h, ds bf16 [item][E][16][128][8] (state slice as [v/8][d][v%8]).
  *
- * tgdn_masks: chunk-local cumulative log gate, UT transform and intra-chunk operators of every chunk.
+ * tgdn_masks: chunk-local cumulative log gate, the gate factors of the recurrences, UT transform and intra-chunk
+ * operators of every chunk.
  * Replaces: cute_triadic_gdn/kernels/sm90_joint_scan.py:92-110 (joint_scan, forward) and
  * cute_triadic_gdn/kernels/sm100_joint_masks.py:291-323 (joint_masks_sm100). */
+int tgdn_gate_item_floats(int E);
 int tgdn_masks(const void* q, const void* k, const float* k2, const float* q2, const float* g, const float* beta,
                float scale, const int32_t* chunk_map, int B, int T, int H, int E, int NC, float* gc, void* AP, void* Pm,
                void* stream);

@@ -16,8 +16,14 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert sorted(_lib.SIGNATURES) == declared
 
 
+def test_gate_item_size_matches_the_host_side():
+    from cute_triadic_gdn_b200.gdn_joint import gate_item_floats
+    for E in (1, 2, 4, 8, 12, 16):
+        assert _lib.lib.tgdn_gate_item_floats(E) == gate_item_floats(E) == 256 * E + 16
+
+
 def test_version_and_error_strings():
-    assert _lib.lib.tgdn_abi_version() >= 100
+    assert _lib.lib.tgdn_abi_version() >= 101
     assert _lib.lib.tgdn_error_string(0) == b"ok"
     for code in (-1, -2, -3, -4, -5, -6, -1002, -77):
         assert len(_lib.lib.tgdn_error_string(code)) > 3

@@ -34,7 +34,7 @@ def test_reverse_recurrence_dense(E, dist):
     assert orc.rel_l2(conv(dU), rv["dU"]) < 8e-3
     assert orc.rel_l2(dV.cpu().float(), grads[2]) < 8e-3
     # the gradient state is stored only for the slices whose chunk decay is at least 2^-24
-    keep = (gc[:, :, :, 63, :] * 1.4426950408889634 >= plan.DD_MIN_LOG2_DECAY).cpu()           # (B, NC, H, E)
+    keep = (gj.chunk_gates(gc, E)[:, :, :, 63, :] * 1.4426950408889634 >= plan.DD_MIN_LOG2_DECAY).cpu()           # (B, NC, H, E)
     keep = keep.permute(0, 2, 1, 3).reshape(B * H, NC, E)
     dsm = decode_items(ds.cpu().float(), state_to_matrix)                                     # (B*H, NC, E, 128, 128)
     if keep.any():

@@ -25,7 +25,7 @@ def test_fake_kernels_give_the_real_shapes_dense(E):
         ins = _fake_inputs(B, T, H, E)
         o, gc, AP, Pm, h, W, U = torch.ops.tgdn_b200.joint_fwd(*ins, 128 ** -0.5, None, None)
         assert o.shape == (B, T, H, 128) and o.dtype == torch.bfloat16 and o.device.type == "cuda"
-        assert gc.shape == (B, NC, H, 64, E) and gc.dtype == torch.float32
+        assert gc.shape == (B, NC, H, 256 * E + 16) and gc.dtype == torch.float32
         assert AP.numel() == B * NC * H * 128 * 64 and Pm.numel() == B * NC * H * 64 * 64
         assert h.shape == (B, NC, H, E, 16, 128, 8) and W.shape == U.shape == (B, NC, H, 64, 128)
         saved = list(ins[:2]) + list(ins[3:]) + [gc, AP, Pm, h, W, U]
@@ -43,7 +43,7 @@ def test_fake_kernels_packed_sizes_depend_only_on_tokens_and_documents():
         assert offsets.shape == (N + 1,) and mapping.shape == (3, cap) and valid.shape == (1,)
         ins = _fake_inputs(1, T, H, E)
         o, gc, AP, Pm, h, W, U = torch.ops.tgdn_b200.joint_fwd(*ins, 0.1, offsets, mapping)
-        assert o.shape == (1, T, H, 128) and gc.shape == (1, cap, H, 64, E) and h.shape[1] == cap
+        assert o.shape == (1, T, H, 128) and gc.shape == (1, cap, H, 256 * E + 16) and h.shape[1] == cap
 
 
 def test_fake_conv():
