@@ -81,11 +81,13 @@ def ncu_traffic(name, E, items):
 # not of the algorithm: `io_bytes` below counts only what the algorithm itself must move.
 def kernel_bytes(name, E):
     K, NV, gates = 1024, (8 if E > 8 else 4), 3 * 64 * E * 4
+    packed = (256 * E + 16) * 4            # the gate tensor of the masks kernel: gc, a, r, c (64 x E each) and d
+    factors = packed - 64 * E * 4          # what the recurrences fetch of it: a, r, c, d
     return {
-        "masks": 32 * K + gates + 256 + 64 * E * 4 + 24 * K,
-        "fwd": 48 * K + 16 * K + gates + 256 + 48 * K + 32 * K * E,
-        "rec": 64 * K + 16 * K + gates + 256 + 32 * K + NV * 16 * K + NV * 64 * E * 4,
-        "sg": 64 * K + 32 * K * E + NV * 16 * K + gates + 32 * K + 2 * 64 * E * 4 + 4 * E,
+        "masks": 32 * K + gates + 256 + packed + 24 * K,
+        "fwd": 48 * K + 16 * K + factors + 256 + 48 * K + 32 * K * E,
+        "rec": 64 * K + 16 * K + factors + 256 + 32 * K + NV * 16 * K + NV * 64 * E * 4,
+        "sg": 64 * K + 32 * K * E + NV * 16 * K + 2 * 64 * E * 4 + 4 * E + 32 * K + 2 * 64 * E * 4 + 4 * E,
         "mat": 96 * K + 16 * K + 32 * K + gates + 256 + 2 * 64 * E * 4 + 4 * E + NV * 64 * E * 4 + 32 * K + gates + 256,
     }[name]
 

@@ -73,6 +73,11 @@ struct RecCfg {
   static constexpr int CW = VC / NCG;             // value columns per thread
   static constexpr int EL = E / NSG;              // slices per thread
   static constexpr int TPC = EL * CW;             // state columns per thread
+  // The two wide products, (a) and (d), go out in PARTS column parts with a commit each: a warpgroup starts its epilogue
+  // when the part that holds its own columns has completed, while the tensor core is still working on the later parts.
+  static constexpr int PN = (NWG * TPC >= 192 && NWG % 2 == 0) ? NWG * TPC / 2 : NWG * TPC;   // columns per part
+  static constexpr int PARTS = NWG * TPC / PN;
+  static_assert((NWG * TPC) % PN == 0 && PN % TPC == 0 && PN % 16 == 0 && PARTS <= 4, "column parts of the wide products");
   static constexpr int ES = E | 1;
   static_assert(NWG % NSG == 0 && E % NSG == 0 && (NSG == 1 || EL % 2 == 0), "slice groups split the slices evenly");
   static constexpr int TMEM_NEED = NCOLS + 2 * VC + 64;       // KG/dG, Y, Z, P
@@ -95,7 +100,7 @@ struct RecCfg {
     const int xu = XU_BYTES < 8192 ? 8192 : XU_BYTES;
     const int upto_dt = STAGES * KQ_BYTES + GX_BYTES + nb * (PM_BYTES + A_BYTES) + xu + 2 * STAGES * DOB + DRP_FLOATS * 4;
     const int off_gt = (upto_dt + 128 + 127) & ~127;
-    return off_gt + nb * GT_STRIDE + 64 + 1024;
+    return off_gt + nb * GT_STRIDE + 128 + 1024;
   }
   // With two stages, Pm, A and the gate factors get a second copy too where that fits.  Where it does not (sixteen slices),
   // they stay single and are requested LATE: each is dead by the end of the epilogue of (c), and the next chunk's copies,
@@ -120,14 +125,15 @@ struct RecCfg {
   static constexpr int OFF_DT = OFF_DRP + DRP_FLOATS * 4;     // exp(gL) of this chunk and the store flags of the next: 2 x 16 words
   static constexpr int OFF_GT = (OFF_DT + 128 + 127) & ~127;
   static constexpr int OFF_CTRL = OFF_GT + NB * GT_STRIDE;
-  static constexpr int SMEM_BYTES = OFF_CTRL + 64 + 1024;
+  static constexpr int SMEM_BYTES = OFF_CTRL + 128 + 1024;
 };
 
 struct RecCtrl {
   uint64_t bar_load[2];      // K/Q tiles, dO and U rows of a stage (STAGES == 1: everything)
   uint64_t bar_late;         // late scheme only: Pm and the gate rows of the chunk
   uint64_t bar_a;            // late scheme only: A of the chunk
-  uint64_t bar_mma;
+  uint64_t bar_mma;          // (c)
+  uint64_t bar_part[4];      // (a) and (d): one per column part
   uint64_t bar_p;
   uint32_t tmem_base;
   int abort;
@@ -178,6 +184,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_init(&ctrl.bar_late, 1);
     mbar_init(&ctrl.bar_a, 1);
     mbar_init(&ctrl.bar_mma, 1);
+    for (int c = 0; c < 4; ++c) mbar_init(&ctrl.bar_part[c], 1);
     mbar_init(&ctrl.bar_p, 1);
     mbar_fence_init();
     ctrl.abort = 0;
@@ -350,7 +357,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   }
   __syncwarp();
   if (count > 1) prefetch_rows(count - 2);
-  uint32_t mma_phase = 0;
+  uint32_t part_phase = 0;                            // completions of this thread's column part so far: two per chunk
+  const int part = wg * TPC / C::PN;
   {
     // the gradient state at the end of the last chunk (zero unless handed in)
     if (tid < E) ftab[tid] = decay_flag((static_cast<int64_t>(b) * p.NC + first + count - 1) * p.H + h, tid);
@@ -395,14 +403,6 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     if (warp_u == ISSUE_WARP && elect_one()) {
       tc_fence_after();
       {
-        const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
-        const uint64_t db = make_desc(smem_u32(smem + C::OFF_GX), 128, 2048, LAYOUT_PLAIN);
-        constexpr uint32_t idesc = make_idesc(128, NCOLS, 0, 1);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16(tmem, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32), desc_advance(db, kk * 256), idesc, kk > 0);
-      }
-      {
         const uint64_t da = make_desc(smem_u32(pm), 128, 1024, LAYOUT_PLAIN);       // Pm^T: MN-major over (i = t, j = s)
         const uint64_t db = make_desc(smem_u32(doimg), 128, 1024, LAYOUT_PLAIN);
         constexpr uint32_t idesc = make_idesc(128, VC, 1, 1);
@@ -410,7 +410,19 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         for (int kk = 0; kk < 4; ++kk)
           umma_bf16(tmem + TM_Y, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
       }
-      umma_commit(&ctrl.bar_mma);
+      {
+        const uint64_t da = make_desc(smem_u32(kq), 16, 1024, LAYOUT_SW128);
+        const uint64_t db = make_desc(smem_u32(smem + C::OFF_GX), 128, 2048, LAYOUT_PLAIN);
+        constexpr uint32_t idesc = make_idesc(128, C::PN, 0, 1);
+#pragma unroll
+        for (int pt = 0; pt < C::PARTS; ++pt) {       // Y and part 0 first; every commit covers all that was issued before it
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_bf16(tmem + pt * C::PN, desc_advance(da, (kk >> 2) * 16384 + (kk & 3) * 32),
+                      desc_advance(db, pt * (C::PN / 8) * 2048 + kk * 256), idesc, kk > 0);
+          umma_commit(&ctrl.bar_part[pt]);
+        }
+      }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
@@ -448,8 +460,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
       if (kstep + 2 < count) prefetch_rows(i - 2);
     }
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    ++mma_phase;
+    mbar_wait_spin(&ctrl.bar_part[part], part_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++part_phase;
     tc_fence_after();
     float du[CW];                                    // K rows: dU of this thread's columns (NSG > 1: its slice group's part)
     if (krow) {
@@ -556,8 +568,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       for (int w = 0; w < NCG; ++w) s4 += drp[(w * 64 + r) * ES + e];
       p.dr[((item * NV + vb) * 64 + r) * E + e] = s4;
     }
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    ++mma_phase;
+    mbar_wait_spin(&ctrl.bar_mma, kstep & 1, ctl, DEV_TIMEOUT_MMA);
     tc_fence_after();
     if constexpr (C::LATE) {                         // (c) has read A: the next chunk's copy may land
       if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
@@ -598,11 +609,14 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       tc_fence_after();
       const uint64_t da = make_desc(smem_u32(kq), 16384, 1024, LAYOUT_SW128);
       const uint64_t db = make_desc(smem_u32(smem + C::OFF_GX), 128, 2048, LAYOUT_PLAIN);
-      constexpr uint32_t idesc = make_idesc(128, NCOLS, 1, 1);
+      constexpr uint32_t idesc = make_idesc(128, C::PN, 1, 1);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        umma_bf16(tmem, desc_advance(da, kk * 2048), desc_advance(db, kk * 256), idesc, kk > 0);
-      umma_commit(&ctrl.bar_mma);
+      for (int pt = 0; pt < C::PARTS; ++pt) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + pt * C::PN, desc_advance(da, kk * 2048), desc_advance(db, pt * (C::PN / 8) * 2048 + kk * 256), idesc, kk > 0);
+        umma_commit(&ctrl.bar_part[pt]);
+      }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
     // meanwhile: P (128 key rows x 64 tokens, f32) -> bf16 operand image (i = d, j = t), SI = 128, SJ = 2048, of this
@@ -623,10 +637,13 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
                          pack_bf16(pv[j + 6], pv[j + 7]));
       }
     }
-    mbar_wait_spin(&ctrl.bar_mma, mma_phase & 1, ctl, DEV_TIMEOUT_MMA);
-    ++mma_phase;
+    mbar_wait_spin(&ctrl.bar_part[part], part_phase & 1, ctl, DEV_TIMEOUT_MMA);
+    ++part_phase;
     tc_fence_after();
-    if (STAGES == 1 && warp_u == COPY_WARP && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);   // the only stage is free once (d) has completed
+    if constexpr (STAGES == 1) {                     // the only stage is free once every part of (d) has completed
+      if (warp_u == COPY_WARP) mbar_wait_spin(&ctrl.bar_part[C::PARTS - 1], (part_phase - 1) & 1, ctl, DEV_TIMEOUT_MMA);
+      if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) issue_loads(i - 1, 0);
+    }
     __syncwarp();
     {
       constexpr int PIECE = TPC < 16 ? TPC : 16;
