@@ -374,14 +374,18 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
   // The chunk decays of the chunk below decide whether its gradient state is stored; they are read a whole chunk before they
   // are looked at (the warp that reads them must not arrive late at the chunk's first barrier).
-  auto decay_of = [&](int i) {                       // local chunk i, slice tid (tid < E)
-    return __ldg(p.gc + ((static_cast<int64_t>(b) * p.NC + first + i) * p.H + h) * gate_item_floats(E) + 63 * E + tid);
+  // (A query-row warp without any other role reads them: the key-row warps are the critical path of the chunk's first phase.)
+  constexpr int FLAG_WARP = 7;
+  static_assert(NWG >= 2, "the flag warp is the last warp of the second warpgroup");
+  const bool flag_lane = warp_u == FLAG_WARP && lane < E;
+  auto decay_of = [&](int i) {                       // local chunk i, slice `lane` (lane < E)
+    return __ldg(p.gc + ((static_cast<int64_t>(b) * p.NC + first + i) * p.H + h) * gate_item_floats(E) + 63 * E + lane);
   };
-  float gl_below = (tid < E && count > 1) ? decay_of(count - 2) : 0.f;
+  float gl_below = (flag_lane && count > 1) ? decay_of(count - 2) : 0.f;
   for (int kstep = 0; kstep < count; ++kstep) {
     const int i = count - 1 - kstep;
     const float gl_use = gl_below;
-    if (tid < E && i > 1) gl_below = decay_of(i - 2);
+    if (flag_lane && i > 1) gl_below = decay_of(i - 2);
     const int st = (STAGES == 2) ? (kstep & 1) : 0;
     int t0, rows;
     chunk_info(i, t0, rows);
@@ -439,8 +443,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       rec_lds_part<EL>(gf + (krow ? 0 : C::GF_C) + t * E + e0, ga);
       if (krow) {
         rec_lds_part<EL>(gf + C::GF_R + t * E + e0, gr);
-        bt = __ldg(p.beta + (tok + min(t, max(rows, 1) - 1)) * p.H + h);
-        if (!live) bt = 0.f;
+        bt = __ldg(p.beta + (tok + min(t, max(rows, 1) - 1)) * p.H + h);   // masked where it is used, after (c): nothing here waits for it
         float uv[CW];
         unpack_piece(image_piece(duimg), true, uv);
         // Xu_e = r_e * U -> operand image (i = t, j = n') of (p)
@@ -454,9 +457,11 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 #pragma unroll
         for (int e = 0; e < EL; ++e) gr[e] = 0.f;
       }
-      if (tid < E) {
-        dtab[tid] = gf[C::GF_D + tid];
-        if (i > 0) ftab[tid] = gl_use * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;   // read after the chunk's last barrier but one
+      if (tid < E) dtab[tid] = gf[C::GF_D + tid];
+      if (flag_lane && i > 0) {
+        float glv = gl_use;
+        asm volatile("" : "+f"(glv));                // the comparison stays here: nothing waits for the load before this point
+        ftab[lane] = glv * LOG2E >= DD_MIN_LOG2_DECAY ? 1 : 0;   // read after the chunk's last barrier but one
       }
       if (kstep + 2 < count) prefetch_rows(i - 2);
     }
@@ -583,6 +588,8 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         float z[CW];
         tmem_ld<CW>(tmem_row + TM_Z + v0, z);
         tmem_wait_ld();
+        asm volatile("" : "+f"(bt));                   // first use of the beta load of phase (a)
+        if (!live) bt = 0.f;
 #pragma unroll
         for (int c = 0; c < CW; ++c) xr[c] = bt * z[c];
         if (live && sgp == 0) store_row_global(p.dV + ((tok + t) * p.H + h) * HEAD + vb * VC + v0, xr);
