@@ -61,8 +61,8 @@ KERNEL_U = {
 # shares the eight value blocks of E = 16 where E = 8 has four: its rec and sg figures come out about 64 KB per item low).
 NCU_DRAM_BYTES_PER_ITEM = {
     # kernel: (bytes per item at E = 8, at E = 16); filled from profiles/core_kernels_prof_workload.md
-    "masks": (0.236e9 / 4096, 0.118e9 / 2048), "fwd": (1.529e9 / 4096, 1.284e9 / 2048), "rec": (0.751e9 / 4096, 0.549e9 / 2048),
-    "sg": (1.779e9 / 4096, 1.583e9 / 2048), "mat": (0.825e9 / 4096, 0.495e9 / 2048),
+    "masks": (0.255e9 / 4096, 0.135e9 / 2048), "fwd": (1.518e9 / 4096, 1.282e9 / 2048), "rec": (0.751e9 / 4096, 0.549e9 / 2048),
+    "sg": (1.771e9 / 4096, 1.574e9 / 2048), "mat": (0.824e9 / 4096, 0.495e9 / 2048),
 }
 
 # DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)
