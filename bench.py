@@ -300,9 +300,12 @@ def parity_check(ins, do, o_dev, grads_dev, cu_host, seed=0, n_slices=2):
     for (b, lo, hi, h) in picks:
         sl = lambda t: t[b:b + 1, lo:hi, h:h + 1].contiguous()
         cu = None if (hi - lo) % 64 == 0 else torch.tensor([0, hi - lo], dtype=torch.int32)
-        o_ref, g_ref = orc.reference_with_grads(orc.chunk_reference, [sl(t) for t in ins], sl(do), cu_seqlens=cu, dtype=torch.float32)
+        if grads_dev is None:                                  # forward-only workload
+            o_ref, eg = orc.chunk_reference(*[sl(t) for t in ins], cu_seqlens=cu, dtype=torch.float32), 0.0
+        else:
+            o_ref, g_ref = orc.reference_with_grads(orc.chunk_reference, [sl(t) for t in ins], sl(do), cu_seqlens=cu, dtype=torch.float32)
+            eg = max(orc.rel_l2(sl(gd).float().cpu(), gr) for gd, gr in zip(grads_dev, g_ref))
         eo = orc.rel_l2(sl(o_dev).float().cpu(), o_ref)
-        eg = max(orc.rel_l2(sl(gd).float().cpu(), gr) for gd, gr in zip(grads_dev, g_ref))
         worst_o, worst_g = max(worst_o, eo), max(worst_g, eg)
         which.append({"row": b, "tokens": [lo, hi], "head": h, "o": eo, "max_grad": eg})
     return {"o": worst_o, "max_grad": worst_g, "slices": which, "tolerance": PARITY_TOL,
@@ -573,10 +576,10 @@ def run_ours(args, rank, world, local_rank):
                 "note": "inference forward: the saved states are not written, the ncu traffic figure (training forward) is an upper bound"}
     # parity at the size that was timed: seeded slices of the last resident step against the CPU oracle
     parity = None
-    if backward and not args.no_parity:
+    if not args.no_parity:
         o_dev = step_resident()
         torch.cuda.synchronize()
-        parity = parity_check(ins, do, o_dev, [t.grad for t in leaves], cu_host, seed=args.steps)
+        parity = parity_check(ins, do, o_dev, [t.grad for t in leaves] if backward else None, cu_host, seed=args.steps)
     # the second mode of the headline configuration and the convolution pre-pass, a few launches each
     aux = {}
     if backward and not args.no_aux and world == 1:
@@ -740,6 +743,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"            # the version banner goes to stdout, which carries the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
         run_ours(args, rank, world, local_rank)
