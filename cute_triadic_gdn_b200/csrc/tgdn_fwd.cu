@@ -468,11 +468,34 @@ fwd_kernel(const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CU
       tmem_ld<CW>(tmem_row + TPC, u);
       tmem_wait_ld();
       if (krow) {
-        if (p.U != nullptr && sw == 0) store_row_global(p.U + (item * 64 + t) * HEAD + v0g, u);
-        // Vn_e = r_e * U -> operand image (i = t, j = n'), this thread's slices
+        // U leaves as bf16 (the backward reads it back in that form); Vn_e = r_e * U is formed from the same packed row,
+        // two products per instruction, and goes into the operand image (i = t, j = n'), this thread's slices
+        uint32_t uw[CW / 2];
+#pragma unroll
+        for (int c = 0; c < CW; c += 2) uw[c >> 1] = pack_bf16(u[c], u[c + 1]);
+        if (p.U != nullptr && sw == 0) {
+          __nv_bfloat16* dst = p.U + (item * 64 + t) * HEAD + v0g;
+          if constexpr (CW >= 8) {
+#pragma unroll
+            for (int c = 0; c < CW / 2; c += 4) *reinterpret_cast<uint4*>(dst + 2 * c) = make_uint4(uw[c], uw[c + 1], uw[c + 2], uw[c + 3]);
+          } else {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(uw[0], uw[1]);
+          }
+        }
         const uint32_t base = smem_u32(vn_img) + (t >> 3) * 128 + (t & 7) * 16;
 #pragma unroll
-        for (int e = 0; e < ET; ++e) store_row_image(base, (e0 + e) * CW, 1024, u, gr[e]);
+        for (int e = 0; e < ET; ++e) {
+          const uint32_t rr = pack_bf16(gr[e], gr[e]);
+          const int n0 = (e0 + e) * CW;
+          if constexpr (CW >= 8) {
+#pragma unroll
+            for (int c = 0; c < CW / 2; c += 4)
+              st_shared_v4(base + ((n0 + 2 * c) >> 3) * 1024, mul_bf16x2(uw[c], rr), mul_bf16x2(uw[c + 1], rr), mul_bf16x2(uw[c + 2], rr),
+                           mul_bf16x2(uw[c + 3], rr));
+          } else {
+            st_shared_v2(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, mul_bf16x2(uw[0], rr), mul_bf16x2(uw[1], rr));
+          }
+        }
       } else if (live && sw == WPC - 1) {
         float ov[CW];
 #pragma unroll

@@ -81,7 +81,8 @@ def forward_stage(K, Q, V, k2, q2, beta, scale, mk, reset, rounding):
         U = mk["A"][:, n] @ bW
         Oi = mk["PA"][:, n] @ bW
         o.append(rd(torch.einsum('nte,netv->ntv', gt["c"][:, n], Rq) + Oi))
-        Vn = rd(gt["r"][:, n].transpose(1, 2)[..., None] * U[:, None])           # (N,E,64,V)
+        # r_e*U is a product of two bf16 values rounded once (the kernel scales the packed row of U it stores)
+        Vn = rd(rd(gt["r"][:, n]).transpose(1, 2)[..., None] * rd(U)[:, None])   # (N,E,64,V)
         S = gt["d"][:, n][..., None, None] * S + torch.einsum('ntd,netv->nedv', K[:, n], Vn)
         Ws.append(rd(W))
         Us.append(rd(U))
@@ -107,8 +108,9 @@ def reverse_stage(K, Q, dO, beta, mk, fw, reset, rounding):
         Z = mk["A"][:, n].transpose(-1, -2) @ dUb
         dW = beta[:, n, :, None] * Z
         dV_[n] = rd(dW)
-        X1 = rd(-gt["a"][:, n].transpose(1, 2)[..., None] * dW[:, None])
-        X2 = rd(gt["c"][:, n].transpose(1, 2)[..., None] * dO[:, n][:, None])
+        # bf16 factors times the bf16 rows that are stored (dV) or were loaded (dO), rounded once
+        X1 = rd(-rd(gt["a"][:, n]).transpose(1, 2)[..., None] * rd(dW)[:, None])
+        X2 = rd(rd(gt["c"][:, n]).transpose(1, 2)[..., None] * dO[:, n][:, None])
         G = gt["d"][:, n][..., None, None] * G + torch.einsum('ntd,netv->nedv', K[:, n], X1) \
             + torch.einsum('ntd,netv->nedv', Q[:, n], X2)
         if reset is not None and bool(reset[n]):
@@ -138,7 +140,7 @@ def state_grad_stage(K, Q, dO, fw, rv, mk, rounding):
     Pq = torch.einsum('nctv,ncedv->ncetd', dO, h)
     # The part of dK that contracts the gradient state is formed in the reverse recurrence, per block of value columns,
     # from r_e*U rounded to bf16, and leaves it rounded to bf16; the blocks are then added up in f32.
-    Vn = rd(r * U[:, :, None])
+    Vn = rd(rd(r) * U[:, :, None])             # U is the stored bf16 tensor; r_e enters as bf16 too
     VC = value_block(E)
     dKg = 0
     for j in range(128 // VC):
