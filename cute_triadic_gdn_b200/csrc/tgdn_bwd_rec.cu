@@ -19,8 +19,8 @@
 // only as d_e*dd_e: slices whose chunk decay is below 2^-24 contribute less than one part in 10^7 of <h_e, G_e> and are
 // skipped there (dd_e = 0); G_e is stored (ds) only for the slices of chunks whose decay is above that threshold.
 //
-// (p) is off the dependent chain of the chunk: it is issued behind (c), completes while the epilogue of (c) reads Z,
-// and is read out of tensor memory while (d) runs.
+// (p) is off the dependent chain of the chunk: it is issued behind (a) as soon as its operand Xu is built, runs while the
+// epilogue of (a) occupies the threads, and is read out of tensor memory while (d) runs.
 //
 // The gate factors (a, r, c per row and slice, d per slice) were formed by the masks kernel and arrive with one bulk copy
 // per chunk; every thread reads those of its own row from shared memory.  The gradient state can be handed in (dL/dS after the last token) and out (before the first), so
@@ -135,6 +135,7 @@ struct RecCtrl {
   uint64_t bar_mma;          // (c)
   uint64_t bar_part[4];      // (a) and (d): one per column part
   uint64_t bar_p;
+  uint64_t bar_xu;           // the key-row warps have written the operand Xu of (p): one arrival per warp
   uint32_t tmem_base;
   int abort;
 };
@@ -186,6 +187,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     mbar_init(&ctrl.bar_mma, 1);
     for (int c = 0; c < 4; ++c) mbar_init(&ctrl.bar_part[c], 1);
     mbar_init(&ctrl.bar_p, 1);
+    mbar_init(&ctrl.bar_xu, NWG * 2);
     mbar_fence_init();
     ctrl.abort = 0;
   }
@@ -431,6 +433,22 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
+    if (warp_u == ISSUE_WARP) {
+      // (p) P = G Xu^T goes out as soon as the key-row warps have built Xu (they do that first thing in this phase): it runs
+      // behind (a), under the epilogue of (a), where the tensor core would otherwise idle, and nobody waits for it later.
+      mbar_wait(&ctrl.bar_xu, kstep & 1, ctl, DEV_TIMEOUT_MMA);
+      if (elect_one()) {
+        tc_fence_after();
+        const uint64_t da = make_desc(smem_u32(smem + C::OFF_GX), 2048, 128, LAYOUT_PLAIN);   // G: K-major over (i = d, j = n')
+        const uint64_t db = make_desc(smem_u32(smem + C::OFF_XU), 1024, 128, LAYOUT_PLAIN);   // Xu: K-major over (i = t, j = n')
+        constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < NCOLS / 16; ++kk)
+          umma_bf16(tmem + TM_P, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
+        umma_commit(&ctrl.bar_p);
+      }
+      __syncwarp();
+    }
     if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {
       if (STAGES == 2) issue_loads(i - 1, st ^ 1); else prefetch_loads(i - 1);
     }
@@ -455,6 +473,9 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
           const int n0 = wg * TPC + e * CW;
           store_row_image_scaled(base + (n0 >> 3) * 1024 + (n0 & 7) * 2, uw, gr[e]);
         }
+        fence_async_smem();                            // Xu is read by the tensor core: say so, one arrival per key-row warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctrl.bar_xu);
       } else {
 #pragma unroll
         for (int e = 0; e < EL; ++e) gr[e] = 0.f;
@@ -526,7 +547,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
 
-    // ---- (c) Z = A^T dU, then (p) P = G Xu^T behind it ----------------------------------------------------------
+    // ---- (c) Z = A^T dU -----------------------------------------------------------------------------------------
     if constexpr (C::LATE) {
       // Pm was last read by the MMAs of (a) and the gate rows by the gate factors before the barrier above: the next chunk's
       // copies are asked for now and have the rest of the chunk to arrive.  A, which (c) is about to read, has its own
@@ -548,15 +569,6 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
         for (int kk = 0; kk < 4; ++kk)
           umma_bf16(tmem + TM_Z, desc_advance(da, kk * 256), desc_advance(db, kk * 256), idesc, kk > 0);
         umma_commit(&ctrl.bar_mma);
-      }
-      {
-        const uint64_t da = make_desc(smem_u32(smem + C::OFF_GX), 2048, 128, LAYOUT_PLAIN);   // G: K-major over (i = d, j = n')
-        const uint64_t db = make_desc(smem_u32(smem + C::OFF_XU), 1024, 128, LAYOUT_PLAIN);   // Xu: K-major over (i = t, j = n')
-        constexpr uint32_t idesc = make_idesc(128, 64, 0, 0);
-#pragma unroll
-        for (int kk = 0; kk < NCOLS / 16; ++kk)
-          umma_bf16(tmem + TM_P, desc_advance(da, kk * 4096), desc_advance(db, kk * 2048), idesc, kk > 0);
-        umma_commit(&ctrl.bar_p);
       }
     }
     __syncwarp();                                    // the other lanes must not run ahead into a spin wait
