@@ -29,6 +29,7 @@ namespace tgdn {
 
 constexpr int SG_THREADS = 256;      // eight worker warps ...
 constexpr int SG_BLOCK = SG_THREADS + 64;   // ... plus one warp that only issues MMAs and one that only issues bulk loads
+constexpr int PF_AHEAD = 8;          // half-slices of h pulled into L2 ahead of the ring's own loads
 
 // Four ring stages: about two half-slice pairs (64 KB) travel while two more wait for their MMAs.  Measured at E = 8:
 // three stages are 3% slower, five were slower too.
@@ -400,6 +401,25 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
       // both readers of the stage are done; this warp never waits on bar_mma, whose phases it could fall behind.
 #pragma unroll 1
       for (int s = 0; s < STEPS; ++s) {
+        // The ring holds NS half-slices (64 KB), less than what keeps this SM's share of HBM busy at HBM latency: the
+        // half-slice PF_AHEAD steps further on (of this item or of the CTA's next one) is pulled into L2 now, so that the
+        // ring's own load of it later finds it there.
+        if (elect_one()) {
+          const int q = s + NS + PF_AHEAD;
+          const int64_t it2 = q < STEPS ? item : nxt;
+          const int q2 = q < STEPS ? q : q - STEPS;
+          if (it2 < n_items && q2 < STEPS)
+            bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + it2 * (static_cast<int64_t>(E) * 32768) + q2 * 16384, 16384);
+          if (s == 0 && nxt < n_items) {                 // and the next item's value-block images and [dW ; dO] tile
+            const int h2 = static_cast<int>(nxt % p.H), b2 = static_cast<int>(nxt / (static_cast<int64_t>(p.H) * p.NC));
+            bulk_prefetch(reinterpret_cast<const uint8_t*>(p.dkg) + nxt * (static_cast<int64_t>(NVB) * 16384), static_cast<uint32_t>(NVB) * 16384);
+            tma_prefetch_4d(&map_dv, 0, h2, t0n, b2);
+            tma_prefetch_4d(&map_do, 0, h2, t0n, b2);
+            tma_prefetch_4d(&map_dv, 64, h2, t0n, b2);
+            tma_prefetch_4d(&map_do, 64, h2, t0n, b2);
+          }
+        }
+        __syncwarp();
         mbar_wait(&sm.bar_read[s % NS], ((s / NS) & 1) ^ step_bit(s), ctl, DEV_TIMEOUT_LOAD);
         if (s + NS < STEPS && elect_one()) {
           issue_h(item, s + NS);
