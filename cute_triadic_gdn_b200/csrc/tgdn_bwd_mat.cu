@@ -102,8 +102,10 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
   WaitCtl ctl{&sm.abort, p.status};
 
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-  const int h = static_cast<int>(item % p.H), n = static_cast<int>((item / p.H) % p.NC);
-  const int b = static_cast<int>(item / (static_cast<int64_t>(p.H) * p.NC));
+  // (items fit in 32 bits, the entry point checks that: 64-bit divisions are a few hundred cycles each on this machine)
+  const int item32 = static_cast<int>(item);
+  const int h = item32 % p.H, n = (item32 / p.H) % p.NC;
+  const int b = item32 / (p.H * p.NC);
   int t0 = n * CHUNK, rows = CHUNK;
   if (p.cmap != nullptr) {
     t0 = p.cmap[n];
@@ -153,9 +155,16 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
       q2_in[it] = __ldg(p.q2 + off);
       da_in[it] = __ldg(p.da + item * (64 * E) + idx);
       dc_in[it] = __ldg(p.dc + item * (64 * E) + idx);
+      const float* drp = p.dr + (item * p.NV * 64 + rr) * E + e;   // value block v is 64 * E floats further on
 #pragma unroll
-      for (int v = 0; v < NV_MAX; ++v)
-        dr_in[it][v] = __ldg(p.dr + ((item * p.NV + min(v, p.NV - 1)) * 64 + rr) * E + e);
+      for (int v = 0; v < 4; ++v) dr_in[it][v] = __ldg(drp + v * (64 * E));
+      if (p.NV > 4) {                                      // four or eight value blocks: the same for every thread
+#pragma unroll
+        for (int v = 4; v < NV_MAX; ++v) dr_in[it][v] = __ldg(drp + v * (64 * E));
+      } else {
+#pragma unroll
+        for (int v = 4; v < NV_MAX; ++v) dr_in[it][v] = 0.f;
+      }
     }
 #pragma unroll
     for (int it = 0; it < GATE_ITERS; ++it) {
@@ -455,8 +464,9 @@ mat_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     if (warp_u == 1) {
       const int64_t item2 = item + gridDim.x;              // this CTA's next item
       if (item2 < n_items) {
-        const int h2 = static_cast<int>(item2 % p.H), n2 = static_cast<int>((item2 / p.H) % p.NC);
-        const int b2 = static_cast<int>(item2 / (static_cast<int64_t>(p.H) * p.NC));
+        const int i2 = static_cast<int>(item2);
+        const int h2 = i2 % p.H, n2 = (i2 / p.H) % p.NC;
+        const int b2 = i2 / (p.H * p.NC);
         int t2 = n2 * CHUNK, rows2 = CHUNK;
         if (p.cmap != nullptr) { t2 = p.cmap[n2]; rows2 = p.cmap[p.NC + n2]; }
         if (rows2 > 0 && rows2 <= CHUNK && t2 >= 0 && t2 + rows2 <= p.T) {

@@ -74,7 +74,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
   // memory and the [I;0] operand.  While the workers finish one item (epilogue) and start the next (prologue), the loads of
   // the next item's first ring round are already in flight.
   auto item_rows = [&](int64_t item, int& t0, int& rows) {       // false: nothing to do for this item
-    const int n = static_cast<int>((item / p.H) % p.NC);
+    const int n = (static_cast<int>(item) / p.H) % p.NC;   // items fit in 32 bits (checked at the entry point); 64-bit divisions are slow
     t0 = n * CHUNK;
     rows = CHUNK;
     if (p.cmap != nullptr) {
@@ -113,7 +113,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
               &sm.bar_pt[st]);
   };
   auto issue_first_round = [&](int64_t item, int t0) { // one lane: the [dW ; dO] tile and the first ring round of an item
-    const int h = static_cast<int>(item % p.H), b = static_cast<int>(item / (static_cast<int64_t>(p.H) * p.NC));
+    const int h = static_cast<int>(item) % p.H, b = static_cast<int>(item) / (p.H * p.NC);
     mbar_expect_tx(&sm.bar_kq, 32768);
     tma_load_4d(sm.xt, &map_dv, &sm.bar_kq, 0, h, t0, b);
     tma_load_4d(sm.xt + 8192, &map_do, &sm.bar_kq, 0, h, t0, b);
@@ -182,7 +182,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
     int t0n = 0, rowsn = 0;
     const int64_t nxt = next_item(item + gridDim.x, t0n, rowsn);
     const float next_gl = load_gl(nxt);                // asked for a whole item ahead
-    const int h = static_cast<int>(item % p.H), b = static_cast<int>(item / (static_cast<int64_t>(p.H) * p.NC));
+    const int h = static_cast<int>(item) % p.H, b = static_cast<int>(item) / (p.H * p.NC);
     const uint32_t fmask = __ballot_sync(0xffffffffu, !worker && lane < E && my_gl * LOG2E >= DD_MIN_LOG2_DECAY);
 
     // ---- workers: prologue.  All global loads go out together, from clamped (always valid) addresses, and are masked when
@@ -411,7 +411,7 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
           if (it2 < n_items && q2 < STEPS)
             bulk_prefetch(reinterpret_cast<const uint8_t*>(p.h) + it2 * (static_cast<int64_t>(E) * 32768) + q2 * 16384, 16384);
           if (s == 0 && nxt < n_items) {                 // and the next item's value-block images and [dW ; dO] tile
-            const int h2 = static_cast<int>(nxt % p.H), b2 = static_cast<int>(nxt / (static_cast<int64_t>(p.H) * p.NC));
+            const int h2 = static_cast<int>(nxt) % p.H, b2 = static_cast<int>(nxt) / (p.H * p.NC);
             bulk_prefetch(reinterpret_cast<const uint8_t*>(p.dkg) + nxt * (static_cast<int64_t>(NVB) * 16384), static_cast<uint32_t>(NVB) * 16384);
             tma_prefetch_4d(&map_dv, 0, h2, t0n, b2);
             tma_prefetch_4d(&map_do, 0, h2, t0n, b2);
@@ -515,6 +515,7 @@ extern "C" int tgdn_bwd_state_grads(const void* q, const void* k, const void* dO
   if (!q || !k || !dO || !dV || !h || !ds || !dkg || !k2 || !q2 || !gc || !dkq || !da || !dc || !dd) return TGDN_ERR_NULL;
   int rc = tgdn_check_core_shape(B, T, H, E, NC, chunk_map != nullptr);
   if (rc) return rc;
+  if (static_cast<long long>(B) * NC * H * 64 > 0x7fffffffLL) return TGDN_ERR_SHAPE;   // item indices are 32-bit in the kernel
   if ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dV) |
        reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(ds) | reinterpret_cast<uintptr_t>(dkg) |
        reinterpret_cast<uintptr_t>(dkq)) & 15)

@@ -814,9 +814,18 @@ glue_gate_kernel(GlueArgs a, int B) {
   const int gbase = 3 * a.H * HEAD;                    // first gate channel
   for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < n;
        idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int u = static_cast<int>(idx % (2 * a.H));    // which * H + head: consecutive threads, consecutive channel groups
-    const int64_t bt = idx / (2 * a.H);
-    const int t = static_cast<int>(bt % a.T), b = static_cast<int>(bt / a.T);
+    int u, t, b;                                        // u = which * H + head: consecutive threads, consecutive channel groups
+    if (n <= 0x7fffffffLL) {                            // 64-bit divisions cost a few hundred cycles each: avoid them where 32 bits do
+      const int i32 = static_cast<int>(idx), bt = i32 / (2 * a.H);
+      u = i32 - bt * (2 * a.H);
+      b = bt / a.T;
+      t = bt - b * a.T;
+    } else {
+      u = static_cast<int>(idx % (2 * a.H));
+      const int64_t bt = idx / (2 * a.H);
+      t = static_cast<int>(bt % a.T);
+      b = static_cast<int>(bt / a.T);
+    }
     const int which = u / a.H, head = u % a.H;
     const int c0 = gbase + u * E;
     int start = 0;                                      // first token of t's document
