@@ -62,7 +62,7 @@ KERNEL_U = {
 NCU_DRAM_BYTES_PER_ITEM = {
     # kernel: (bytes per item at E = 8, at E = 16); filled from profiles/core_kernels_prof_workload.md
     "masks": (0.255e9 / 4096, 0.135e9 / 2048), "fwd": (1.518e9 / 4096, 1.282e9 / 2048), "rec": (0.751e9 / 4096, 0.549e9 / 2048),
-    "sg": (1.865e9 / 4096, 1.906e9 / 2048), "mat": (0.824e9 / 4096, 0.495e9 / 2048),
+    "sg": (1.865e9 / 4096, 1.574e9 / 2048), "mat": (0.824e9 / 4096, 0.495e9 / 2048),
 }
 
 # DRAM bytes (read + write) per element of the conv kernels, from one ncu capture at (1, 8192, 13056)

@@ -404,7 +404,9 @@ sg_kernel(const __grid_constant__ CUtensorMap map_dv, const __grid_constant__ CU
         // The ring holds NS half-slices (64 KB), less than what keeps this SM's share of HBM busy at HBM latency: the
         // half-slice PF_AHEAD steps further on (of this item or of the CTA's next one) is pulled into L2 now, so that the
         // ring's own load of it later finds it there.
-        if (elect_one()) {
+        // (Up to eight slices: at twelve and sixteen the pulled lines were evicted again before the ring asked for them, 22%
+        // more DRAM traffic for no gain.)
+        if (E <= 8 && elect_one()) {
           const int q = s + NS + PF_AHEAD;
           const int64_t it2 = q < STEPS ? item : nxt;
           const int q2 = q < STEPS ? q : q - STEPS;
