@@ -9,7 +9,7 @@ torch.distributed works, the CPU tests use gloo); there is no collective.
 
 The per-segment operator is `chunk_gdn_joint_segment` (state in, state out, differentiable through both); the exchange is
 expressed as autograd functions, so `loss.backward()` runs the reverse wavefront by itself.  The reference has no such
-path (its sequences live on one GPU: cute_triadic_gdn/ops/gdn_joint.py:252-278); SURVEY lists it as the last "next" row.
+path: its sequences live on one GPU (cute_triadic_gdn/ops/gdn_joint.py:252-278).
 """
 from __future__ import annotations
 

@@ -130,7 +130,7 @@ struct RecCfg {
 
 struct RecCtrl {
   uint64_t bar_load[2];      // K/Q tiles, dO and U rows of a stage (STAGES == 1: everything)
-  uint64_t bar_late;         // late scheme only: Pm and the gate rows of the chunk
+  uint64_t bar_late;         // late scheme only: Pm and the gate factors of the chunk
   uint64_t bar_a;            // late scheme only: A of the chunk
   uint64_t bar_mma;          // (c)
   uint64_t bar_part[4];      // (a) and (d): one per column part
@@ -397,7 +397,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
     const int64_t tok = static_cast<int64_t>(b) * p.T + t0;
     const bool live = t < rows;
     uint8_t* kq = smem + C::OFF_KQ + st * C::KQ_BYTES;
-    const int nbi = C::NB == 2 ? st : 0;             // which copy of Pm, A and the gate rows this chunk uses
+    const int nbi = C::NB == 2 ? st : 0;             // which copy of Pm, A and the gate factors this chunk uses
     uint8_t* am = smem + C::OFF_A + nbi * C::A_BYTES;
     uint8_t* pm = smem + C::OFF_PM + nbi * C::PM_BYTES;
     const int v0 = cgp * CW;                         // first value column of this thread inside the block
@@ -549,7 +549,7 @@ rec_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CU
 
     // ---- (c) Z = A^T dU -----------------------------------------------------------------------------------------
     if constexpr (C::LATE) {
-      // Pm was last read by the MMAs of (a) and the gate rows by the gate factors before the barrier above: the next chunk's
+      // Pm was last read by the MMAs of (a) and the gate factors by every thread before the barrier above: the next chunk's
       // copies are asked for now and have the rest of the chunk to arrive.  A, which (c) is about to read, has its own
       // barrier and was asked for when the previous chunk's (c) had completed.
       if (warp_u == COPY_WARP && kstep + 1 < count && elect_one()) {

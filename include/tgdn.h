@@ -113,7 +113,9 @@ int tgdn_masks(const void* q, const void* k, const float* k2, const float* q2, c
                void* stream);
 
 /* tgdn_fwd: the forward chunk recurrence; writes o and, unless NULL, the tensors the backward needs (W, U, h).
- * k2, q2 and gc must be 16-byte aligned.
+ * gc is the tensor tgdn_masks wrote with the same scale (the recurrences read the gate factors a, r, c, d from it; k2 and
+ * q2 stay in the signature as the inputs those factors came from and are not read again); k2, q2 and gc must be 16-byte
+ * aligned.
  * Replaces: cute_triadic_gdn/kernels/sm100_joint_fwd.py:569-618 (joint_fwd_sm100). */
 int tgdn_fwd(const void* q, const void* k, const void* v, const float* k2, const float* q2, const float* beta,
              const float* gc, const void* AP, float scale, const int32_t* doc_offsets, const int32_t* chunk_map,
