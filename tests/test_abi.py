@@ -22,6 +22,17 @@ def test_gate_item_size_matches_the_host_side():
         assert _lib.lib.tgdn_gate_item_floats(E) == gate_item_floats(E) == 256 * E + 16
 
 
+def test_chunk_gates_is_a_view_of_the_first_block():
+    import torch
+    from cute_triadic_gdn_b200.gdn_joint import chunk_gates, gate_item_floats
+    E = 4
+    gc = torch.arange(2 * 3 * 5 * gate_item_floats(E), dtype=torch.float32).reshape(2, 3, 5, gate_item_floats(E))
+    view = chunk_gates(gc, E)
+    assert view.shape == (2, 3, 5, 64, E)
+    assert view.data_ptr() == gc.data_ptr()
+    assert torch.equal(view[1, 2, 4, 63], gc[1, 2, 4, 63 * E:64 * E])
+
+
 def test_version_and_error_strings():
     assert _lib.lib.tgdn_abi_version() >= 101
     assert _lib.lib.tgdn_error_string(0) == b"ok"
